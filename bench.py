@@ -1,0 +1,412 @@
+#!/usr/bin/env python
+"""Benchmark of the mLSTM hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+One step = one chunkwise mLSTMexp forward+backward over one synthetic 65,536-token batch
+(B=8, S=8192, NH=16, DHQK=DHHV=256, chunk 128, bf16; seeded q,k,v,i ~ N(0,1), f = 3 + N(0,1),
+dH ~ N(0,1)).  With N > 1 (torchrun, one rank per GPU) every rank processes its own batch of the
+same size: batch x heads are independent units, there is no data-path collective (weak scaling).
+
+Prints ONE JSON line.  `value` is TFLOP/s of algorithmic FLOPs with inputs resident in HBM;
+`e2e` is the same metric through the public API with host (pinned) buffers, host<->device copies
+inside the timed region.  `--impl reference` times the CPU restatement of the reference's native
+PyTorch path (the oracle) on the host cores on a bounded sample of the same workload.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+WORKLOAD = dict(name="c2_chunkwise_fwbw_mLSTMexp_B8_S8192_NH16_DHQK256_DHHV256_L128_bf16",
+                B=8, S=8192, NH=16, DHQK=256, DHHV=256, L=128)
+# bounded CPU sample of the same workload: same S, head dims and chunk size, fewer (batch, head) units
+CPU_SAMPLE = dict(B=1, NH=16)
+
+
+def fw_flops(B, NH, S, DHQK, DHHV, L):
+    return B * NH * S * (4 * DHQK * DHHV + L * (DHQK + DHHV))
+
+
+def bw_flops(B, NH, S, DHQK, DHHV, L):
+    return B * NH * S * (8 * DHQK * DHHV + L * (3 * DHQK + 2 * DHHV))
+
+
+def phase_flops(B, NH, S, DHQK, DHHV, L):
+    t = B * NH * S
+    return {
+        "recurrent_fw": t * 2 * DHQK * DHHV,
+        "parallel_fw": t * (2 * DHQK * DHHV + L * (DHQK + DHHV)),
+        "recurrent_bw": t * 2 * DHQK * DHHV,
+        "parallel_bw": t * (6 * DHQK * DHHV + L * (3 * DHQK + 2 * DHHV)),
+    }
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return dict(tflops=d["bf16_tflops"], tflops_sustained=d.get("bf16_tflops_sustained"), hbm=d["hbm_gbs"],
+                    source="measured")
+    return dict(tflops=1590.0, tflops_sustained=1400.0, hbm=6650.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1])); mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for nm, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(nm)
+        if not sm:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["no samples"])
+        return dict(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+
+
+def make_inputs_np(B, NH, S, DHQK, DHHV, seed):
+    import numpy as np
+    rng = np.random.default_rng(seed)
+    out = dict(
+        q=rng.standard_normal((B, NH, S, DHQK), dtype=np.float32),
+        k=rng.standard_normal((B, NH, S, DHQK), dtype=np.float32),
+        v=rng.standard_normal((B, NH, S, DHHV), dtype=np.float32),
+        i=rng.standard_normal((B, NH, S), dtype=np.float32),
+        f=3.0 + rng.standard_normal((B, NH, S), dtype=np.float32),
+        dH=rng.standard_normal((B, NH, S, DHHV), dtype=np.float32),
+    )
+    return out
+
+
+def cpu_port_step(inp, L):
+    """One forward+backward of the numpy restatement of the reference's native path (float32)."""
+    import numpy as np
+    from oracle import mlstm_oracle as O
+    O.chunkwise_fwbw(inp["q"], inp["k"], inp["v"], inp["i"], inp["f"], inp["dH"], chunk_size=L, dtype=np.float32)
+
+
+def time_cpu_port(steps, warmup):
+    w = WORKLOAD
+    B, NH = CPU_SAMPLE["B"], CPU_SAMPLE["NH"]
+    inp = make_inputs_np(B, NH, w["S"], w["DHQK"], w["DHHV"], seed=1)
+    for _ in range(warmup):
+        cpu_port_step(inp, w["L"])
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        cpu_port_step(inp, w["L"])
+    dt = (time.perf_counter() - t0) / steps
+    fl = fw_flops(B, NH, w["S"], w["DHQK"], w["DHHV"], w["L"]) + bw_flops(B, NH, w["S"], w["DHQK"], w["DHHV"], w["L"])
+    sample = (f"B={B} NH={NH} of the workload's B={w['B']} NH={w['NH']} (same S={w['S']}, head dims, chunk size), "
+              f"float32, {steps} timed steps of {dt:.2f} s")
+    return fl / dt / 1e12, dt, sample
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    val, dt, sample = time_cpu_port(args.steps, args.warmup)
+    w = WORKLOAD
+    line = {
+        "impl": "reference", "metric": "chunkwise_fwbw_tflops_64k_tokens", "value": val, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": w["name"], "note": "CPU restatement (numpy, BLAS threads) of the reference's native "
+                   "PyTorch chunkwise path; each step is a bounded sample of the workload"},
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def run_b200(args):
+    import torch
+    import torch.distributed as dist
+
+    import mlstm_kernels_b200 as mk
+    from mlstm_kernels_b200 import _lib
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    w = WORKLOAD
+    B, S, NH, DHQK, DHHV, L = (w[x] for x in ("B", "S", "NH", "DHQK", "DHHV", "L"))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- inputs: pinned host copies (for the end-to-end leg) and device-resident copies ----
+    g = torch.Generator().manual_seed(1 + rank)
+    host = {}
+    for name, shape in (("q", (B, NH, S, DHQK)), ("k", (B, NH, S, DHQK)), ("v", (B, NH, S, DHHV)),
+                        ("i", (B, NH, S)), ("f", (B, NH, S)), ("dH", (B, NH, S, DHHV))):
+        t = torch.randn(shape, generator=g, dtype=torch.float32)
+        if name == "f":
+            t += 3.0
+        host[name] = t.bfloat16().pin_memory()
+    devin = {n: t.to(dev) for n, t in host.items()}
+    leaf = {n: devin[n].clone().requires_grad_(True) for n in "qkvif"}
+
+    def step_resident():
+        for t in leaf.values():
+            t.grad = None
+        H = mk.mlstm_chunkwise__b200_xl_chunk(leaf["q"], leaf["k"], leaf["v"], leaf["i"], leaf["f"], chunk_size=L)
+        H.backward(devin["dH"])
+        return H
+
+    def fw_only():
+        with torch.no_grad():
+            return mk.mlstm_chunkwise__b200_xl_chunk(devin["q"], devin["k"], devin["v"], devin["i"], devin["f"],
+                                                     chunk_size=L)
+
+    host_out = {n: torch.empty_like(host[n]).pin_memory() for n in ("q", "k", "v", "i", "f")}
+    host_out["H"] = torch.empty_like(host["v"]).pin_memory()
+
+    def step_e2e():
+        d = {n: host[n].to(dev, non_blocking=True) for n in host}
+        lf = {n: d[n].requires_grad_(True) for n in "qkvif"}
+        H = mk.mlstm_chunkwise__b200_xl_chunk(lf["q"], lf["k"], lf["v"], lf["i"], lf["f"], chunk_size=L)
+        H.backward(d["dH"])
+        host_out["H"].copy_(H.detach(), non_blocking=True)
+        for n in "qkvif":
+            host_out[n].copy_(lf[n].grad, non_blocking=True)
+
+    h2d = sum(t.numel() * t.element_size() for t in host.values())
+    d2h = sum(t.numel() * t.element_size() for t in host_out.values())
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        return max_over_ranks(e0.elapsed_time(e1) / steps)
+
+    flops_fw = fw_flops(B, NH, S, DHQK, DHHV, L)
+    flops_fwbw = flops_fw + bw_flops(B, NH, S, DHQK, DHHV, L)
+
+    # ---- headline: fw+bw, inputs resident ----
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    n_before = _lib.launch_count()
+    ms = timed(step_resident, args.steps, args.warmup)
+    launches = (_lib.launch_count() - n_before) * args.steps // (args.steps + args.warmup)
+    clocks = sampler.stop() if rank == 0 else None
+    value = world * flops_fwbw / (ms * 1e-3) / 1e12
+
+    # ---- end to end through the public API with host buffers ----
+    e2e_steps = max(2, min(args.steps, 5))
+    ms_e2e = timed(step_e2e, e2e_steps, 1)
+    e2e_val = world * flops_fwbw / (ms_e2e * 1e-3) / 1e12
+
+    # ---- per-kernel device time (CUDA events inside the library, on the launching stream) ----
+    peaks = measured_peaks()
+    _lib.profile_enable(True)
+    prof_steps = max(2, min(args.steps, 5))
+    for _ in range(prof_steps):
+        step_resident()
+    torch.cuda.synchronize()
+    prof = _lib.profile_read()
+    _lib.profile_enable(False)
+    pf = phase_flops(B, NH, S, DHQK, DHHV, L)
+    kernels = {}
+    for name, (tot, cnt) in prof.items():
+        if cnt:
+            kernels[name] = dict(ms=tot / cnt, launches_per_step=cnt / prof_steps)
+            if name in pf:
+                kernels[name]["tflops"] = pf[name] / (tot / cnt * 1e-3) / 1e12
+    dom = max((n for n in kernels if n in pf), key=lambda n: kernels[n]["ms"] * kernels[n]["launches_per_step"])
+    traffic = None
+    tpath = os.path.join(ROOT, "profiles", "roofline_traffic.json")
+    if os.path.exists(tpath):
+        traffic = json.load(open(tpath)).get(dom)
+    impl_used = "tcgen05" if _lib.load().mlstm_b200_chunkwise_has_tcgen05(S, DHQK, DHHV, L, _lib.BF16) else "simt"
+    roofline = {"bound": "tensor", "kernel": dom, "achieved": kernels[dom]["tflops"], "peak": peaks["tflops"],
+                "unit": "TFLOP/s", "frac": kernels[dom]["tflops"] / peaks["tflops"], "traffic": traffic,
+                "peak_source": peaks["source"] + " (burst bf16 GEMM)", "impl": impl_used,
+                "whole_step_frac": (flops_fwbw / (ms * 1e-3) / 1e12) / peaks["tflops"],
+                "kernels": kernels}
+
+    # ---- secondary numbers (not the headline): forward only, mLSTMsig, decode step ----
+    extra = {}
+    if rank == 0 and not args.no_extra:
+        ms_fw = timed_local(torch, fw_only, 5, 3)
+        extra["fw_only"] = dict(ms=ms_fw, tflops=flops_fw / (ms_fw * 1e-3) / 1e12,
+                                frac_of_peak=flops_fw / (ms_fw * 1e-3) / 1e12 / peaks["tflops"])
+
+        def sig_step():
+            for t in leaf.values():
+                t.grad = None
+            H = mk.mlstm_siging_chunkwise__b200_xl_chunk(leaf["q"], leaf["k"], leaf["v"], leaf["i"], leaf["f"],
+                                                         chunk_size=L, normalize=True)
+            H.backward(devin["dH"])
+        ms_sig = timed_local(torch, sig_step, 5, 3)
+        extra["fwbw_mLSTMsig"] = dict(ms=ms_sig, tflops=flops_fwbw / (ms_sig * 1e-3) / 1e12)
+        extra["step_decode"] = bench_step(torch, mk, dev, peaks)
+    if world > 1:
+        dist.barrier()
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        val, dt, sample = time_cpu_port(5, 1)
+        cpu = {"value": val, "unit": "TFLOP/s", "cores": os.cpu_count() or 1, "kind": "port", "sample": sample}
+
+    if rank == 0:
+        line = {
+            "metric": "chunkwise_fwbw_tflops_64k_tokens", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": w["name"], "tokens_per_step_per_gpu": B * S,
+                       "tokens_per_s": world * B * S / (ms * 1e-3), "sharding": "batch x heads, no collective",
+                       "l2": "inputs (2.2 GB per step) larger than L2; no flush", "impl": impl_used},
+            "roofline": roofline, "cpu_baseline": cpu,
+            "e2e": {"value": e2e_val, "unit": "TFLOP/s", "ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h},
+            "gpu_launches": int(launches), "clocks": clocks, "extra": extra,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def timed_local(torch, fn, steps, warmup):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def bench_step(torch, mk, dev, peaks):
+    """Decode at the xLSTM-7B head geometry NH=8, 256/512, bf16 tokens, f32 state; chained steps."""
+    NH, DHQK, DHHV = 8, 256, 512
+    out = {}
+    for B in (1, 8, 64, 256):
+        g = torch.Generator(device=dev).manual_seed(B)
+        c = torch.randn(B, NH, DHQK, DHHV, device=dev, generator=g) * 0.1
+        n = torch.randn(B, NH, DHQK, device=dev, generator=g).abs()
+        m = torch.randn(B, NH, 1, device=dev, generator=g)
+        c2, n2, m2 = torch.empty_like(c), torch.empty_like(n), torch.empty_like(m)
+        T = 64
+        q = torch.randn(T, B, NH, DHQK, device=dev, generator=g).bfloat16()
+        k = torch.randn(T, B, NH, DHQK, device=dev, generator=g).bfloat16()
+        v = torch.randn(T, B, NH, DHHV, device=dev, generator=g).bfloat16()
+        i = torch.randn(T, B, NH, 1, device=dev, generator=g).bfloat16()
+        f = (3 + torch.randn(T, B, NH, 1, device=dev, generator=g)).bfloat16()
+        state = [(c, n, m), (c2, n2, m2)]
+
+        def run(nsteps):
+            for t in range(nsteps):
+                (ci, ni, mi), (co, no, mo) = state[t % 2], state[(t + 1) % 2]
+                mk.mlstm_recurrent_step__b200_fw(ci, ni, mi, q[t % T], k[t % T], v[t % T], i[t % T], f[t % T],
+                                                 matC_new=co, vecN_new=no, scaM_new=mo)
+        nsteps = 1024 if B <= 64 else 256
+        run(16)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        run(nsteps)
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) / nsteps * 1e3
+        nbytes = B * NH * (2 * DHQK * DHHV * 4 + 2 * DHQK * 4 + 8 + (2 * DHQK + 2 * DHHV) * 2 + 4)
+        gbs = nbytes / (us * 1e-6) / 1e9
+        out[f"B{B}"] = dict(us_per_step=us, tokens_per_s=B / (us * 1e-6), gbs=gbs, frac_of_hbm=gbs / peaks["hbm"],
+                            note="includes Python launch overhead per step" if B <= 8 else "")
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-extra", action="store_true", help="skip the secondary measurements")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "b200":
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

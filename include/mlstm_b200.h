@@ -1,0 +1,163 @@
+/*
+ * C ABI of the B200 (sm_100a) mLSTM kernel library, libmlstm_b200.so.
+ *
+ * Every entry point takes raw DEVICE pointers, sizes and a CUDA stream handle
+ * (cudaStream_t passed as void*; NULL = the legacy default stream), enqueues its
+ * kernels on that stream and returns without synchronising.  The caller owns all
+ * buffers.  Tensors are contiguous row-major with the shapes given below and all
+ * pointers must be 16-byte aligned.  Return value: MLSTM_OK (0) on success, a
+ * negative MLSTM_ERR_* code otherwise (mlstm_b200_error_string() gives the text).
+ * Nothing in this library allocates device memory or touches host copies of the
+ * data, and there is no CPU fallback.
+ *
+ * Each entry point names the interface of NX-AI/mlstm_kernels that it replaces
+ * (paths relative to that project's root).
+ */
+#ifndef MLSTM_B200_H
+#define MLSTM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+#if defined(__GNUC__)
+#pragma GCC visibility push(default)
+#endif
+
+/* element types of q, k, v, i, f, h and of the gradients */
+enum { MLSTM_F32 = 0, MLSTM_BF16 = 1, MLSTM_F16 = 2 };
+
+/* gate variant: exponential input gate with max-state m (mLSTMexp),
+ * sigmoid input gate with denominator max(|n|,1) (mLSTMsig, normalize=True),
+ * sigmoid input gate without normaliser (mLSTMsig, normalize=False) */
+enum { MLSTM_EXP = 0, MLSTM_SIG = 1, MLSTM_SIG_NONORM = 2 };
+
+/* which implementation to run: AUTO picks the tcgen05/TMA kernels whenever the
+ * shape allows and the portable CUDA-core kernels otherwise */
+enum { MLSTM_IMPL_AUTO = 0, MLSTM_IMPL_SIMT = 1, MLSTM_IMPL_TCGEN05 = 2 };
+
+enum {
+  MLSTM_OK = 0,
+  MLSTM_ERR_SHAPE = -1,      /* unsupported or inconsistent sizes */
+  MLSTM_ERR_DTYPE = -2,      /* unsupported element type */
+  MLSTM_ERR_NULL = -3,       /* a required pointer is NULL */
+  MLSTM_ERR_ALIGN = -4,      /* a pointer is not 16-byte aligned */
+  MLSTM_ERR_WORKSPACE = -5,  /* workspace too small */
+  MLSTM_ERR_CUDA = -6,       /* a CUDA runtime / driver call failed */
+  MLSTM_ERR_UNSUPPORTED = -7 /* requested implementation cannot run this case */
+};
+
+int mlstm_b200_version(void);
+const char* mlstm_b200_error_string(int code);
+/* text of the last CUDA error seen by the calling thread inside this library */
+const char* mlstm_b200_last_cuda_error(void);
+
+/* Number of kernels this library has launched in the calling process so far. */
+long long mlstm_b200_launch_count(void);
+
+/*
+ * Per-phase device timing.  After mlstm_b200_profile_enable(1) every phase of the entry points
+ * below is bracketed by CUDA events on the launching stream; mlstm_b200_profile_read() waits for
+ * them, adds up the elapsed milliseconds and the number of occurrences per phase into arrays of
+ * mlstm_b200_profile_phases() elements, and clears the record.  Replaces the torch.profiler hook of
+ * the reference's benchmark loop (mlstm_kernels/utils/benchmark/runtime.py:56-60,135-136).
+ */
+int mlstm_b200_profile_enable(int on);
+int mlstm_b200_profile_phases(void);
+const char* mlstm_b200_profile_phase_name(int phase);
+int mlstm_b200_profile_read(float* total_ms, int* count);
+
+/* 1 if the tcgen05 path covers this chunkwise case, else 0. */
+int mlstm_b200_chunkwise_has_tcgen05(int S, int DHQK, int DHHV, int L, int dtype);
+
+/* Element type (MLSTM_F32 or MLSTM_BF16) of the per-chunk C state buffer that
+ * mlstm_b200_chunkwise_fw writes and mlstm_b200_chunkwise_bw reads, for the given
+ * case and implementation choice. */
+int mlstm_b200_chunkwise_state_dtype(int S, int DHQK, int DHHV, int L, int dtype, int impl);
+
+/* Scratch bytes the forward (backward = 0) or backward (backward = 1) call needs. */
+size_t mlstm_b200_chunkwise_workspace_bytes(int B, int NH, int S, int DHQK, int DHHV, int L,
+                                            int dtype, int variant, int impl, int backward);
+
+/*
+ * Chunkwise forward for mLSTMexp / mLSTMsig.
+ * Replaces mlstm_chunkwise_fw (mlstm_kernels/torch/chunkwise/triton_xl_chunk/fw.py:20-136)
+ * with its two launches, mlstm_chunkwise__recurrent_fw_C (fw_recurrent.py:13-144) and
+ * mlstm_chunkwise__parallel_fw_Hintra (fw_parallel.py:14-136), and the sigmoid-gate twin
+ * mlstm_siging_chunkwise_fw (mlstm_kernels/torch/chunkwise/triton_xl_chunk_siging/fw.py:20-140).
+ *
+ *   q, k        (B,NH,S,DHQK)   dtype          v (B,NH,S,DHHV) dtype     i, f (B,NH,S) gate_dtype
+ *   c_initial   (B,NH,DHQK,DHHV) f32, n_initial (B,NH,DHQK) f32, m_initial (B,NH) f32; each may be NULL (= zeros)
+ *   h           (B,NH,S,DHHV)   dtype   out
+ *   n_out,m_out (B,NH,S)        f32     out: denominator max(|n|,e^-m) and combined max state per token
+ *   c_states    (B,NH,NC+1,DHQK,DHHV)   out, element type mlstm_b200_chunkwise_state_dtype(); slot k = state
+ *                                        before chunk k, slot NC = final state
+ *   n_states    (B,NH,NC+1,DHQK) f32 out,  m_states (B,NH,NC+1) f32 out
+ *   c_last,n_last,m_last  f32 copies of the final state (B,NH,DHQK,DHHV),(B,NH,DHQK),(B,NH); each may be NULL
+ *   S % L == 0, L a power of two >= 16.
+ */
+int mlstm_b200_chunkwise_fw(const void* q, const void* k, const void* v, const void* i, const void* f,
+                            const float* c_initial, const float* n_initial, const float* m_initial,
+                            void* h, float* n_out, float* m_out,
+                            void* c_states, float* n_states, float* m_states,
+                            float* c_last, float* n_last, float* m_last,
+                            void* workspace, size_t workspace_bytes,
+                            int B, int NH, int S, int DHQK, int DHHV, int L,
+                            int dtype, int gate_dtype, int variant, int impl, float eps, void* stream);
+
+/*
+ * Chunkwise backward (the hand-derived one that ignores the gradient through the
+ * denominator).  Replaces mlstm_chunkwise_bw
+ * (mlstm_kernels/torch/chunkwise/triton_xl_chunk/bw.py:27-227: bw_recurrent.py:13-120,
+ * bw_parallel_dV.py, bw_parallel_dK.py, bw_parallel_dQ.py, chunkwise_gates.py:68-95) and
+ * mlstm_siging_chunkwise_bw (mlstm_kernels/torch/chunkwise/triton_xl_chunk_siging/bw.py).
+ *
+ *   q,k,v,i,f, m_initial as in the forward; c_states, n_out as written by the forward
+ *   dh        (B,NH,S,DHHV) dtype;  dc_last (B,NH,DHQK,DHHV) f32 or NULL
+ *   dq,dk (B,NH,S,DHQK) dtype out;  dv (B,NH,S,DHHV) dtype out;  di,df (B,NH,S) f32 out
+ *   dc_initial (B,NH,DHQK,DHHV) f32 out or NULL
+ */
+int mlstm_b200_chunkwise_bw(const void* q, const void* k, const void* v, const void* i, const void* f,
+                            const float* m_initial, const void* c_states, const float* n_out,
+                            const void* dh, const float* dc_last,
+                            void* dq, void* dk, void* dv, float* di, float* df, float* dc_initial,
+                            void* workspace, size_t workspace_bytes,
+                            int B, int NH, int S, int DHQK, int DHHV, int L,
+                            int dtype, int gate_dtype, int variant, int impl, float eps, void* stream);
+
+/*
+ * One recurrent decode step.  Replaces mlstm_recurrent_step__triton_fw
+ * (mlstm_kernels/torch/recurrent/triton_step.py:15-127) and its kernel
+ * recurrent_step_fw_kernel (mlstm_kernels/triton/recurrent/fw_step_fused.py:19-195).
+ *
+ *   q,k (B,NH,DHQK) dtype; v (B,NH,DHHV) dtype; i,f (B,NH) dtype
+ *   c (B,NH,DHQK,DHHV), n (B,NH,DHQK), m (B,NH) in state_dtype (MLSTM_F32 or MLSTM_BF16)
+ *   h (B,NH,DHHV) dtype out; c_new, n_new, m_new out, state_dtype.
+ *   c_new may alias c (each element is read and written by the same thread); n_new and
+ *   m_new must not alias n and m.  DHHV % 4 == 0.
+ */
+int mlstm_b200_step(const void* q, const void* k, const void* v, const void* i, const void* f,
+                    const void* c, const void* n, const void* m,
+                    void* h, void* c_new, void* n_new, void* m_new,
+                    int B, int NH, int DHQK, int DHHV, int dtype, int state_dtype, float eps, void* stream);
+
+/*
+ * T decode steps in one launch with the state kept on chip between tokens.
+ * Replaces the per-token Python loop _mlstm_recurrent_sequence_loop_fw
+ * (mlstm_kernels/torch/recurrent/native_sequence.py:13-122) over the step kernel.
+ *   q,k (B,NH,T,DHQK); v (B,NH,T,DHHV); i,f (B,NH,T); h (B,NH,T,DHHV); states f32 as in mlstm_b200_step.
+ */
+int mlstm_b200_step_sequence(const void* q, const void* k, const void* v, const void* i, const void* f,
+                             const float* c, const float* n, const float* m,
+                             void* h, float* c_new, float* n_new, float* m_new,
+                             int B, int NH, int T, int DHQK, int DHHV, int dtype, float eps, void* stream);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+#ifdef __cplusplus
+}
+#endif
+#endif /* MLSTM_B200_H */

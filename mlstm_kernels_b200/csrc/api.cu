@@ -1,0 +1,291 @@
+// extern "C" entry points of libmlstm_b200.so: argument validation, workspace carving, dispatch.
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <vector>
+
+#include "common.cuh"
+#include "launch.cuh"
+
+namespace mlstm {
+
+static thread_local char g_last_cuda_error[512] = "";
+
+void set_last_cuda_error(cudaError_t e, const char* where) {
+  snprintf(g_last_cuda_error, sizeof(g_last_cuda_error), "%s: %s (%s)", cudaGetErrorName(e), cudaGetErrorString(e),
+           where);
+}
+
+// ---- launch counter and phase profiler ----------------------------------------------------------
+static std::atomic<long long> g_launches{0};
+void note_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+struct PhaseRec { int phase; cudaEvent_t a, b; };
+static std::mutex g_prof_mu;
+static bool g_prof_on = false;
+static std::vector<PhaseRec> g_prof_recs;
+static const size_t kMaxPhaseRecs = 1 << 16;
+
+PhaseScope::PhaseScope(int phase, cudaStream_t s) : slot(-1), st(s) {
+  if (!g_prof_on) return;
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  if (g_prof_recs.size() >= kMaxPhaseRecs) return;
+  PhaseRec r{phase, nullptr, nullptr};
+  if (cudaEventCreate(&r.a) != cudaSuccess || cudaEventCreate(&r.b) != cudaSuccess) return;
+  cudaEventRecord(r.a, st);
+  g_prof_recs.push_back(r);
+  slot = (int)g_prof_recs.size() - 1;
+}
+PhaseScope::~PhaseScope() {
+  if (slot < 0) return;
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  if (slot < (int)g_prof_recs.size()) cudaEventRecord(g_prof_recs[slot].b, st);
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+static int check_dims(int B, int NH, int S, int DHQK, int DHHV, int L) {
+  if (B <= 0 || NH <= 0 || S <= 0 || DHQK <= 0 || DHHV <= 0 || L <= 0) return MLSTM_ERR_SHAPE;
+  if (S % L != 0) return MLSTM_ERR_SHAPE;
+  if (!is_pow2(L) || L < 16 || L > 1024) return MLSTM_ERR_SHAPE;
+  return MLSTM_OK;
+}
+
+static int resolve_impl(int impl, int S, int DHQK, int DHHV, int L, int dtype, bool* use_sm100) {
+  const bool ok = sm100_supported(S, DHQK, DHHV, L, dtype);
+  if (impl == MLSTM_IMPL_AUTO) { *use_sm100 = ok; return MLSTM_OK; }
+  if (impl == MLSTM_IMPL_SIMT) { *use_sm100 = false; return MLSTM_OK; }
+  if (impl == MLSTM_IMPL_TCGEN05) { *use_sm100 = true; return ok ? MLSTM_OK : MLSTM_ERR_UNSUPPORTED; }
+  return MLSTM_ERR_UNSUPPORTED;
+}
+
+// carve f32 arrays out of the workspace, each start 256-byte aligned
+struct Carver {
+  char* base; size_t off = 0;
+  explicit Carver(void* p) : base(static_cast<char*>(p)) {}
+  template <typename T> T* take(size_t count) {
+    off = align_up(off, 256);
+    T* p = base ? reinterpret_cast<T*>(base + off) : nullptr;
+    off += count * sizeof(T);
+    return p;
+  }
+};
+
+struct FwLayout { GateBuffers gb; size_t bytes; };
+static FwLayout carve_fw(void* ws, int BNH, int S, int NC, float* m_out) {
+  Carver c(ws);
+  FwLayout l{};
+  const size_t tok = (size_t)BNH * S;
+  l.gb.vecB = c.take<float>(tok);
+  l.gb.iota = c.take<float>(tok);
+  l.gb.abar = c.take<float>(tok);
+  l.gb.bbar = c.take<float>(tok);
+  l.gb.gbar = c.take<float>((size_t)BNH * NC);
+  l.gb.scratch = c.take<float>((size_t)BNH * NC * 2);
+  l.gb.m_tok = m_out;
+  l.gb.inv_den = nullptr;
+  l.bytes = align_up(c.off, 256);
+  return l;
+}
+
+struct BwLayout { GateBuffers gb; float* m_states; float* acc; float* kdk; void* dc_states; size_t bytes; };
+static BwLayout carve_bw(void* ws, int BNH, int S, int NC, int DHQK, int DHHV, size_t state_elem) {
+  Carver c(ws);
+  BwLayout l{};
+  const size_t tok = (size_t)BNH * S;
+  l.gb.vecB = c.take<float>(tok);
+  l.gb.iota = c.take<float>(tok);
+  l.gb.m_tok = c.take<float>(tok);
+  l.gb.abar = c.take<float>(tok);
+  l.gb.bbar = c.take<float>(tok);
+  l.gb.inv_den = c.take<float>(tok);
+  l.gb.gbar = c.take<float>((size_t)BNH * NC);
+  l.gb.scratch = c.take<float>((size_t)BNH * NC * 2);
+  l.m_states = c.take<float>((size_t)BNH * (NC + 1));
+  l.acc = c.take<float>(tok);
+  l.kdk = c.take<float>(tok);
+  l.dc_states = c.take<char>((size_t)BNH * (NC + 1) * DHQK * DHHV * state_elem);
+  l.bytes = align_up(c.off, 256);
+  return l;
+}
+
+}  // namespace mlstm
+
+using namespace mlstm;
+
+extern "C" {
+
+int mlstm_b200_version(void) { return 100; }
+
+const char* mlstm_b200_error_string(int code) {
+  switch (code) {
+    case MLSTM_OK: return "ok";
+    case MLSTM_ERR_SHAPE: return "unsupported or inconsistent sizes";
+    case MLSTM_ERR_DTYPE: return "unsupported element type";
+    case MLSTM_ERR_NULL: return "a required pointer is NULL";
+    case MLSTM_ERR_ALIGN: return "a pointer is not 16-byte aligned";
+    case MLSTM_ERR_WORKSPACE: return "workspace too small";
+    case MLSTM_ERR_CUDA: return "a CUDA call failed";
+    case MLSTM_ERR_UNSUPPORTED: return "requested implementation cannot run this case";
+  }
+  return "unknown error code";
+}
+
+const char* mlstm_b200_last_cuda_error(void) { return g_last_cuda_error; }
+
+long long mlstm_b200_launch_count(void) { return g_launches.load(); }
+
+int mlstm_b200_profile_enable(int on) {
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  for (auto& r : g_prof_recs) { cudaEventDestroy(r.a); cudaEventDestroy(r.b); }
+  g_prof_recs.clear();
+  g_prof_on = on != 0;
+  return MLSTM_OK;
+}
+
+int mlstm_b200_profile_phases(void) { return PH_COUNT; }
+
+const char* mlstm_b200_profile_phase_name(int phase) {
+  static const char* names[PH_COUNT] = {"gates", "recurrent_fw", "parallel_fw", "recurrent_bw",
+                                        "parallel_bw", "gate_grads", "step"};
+  return (phase >= 0 && phase < PH_COUNT) ? names[phase] : "?";
+}
+
+int mlstm_b200_profile_read(float* total_ms, int* count) {
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  for (int p = 0; p < PH_COUNT; ++p) { total_ms[p] = 0.f; count[p] = 0; }
+  for (auto& r : g_prof_recs) {
+    MLSTM_CUDA_CHECK(cudaEventSynchronize(r.b));
+    float ms = 0.f;
+    MLSTM_CUDA_CHECK(cudaEventElapsedTime(&ms, r.a, r.b));
+    total_ms[r.phase] += ms;
+    count[r.phase] += 1;
+  }
+  for (auto& r : g_prof_recs) { cudaEventDestroy(r.a); cudaEventDestroy(r.b); }
+  g_prof_recs.clear();
+  return MLSTM_OK;
+}
+
+int mlstm_b200_chunkwise_has_tcgen05(int S, int DHQK, int DHHV, int L, int dtype) {
+  return sm100_supported(S, DHQK, DHHV, L, dtype) ? 1 : 0;
+}
+
+int mlstm_b200_chunkwise_state_dtype(int S, int DHQK, int DHHV, int L, int dtype, int impl) {
+  bool use_sm100 = false;
+  if (resolve_impl(impl, S, DHQK, DHHV, L, dtype, &use_sm100) != MLSTM_OK) return MLSTM_F32;
+  return use_sm100 ? MLSTM_BF16 : MLSTM_F32;
+}
+
+size_t mlstm_b200_chunkwise_workspace_bytes(int B, int NH, int S, int DHQK, int DHHV, int L, int dtype, int variant,
+                                            int impl, int backward) {
+  (void)variant;
+  if (check_dims(B, NH, S, DHQK, DHHV, L) != MLSTM_OK) return 0;
+  const int NC = S / L;
+  if (!backward) return carve_fw(nullptr, B * NH, S, NC, nullptr).bytes;
+  const size_t se = dtype_size(mlstm_b200_chunkwise_state_dtype(S, DHQK, DHHV, L, dtype, impl));
+  return carve_bw(nullptr, B * NH, S, NC, DHQK, DHHV, se).bytes;
+}
+
+int mlstm_b200_chunkwise_fw(const void* q, const void* k, const void* v, const void* i, const void* f,
+                            const float* c_initial, const float* n_initial, const float* m_initial, void* h,
+                            float* n_out, float* m_out, void* c_states, float* n_states, float* m_states,
+                            float* c_last, float* n_last, float* m_last, void* workspace, size_t workspace_bytes,
+                            int B, int NH, int S, int DHQK, int DHHV, int L, int dtype, int gate_dtype, int variant,
+                            int impl, float eps, void* stream) {
+  int rc = check_dims(B, NH, S, DHQK, DHHV, L);
+  if (rc != MLSTM_OK) return rc;
+  if (dtype != MLSTM_F32 && dtype != MLSTM_BF16 && dtype != MLSTM_F16) return MLSTM_ERR_DTYPE;
+  if (gate_dtype != MLSTM_F32 && gate_dtype != MLSTM_BF16 && gate_dtype != MLSTM_F16) return MLSTM_ERR_DTYPE;
+  if (variant < MLSTM_EXP || variant > MLSTM_SIG_NONORM) return MLSTM_ERR_UNSUPPORTED;
+  if (!q || !k || !v || !i || !f || !h || !n_out || !m_out || !c_states || !n_states || !m_states || !workspace)
+    return MLSTM_ERR_NULL;
+  const void* ptrs[] = {q, k, v, i, f, c_initial, n_initial, m_initial, h, n_out, m_out, c_states, n_states, m_states,
+                        c_last, n_last, m_last, workspace};
+  for (const void* p : ptrs) if (p && !aligned16(p)) return MLSTM_ERR_ALIGN;
+  bool use_sm100 = false;
+  if ((rc = resolve_impl(impl, S, DHQK, DHHV, L, dtype, &use_sm100)) != MLSTM_OK) return rc;
+
+  ChunkwiseDims d{B, NH, S, DHQK, DHHV, L, S / L, variant, eps, 1.0f / sqrtf((float)DHQK)};
+  FwLayout lay = carve_fw(workspace, B * NH, S, d.NC, m_out);
+  if (workspace_bytes < lay.bytes) return MLSTM_ERR_WORKSPACE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+  if ((rc = launch_gates(gate_dtype, i, f, variant == MLSTM_EXP ? m_initial : nullptr, nullptr, lay.gb, m_states, d, st)) != MLSTM_OK) return rc;
+  if (use_sm100) {
+    if ((rc = sm100_recurrent_fw(k, v, lay.gb, c_initial, n_initial, c_states, n_states, c_last, n_last, d, st)) != MLSTM_OK) return rc;
+    if ((rc = sm100_parallel_fw(q, k, v, lay.gb, c_states, n_states, h, n_out, d, st)) != MLSTM_OK) return rc;
+  } else {
+    if ((rc = simt_recurrent_fw(dtype, MLSTM_F32, k, v, lay.gb, c_initial, n_initial, c_states, n_states, c_last, n_last, d, st)) != MLSTM_OK) return rc;
+    if ((rc = simt_parallel_fw(dtype, MLSTM_F32, q, k, v, lay.gb, c_states, n_states, h, n_out, d, st)) != MLSTM_OK) return rc;
+  }
+  if (m_last) {
+    MLSTM_CUDA_CHECK(cudaMemcpy2DAsync(m_last, sizeof(float), m_states + d.NC, sizeof(float) * (d.NC + 1),
+                                       sizeof(float), (size_t)B * NH, cudaMemcpyDeviceToDevice, st));
+  }
+  return MLSTM_OK;
+}
+
+int mlstm_b200_chunkwise_bw(const void* q, const void* k, const void* v, const void* i, const void* f,
+                            const float* m_initial, const void* c_states, const float* n_out, const void* dh,
+                            const float* dc_last, void* dq, void* dk, void* dv, float* di, float* df,
+                            float* dc_initial, void* workspace, size_t workspace_bytes, int B, int NH, int S, int DHQK,
+                            int DHHV, int L, int dtype, int gate_dtype, int variant, int impl, float eps, void* stream) {
+  int rc = check_dims(B, NH, S, DHQK, DHHV, L);
+  if (rc != MLSTM_OK) return rc;
+  if (dtype != MLSTM_F32 && dtype != MLSTM_BF16 && dtype != MLSTM_F16) return MLSTM_ERR_DTYPE;
+  if (gate_dtype != MLSTM_F32 && gate_dtype != MLSTM_BF16 && gate_dtype != MLSTM_F16) return MLSTM_ERR_DTYPE;
+  if (variant < MLSTM_EXP || variant > MLSTM_SIG_NONORM) return MLSTM_ERR_UNSUPPORTED;
+  if (!q || !k || !v || !i || !f || !c_states || !dh || !dq || !dk || !dv || !di || !df || !workspace)
+    return MLSTM_ERR_NULL;
+  if (variant != MLSTM_SIG_NONORM && !n_out) return MLSTM_ERR_NULL;
+  const void* ptrs[] = {q, k, v, i, f, m_initial, c_states, n_out, dh, dc_last, dq, dk, dv, di, df, dc_initial, workspace};
+  for (const void* p : ptrs) if (p && !aligned16(p)) return MLSTM_ERR_ALIGN;
+  bool use_sm100 = false;
+  if ((rc = resolve_impl(impl, S, DHQK, DHHV, L, dtype, &use_sm100)) != MLSTM_OK) return rc;
+
+  ChunkwiseDims d{B, NH, S, DHQK, DHHV, L, S / L, variant, eps, 1.0f / sqrtf((float)DHQK)};
+  const int sdt = use_sm100 ? MLSTM_BF16 : MLSTM_F32;
+  BwLayout lay = carve_bw(workspace, B * NH, S, d.NC, DHQK, DHHV, dtype_size(sdt));
+  if (workspace_bytes < lay.bytes) return MLSTM_ERR_WORKSPACE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+  if ((rc = launch_gates(gate_dtype, i, f, variant == MLSTM_EXP ? m_initial : nullptr, n_out, lay.gb, lay.m_states, d, st)) != MLSTM_OK) return rc;
+  if (use_sm100) {
+    if ((rc = sm100_recurrent_bw(q, dh, lay.gb, dc_last, lay.dc_states, dc_initial, d, st)) != MLSTM_OK) return rc;
+    if ((rc = sm100_parallel_bw(q, k, v, dh, lay.gb, c_states, lay.dc_states, dq, dk, dv, lay.acc, lay.kdk, d, st)) != MLSTM_OK) return rc;
+    if ((rc = launch_gate_grad_scan(gate_dtype, i, f, lay.acc, lay.kdk, di, df, d, st)) != MLSTM_OK) return rc;
+  } else {
+    if ((rc = simt_recurrent_bw(dtype, sdt, q, dh, lay.gb, dc_last, lay.dc_states, dc_initial, d, st)) != MLSTM_OK) return rc;
+    if ((rc = simt_parallel_bw(dtype, sdt, q, k, v, dh, lay.gb, c_states, lay.dc_states, dq, dk, dv, d, st)) != MLSTM_OK) return rc;
+    if ((rc = launch_gate_grads(dtype, gate_dtype, q, k, dq, dk, i, f, lay.acc, lay.kdk, di, df, d, st)) != MLSTM_OK) return rc;
+  }
+  return MLSTM_OK;
+}
+
+int mlstm_b200_step(const void* q, const void* k, const void* v, const void* i, const void* f, const void* c,
+                    const void* n, const void* m, void* h, void* c_new, void* n_new, void* m_new, int B, int NH,
+                    int DHQK, int DHHV, int dtype, int state_dtype, float eps, void* stream) {
+  if (B <= 0 || NH <= 0 || DHQK <= 0 || DHHV <= 0 || DHHV % 4 != 0) return MLSTM_ERR_SHAPE;
+  if (!q || !k || !v || !i || !f || !c || !n || !m || !h || !c_new || !n_new || !m_new) return MLSTM_ERR_NULL;
+  if (n_new == n || m_new == m) return MLSTM_ERR_UNSUPPORTED;
+  const void* ptrs[] = {q, k, v, c, n, h, c_new, n_new};
+  for (const void* p : ptrs) if (!aligned16(p)) return MLSTM_ERR_ALIGN;
+  if (state_dtype != MLSTM_F32 && state_dtype != MLSTM_BF16) return MLSTM_ERR_DTYPE;
+  return launch_step(q, k, v, i, f, c, n, m, h, c_new, n_new, m_new, B, NH, DHQK, DHHV, dtype, state_dtype, eps,
+                     static_cast<cudaStream_t>(stream));
+}
+
+int mlstm_b200_step_sequence(const void* q, const void* k, const void* v, const void* i, const void* f,
+                             const float* c, const float* n, const float* m, void* h, float* c_new, float* n_new,
+                             float* m_new, int B, int NH, int T, int DHQK, int DHHV, int dtype, float eps,
+                             void* stream) {
+  if (B <= 0 || NH <= 0 || T <= 0 || DHQK <= 0 || DHHV <= 0 || DHHV % 4 != 0 || DHQK > 512) return MLSTM_ERR_SHAPE;
+  if (!q || !k || !v || !i || !f || !h || !c_new || !n_new || !m_new) return MLSTM_ERR_NULL;
+  const void* ptrs[] = {q, k, v, c, h, c_new};
+  for (const void* p : ptrs) if (p && !aligned16(p)) return MLSTM_ERR_ALIGN;
+  return launch_step_sequence(q, k, v, i, f, c, n, m, h, c_new, n_new, m_new, B, NH, T, DHQK, DHHV, dtype, eps,
+                              static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

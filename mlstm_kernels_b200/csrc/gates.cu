@@ -1,0 +1,273 @@
+// Gate pre-pass and gate-gradient kernels (scalar work per token; HBM traffic is negligible).
+//
+// Pre-pass: from the raw gate logits i, f produce every per-token and per-chunk scalar the
+// contraction kernels need, including the serial max-state recursion over chunks, which is
+// evaluated as a block-wide scan over (max,+) affine maps.
+// Follows mlstm_kernels/torch/chunkwise/triton_xl_chunk/chunkwise_gates.py:15-65 (vecB, vecA),
+// mlstm_kernels/triton/chunkwise/xl_chunk/fw_kernel_recurrent.py:150-176 (m recursion) and
+// mlstm_kernels/torch/chunkwise/native/fw.py:178-195 (per-token max state).
+#include "common.cuh"
+#include "launch.cuh"
+
+namespace mlstm {
+
+constexpr int kGateThreads = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(kGateThreads)
+gates_kernel(const T* __restrict__ vecI, const T* __restrict__ vecF, const float* __restrict__ m_initial,
+             const float* __restrict__ n_out, GateBuffers gb, float* __restrict__ m_states,
+             int S, int L, int NC, int variant, float eps) {
+  const int bh = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = kGateThreads / 32;
+  const bool siging = variant != MLSTM_EXP;
+  const size_t tok0 = (size_t)bh * S;
+  float* g_arr = gb.scratch + (size_t)bh * 2 * NC;
+  float* amax_arr = g_arr + NC;
+
+  // ---- phase 1: b_j, a_j, g_k, max_j a_j per chunk (one warp per chunk) ----
+  for (int k = warp; k < NC; k += nwarps) {
+    const size_t base = tok0 + (size_t)k * L;
+    float carry = 0.f;
+    for (int j0 = 0; j0 < L; j0 += 32) {
+      const int j = j0 + lane;
+      float x = (j < L) ? logsigmoid_f(to_f32(vecF[base + j])) : 0.f;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        float y = __shfl_up_sync(0xffffffffu, x, o);
+        if (lane >= o) x += y;
+      }
+      x += carry;
+      if (j < L) gb.vecB[base + j] = x;
+      carry = __shfl_sync(0xffffffffu, x, 31);
+    }
+    const float g = carry;
+    // a_j = sum_{t>j} lf_t + iota_j as a reverse scan that never includes position j
+    float suffix = 0.f, amax = -INFINITY;
+    for (int j0 = ((L - 1) / 32) * 32; j0 >= 0; j0 -= 32) {
+      const int j = j0 + lane;
+      float x = (j < L) ? logsigmoid_f(to_f32(vecF[base + j])) : 0.f;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        float y = __shfl_down_sync(0xffffffffu, x, o);
+        if (lane + o < 32) x += y;
+      }
+      float excl = __shfl_down_sync(0xffffffffu, x, 1);
+      if (lane == 31) excl = 0.f;
+      excl += suffix;
+      suffix += __shfl_sync(0xffffffffu, x, 0);
+      if (j < L) {
+        const float iv = to_f32(vecI[base + j]);
+        const float iota = siging ? logsigmoid_f(iv) : iv;
+        const float a = excl + iota;
+        gb.iota[base + j] = iota;
+        gb.abar[base + j] = a;  // finalised in phase 3
+        amax = fmaxf(amax, a);
+      }
+    }
+    amax = warp_max(amax);
+    if (lane == 0) { g_arr[k] = g; amax_arr[k] = amax; }
+  }
+  __syncthreads();
+
+  // ---- phase 2: m_{k+1} = max(g_k + m_k, amax_k) as a scan over maps x -> max(x + G, A) ----
+  __shared__ float sG[kGateThreads], sA[kGateThreads], sMin[kGateThreads];
+  {
+    const int t = threadIdx.x;
+    const int seg = (NC + kGateThreads - 1) / kGateThreads;
+    const int k0 = min(NC, t * seg), k1 = min(NC, (t + 1) * seg);
+    if (!siging) {
+      float G = 0.f, A = -INFINITY;
+      for (int k = k0; k < k1; ++k) { A = fmaxf(A + g_arr[k], amax_arr[k]); G += g_arr[k]; }
+      sG[t] = G; sA[t] = A;
+      __syncthreads();
+      if (t == 0) {
+        float m = m_initial ? m_initial[bh] : 0.f;
+        for (int u = 0; u < kGateThreads; ++u) { sMin[u] = m; m = fmaxf(m + sG[u], sA[u]); }
+      }
+      __syncthreads();
+      float m = sMin[t];
+      float* ms = m_states + (size_t)bh * (NC + 1);
+      for (int k = k0; k < k1; ++k) {
+        ms[k] = m;
+        const float mn = fmaxf(g_arr[k] + m, amax_arr[k]);
+        gb.gbar[(size_t)bh * NC + k] = expf(g_arr[k] + m - mn);
+        m = mn;
+        if (k == NC - 1) ms[NC] = m;
+      }
+    } else {
+      float* ms = m_states + (size_t)bh * (NC + 1);
+      for (int k = k0; k < k1; ++k) {
+        ms[k] = 0.f;
+        gb.gbar[(size_t)bh * NC + k] = expf(g_arr[k]);
+        if (k == NC - 1) ms[NC] = 0.f;
+      }
+    }
+  }
+  __syncthreads();
+
+  // ---- phase 3: per-token stabiliser and the three exponentiated gate vectors ----
+  for (int k = warp; k < NC; k += nwarps) {
+    const size_t base = tok0 + (size_t)k * L;
+    const float m_prev = m_states[(size_t)bh * (NC + 1) + k];
+    const float m_next = m_states[(size_t)bh * (NC + 1) + k + 1];
+    float carry = -INFINITY;
+    for (int j0 = 0; j0 < L; j0 += 32) {
+      const int j = j0 + lane;
+      float b = 0.f, x = -INFINITY;
+      if (j < L) { b = gb.vecB[base + j]; x = gb.iota[base + j] - b; }
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        float y = __shfl_up_sync(0xffffffffu, x, o);
+        if (lane >= o) x = fmaxf(x, y);
+      }
+      x = fmaxf(x, carry);
+      carry = __shfl_sync(0xffffffffu, x, 31);
+      if (j < L) {
+        float m_i, bbar, abar;
+        const float a = gb.abar[base + j];
+        if (siging) {
+          m_i = 0.f; bbar = expf(b); abar = expf(a);
+        } else {
+          m_i = fmaxf(b + m_prev, b + x);
+          bbar = expf(b + m_prev - m_i);
+          abar = expf(a - m_next);
+        }
+        gb.m_tok[base + j] = m_i;
+        gb.bbar[base + j] = bbar;
+        gb.abar[base + j] = abar;
+        if (gb.inv_den) {
+          gb.inv_den[base + j] = (variant == MLSTM_SIG_NONORM || n_out == nullptr) ? 1.f : 1.f / (n_out[base + j] + eps);
+        }
+      }
+    }
+  }
+}
+
+// Per-token reductions for the gate gradients:
+//   acc_t = sum_d (q dq - k dk),  kdk_t = sum_d k dk
+// mlstm_kernels/torch/chunkwise/triton_xl_chunk/chunkwise_gates.py:68-95. One warp per token.
+template <typename T>
+__global__ void __launch_bounds__(256)
+gate_grad_rows_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ dq,
+                      const T* __restrict__ dk, float* __restrict__ acc, float* __restrict__ kdk,
+                      size_t ntok, int DHQK) {
+  const size_t tok = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (tok >= ntok) return;
+  const int lane = threadIdx.x & 31;
+  const size_t base = tok * DHQK;
+  float a = 0.f, b = 0.f;
+  for (int d = lane; d < DHQK; d += 32) {
+    const float kk = to_f32(k[base + d]) * to_f32(dk[base + d]);
+    a += to_f32(q[base + d]) * to_f32(dq[base + d]) - kk;
+    b += kk;
+  }
+  a = warp_sum(a); b = warp_sum(b);
+  if (lane == 0) { acc[tok] = a; kdk[tok] = b; }
+}
+
+// deltaF_t = sigmoid(-f_t) * sum_{t' >= t over the whole sequence} acc_t' ; deltaI_t = kdk_t (* sigmoid(-i_t)).
+// One CTA per (batch, head); each thread owns a contiguous token range, block scan over the range sums.
+constexpr int kScanThreads = 1024;
+template <typename T>
+__global__ void __launch_bounds__(kScanThreads)
+gate_grad_scan_kernel(const T* __restrict__ vecI, const T* __restrict__ vecF, const float* __restrict__ acc,
+                      const float* __restrict__ kdk, float* __restrict__ dI, float* __restrict__ dF,
+                      int S, int variant) {
+  __shared__ float s_part[kScanThreads];
+  const int bh = blockIdx.x, t = threadIdx.x;
+  const size_t base = (size_t)bh * S;
+  const int seg = (S + kScanThreads - 1) / kScanThreads;
+  const int s0 = min(S, t * seg), s1 = min(S, (t + 1) * seg);
+  float sum = 0.f;
+  for (int s = s0; s < s1; ++s) sum += acc[base + s];
+  s_part[t] = sum;
+  __syncthreads();
+  // suffix sums over threads (exclusive): sum of the ranges to the right
+  for (int o = 1; o < kScanThreads; o <<= 1) {
+    float y = (t + o < kScanThreads) ? s_part[t + o] : 0.f;
+    __syncthreads();
+    s_part[t] += y;
+    __syncthreads();
+  }
+  float run = (t + 1 < kScanThreads) ? s_part[t + 1] : 0.f;
+  for (int s = s1 - 1; s >= s0; --s) {
+    run += acc[base + s];
+    dF[base + s] = run * sigmoid_f(-to_f32(vecF[base + s]));
+    float di = kdk[base + s];
+    if (variant != MLSTM_EXP) di *= sigmoid_f(-to_f32(vecI[base + s]));
+    dI[base + s] = di;
+  }
+}
+
+// ---- launchers ----------------------------------------------------------------------------------
+template <typename T>
+int launch_gates_t(const void* i, const void* f, const float* m_initial, const float* n_out, const GateBuffers& gb,
+                   float* m_states, const ChunkwiseDims& d, cudaStream_t st) {
+  PhaseScope ps(PH_GATES, st);
+  gates_kernel<T><<<d.B * d.NH, kGateThreads, 0, st>>>((const T*)i, (const T*)f, m_initial, n_out, gb, m_states,
+                                                     d.S, d.L, d.NC, d.variant, d.eps);
+  MLSTM_LAUNCH_CHECK();
+  return MLSTM_OK;
+}
+
+int launch_gates(int dtype, const void* i, const void* f, const float* m_initial, const float* n_out,
+                 const GateBuffers& gb, float* m_states, const ChunkwiseDims& d, cudaStream_t st) {
+  switch (dtype) {
+    case MLSTM_F32: return launch_gates_t<float>(i, f, m_initial, n_out, gb, m_states, d, st);
+    case MLSTM_BF16: return launch_gates_t<__nv_bfloat16>(i, f, m_initial, n_out, gb, m_states, d, st);
+    case MLSTM_F16: return launch_gates_t<__half>(i, f, m_initial, n_out, gb, m_states, d, st);
+  }
+  return MLSTM_ERR_DTYPE;
+}
+
+template <typename T>
+int launch_gate_grad_rows_t(const void* q, const void* k, const void* dq, const void* dk, float* acc, float* kdk,
+                            const ChunkwiseDims& d, cudaStream_t st) {
+  const size_t ntok = (size_t)d.B * d.NH * d.S;
+  gate_grad_rows_kernel<T><<<(unsigned)((ntok + 7) / 8), 256, 0, st>>>((const T*)q, (const T*)k, (const T*)dq,
+                                                                        (const T*)dk, acc, kdk, ntok, d.DHQK);
+  MLSTM_LAUNCH_CHECK();
+  return MLSTM_OK;
+}
+
+int launch_gate_grad_scan(int gate_dtype, const void* i, const void* f, const float* acc, const float* kdk, float* dI,
+                          float* dF, const ChunkwiseDims& d, cudaStream_t st);
+
+int launch_gate_grads(int dtype, int gate_dtype, const void* q, const void* k, const void* dq, const void* dk,
+                      const void* i, const void* f, float* acc, float* kdk, float* dI, float* dF,
+                      const ChunkwiseDims& d, cudaStream_t st) {
+  PhaseScope ps(PH_GATE_GRADS, st);
+  int rc = MLSTM_ERR_DTYPE;
+  switch (dtype) {
+    case MLSTM_F32: rc = launch_gate_grad_rows_t<float>(q, k, dq, dk, acc, kdk, d, st); break;
+    case MLSTM_BF16: rc = launch_gate_grad_rows_t<__nv_bfloat16>(q, k, dq, dk, acc, kdk, d, st); break;
+    case MLSTM_F16: rc = launch_gate_grad_rows_t<__half>(q, k, dq, dk, acc, kdk, d, st); break;
+  }
+  if (rc != MLSTM_OK) return rc;
+  return launch_gate_grad_scan(gate_dtype, i, f, acc, kdk, dI, dF, d, st);
+}
+
+// Scan-only entry: acc / kdk were already produced (in f32, before rounding) by the backward kernels.
+int launch_gate_grad_scan(int dtype, const void* i, const void* f, const float* acc, const float* kdk, float* dI,
+                          float* dF, const ChunkwiseDims& d, cudaStream_t st) {
+  switch (dtype) {
+    case MLSTM_F32:
+      gate_grad_scan_kernel<float><<<d.B * d.NH, kScanThreads, 0, st>>>((const float*)i, (const float*)f, acc, kdk,
+                                                                        dI, dF, d.S, d.variant);
+      break;
+    case MLSTM_BF16:
+      gate_grad_scan_kernel<__nv_bfloat16><<<d.B * d.NH, kScanThreads, 0, st>>>(
+          (const __nv_bfloat16*)i, (const __nv_bfloat16*)f, acc, kdk, dI, dF, d.S, d.variant);
+      break;
+    case MLSTM_F16:
+      gate_grad_scan_kernel<__half><<<d.B * d.NH, kScanThreads, 0, st>>>((const __half*)i, (const __half*)f, acc, kdk,
+                                                                         dI, dF, d.S, d.variant);
+      break;
+    default: return MLSTM_ERR_DTYPE;
+  }
+  MLSTM_LAUNCH_CHECK();
+  return MLSTM_OK;
+}
+
+}  // namespace mlstm

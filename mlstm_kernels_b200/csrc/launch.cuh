@@ -1,0 +1,51 @@
+// Host-side launcher prototypes shared between the translation units of libmlstm_b200.so.
+#pragma once
+#include "common.cuh"
+
+namespace mlstm {
+
+// gates.cu
+int launch_gates(int dtype, const void* i, const void* f, const float* m_initial, const float* n_out,
+                 const GateBuffers& gb, float* m_states, const ChunkwiseDims& d, cudaStream_t st);
+int launch_gate_grads(int dtype, int gate_dtype, const void* q, const void* k, const void* dq, const void* dk, const void* i,
+                      const void* f, float* acc, float* kdk, float* dI, float* dF, const ChunkwiseDims& d,
+                      cudaStream_t st);
+int launch_gate_grad_scan(int dtype, const void* i, const void* f, const float* acc, const float* kdk, float* dI,
+                          float* dF, const ChunkwiseDims& d, cudaStream_t st);
+
+// chunkwise_simt.cu : portable CUDA-core kernels, any shape, any element type
+int simt_recurrent_fw(int dtype, int state_dtype, const void* k, const void* v, const GateBuffers& gb,
+                      const float* c_initial, const float* n_initial, void* c_states, float* n_states,
+                      float* c_last, float* n_last, const ChunkwiseDims& d, cudaStream_t st);
+int simt_parallel_fw(int dtype, int state_dtype, const void* q, const void* k, const void* v, const GateBuffers& gb,
+                     const void* c_states, const float* n_states, void* h, float* n_out, const ChunkwiseDims& d,
+                     cudaStream_t st);
+int simt_recurrent_bw(int dtype, int state_dtype, const void* q, const void* dh, const GateBuffers& gb,
+                      const float* dc_last, void* dc_states, float* dc_initial, const ChunkwiseDims& d,
+                      cudaStream_t st);
+int simt_parallel_bw(int dtype, int state_dtype, const void* q, const void* k, const void* v, const void* dh,
+                     const GateBuffers& gb, const void* c_states, const void* dc_states, void* dq, void* dk, void* dv,
+                     const ChunkwiseDims& d, cudaStream_t st);
+
+// chunkwise_sm100.cu : tcgen05 + TMA kernels (bf16, L = 128, head dims multiples of 64)
+bool sm100_supported(int S, int DHQK, int DHHV, int L, int dtype);
+int sm100_recurrent_fw(const void* k, const void* v, const GateBuffers& gb, const float* c_initial,
+                       const float* n_initial, void* c_states, float* n_states, float* c_last, float* n_last,
+                       const ChunkwiseDims& d, cudaStream_t st);
+int sm100_parallel_fw(const void* q, const void* k, const void* v, const GateBuffers& gb, const void* c_states,
+                      const float* n_states, void* h, float* n_out, const ChunkwiseDims& d, cudaStream_t st);
+int sm100_recurrent_bw(const void* q, const void* dh, const GateBuffers& gb, const float* dc_last, void* dc_states,
+                       float* dc_initial, const ChunkwiseDims& d, cudaStream_t st);
+int sm100_parallel_bw(const void* q, const void* k, const void* v, const void* dh, const GateBuffers& gb,
+                      const void* c_states, const void* dc_states, void* dq, void* dk, void* dv, float* acc,
+                      float* kdk, const ChunkwiseDims& d, cudaStream_t st);
+
+// step.cu
+int launch_step(const void* q, const void* k, const void* v, const void* i, const void* f, const void* c,
+                const void* n, const void* m, void* h, void* c_new, void* n_new, void* m_new, int B, int NH, int DHQK,
+                int DHHV, int dtype, int state_dtype, float eps, cudaStream_t st);
+int launch_step_sequence(const void* q, const void* k, const void* v, const void* i, const void* f, const float* c,
+                         const float* n, const float* m, void* h, float* c_new, float* n_new, float* m_new, int B,
+                         int NH, int T, int DHQK, int DHHV, int dtype, float eps, cudaStream_t st);
+
+}  // namespace mlstm

@@ -1,0 +1,178 @@
+"""GPU parity tests of the chunkwise kernels: CUDA path (through the C ABI) vs the numpy oracle and
+the committed golden vectors of the reference.  Error measure: max |x - ref| / max |ref|.
+
+Stated tolerances
+  f32 inputs : H, states 1e-4 ; gradients 1e-3
+  bf16 inputs: H, gradients 2e-2 ; states 2e-2 (inputs of the oracle are rounded to bf16 first)
+"""
+
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import mlstm_kernels_b200 as mk
+from inputs import CASES, make_chunkwise_inputs, max_rel_err, subsample
+from util_gpu import case_inputs, npy, run_cuda_fwbw, run_oracle_fwbw, to_dev
+
+pytestmark = pytest.mark.gpu
+
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+TOL_F32_FW, TOL_F32_BW, TOL_BF16 = 1e-4, 1e-3, 2e-2
+FW_KEYS = ("H", "C_last", "n_last", "m_last")
+BW_KEYS = ("dQ", "dK", "dV", "dI", "dF")
+
+
+def compare(got, ref, tol_fw, tol_bw, keys_fw=FW_KEYS, stride=1):
+    for key in keys_fw:
+        if key in got and key in ref:
+            assert max_rel_err(subsample(got[key], stride), subsample(np.asarray(ref[key]), stride) if stride > 1 and ref[key].ndim > 1 else ref[key]) < tol_fw, key
+    for key in BW_KEYS + ("dC_initial",):
+        if key in got and key in ref:
+            assert max_rel_err(subsample(got[key], stride), subsample(np.asarray(ref[key]), stride) if stride > 1 and ref[key].ndim > 1 else ref[key]) < tol_bw, key
+
+
+@pytest.mark.parametrize("name", [n for n, c in CASES.items() if c["kind"] == "exp_chunkwise"])
+def test_exp_f32_vs_reference_golden(name):
+    case = CASES[name]
+    gold = dict(np.load(os.path.join(GOLD, f"{name}.npz")))
+    got = run_cuda_fwbw(make_chunkwise_inputs(case), case["L"])
+    compare(got, gold, TOL_F32_FW, TOL_F32_BW, stride=case.get("stride", 1))
+
+
+@pytest.mark.parametrize("name", ["sig_norm", "sig_nonorm"])
+@pytest.mark.parametrize("L", [64, 128])
+def test_sig_f32_vs_reference_golden(name, L):
+    case = CASES[name]
+    gold = dict(np.load(os.path.join(GOLD, f"{name}.npz")))
+    got = run_cuda_fwbw(make_chunkwise_inputs(case), L, siging=True, normalize=case["normalize"])
+    compare(got, gold, TOL_F32_FW, TOL_F32_BW, keys_fw=("H",))
+
+
+def test_exp_f32_vs_reference_parallel_golden():
+    case = CASES["exp_parallel"]
+    gold = dict(np.load(os.path.join(GOLD, "exp_parallel.npz")))
+    got = run_cuda_fwbw(make_chunkwise_inputs(case), case["L"])
+    compare(got, gold, TOL_F32_FW, TOL_F32_BW, keys_fw=("H",))
+
+
+SHAPES = [
+    # B, NH, S, DHQK, DHHV, L
+    (1, 2, 64, 32, 64, 16),     # S < 128: one chunk of 64 (reference heuristic)
+    (2, 2, 128, 64, 64, 16),
+    (1, 3, 256, 48, 96, 32),    # head dims that are not powers of two
+    (1, 2, 256, 24, 48, 64),
+    (1, 2, 512, 128, 128, 128),
+    (1, 1, 512, 64, 128, 256),
+    (2, 1, 256, 256, 512, 128),  # decode-model head geometry
+]
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("variant", ["exp", "sig", "sig_nonorm"])
+def test_f32_vs_oracle_shapes(shape, variant):
+    B, NH, S, DHQK, DHHV, L = shape
+    inp = case_inputs(11, B, NH, S, DHQK, DHHV, init=True, dC_last=True)
+    siging, normalize = variant != "exp", variant != "sig_nonorm"
+    Leff = mk.select_chunk_size(S, L)
+    got = run_cuda_fwbw(inp, L, siging=siging, normalize=normalize)
+    ref = run_oracle_fwbw(inp, Leff, siging=siging, normalize=normalize)
+    keys = FW_KEYS if not siging else (("H", "C_last", "n_last") if normalize else ("H", "C_last"))
+    compare(got, ref, TOL_F32_FW, TOL_F32_BW, keys_fw=keys)
+
+
+@pytest.mark.parametrize("shape", [(2, 2, 256, 64, 128, 64), (1, 2, 512, 128, 128, 128), (1, 2, 256, 256, 256, 128)])
+@pytest.mark.parametrize("variant", ["exp", "sig", "sig_nonorm"])
+@pytest.mark.parametrize("impl", ["simt", "auto"])
+def test_bf16_vs_oracle(shape, variant, impl):
+    B, NH, S, DHQK, DHHV, L = shape
+    inp = case_inputs(12, B, NH, S, DHQK, DHHV)
+    siging, normalize = variant != "exp", variant != "sig_nonorm"
+    got = run_cuda_fwbw(inp, L, dtype=torch.bfloat16, siging=siging, normalize=normalize, impl=impl)
+    ref = run_oracle_fwbw(inp, L, dtype=torch.bfloat16, siging=siging, normalize=normalize)
+    keys = FW_KEYS if not siging else (("H", "C_last", "n_last") if normalize else ("H", "C_last"))
+    compare(got, ref, TOL_BF16, TOL_BF16, keys_fw=keys)
+
+
+@pytest.mark.parametrize("variant", ["exp", "sig"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_state_passing(variant, dtype):
+    """Four segments chained through the returned states equal one pass (reference:
+    tests/torch/chunkwise/test_chunkwise_triton_xl_chunk.py:58-72, fixture seed 42 (2,4,256,16,32))."""
+    inp = case_inputs(42, 2, 4, 256, 16, 32)
+    q, k, v, i, f = (to_dev(inp[n], dtype) for n in "qkvif")
+    fn = mk.mlstm_chunkwise__b200_xl_chunk if variant == "exp" else mk.mlstm_siging_chunkwise__b200_xl_chunk
+    H_full, last_full = fn(q, k, v, i, f, return_last_states=True, chunk_size=64)
+    states = (None,) * (3 if variant == "exp" else 2)
+    hs = []
+    for s0 in range(0, 256, 64):
+        sl = slice(s0, s0 + 64)
+        if variant == "exp":
+            h, states = fn(q[:, :, sl], k[:, :, sl], v[:, :, sl], i[:, :, sl], f[:, :, sl], states[0], states[1],
+                           states[2], return_last_states=True, chunk_size=64)
+        else:
+            h, states = fn(q[:, :, sl], k[:, :, sl], v[:, :, sl], i[:, :, sl], f[:, :, sl], states[0], states[1],
+                           None, return_last_states=True, chunk_size=64)
+        hs.append(h)
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    assert max_rel_err(npy(torch.cat(hs, 2)), npy(H_full)) < tol
+    for a, b in zip(states, last_full):
+        assert a.dtype == torch.float32
+        assert max_rel_err(npy(a), npy(b)) < 1e-5
+
+
+def test_chunk_size_independence_full_head_dims():
+    """H does not depend on the chunk size (size-independent property at the benchmark head geometry
+    NH=16-style 256/256, and 256/512)."""
+    for DHQK, DHHV in ((256, 256), (256, 512)):
+        inp = case_inputs(5, 1, 2, 1024, DHQK, DHHV)
+        q, k, v, i, f = (to_dev(inp[n], torch.bfloat16) for n in "qkvif")
+        hs = [mk.mlstm_chunkwise__b200_xl_chunk(q, k, v, i, f, chunk_size=L) for L in (64, 128, 256)]
+        for h in hs[1:]:
+            assert max_rel_err(npy(h), npy(hs[0])) < TOL_BF16
+
+
+def test_deterministic_and_inputs_untouched():
+    inp = case_inputs(3, 1, 2, 512, 128, 128)
+    q, k, v, i, f = (to_dev(inp[n], torch.bfloat16) for n in "qkvif")
+    q0 = q.clone()
+    a = mk.mlstm_chunkwise__b200_xl_chunk(q, k, v, i, f, chunk_size=128)
+    b = mk.mlstm_chunkwise__b200_xl_chunk(q, k, v, i, f, chunk_size=128)
+    assert torch.equal(a, b)
+    assert torch.equal(q, q0)
+    assert not torch.isnan(a).any()
+
+
+def test_return_conventions_and_dtypes():
+    inp = case_inputs(4, 1, 2, 128, 32, 64)
+    for dt in (torch.float32, torch.bfloat16, torch.float16):
+        q, k, v, i, f = (to_dev(inp[n], dt) for n in "qkvif")
+        h = mk.mlstm_chunkwise__b200_xl_chunk(q, k, v, i, f)
+        assert isinstance(h, torch.Tensor) and h.dtype == dt and h.shape == v.shape
+        h, (c, n, m) = mk.mlstm_chunkwise__b200_xl_chunk(q, k, v, i, f, return_last_states=True)
+        assert c.shape == (1, 2, 32, 64) and n.shape == (1, 2, 32) and m.shape == (1, 2, 1)
+        assert c.dtype == n.dtype == m.dtype == torch.float32 and c.is_contiguous()
+        h, st = mk.mlstm_siging_chunkwise__b200_xl_chunk(q, k, v, i, f, return_last_states=True, normalize=False)
+        assert len(st) == 2
+
+
+def test_shape_errors():
+    inp = case_inputs(4, 1, 1, 128, 32, 64)
+    q, k, v, i, f = (to_dev(inp[n], torch.float32) for n in "qkvif")
+    with pytest.raises(ValueError):
+        mk.mlstm_chunkwise__b200_xl_chunk(q[:, :, :100], k[:, :, :100], v[:, :, :100], i[:, :, :100], f[:, :, :100])
+    with pytest.raises(ValueError):
+        mk.mlstm_chunkwise__b200_xl_chunk(q, k, v, i, f, chunk_size=48)
+    with pytest.raises(ValueError):
+        mk.mlstm_chunkwise__b200_xl_chunk(q, k, v, i, f, autocast_kernel_dtype=torch.float64)
+    with pytest.raises(RuntimeError):
+        mk.mlstm_chunkwise__b200_xl_chunk(q.cpu(), k.cpu(), v.cpu(), i.cpu(), f.cpu())
+
+
+def test_autocast_casts_inputs():
+    inp = case_inputs(4, 1, 2, 128, 32, 64)
+    q, k, v, i, f = (to_dev(inp[n], torch.float32) for n in "qkvif")
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        h = mk.mlstm_chunkwise__b200_xl_chunk(q, k, v, i, f, autocast_kernel_dtype=torch.bfloat16)
+    assert h.dtype == torch.bfloat16

@@ -1,0 +1,109 @@
+"""GPU parity tests of the recurrent decode kernels vs the oracle and the reference golden vectors.
+Tolerances: f32 1e-5 on h and states; bf16 inputs 2e-2 on h, f32 states 1e-4 (oracle fed bf16-rounded inputs)."""
+
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import mlstm_kernels_b200 as mk
+from inputs import CASES, make_step_inputs, max_rel_err
+from oracle import mlstm_oracle as O
+from util_gpu import case_inputs, npy, rounded, to_dev
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def test_step_f32_vs_reference_golden():
+    case = CASES["step_small"]
+    gold = dict(np.load(os.path.join(GOLD, "step_small.npz")))
+    inp = make_step_inputs(case)
+    c, n, m = (to_dev(inp[x], torch.float32) for x in "cnm")
+    for s in range(case["steps"]):
+        q, k, v, i, f = (to_dev(inp[x][s], torch.float32) for x in "qkvif")
+        c_old = c.clone()
+        h, (c2, n2, m2) = mk.mlstm_recurrent_step__b200(q, k, v, i, f, c, n, m)
+        assert torch.equal(c, c_old), "old state must stay untouched"
+        c, n, m = c2, n2, m2
+        assert max_rel_err(npy(h), gold["h"][s]) < 1e-5
+    assert max_rel_err(npy(c), gold["c"]) < 1e-5
+    assert max_rel_err(npy(n), gold["n"]) < 1e-5
+    assert max_rel_err(npy(m), gold["m"]) < 1e-5
+
+
+@pytest.mark.parametrize("B,NH,DHQK,DHHV", [(1, 8, 256, 512), (8, 8, 256, 512), (3, 2, 48, 96), (2, 4, 64, 128)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32, torch.float16])
+def test_step_vs_oracle(B, NH, DHQK, DHHV, dtype):
+    inp = make_step_inputs(dict(seed=9, B=B, NH=NH, DHQK=DHQK, DHHV=DHHV, steps=3))
+    c, n, m = (to_dev(inp[x], torch.float32) for x in "cnm")
+    co, no, mo = inp["c"], inp["n"], inp["m"]
+    for s in range(3):
+        q, k, v, i, f = (to_dev(inp[x][s], dtype) for x in "qkvif")
+        h, (c, n, m) = mk.mlstm_recurrent_step__b200(q, k, v, i, f, c, n, m)
+        ho, (co, no, mo) = O.recurrent_step(*(rounded(inp[x][s], dtype) for x in "qkvif"), co, no, mo)
+        assert max_rel_err(npy(h), ho) < (1e-5 if dtype == torch.float32 else 2e-2)
+    assert max_rel_err(npy(c), co) < 1e-4
+    assert max_rel_err(npy(n), no) < 1e-4
+    assert max_rel_err(npy(m), mo) < 1e-4
+
+
+def test_step_bf16_state_and_out_buffers():
+    inp = make_step_inputs(dict(seed=10, B=2, NH=2, DHQK=64, DHHV=128, steps=1))
+    q, k, v, i, f = (to_dev(inp[x][0], torch.bfloat16) for x in "qkvif")
+    c, n, m = (to_dev(inp[x], torch.bfloat16) for x in "cnm")
+    h, (c2, n2, m2) = mk.mlstm_recurrent_step__b200(q, k, v, i, f, c, n, m, dtype_state=torch.bfloat16)
+    assert c2.dtype == torch.bfloat16 and h.dtype == torch.bfloat16
+    ho, (co, _, _) = O.recurrent_step(*(rounded(inp[x][0], torch.bfloat16) for x in "qkvif"),
+                                      *(rounded(inp[x], torch.bfloat16) for x in "cnm"))
+    assert max_rel_err(npy(h), ho) < 2e-2
+    assert max_rel_err(npy(c2), co) < 1e-2
+    # caller-provided output buffers; C may be updated in place
+    cf = c.float()
+    nb, mb = torch.empty_like(n, dtype=torch.float32), torch.empty_like(m, dtype=torch.float32)
+    h3, (c3, n3, m3) = mk.mlstm_recurrent_step__b200_fw(cf, n.float(), m.float(), q, k, v, i, f, matC_new=cf,
+                                                        vecN_new=nb, scaM_new=mb)
+    assert c3.data_ptr() == cf.data_ptr()
+    assert max_rel_err(npy(h3), ho) < 2e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_sequence_kernel_equals_step_loop_and_chunkwise(dtype):
+    inp = case_inputs(21, 2, 2, 32, 64, 128)
+    q, k, v, i, f = (to_dev(inp[x], dtype) for x in "qkvif")
+    h_seq, (c_s, n_s, m_s) = mk.mlstm_recurrent_sequence__b200(q, k, v, i, f, return_last_states=True)
+    c = torch.zeros(2, 2, 64, 128, device="cuda"); n = torch.zeros(2, 2, 64, device="cuda")
+    m = torch.zeros(2, 2, 1, device="cuda")
+    hs = []
+    for t in range(32):
+        h, (c, n, m) = mk.mlstm_recurrent_step__b200(q[:, :, t], k[:, :, t], v[:, :, t], i[:, :, t, None],
+                                                     f[:, :, t, None], c, n, m)
+        hs.append(h)
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    assert max_rel_err(npy(h_seq), npy(torch.stack(hs, 2))) < tol
+    assert max_rel_err(npy(c_s), npy(c)) < 1e-5
+    h_cw = mk.mlstm_chunkwise__b200_xl_chunk(q, k, v, i, f, chunk_size=16)
+    assert max_rel_err(npy(h_seq), npy(h_cw)) < (1e-4 if dtype == torch.float32 else 2e-2)
+
+
+def test_step_full_size_decay_property():
+    """Size-independent check at the full decode geometry (B=64, NH=8, 256/512): with k = 0 the step
+    must scale C by exp(logsigmoid(f) + m - m') exactly and leave it otherwise unchanged."""
+    B, NH, DHQK, DHHV = 64, 8, 256, 512
+    g = torch.Generator(device="cuda").manual_seed(0)
+    c = torch.randn(B, NH, DHQK, DHHV, device="cuda", generator=g) * 0.1
+    n = torch.randn(B, NH, DHQK, device="cuda", generator=g).abs()
+    m = torch.randn(B, NH, 1, device="cuda", generator=g)
+    q = torch.randn(B, NH, DHQK, device="cuda", generator=g).bfloat16()
+    k = torch.zeros_like(q)
+    v = torch.randn(B, NH, DHHV, device="cuda", generator=g).bfloat16()
+    i = torch.randn(B, NH, 1, device="cuda", generator=g).bfloat16()
+    f = (3 + torch.randn(B, NH, 1, device="cuda", generator=g)).bfloat16()
+    h, (c2, n2, m2) = mk.mlstm_recurrent_step__b200(q, k, v, i, f, c, n, m)
+    lf = torch.nn.functional.logsigmoid(f.float())
+    m_new = torch.maximum(lf + m, i.float())
+    scale = torch.exp(lf + m - m_new)
+    assert torch.allclose(m2, m_new, rtol=1e-6, atol=1e-6)
+    assert torch.allclose(c2, c * scale[..., None], rtol=1e-5, atol=1e-7)
+    assert torch.allclose(n2, n * scale, rtol=1e-5, atol=1e-7)
