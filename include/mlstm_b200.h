@@ -58,6 +58,13 @@ const char* mlstm_b200_last_cuda_error(void);
 long long mlstm_b200_launch_count(void);
 
 /*
+ * Waits for the device to go idle and returns the status word of the tcgen05 kernels: 0, or the
+ * code (> 0) of the first bounded wait that ran out (the kernel then stopped and its results are
+ * invalid); a negative MLSTM_ERR_* value if the query itself failed.  reset != 0 clears the word.
+ */
+int mlstm_b200_device_status(int reset);
+
+/*
  * Per-phase device timing.  After mlstm_b200_profile_enable(1) every phase of the entry points
  * below is bracketed by CUDA events on the launching stream; mlstm_b200_profile_read() waits for
  * them, adds up the elapsed milliseconds and the number of occurrences per phase into arrays of

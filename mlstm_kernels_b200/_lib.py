@@ -28,6 +28,7 @@ SIGNATURES = {
     "mlstm_b200_error_string": (C.c_char_p, [_i]),
     "mlstm_b200_last_cuda_error": (C.c_char_p, []),
     "mlstm_b200_launch_count": (C.c_longlong, []),
+    "mlstm_b200_device_status": (_i, [_i]),
     "mlstm_b200_profile_enable": (_i, [_i]),
     "mlstm_b200_profile_phases": (_i, []),
     "mlstm_b200_profile_phase_name": (C.c_char_p, [_i]),
@@ -116,3 +117,11 @@ def profile_read() -> dict:
     cnt = (C.c_int * n)()
     check(lib.mlstm_b200_profile_read(ms, cnt), "mlstm_b200_profile_read")
     return {lib.mlstm_b200_profile_phase_name(p).decode(): (float(ms[p]), int(cnt[p])) for p in range(n)}
+
+
+def device_status(reset: bool = True) -> int:
+    """Synchronise and return the status word of the tcgen05 kernels (0 = no bounded wait ran out)."""
+    rc = int(load().mlstm_b200_device_status(1 if reset else 0))
+    if rc < 0:
+        check(rc, "mlstm_b200_device_status")
+    return rc

@@ -136,6 +136,12 @@ const char* mlstm_b200_last_cuda_error(void) { return g_last_cuda_error; }
 
 long long mlstm_b200_launch_count(void) { return g_launches.load(); }
 
+int mlstm_b200_device_status(int reset) {
+  int status = 0;
+  const int rc = sm100_device_status(reset, &status);
+  return rc != MLSTM_OK ? rc : status;
+}
+
 int mlstm_b200_profile_enable(int on) {
   std::lock_guard<std::mutex> lk(g_prof_mu);
   for (auto& r : g_prof_recs) { cudaEventDestroy(r.a); cudaEventDestroy(r.b); }
@@ -254,7 +260,7 @@ int mlstm_b200_chunkwise_bw(const void* q, const void* k, const void* v, const v
   if (use_sm100) {
     if ((rc = sm100_recurrent_bw(q, dh, lay.gb, dc_last, lay.dc_states, dc_initial, d, st)) != MLSTM_OK) return rc;
     if ((rc = sm100_parallel_bw(q, k, v, dh, lay.gb, c_states, lay.dc_states, dq, dk, dv, lay.acc, lay.kdk, d, st)) != MLSTM_OK) return rc;
-    if ((rc = launch_gate_grad_scan(gate_dtype, i, f, lay.acc, lay.kdk, di, df, d, st)) != MLSTM_OK) return rc;
+    if ((rc = launch_gate_grads(dtype, gate_dtype, q, k, dq, dk, i, f, lay.acc, lay.kdk, di, df, d, st)) != MLSTM_OK) return rc;
   } else {
     if ((rc = simt_recurrent_bw(dtype, sdt, q, dh, lay.gb, dc_last, lay.dc_states, dc_initial, d, st)) != MLSTM_OK) return rc;
     if ((rc = simt_parallel_bw(dtype, sdt, q, k, v, dh, lay.gb, c_states, lay.dc_states, dq, dk, dv, d, st)) != MLSTM_OK) return rc;

@@ -1,10 +1,613 @@
-// placeholder, replaced below
+// tcgen05 / TMEM / TMA implementation of the chunkwise mLSTM kernels for B200 (sm_100a).
+// bf16 operands, f32 accumulation in tensor memory, chunk size 128, head dims multiples of 128.
+//
+//   rec_sm100<BWD>   inter-chunk recurrence (forward C_k, n_k; backward deltaC_k).  A CTA owns a 128 x 128 tile
+//                    of the state for one (batch, head) and walks the chunks in order; per chunk one
+//                    (gated left)^T x right contraction on the tensor cores into a double-buffered TMEM
+//                    accumulator, decay + accumulate of the running state in registers, bf16 state store.
+//                    mlstm_kernels/triton/chunkwise/xl_chunk/fw_kernel_recurrent.py:14-230, bw_kernel_recurrent.py:15-181
+//   par_sm100<MODE>  intra-chunk kernel for H, deltaV, deltaK, deltaQ.  Per (batch, head, chunk, 128-wide output tile):
+//                    score = A B^T (TMEM) -> gate matrix applied by the CUDA cores, bf16 result written back to
+//                    TMEM and used as the A operand of score x X; the inter-chunk term A x state is accumulated
+//                    into the same TMEM tile first and row-scaled in place.  The L x L gate matrix never
+//                    leaves the SM.
+//                    fw_kernel_parallel.py:14-289, bw_kernel_parallel_dV.py, bw_kernel_parallel_dK.py, bw_kernel_parallel_dQ.py
+// Operands arrive by TMA (128-byte swizzle, no multicast) through a two-stage mbarrier ring; one warp produces,
+// one thread issues the MMAs, the remaining warps do the element-wise work.  Every wait is bounded.
 #include "common.cuh"
 #include "launch.cuh"
+#include "sm100.cuh"
+
 namespace mlstm {
-bool sm100_supported(int, int, int, int, int) { return false; }
-int sm100_recurrent_fw(const void*, const void*, const GateBuffers&, const float*, const float*, void*, float*, float*, float*, const ChunkwiseDims&, cudaStream_t) { return MLSTM_ERR_UNSUPPORTED; }
-int sm100_parallel_fw(const void*, const void*, const void*, const GateBuffers&, const void*, const float*, void*, float*, const ChunkwiseDims&, cudaStream_t) { return MLSTM_ERR_UNSUPPORTED; }
-int sm100_recurrent_bw(const void*, const void*, const GateBuffers&, const float*, void*, float*, const ChunkwiseDims&, cudaStream_t) { return MLSTM_ERR_UNSUPPORTED; }
-int sm100_parallel_bw(const void*, const void*, const void*, const void*, const GateBuffers&, const void*, const void*, void*, void*, void*, float*, float*, const ChunkwiseDims&, cudaStream_t) { return MLSTM_ERR_UNSUPPORTED; }
+
+using namespace sm100;
+
+__device__ int g_sm100_status = 0;  // first error code raised by a bounded wait (0 = none)
+
+constexpr int CL = 128;  // chunk length handled by these kernels
+
+// =====================================================================================================
+// Inter-chunk recurrence
+// =====================================================================================================
+struct RecParams {
+  const float* lscale;  // per token: abar (fw) or bbar (bw)
+  const float* rscale;  // per token: nullptr (fw) or 1/(den+eps) (bw)
+  float lmul;           // 1 (fw) or qk_scale (bw)
+  const float* gbar;    // (BNH, NC)
+  const float* c_init;  // (BNH, DHQK, DHHV) f32 or nullptr
+  const float* n_init;  // (BNH, DHQK) or nullptr
+  __nv_bfloat16* c_states;  // (BNH, NC+1, DHQK, DHHV)
+  float* n_states;          // (BNH, NC+1, DHQK) or nullptr
+  float* c_final;           // (BNH, DHQK, DHHV) f32 or nullptr
+  float* n_final;
+  int S, NC, DHQK, DHHV;
+};
+
+constexpr int REC_THREADS = 320;                 // warp 0 TMA, warp 1 MMA, warps 2..9 element-wise
+constexpr int REC_STAGE_BYTES = 65536;           // left tile 32 KB + right tile 32 KB
+constexpr int REC_SMEM = 2 * REC_STAGE_BYTES + 1024;
+
+template <bool BWD>
+__global__ void __launch_bounds__(REC_THREADS, 1)
+rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUtensorMap mapR, RecParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  __shared__ uint64_t bar_full[2], bar_empty[2], bar_scaled[2], bar_acc_full[2], bar_acc_free[2], bar_nsum[2];
+  __shared__ uint32_t s_tmem;
+  __shared__ float s_nsum[2][128];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int e0 = blockIdx.x * 128, d0 = blockIdx.y * 128, bh = blockIdx.z;
+  const int NC = p.NC;
+  const bool do_n = (!BWD) && blockIdx.x == 0 && p.n_states != nullptr;
+
+  if (tid == 0) {
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bar_full[s], 1); mbar_init(&bar_empty[s], 1); mbar_init(&bar_scaled[s], 256);
+      mbar_init(&bar_acc_full[s], 1); mbar_init(&bar_acc_free[s], 256); mbar_init(&bar_nsum[s], 256);
+    }
+    fence_barrier_init();
+    tma_prefetch_desc(&mapL); tma_prefetch_desc(&mapR);
+  }
+  if (tid < 256) { s_nsum[0][tid & 127] = 0.f; s_nsum[1][tid & 127] = 0.f; }
+  if (warp == 1) { tmem_alloc(&s_tmem, 256); tmem_relinquish(); }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = s_tmem;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int issued = 0;
+      for (int s = 0; s < NC; ++s) {
+        const int st = s & 1;
+        if (!mbar_wait(&bar_empty[st], ((s >> 1) & 1) ^ 1, &g_sm100_status, 101)) break;
+        const int ck = BWD ? NC - 1 - s : s;
+        const int row0 = bh * p.S + ck * CL;
+        uint8_t* sl = smem + st * REC_STAGE_BYTES;
+        mbar_expect_tx(&bar_full[st], REC_STAGE_BYTES);
+        tma_load_2d(sl, &mapL, &bar_full[st], d0, row0);
+        tma_load_2d(sl + 16384, &mapL, &bar_full[st], d0 + 64, row0);
+        tma_load_2d(sl + 32768, &mapR, &bar_full[st], e0, row0);
+        tma_load_2d(sl + 49152, &mapR, &bar_full[st], e0 + 64, row0);
+        issued = s + 1;
+      }
+      if (issued < NC && issued > 0) {  // error path: let the copies in flight land before the CTA retires
+        int dummy = 1;
+        for (int s = max(0, issued - 2); s < issued; ++s) mbar_wait(&bar_full[s & 1], (s >> 1) & 1, &dummy, 1);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(128, 128, 1, 1);
+      for (int s = 0; s < NC; ++s) {
+        const int st = s & 1, buf = s & 1;
+        if (!mbar_wait(&bar_scaled[st], (s >> 1) & 1, &g_sm100_status, 102)) break;
+        if (!mbar_wait(&bar_acc_free[buf], ((s >> 1) & 1) ^ 1, &g_sm100_status, 103)) break;
+        tc_fence_after_sync();
+        const uint32_t sl = smem_u32(smem + st * REC_STAGE_BYTES), sr = sl + 32768;
+#pragma unroll
+        for (int kk = 0; kk < CL / 16; ++kk)
+          umma_ss(tmem + buf * 128, umma_desc_sw128(sl + kk * 2048, 16384, 1024),
+                  umma_desc_sw128(sr + kk * 2048, 16384, 1024), idesc, kk > 0);
+        umma_commit(&bar_empty[st]);
+        umma_commit(&bar_acc_full[buf]);
+      }
+    }
+  } else {
+    // ---------------- element-wise warps: gate the left tile, fold the accumulator into the running state ----
+    const int ct = tid - 64;                       // 0..255
+    const int quarter = warp & 3, half = (warp - 2) >> 2;
+    const int row = quarter * 32 + lane;           // state row (d) owned for the accumulator
+    const int d = d0 + row, ecol = e0 + half * 64;
+    float C[64];
+    if (p.c_init) {
+      const float4* src = reinterpret_cast<const float4*>(p.c_init + ((size_t)bh * p.DHQK + d) * p.DHHV + ecol);
+#pragma unroll
+      for (int c = 0; c < 16; ++c) { float4 v = src[c]; C[4 * c] = v.x; C[4 * c + 1] = v.y; C[4 * c + 2] = v.z; C[4 * c + 3] = v.w; }
+    } else {
+#pragma unroll
+      for (int c = 0; c < 64; ++c) C[c] = 0.f;
+    }
+    float nval = 0.f;
+    if (do_n && ct < 128 && p.n_init) nval = p.n_init[(size_t)bh * p.DHQK + d0 + ct];
+
+    auto store_c = [&](int slot) {
+      uint4* dst = reinterpret_cast<uint4*>(p.c_states + (((size_t)bh * (NC + 1) + slot) * p.DHQK + d) * p.DHHV + ecol);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        uint4 v;
+        v.x = pack_bf16(C[8 * c], C[8 * c + 1]); v.y = pack_bf16(C[8 * c + 2], C[8 * c + 3]);
+        v.z = pack_bf16(C[8 * c + 4], C[8 * c + 5]); v.w = pack_bf16(C[8 * c + 6], C[8 * c + 7]);
+        dst[c] = v;
+      }
+    };
+    auto epilogue = [&](int s) -> bool {   // fold the product of chunk step s into the running state
+      const int buf = s & 1;
+      if (!mbar_wait(&bar_acc_full[buf], (s >> 1) & 1, &g_sm100_status, 104)) return false;
+      tc_fence_after_sync();
+      const int ck = BWD ? NC - 1 - s : s;
+      const float g = p.gbar[(size_t)bh * NC + ck];
+      const uint32_t ta = tmem + ((uint32_t)(quarter * 32) << 16) + buf * 128 + half * 64;
+      uint32_t r0[32], r1[32];
+      tmem_ld32(ta, r0);
+      tmem_ld32(ta + 32, r1);
+      tmem_wait_ld();
+      tc_fence_before_sync();
+      mbar_arrive(&bar_acc_free[buf]);
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        C[c] = fmaf(g, C[c], __uint_as_float(r0[c]));
+        C[32 + c] = fmaf(g, C[32 + c], __uint_as_float(r1[c]));
+      }
+      return true;
+    };
+
+    // slot written before step s: forward s, backward NC - s
+    store_c(BWD ? NC : 0);
+    if (do_n && ct < 128) p.n_states[((size_t)bh * (NC + 1)) * p.DHQK + d0 + ct] = nval;
+    bool ok = true;
+    for (int s = 0; s < NC; ++s) {
+      const int st = s & 1;
+      const int ck = BWD ? NC - 1 - s : s;
+      const size_t tok0 = (size_t)bh * p.S + (size_t)ck * CL;
+      if (!mbar_wait(&bar_full[st], (s >> 1) & 1, &g_sm100_status, 105)) { ok = false; break; }
+      // scale the rows of the left tile in place (two 64-column boxes of 128 rows x 128 B, 128-byte swizzle)
+      uint8_t* sl = smem + st * REC_STAGE_BYTES;
+      float ns[2][8];
+#pragma unroll
+      for (int b = 0; b < 2; ++b)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ns[b][e] = 0.f;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int r = (ct >> 3) + 32 * (u & 3);
+        float sc = p.lscale[tok0 + r] * p.lmul;
+        if (BWD) sc *= p.rscale[tok0 + r];
+        uint4* ptr = reinterpret_cast<uint4*>(sl + (u >> 2) * 16384 + r * 128 + (ct & 7) * 16);
+        uint4 v = *ptr;
+        uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          __nv_bfloat162 h2 = *reinterpret_cast<__nv_bfloat162*>(&w[e]);
+          const float lo = __low2float(h2) * sc, hi = __high2float(h2) * sc;
+          ns[u >> 2][2 * e] += lo; ns[u >> 2][2 * e + 1] += hi;
+          w[e] = pack_bf16(lo, hi);
+        }
+        *ptr = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      if (do_n) {
+        const int lc = (ct & 7) ^ ((ct >> 3) & 7);   // logical 16-byte column chunk behind the swizzle
+#pragma unroll
+        for (int b = 0; b < 2; ++b)
+#pragma unroll
+          for (int e = 0; e < 8; ++e) atomicAdd(&s_nsum[st][b * 64 + lc * 8 + e], ns[b][e]);
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(&bar_scaled[st]);
+      if (do_n) {   // n does not need the tensor cores: n_{s+1} = gbar n_s + column sums of the gated left tile
+        mbar_arrive(&bar_nsum[st]);
+        if (!mbar_wait(&bar_nsum[st], (s >> 1) & 1, &g_sm100_status, 106)) { ok = false; break; }
+        if (ct < 128) {
+          nval = fmaf(p.gbar[(size_t)bh * NC + ck], nval, s_nsum[st][ct]);
+          s_nsum[st][ct] = 0.f;
+          p.n_states[((size_t)bh * (NC + 1) + s + 1) * p.DHQK + d0 + ct] = nval;
+        }
+      }
+      if (s > 0) {
+        if (!epilogue(s - 1)) { ok = false; break; }
+        store_c(BWD ? NC - s : s);
+      }
+    }
+    if (ok && NC > 0) ok = epilogue(NC - 1);
+    if (ok) {
+      store_c(BWD ? 0 : NC);
+      if (p.c_final) {
+        float4* fd = reinterpret_cast<float4*>(p.c_final + ((size_t)bh * p.DHQK + d) * p.DHHV + ecol);
+#pragma unroll
+        for (int c = 0; c < 16; ++c) fd[c] = make_float4(C[4 * c], C[4 * c + 1], C[4 * c + 2], C[4 * c + 3]);
+      }
+      if (do_n && p.n_final && ct < 128) p.n_final[(size_t)bh * p.DHQK + d0 + ct] = nval;
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, 256);
 }
+
+
+// =====================================================================================================
+// Intra-chunk kernel.  Output tile rows r = tokens of one chunk, 128 output columns.
+//   out[r,:] = sum_c G[r,c] X[c,:] + rowscale_r * (A[r,:] . State)
+//   G[r,c]   = gate(r,c) * (A[r,:] . B[c,:])
+//   mode  A    B    contraction  gate   X    State operand                  rowscale            out
+//   H     Q    K    DHQK         lower  V    C_k        [DHQK x DHHV]       s*bbar_r            H (divided by den)
+//   DV    K    Q    DHQK         upper  dH   dC_{k+1}   [DHQK x DHHV]       abar_r              dV
+//   DK    V    dH   DHHV         upper  Q    dC_{k+1}^T (rows d, cols e)    abar_r              dK
+//   DQ    dH   V    DHHV         lower  K    C_k^T      (rows d, cols e)    s*bbar_r/(den_r+e)  dQ
+// lower: c <= r, (i,j) = (r,c); upper: c >= r, (i,j) = (c,r);
+// gate = s * exp((b_i - b_j) + iota_j - m_i) [* 1/(den_i+eps) in the three backward modes].
+// grid (DO/128, NC, B*NH); 192 threads: warp 0 TMA, warp 1 MMA, warps 2..5 element-wise (thread = row).
+// =====================================================================================================
+enum { PM_H = 0, PM_DV = 1, PM_DK = 2, PM_DQ = 3 };
+
+struct ParParams {
+  const float *vecB, *iota, *m_tok, *abar, *bbar, *inv_den;  // per token, f32
+  const float* n_states;                                     // H only
+  const __nv_bfloat16* q;                                    // H only (q . n)
+  __nv_bfloat16* out;
+  float* n_out;  // H only
+  int S, NC, DI, DO, DHQK, DHHV, variant;
+  float eps, qk_scale;
+};
+
+constexpr int PAR_THREADS = 192;
+constexpr int PAR_STAGE = 49152;  // A slice 16 KB + B slice 16 KB + state slice 16 KB (or the 32 KB X tile)
+constexpr int PAR_SMEM = 2 * PAR_STAGE + 1024;
+
+template <int MODE>
+__global__ void __launch_bounds__(PAR_THREADS, 2)
+par_sm100(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+          const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapSt, ParParams p) {
+  constexpr bool LOWER = (MODE == PM_H || MODE == PM_DQ);
+  constexpr bool ST_MN = (MODE == PM_H || MODE == PM_DV);  // state operand N-contiguous in shared memory
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  __shared__ uint64_t bar_full[2], bar_empty[2], bar_sfull, bar_gated, bar_hfull;
+  __shared__ uint32_t s_tmem;
+  __shared__ float s_b[CL], s_iota[CL], s_m[CL], s_inv[CL];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int o0 = blockIdx.x * 128, ck = blockIdx.y, bh = blockIdx.z;
+  const int NC = p.NC, ND = p.DI / 64;
+  const int row0 = bh * p.S + ck * CL;
+
+  if (tid == 0) {
+    for (int s = 0; s < 2; ++s) { mbar_init(&bar_full[s], 1); mbar_init(&bar_empty[s], 1); }
+    mbar_init(&bar_sfull, 1); mbar_init(&bar_gated, 128); mbar_init(&bar_hfull, 1);
+    fence_barrier_init();
+    tma_prefetch_desc(&mapA); tma_prefetch_desc(&mapB); tma_prefetch_desc(&mapX); tma_prefetch_desc(&mapSt);
+  }
+  if (warp == 1) { tmem_alloc(&s_tmem, 256); tmem_relinquish(); }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = s_tmem;
+  const uint32_t tS = tmem, tAcc = tmem + 128;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      const int slot = (MODE == PM_H || MODE == PM_DQ) ? ck : ck + 1;
+      const int srow = (bh * (NC + 1) + slot) * p.DHQK;
+      int issued = 0;
+      for (int it = 0; it <= ND; ++it) {
+        const int st = it & 1;
+        if (!mbar_wait(&bar_empty[st], ((it >> 1) & 1) ^ 1, &g_sm100_status, 201)) break;
+        uint8_t* sb = smem + st * PAR_STAGE;
+        if (it < ND) {
+          mbar_expect_tx(&bar_full[st], PAR_STAGE);
+          tma_load_2d(sb, &mapA, &bar_full[st], 64 * it, row0);
+          tma_load_2d(sb + 16384, &mapB, &bar_full[st], 64 * it, row0);
+          if (ST_MN) {
+            tma_load_2d(sb + 32768, &mapSt, &bar_full[st], o0, srow + 64 * it);
+            tma_load_2d(sb + 32768 + 8192, &mapSt, &bar_full[st], o0 + 64, srow + 64 * it);
+          } else {
+            tma_load_2d(sb + 32768, &mapSt, &bar_full[st], 64 * it, srow + o0);
+          }
+        } else {
+          mbar_expect_tx(&bar_full[st], 32768);
+          tma_load_2d(sb, &mapX, &bar_full[st], o0, row0);
+          tma_load_2d(sb + 16384, &mapX, &bar_full[st], o0 + 64, row0);
+        }
+        issued = it + 1;
+      }
+      if (issued <= ND && issued > 0) {  // error path: let the copies in flight land before the CTA retires
+        int dummy = 1;
+        for (int it = max(0, issued - 2); it < issued; ++it) mbar_wait(&bar_full[it & 1], (it >> 1) & 1, &dummy, 1);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);
+      constexpr uint32_t idesc_st = umma_idesc_bf16(128, 128, 0, ST_MN ? 1 : 0);
+      constexpr uint32_t idesc_x = umma_idesc_bf16(128, 128, 0, 1);
+      bool ok = true;
+      for (int it = 0; it < ND; ++it) {
+        const int st = it & 1;
+        if (!mbar_wait(&bar_full[st], (it >> 1) & 1, &g_sm100_status, 202)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t sa = smem_u32(smem + st * PAR_STAGE), sb = sa + 16384, ss = sa + 32768;
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          umma_ss(tS, umma_desc_sw128(sa + kk * 32, 16, 1024), umma_desc_sw128(sb + kk * 32, 16, 1024), idesc_s,
+                  (it > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+          const uint64_t bdesc = ST_MN ? umma_desc_sw128(ss + kk * 2048, 8192, 1024) : umma_desc_sw128(ss + kk * 32, 16, 1024);
+          umma_ss(tAcc, umma_desc_sw128(sa + kk * 32, 16, 1024), bdesc, idesc_st, (it > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(&bar_empty[st]);
+      }
+      if (ok) {
+        umma_commit(&bar_sfull);
+        const int stx = ND & 1;
+        ok = mbar_wait(&bar_full[stx], (ND >> 1) & 1, &g_sm100_status, 203) &&
+             mbar_wait(&bar_gated, 0, &g_sm100_status, 204);
+        if (ok) {
+          tc_fence_after_sync();
+          const uint32_t sx = smem_u32(smem + stx * PAR_STAGE);
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk)
+            umma_ts(tAcc, tS + kk * 8, umma_desc_sw128(sx + kk * 2048, 16384, 1024), idesc_x, 1u);
+          umma_commit(&bar_hfull);
+        }
+      }
+    }
+  } else {
+    // ---------------- element-wise warps ----------------
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const size_t tok = (size_t)row0 + r;
+    const float b_r = p.vecB[tok], iota_r = p.iota[tok], m_r = p.m_tok[tok];
+    const float inv_r = (MODE == PM_H) ? 1.f : p.inv_den[tok];
+    s_b[r] = b_r; s_iota[r] = iota_r; s_m[r] = m_r; s_inv[r] = inv_r;
+    float rowscale;
+    if (MODE == PM_H) rowscale = p.qk_scale * p.bbar[tok];
+    else if (MODE == PM_DQ) rowscale = p.qk_scale * p.bbar[tok] * inv_r;
+    else rowscale = p.abar[tok];
+
+    // q . n_{k-1} for the denominator (H only): coalesced row reads, one warp reduction per row
+    float qn = 0.f;
+    if (MODE == PM_H && p.variant != MLSTM_SIG_NONORM && p.n_states != nullptr) {
+      const float* nsrc = p.n_states + ((size_t)bh * (NC + 1) + ck) * p.DHQK;
+      float n8[2][8];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int d8 = h * 256 + lane * 8;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) n8[h][e] = (d8 < p.DHQK) ? nsrc[d8 + e] : 0.f;
+      }
+      for (int rr = 0; rr < 32; ++rr) {
+        const __nv_bfloat16* qrow = p.q + ((size_t)row0 + quarter * 32 + rr) * p.DHQK;
+        float acc = 0.f;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int d8 = h * 256 + lane * 8;
+          if (d8 < p.DHQK) {
+            const uint4 v = *reinterpret_cast<const uint4*>(qrow + d8);
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const __nv_bfloat162 h2 = *reinterpret_cast<const __nv_bfloat162*>(&w[e]);
+              acc = fmaf(__low2float(h2), n8[h][2 * e], acc);
+              acc = fmaf(__high2float(h2), n8[h][2 * e + 1], acc);
+            }
+          }
+        }
+        acc = warp_sum(acc);
+        if (lane == rr) qn = acc;
+      }
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");  // gate vectors visible to the four element-wise warps
+
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    float rowsum = 0.f;
+    bool ok = mbar_wait(&bar_sfull, 0, &g_sm100_status, 205);
+    if (ok) {
+      tc_fence_after_sync();
+      // row-scale the inter-chunk term in place
+#pragma unroll 1
+      for (int c0 = 0; c0 < 128; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld32(tAcc + lane_base + c0, v);
+        tmem_wait_ld();
+#pragma unroll
+        for (int c = 0; c < 32; ++c) v[c] = __float_as_uint(__uint_as_float(v[c]) * rowscale);
+        tmem_st32(tAcc + lane_base + c0, v);
+      }
+      // gate the score tile, write it back as the bf16 A operand of the second product
+      const float f_r = (MODE == PM_DQ) ? p.qk_scale * inv_r : p.qk_scale;
+#pragma unroll 1
+      for (int cq = 0; cq < 4; ++cq) {
+        const int c0 = cq * 32;
+        uint32_t pk[16];
+        const bool skip = LOWER ? (cq > quarter) : (cq < quarter);
+        if (skip) {
+#pragma unroll
+          for (int c = 0; c < 16; ++c) pk[c] = 0u;
+        } else {
+          uint32_t v[32];
+          tmem_ld32(tS + lane_base + c0, v);
+          tmem_wait_ld();
+          float g[32];
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            const int col = c0 + c;
+            float val = 0.f;
+            if (LOWER) {
+              if (col <= r) val = __uint_as_float(v[c]) * f_r * __expf((b_r - s_b[col]) + s_iota[col] - m_r);
+            } else {
+              if (col >= r) val = __uint_as_float(v[c]) * (p.qk_scale * s_inv[col]) * __expf((s_b[col] - b_r) + iota_r - s_m[col]);
+            }
+            g[c] = val;
+            rowsum += val;
+          }
+#pragma unroll
+          for (int c = 0; c < 16; ++c) pk[c] = pack_bf16(g[2 * c], g[2 * c + 1]);
+        }
+        tmem_st16(tS + lane_base + cq * 16, pk);
+      }
+      tmem_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(&bar_gated);
+      ok = mbar_wait(&bar_hfull, 0, &g_sm100_status, 206);
+    }
+    if (ok) {
+      tc_fence_after_sync();
+      float inv = 1.f;
+      if (MODE == PM_H) {
+        float den = 1.f;
+        const float nn = rowsum + rowscale * qn;
+        if (p.variant == MLSTM_EXP) den = fmaxf(fabsf(nn), __expf(-m_r));
+        else if (p.variant == MLSTM_SIG) den = fmaxf(fabsf(nn), 1.f);
+        if (p.variant != MLSTM_SIG_NONORM) inv = 1.f / (den + p.eps);
+        if (blockIdx.x == 0) p.n_out[tok] = den;
+      }
+      __nv_bfloat16* orow = p.out + tok * p.DO + o0;
+#pragma unroll 1
+      for (int c0 = 0; c0 < 128; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld32(tAcc + lane_base + c0, v);
+        tmem_wait_ld();
+        uint4* dst = reinterpret_cast<uint4*>(orow + c0);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint4 o;
+          o.x = pack_bf16(__uint_as_float(v[8 * c]) * inv, __uint_as_float(v[8 * c + 1]) * inv);
+          o.y = pack_bf16(__uint_as_float(v[8 * c + 2]) * inv, __uint_as_float(v[8 * c + 3]) * inv);
+          o.z = pack_bf16(__uint_as_float(v[8 * c + 4]) * inv, __uint_as_float(v[8 * c + 5]) * inv);
+          o.w = pack_bf16(__uint_as_float(v[8 * c + 6]) * inv, __uint_as_float(v[8 * c + 7]) * inv);
+          dst[c] = o;
+        }
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, 256);
+}
+
+// =====================================================================================================
+// Host side
+// =====================================================================================================
+bool sm100_supported(int S, int DHQK, int DHHV, int L, int dtype) {
+  return dtype == MLSTM_BF16 && L == CL && S % CL == 0 && DHQK % 128 == 0 && DHHV % 128 == 0 && DHQK <= 512 &&
+         DHHV <= 1024;
+}
+
+static bool tok_map(CUtensorMap* m, const void* base, const ChunkwiseDims& d, int cols) {
+  return sm100_host::make_map_bf16(m, base, (uint64_t)d.B * d.NH * d.S, (uint64_t)cols, 128, 64);
+}
+static bool state_map(CUtensorMap* m, const void* base, const ChunkwiseDims& d, int box_rows) {
+  return sm100_host::make_map_bf16(m, base, (uint64_t)d.B * d.NH * (d.NC + 1) * d.DHQK, (uint64_t)d.DHHV, box_rows, 64);
+}
+
+template <bool BWD>
+static int launch_rec(const void* left, const void* right, const RecParams& rp, const ChunkwiseDims& d, cudaStream_t st) {
+  CUtensorMap mL, mR;
+  if (!tok_map(&mL, left, d, d.DHQK) || !tok_map(&mR, right, d, d.DHHV)) return MLSTM_ERR_CUDA;
+  auto kern = rec_sm100<BWD>;
+  MLSTM_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, REC_SMEM));
+  dim3 grid(d.DHHV / 128, d.DHQK / 128, d.B * d.NH);
+  kern<<<grid, REC_THREADS, REC_SMEM, st>>>(mL, mR, rp);
+  MLSTM_LAUNCH_CHECK();
+  return MLSTM_OK;
+}
+
+int sm100_recurrent_fw(const void* k, const void* v, const GateBuffers& gb, const float* c_initial,
+                       const float* n_initial, void* c_states, float* n_states, float* c_last, float* n_last,
+                       const ChunkwiseDims& d, cudaStream_t st) {
+  PhaseScope ps(PH_REC_FW, st);
+  RecParams rp{gb.abar, nullptr, 1.f, gb.gbar, c_initial, n_initial, (__nv_bfloat16*)c_states,
+               d.variant == MLSTM_SIG_NONORM ? nullptr : n_states, c_last, n_last, d.S, d.NC, d.DHQK, d.DHHV};
+  return launch_rec<false>(k, v, rp, d, st);
+}
+
+int sm100_recurrent_bw(const void* q, const void* dh, const GateBuffers& gb, const float* dc_last, void* dc_states,
+                       float* dc_initial, const ChunkwiseDims& d, cudaStream_t st) {
+  PhaseScope ps(PH_REC_BW, st);
+  RecParams rp{gb.bbar, gb.inv_den, d.qk_scale, gb.gbar, dc_last, nullptr, (__nv_bfloat16*)dc_states, nullptr,
+               dc_initial, nullptr, d.S, d.NC, d.DHQK, d.DHHV};
+  return launch_rec<true>(q, dh, rp, d, st);
+}
+
+template <int MODE>
+static int launch_par(const CUtensorMap& mA, const CUtensorMap& mB, const CUtensorMap& mX, const CUtensorMap& mSt,
+                      const ParParams& pp, const ChunkwiseDims& d, cudaStream_t st) {
+  auto kern = par_sm100<MODE>;
+  MLSTM_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PAR_SMEM));
+  dim3 grid(pp.DO / 128, d.NC, d.B * d.NH);
+  kern<<<grid, PAR_THREADS, PAR_SMEM, st>>>(mA, mB, mX, mSt, pp);
+  MLSTM_LAUNCH_CHECK();
+  return MLSTM_OK;
+}
+
+static ParParams base_params(const GateBuffers& gb, const ChunkwiseDims& d) {
+  ParParams pp{};
+  pp.vecB = gb.vecB; pp.iota = gb.iota; pp.m_tok = gb.m_tok; pp.abar = gb.abar; pp.bbar = gb.bbar;
+  pp.inv_den = gb.inv_den;
+  pp.S = d.S; pp.NC = d.NC; pp.DHQK = d.DHQK; pp.DHHV = d.DHHV; pp.variant = d.variant; pp.eps = d.eps;
+  pp.qk_scale = d.qk_scale;
+  return pp;
+}
+
+int sm100_parallel_fw(const void* q, const void* k, const void* v, const GateBuffers& gb, const void* c_states,
+                      const float* n_states, void* h, float* n_out, const ChunkwiseDims& d, cudaStream_t st) {
+  PhaseScope ps(PH_PAR_FW, st);
+  CUtensorMap mQ, mK, mV, mC;
+  if (!tok_map(&mQ, q, d, d.DHQK) || !tok_map(&mK, k, d, d.DHQK) || !tok_map(&mV, v, d, d.DHHV) ||
+      !state_map(&mC, c_states, d, 64))
+    return MLSTM_ERR_CUDA;
+  ParParams pp = base_params(gb, d);
+  pp.n_states = n_states; pp.q = (const __nv_bfloat16*)q; pp.out = (__nv_bfloat16*)h; pp.n_out = n_out;
+  pp.DI = d.DHQK; pp.DO = d.DHHV;
+  return launch_par<PM_H>(mQ, mK, mV, mC, pp, d, st);
+}
+
+int sm100_parallel_bw(const void* q, const void* k, const void* v, const void* dh, const GateBuffers& gb,
+                      const void* c_states, const void* dc_states, void* dq, void* dk, void* dv, float* acc,
+                      float* kdk, const ChunkwiseDims& d, cudaStream_t st) {
+  (void)acc; (void)kdk;
+  PhaseScope ps(PH_PAR_BW, st);
+  CUtensorMap mQ, mK, mV, mDH, mC_k, mdC_mn, mdC_k;
+  if (!tok_map(&mQ, q, d, d.DHQK) || !tok_map(&mK, k, d, d.DHQK) || !tok_map(&mV, v, d, d.DHHV) ||
+      !tok_map(&mDH, dh, d, d.DHHV) || !state_map(&mC_k, c_states, d, 128) || !state_map(&mdC_mn, dc_states, d, 64) ||
+      !state_map(&mdC_k, dc_states, d, 128))
+    return MLSTM_ERR_CUDA;
+  int rc;
+  ParParams pp = base_params(gb, d);
+  pp.DI = d.DHQK; pp.DO = d.DHHV; pp.out = (__nv_bfloat16*)dv;
+  if ((rc = launch_par<PM_DV>(mK, mQ, mDH, mdC_mn, pp, d, st)) != MLSTM_OK) return rc;
+  pp.DI = d.DHHV; pp.DO = d.DHQK; pp.out = (__nv_bfloat16*)dk;
+  if ((rc = launch_par<PM_DK>(mV, mDH, mQ, mdC_k, pp, d, st)) != MLSTM_OK) return rc;
+  pp.out = (__nv_bfloat16*)dq;
+  if ((rc = launch_par<PM_DQ>(mDH, mV, mK, mC_k, pp, d, st)) != MLSTM_OK) return rc;
+  return MLSTM_OK;
+}
+
+// Reads (and optionally clears) the status word the bounded waits write on a timeout.  Synchronises the device.
+int sm100_device_status(int reset, int* status) {
+  MLSTM_CUDA_CHECK(cudaDeviceSynchronize());
+  MLSTM_CUDA_CHECK(cudaMemcpyFromSymbol(status, g_sm100_status, sizeof(int)));
+  if (reset) {
+    const int zero = 0;
+    MLSTM_CUDA_CHECK(cudaMemcpyToSymbol(g_sm100_status, &zero, sizeof(int)));
+  }
+  return MLSTM_OK;
+}
+
+}  // namespace mlstm

@@ -40,6 +40,8 @@ int sm100_parallel_bw(const void* q, const void* k, const void* v, const void* d
                       const void* c_states, const void* dc_states, void* dq, void* dk, void* dv, float* acc,
                       float* kdk, const ChunkwiseDims& d, cudaStream_t st);
 
+int sm100_device_status(int reset, int* status);
+
 // step.cu
 int launch_step(const void* q, const void* k, const void* v, const void* i, const void* f, const void* c,
                 const void* n, const void* m, void* h, void* c_new, void* n_new, void* m_new, int B, int NH, int DHQK,

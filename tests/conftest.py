@@ -28,3 +28,16 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+@pytest.fixture(autouse=True)
+def _tcgen05_status_clean(request):
+    """After every GPU test: no bounded wait of the tcgen05 kernels may have run out."""
+    yield
+    if "gpu" in request.keywords:
+        import torch
+
+        if torch.cuda.is_available():
+            from mlstm_kernels_b200 import _lib
+
+            assert _lib.device_status() == 0
