@@ -103,8 +103,9 @@ static BwLayout carve_bw(void* ws, int BNH, int S, int NC, int DHQK, int DHHV, s
   l.gb.gbar = c.take<float>((size_t)BNH * NC);
   l.gb.scratch = c.take<float>((size_t)BNH * NC * 2);
   l.m_states = c.take<float>((size_t)BNH * (NC + 1));
-  l.acc = c.take<float>(tok);
-  l.kdk = c.take<float>(tok);
+  const size_t parts = (size_t)(DHQK + 127) / 128;  // one partial row sum per 128-wide tile of DHQK
+  l.acc = c.take<float>(tok * parts);
+  l.kdk = c.take<float>(tok * parts);
   l.dc_states = c.take<char>((size_t)BNH * (NC + 1) * DHQK * DHHV * state_elem);
   l.bytes = align_up(c.off, 256);
   return l;
@@ -260,7 +261,10 @@ int mlstm_b200_chunkwise_bw(const void* q, const void* k, const void* v, const v
   if (use_sm100) {
     if ((rc = sm100_recurrent_bw(q, dh, lay.gb, dc_last, lay.dc_states, dc_initial, d, st)) != MLSTM_OK) return rc;
     if ((rc = sm100_parallel_bw(q, k, v, dh, lay.gb, c_states, lay.dc_states, dq, dk, dv, lay.acc, lay.kdk, d, st)) != MLSTM_OK) return rc;
-    if ((rc = launch_gate_grads(dtype, gate_dtype, q, k, dq, dk, i, f, lay.acc, lay.kdk, di, df, d, st)) != MLSTM_OK) return rc;
+    {
+      PhaseScope ps(PH_GATE_GRADS, st);
+      if ((rc = launch_gate_grad_scan(gate_dtype, i, f, lay.acc, lay.kdk, DHQK / 128, di, df, d, st)) != MLSTM_OK) return rc;
+    }
   } else {
     if ((rc = simt_recurrent_bw(dtype, sdt, q, dh, lay.gb, dc_last, lay.dc_states, dc_initial, d, st)) != MLSTM_OK) return rc;
     if ((rc = simt_parallel_bw(dtype, sdt, q, k, v, dh, lay.gb, c_states, lay.dc_states, dq, dk, dv, d, st)) != MLSTM_OK) return rc;

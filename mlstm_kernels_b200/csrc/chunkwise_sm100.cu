@@ -45,7 +45,8 @@ struct RecParams {
 
 constexpr int REC_THREADS = 320;                 // warp 0 TMA, warp 1 MMA, warps 2..9 element-wise
 constexpr int REC_STAGE_BYTES = 65536;           // left tile 32 KB + right tile 32 KB
-constexpr int REC_SMEM = 2 * REC_STAGE_BYTES + 1024;
+constexpr int REC_NPART_BYTES = 2 * 32 * 128 * 4;   // per-stage partial column sums of the gated left tile
+constexpr int REC_SMEM = 2 * REC_STAGE_BYTES + REC_NPART_BYTES + 1024;
 
 template <bool BWD>
 __global__ void __launch_bounds__(REC_THREADS, 1)
@@ -54,7 +55,6 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   __shared__ uint64_t bar_full[2], bar_empty[2], bar_scaled[2], bar_acc_full[2], bar_acc_free[2], bar_nsum[2];
   __shared__ uint32_t s_tmem;
-  __shared__ float s_nsum[2][128];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int e0 = blockIdx.x * 128, d0 = blockIdx.y * 128, bh = blockIdx.z;
@@ -69,7 +69,6 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
     fence_barrier_init();
     tma_prefetch_desc(&mapL); tma_prefetch_desc(&mapR);
   }
-  if (tid < 256) { s_nsum[0][tid & 127] = 0.f; s_nsum[1][tid & 127] = 0.f; }
   if (warp == 1) { tmem_alloc(&s_tmem, 256); tmem_relinquish(); }
   tc_fence_before_sync();
   __syncthreads();
@@ -198,12 +197,15 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
         }
         *ptr = make_uint4(w[0], w[1], w[2], w[3]);
       }
+      float* npart = reinterpret_cast<float*>(smem + 2 * REC_STAGE_BYTES) + st * (32 * 128);
       if (do_n) {
         const int lc = (ct & 7) ^ ((ct >> 3) & 7);   // logical 16-byte column chunk behind the swizzle
 #pragma unroll
-        for (int b = 0; b < 2; ++b)
-#pragma unroll
-          for (int e = 0; e < 8; ++e) atomicAdd(&s_nsum[st][b * 64 + lc * 8 + e], ns[b][e]);
+        for (int b = 0; b < 2; ++b) {
+          float4* dst = reinterpret_cast<float4*>(npart + (ct >> 3) * 128 + b * 64 + lc * 8);
+          dst[0] = make_float4(ns[b][0], ns[b][1], ns[b][2], ns[b][3]);
+          dst[1] = make_float4(ns[b][4], ns[b][5], ns[b][6], ns[b][7]);
+        }
       }
       fence_proxy_async_smem();
       mbar_arrive(&bar_scaled[st]);
@@ -211,8 +213,10 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
         mbar_arrive(&bar_nsum[st]);
         if (!mbar_wait(&bar_nsum[st], (s >> 1) & 1, &g_sm100_status, 106)) { ok = false; break; }
         if (ct < 128) {
-          nval = fmaf(p.gbar[(size_t)bh * NC + ck], nval, s_nsum[st][ct]);
-          s_nsum[st][ct] = 0.f;
+          float colsum = 0.f;   // fixed summation order: the result does not depend on scheduling
+#pragma unroll 8
+          for (int g = 0; g < 32; ++g) colsum += npart[g * 128 + ct];
+          nval = fmaf(p.gbar[(size_t)bh * NC + ck], nval, colsum);
           p.n_states[((size_t)bh * (NC + 1) + s + 1) * p.DHQK + d0 + ct] = nval;
         }
       }
@@ -256,37 +260,44 @@ enum { PM_H = 0, PM_DV = 1, PM_DK = 2, PM_DQ = 3 };
 struct ParParams {
   const float *vecB, *iota, *m_tok, *abar, *bbar, *inv_den;  // per token, f32
   const float* n_states;                                     // H only
-  const __nv_bfloat16* q;                                    // H only (q . n)
   __nv_bfloat16* out;
-  float* n_out;  // H only
+  float* n_out;    // H only
+  float* rowdot;   // DQ: sum_d q dq, DK: sum_d k dk; one partial per output tile: [DO/128][tokens]
   int S, NC, DI, DO, DHQK, DHHV, variant;
   float eps, qk_scale;
 };
 
-constexpr int PAR_THREADS = 192;
-constexpr int PAR_STAGE = 49152;  // A slice 16 KB + B slice 16 KB + state slice 16 KB (or the 32 KB X tile)
+constexpr int PAR_THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2..9 element-wise
+constexpr int PAR_STAGE = 49152;  // A slice 16 KB + B slice 16 KB + state slice 16 KB (or a 32 KB 128 x 128 tile)
 constexpr int PAR_SMEM = 2 * PAR_STAGE + 1024;
 
 template <int MODE>
 __global__ void __launch_bounds__(PAR_THREADS, 2)
 par_sm100(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
-          const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapSt, ParParams p) {
+          const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapSt,
+          const __grid_constant__ CUtensorMap mapE, ParParams p) {
   constexpr bool LOWER = (MODE == PM_H || MODE == PM_DQ);
   constexpr bool ST_MN = (MODE == PM_H || MODE == PM_DV);  // state operand N-contiguous in shared memory
+  constexpr bool HAS_E = (MODE == PM_DQ || MODE == PM_DK);  // extra tile for the gate-gradient row sums
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  __shared__ uint64_t bar_full[2], bar_empty[2], bar_sfull, bar_gated, bar_hfull;
+  __shared__ uint64_t bar_full[2], bar_empty[2], bar_sfull, bar_gated, bar_hfull, bar_dot, bar_pair[4];
   __shared__ uint32_t s_tmem;
   __shared__ float s_b[CL], s_iota[CL], s_m[CL], s_inv[CL];
+  __shared__ float s_part[2][CL];   // per-row partial sums exchanged between the two warps of a row
+  __shared__ float s_qn[2][CL];
+  __shared__ float s_n[512];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int o0 = blockIdx.x * 128, ck = blockIdx.y, bh = blockIdx.z;
   const int NC = p.NC, ND = p.DI / 64;
   const int row0 = bh * p.S + ck * CL;
+  const bool use_n = (MODE == PM_H) && p.variant != MLSTM_SIG_NONORM && p.n_states != nullptr;
 
   if (tid == 0) {
-    for (int s = 0; s < 2; ++s) { mbar_init(&bar_full[s], 1); mbar_init(&bar_empty[s], 1); }
-    mbar_init(&bar_sfull, 1); mbar_init(&bar_gated, 128); mbar_init(&bar_hfull, 1);
+    for (int s = 0; s < 2; ++s) { mbar_init(&bar_full[s], 1); mbar_init(&bar_empty[s], use_n ? 9 : 1); }
+    mbar_init(&bar_sfull, 1); mbar_init(&bar_gated, 256); mbar_init(&bar_hfull, 1); mbar_init(&bar_dot, 256);
+    for (int s = 0; s < 4; ++s) mbar_init(&bar_pair[s], 64);
     fence_barrier_init();
     tma_prefetch_desc(&mapA); tma_prefetch_desc(&mapB); tma_prefetch_desc(&mapX); tma_prefetch_desc(&mapSt);
   }
@@ -296,6 +307,7 @@ par_sm100(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
   tc_fence_after_sync();
   const uint32_t tmem = s_tmem;
   const uint32_t tS = tmem, tAcc = tmem + 128;
+  const int n_loads = ND + 1 + (HAS_E ? 1 : 0);
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -303,7 +315,7 @@ par_sm100(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
       const int slot = (MODE == PM_H || MODE == PM_DQ) ? ck : ck + 1;
       const int srow = (bh * (NC + 1) + slot) * p.DHQK;
       int issued = 0;
-      for (int it = 0; it <= ND; ++it) {
+      for (int it = 0; it < n_loads; ++it) {
         const int st = it & 1;
         if (!mbar_wait(&bar_empty[st], ((it >> 1) & 1) ^ 1, &g_sm100_status, 201)) break;
         uint8_t* sb = smem + st * PAR_STAGE;
@@ -318,13 +330,14 @@ par_sm100(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
             tma_load_2d(sb + 32768, &mapSt, &bar_full[st], 64 * it, srow + o0);
           }
         } else {
+          const CUtensorMap* m = (it == ND) ? &mapX : &mapE;
           mbar_expect_tx(&bar_full[st], 32768);
-          tma_load_2d(sb, &mapX, &bar_full[st], o0, row0);
-          tma_load_2d(sb + 16384, &mapX, &bar_full[st], o0 + 64, row0);
+          tma_load_2d(sb, m, &bar_full[st], o0, row0);
+          tma_load_2d(sb + 16384, m, &bar_full[st], o0 + 64, row0);
         }
         issued = it + 1;
       }
-      if (issued <= ND && issued > 0) {  // error path: let the copies in flight land before the CTA retires
+      if (issued < n_loads && issued > 0) {  // error path: let the copies in flight land before the CTA retires
         int dummy = 1;
         for (int it = max(0, issued - 2); it < issued; ++it) mbar_wait(&bar_full[it & 1], (it >> 1) & 1, &dummy, 1);
       }
@@ -368,130 +381,170 @@ par_sm100(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
       }
     }
   } else {
-    // ---------------- element-wise warps ----------------
-    const int quarter = warp & 3;
+    // ---------------- element-wise warps: two warps per 32-row quarter, each owning two 32-column chunks ----
+    const int quarter = warp & 3, half = (warp - 2) >> 2;
     const int r = quarter * 32 + lane;
     const size_t tok = (size_t)row0 + r;
     const float b_r = p.vecB[tok], iota_r = p.iota[tok], m_r = p.m_tok[tok];
     const float inv_r = (MODE == PM_H) ? 1.f : p.inv_den[tok];
-    s_b[r] = b_r; s_iota[r] = iota_r; s_m[r] = m_r; s_inv[r] = inv_r;
+    if (half == 0) { s_b[r] = b_r; s_iota[r] = iota_r; s_m[r] = m_r; s_inv[r] = inv_r; }
     float rowscale;
     if (MODE == PM_H) rowscale = p.qk_scale * p.bbar[tok];
     else if (MODE == PM_DQ) rowscale = p.qk_scale * p.bbar[tok] * inv_r;
     else rowscale = p.abar[tok];
-
-    // q . n_{k-1} for the denominator (H only): coalesced row reads, one warp reduction per row
-    float qn = 0.f;
-    if (MODE == PM_H && p.variant != MLSTM_SIG_NONORM && p.n_states != nullptr) {
+    if (use_n) {
       const float* nsrc = p.n_states + ((size_t)bh * (NC + 1) + ck) * p.DHQK;
-      float n8[2][8];
+      for (int dd = tid - 64; dd < p.DHQK; dd += 256) s_n[dd] = nsrc[dd];
+    }
+    asm volatile("bar.sync 1, 256;" ::: "memory");  // gate vectors and n visible to the element-wise warps
+
+    bool ok = true;
+    // q . n_{k-1} for the denominator (H only): each thread reads half of its row of every Q slice from the
+    // TMA stage (the stage is released to the producer only after these reads)
+    float qn = 0.f;
+    if (use_n) {
+      for (int it = 0; it < ND && ok; ++it) {
+        const int st = it & 1;
+        if (!mbar_wait(&bar_full[st], (it >> 1) & 1, &g_sm100_status, 207)) { ok = false; break; }
+        const uint8_t* rowp = smem + st * PAR_STAGE + r * 128;
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int d8 = h * 256 + lane * 8;
+        for (int cc = 0; cc < 4; ++cc) {
+          const int lc = half * 4 + cc;                      // logical 16-byte chunk of the 64-column slice
+          const uint4 v = *reinterpret_cast<const uint4*>(rowp + ((lc ^ (r & 7)) << 4));
+          const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+          const float* nn = s_n + it * 64 + lc * 8;
 #pragma unroll
-        for (int e = 0; e < 8; ++e) n8[h][e] = (d8 < p.DHQK) ? nsrc[d8 + e] : 0.f;
-      }
-      for (int rr = 0; rr < 32; ++rr) {
-        const __nv_bfloat16* qrow = p.q + ((size_t)row0 + quarter * 32 + rr) * p.DHQK;
-        float acc = 0.f;
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const int d8 = h * 256 + lane * 8;
-          if (d8 < p.DHQK) {
-            const uint4 v = *reinterpret_cast<const uint4*>(qrow + d8);
-            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const __nv_bfloat162 h2 = *reinterpret_cast<const __nv_bfloat162*>(&w[e]);
-              acc = fmaf(__low2float(h2), n8[h][2 * e], acc);
-              acc = fmaf(__high2float(h2), n8[h][2 * e + 1], acc);
-            }
+          for (int e = 0; e < 4; ++e) {
+            const __nv_bfloat162 h2 = *reinterpret_cast<const __nv_bfloat162*>(&w[e]);
+            qn = fmaf(__low2float(h2), nn[2 * e], qn);
+            qn = fmaf(__high2float(h2), nn[2 * e + 1], qn);
           }
         }
-        acc = warp_sum(acc);
-        if (lane == rr) qn = acc;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar_empty[st]);
       }
+      s_qn[half][r] = qn;
     }
-    asm volatile("bar.sync 1, 128;" ::: "memory");  // gate vectors visible to the four element-wise warps
 
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     float rowsum = 0.f;
-    bool ok = mbar_wait(&bar_sfull, 0, &g_sm100_status, 205);
+    ok = ok && mbar_wait(&bar_sfull, 0, &g_sm100_status, 205);
     if (ok) {
       tc_fence_after_sync();
       // row-scale the inter-chunk term in place
 #pragma unroll 1
-      for (int c0 = 0; c0 < 128; c0 += 32) {
+      for (int cq = half; cq < 4; cq += 2) {
         uint32_t v[32];
-        tmem_ld32(tAcc + lane_base + c0, v);
+        tmem_ld32(tAcc + lane_base + cq * 32, v);
         tmem_wait_ld();
 #pragma unroll
         for (int c = 0; c < 32; ++c) v[c] = __float_as_uint(__uint_as_float(v[c]) * rowscale);
-        tmem_st32(tAcc + lane_base + c0, v);
+        tmem_st32(tAcc + lane_base + cq * 32, v);
       }
-      // gate the score tile, write it back as the bf16 A operand of the second product
+      // gate the score tile; the bf16 result goes back to tensor memory as the A operand of the second product.
+      // Both warps of a quarter first read their chunks, then (after a warp-pair sync) write: the bf16 words of
+      // chunk cq land on columns [16 cq, 16 cq + 16), which the partner warp may still have to read.
       const float f_r = (MODE == PM_DQ) ? p.qk_scale * inv_r : p.qk_scale;
-#pragma unroll 1
-      for (int cq = 0; cq < 4; ++cq) {
+      uint32_t pk[2][16];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int cq = half + 2 * u;
         const int c0 = cq * 32;
-        uint32_t pk[16];
         const bool skip = LOWER ? (cq > quarter) : (cq < quarter);
         if (skip) {
 #pragma unroll
-          for (int c = 0; c < 16; ++c) pk[c] = 0u;
+          for (int c = 0; c < 16; ++c) pk[u][c] = 0u;
         } else {
           uint32_t v[32];
           tmem_ld32(tS + lane_base + c0, v);
           tmem_wait_ld();
-          float g[32];
 #pragma unroll
-          for (int c = 0; c < 32; ++c) {
-            const int col = c0 + c;
-            float val = 0.f;
-            if (LOWER) {
-              if (col <= r) val = __uint_as_float(v[c]) * f_r * __expf((b_r - s_b[col]) + s_iota[col] - m_r);
-            } else {
-              if (col >= r) val = __uint_as_float(v[c]) * (p.qk_scale * s_inv[col]) * __expf((s_b[col] - b_r) + iota_r - s_m[col]);
+          for (int c = 0; c < 16; ++c) {
+            float g2[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const int col = c0 + 2 * c + h;
+              float val = 0.f;
+              if (LOWER) {
+                if (col <= r) val = __uint_as_float(v[2 * c + h]) * f_r * __expf((b_r - s_b[col]) + s_iota[col] - m_r);
+              } else {
+                if (col >= r) val = __uint_as_float(v[2 * c + h]) * (p.qk_scale * s_inv[col]) * __expf((s_b[col] - b_r) + iota_r - s_m[col]);
+              }
+              g2[h] = val;
+              rowsum += val;
             }
-            g[c] = val;
-            rowsum += val;
+            pk[u][c] = pack_bf16(g2[0], g2[1]);
           }
-#pragma unroll
-          for (int c = 0; c < 16; ++c) pk[c] = pack_bf16(g[2 * c], g[2 * c + 1]);
         }
-        tmem_st16(tS + lane_base + cq * 16, pk);
       }
-      tmem_wait_st();
+      // pair sync (bounded): both warps of the quarter have finished reading the score tile
       tc_fence_before_sync();
-      mbar_arrive(&bar_gated);
-      ok = mbar_wait(&bar_hfull, 0, &g_sm100_status, 206);
+      mbar_arrive(&bar_pair[quarter]);
+      ok = mbar_wait(&bar_pair[quarter], 0, &g_sm100_status, 210);
+      if (ok) {
+        tc_fence_after_sync();
+#pragma unroll
+        for (int u = 0; u < 2; ++u) tmem_st16(tS + lane_base + (half + 2 * u) * 16, pk[u]);
+        s_part[half][r] = rowsum;
+        tmem_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive(&bar_gated);
+        ok = mbar_wait(&bar_hfull, 0, &g_sm100_status, 206);
+      }
     }
     if (ok) {
       tc_fence_after_sync();
       float inv = 1.f;
       if (MODE == PM_H) {
         float den = 1.f;
-        const float nn = rowsum + rowscale * qn;
+        const float nn = (s_part[0][r] + s_part[1][r]) + rowscale * (use_n ? (s_qn[0][r] + s_qn[1][r]) : 0.f);
         if (p.variant == MLSTM_EXP) den = fmaxf(fabsf(nn), __expf(-m_r));
         else if (p.variant == MLSTM_SIG) den = fmaxf(fabsf(nn), 1.f);
         if (p.variant != MLSTM_SIG_NONORM) inv = 1.f / (den + p.eps);
-        if (blockIdx.x == 0) p.n_out[tok] = den;
+        if (blockIdx.x == 0 && half == 0) p.n_out[tok] = den;
       }
+      const uint8_t* erow = nullptr;
+      if (HAS_E) {
+        const int ste = (ND + 1) & 1;
+        ok = mbar_wait(&bar_full[ste], ((ND + 1) >> 1) & 1, &g_sm100_status, 208);
+        erow = smem + ste * PAR_STAGE + r * 128;
+      }
+      float dot = 0.f;
       __nv_bfloat16* orow = p.out + tok * p.DO + o0;
+      if (ok) {
 #pragma unroll 1
-      for (int c0 = 0; c0 < 128; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld32(tAcc + lane_base + c0, v);
-        tmem_wait_ld();
-        uint4* dst = reinterpret_cast<uint4*>(orow + c0);
+        for (int cq = half; cq < 4; cq += 2) {
+          uint32_t v[32];
+          tmem_ld32(tAcc + lane_base + cq * 32, v);
+          tmem_wait_ld();
+          uint4* dst = reinterpret_cast<uint4*>(orow + cq * 32);
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint4 o;
-          o.x = pack_bf16(__uint_as_float(v[8 * c]) * inv, __uint_as_float(v[8 * c + 1]) * inv);
-          o.y = pack_bf16(__uint_as_float(v[8 * c + 2]) * inv, __uint_as_float(v[8 * c + 3]) * inv);
-          o.z = pack_bf16(__uint_as_float(v[8 * c + 4]) * inv, __uint_as_float(v[8 * c + 5]) * inv);
-          o.w = pack_bf16(__uint_as_float(v[8 * c + 6]) * inv, __uint_as_float(v[8 * c + 7]) * inv);
-          dst[c] = o;
+          for (int c = 0; c < 4; ++c) {
+            float x[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) x[e] = __uint_as_float(v[8 * c + e]) * inv;
+            if (HAS_E) {
+              // logical 16-byte chunk (cq*4 + c) of the 128-column row: box (cq >> 1), chunk ((cq & 1) * 4 + c)
+              const uint4 ev = *reinterpret_cast<const uint4*>(erow + (cq >> 1) * 16384 + ((((cq & 1) * 4 + c) ^ (r & 7)) << 4));
+              const uint32_t w[4] = {ev.x, ev.y, ev.z, ev.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const __nv_bfloat162 h2 = *reinterpret_cast<const __nv_bfloat162*>(&w[e]);
+                dot = fmaf(__low2float(h2), x[2 * e], dot);
+                dot = fmaf(__high2float(h2), x[2 * e + 1], dot);
+              }
+            }
+            uint4 o;
+            o.x = pack_bf16(x[0], x[1]); o.y = pack_bf16(x[2], x[3]);
+            o.z = pack_bf16(x[4], x[5]); o.w = pack_bf16(x[6], x[7]);
+            dst[c] = o;
+          }
+        }
+        if (HAS_E) {
+          s_qn[half][r] = dot;
+          mbar_arrive(&bar_dot);
+          if (half == 0 && mbar_wait(&bar_dot, 0, &g_sm100_status, 209))
+            p.rowdot[(size_t)blockIdx.x * ((size_t)gridDim.z * p.S) + tok] = s_qn[0][r] + s_qn[1][r];
         }
       }
     }
@@ -547,11 +600,11 @@ int sm100_recurrent_bw(const void* q, const void* dh, const GateBuffers& gb, con
 
 template <int MODE>
 static int launch_par(const CUtensorMap& mA, const CUtensorMap& mB, const CUtensorMap& mX, const CUtensorMap& mSt,
-                      const ParParams& pp, const ChunkwiseDims& d, cudaStream_t st) {
+                      const CUtensorMap& mE, const ParParams& pp, const ChunkwiseDims& d, cudaStream_t st) {
   auto kern = par_sm100<MODE>;
   MLSTM_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PAR_SMEM));
   dim3 grid(pp.DO / 128, d.NC, d.B * d.NH);
-  kern<<<grid, PAR_THREADS, PAR_SMEM, st>>>(mA, mB, mX, mSt, pp);
+  kern<<<grid, PAR_THREADS, PAR_SMEM, st>>>(mA, mB, mX, mSt, mE, pp);
   MLSTM_LAUNCH_CHECK();
   return MLSTM_OK;
 }
@@ -573,15 +626,14 @@ int sm100_parallel_fw(const void* q, const void* k, const void* v, const GateBuf
       !state_map(&mC, c_states, d, 64))
     return MLSTM_ERR_CUDA;
   ParParams pp = base_params(gb, d);
-  pp.n_states = n_states; pp.q = (const __nv_bfloat16*)q; pp.out = (__nv_bfloat16*)h; pp.n_out = n_out;
+  pp.n_states = n_states; pp.out = (__nv_bfloat16*)h; pp.n_out = n_out;
   pp.DI = d.DHQK; pp.DO = d.DHHV;
-  return launch_par<PM_H>(mQ, mK, mV, mC, pp, d, st);
+  return launch_par<PM_H>(mQ, mK, mV, mC, mV, pp, d, st);
 }
 
 int sm100_parallel_bw(const void* q, const void* k, const void* v, const void* dh, const GateBuffers& gb,
-                      const void* c_states, const void* dc_states, void* dq, void* dk, void* dv, float* acc,
-                      float* kdk, const ChunkwiseDims& d, cudaStream_t st) {
-  (void)acc; (void)kdk;
+                      const void* c_states, const void* dc_states, void* dq, void* dk, void* dv, float* qdq_parts,
+                      float* kdk_parts, const ChunkwiseDims& d, cudaStream_t st) {
   PhaseScope ps(PH_PAR_BW, st);
   CUtensorMap mQ, mK, mV, mDH, mC_k, mdC_mn, mdC_k;
   if (!tok_map(&mQ, q, d, d.DHQK) || !tok_map(&mK, k, d, d.DHQK) || !tok_map(&mV, v, d, d.DHHV) ||
@@ -591,11 +643,11 @@ int sm100_parallel_bw(const void* q, const void* k, const void* v, const void* d
   int rc;
   ParParams pp = base_params(gb, d);
   pp.DI = d.DHQK; pp.DO = d.DHHV; pp.out = (__nv_bfloat16*)dv;
-  if ((rc = launch_par<PM_DV>(mK, mQ, mDH, mdC_mn, pp, d, st)) != MLSTM_OK) return rc;
-  pp.DI = d.DHHV; pp.DO = d.DHQK; pp.out = (__nv_bfloat16*)dk;
-  if ((rc = launch_par<PM_DK>(mV, mDH, mQ, mdC_k, pp, d, st)) != MLSTM_OK) return rc;
-  pp.out = (__nv_bfloat16*)dq;
-  if ((rc = launch_par<PM_DQ>(mDH, mV, mK, mC_k, pp, d, st)) != MLSTM_OK) return rc;
+  if ((rc = launch_par<PM_DV>(mK, mQ, mDH, mdC_mn, mDH, pp, d, st)) != MLSTM_OK) return rc;
+  pp.DI = d.DHHV; pp.DO = d.DHQK; pp.out = (__nv_bfloat16*)dk; pp.rowdot = kdk_parts;
+  if ((rc = launch_par<PM_DK>(mV, mDH, mQ, mdC_k, mK, pp, d, st)) != MLSTM_OK) return rc;
+  pp.out = (__nv_bfloat16*)dq; pp.rowdot = qdq_parts;
+  if ((rc = launch_par<PM_DQ>(mDH, mV, mK, mC_k, mQ, pp, d, st)) != MLSTM_OK) return rc;
   return MLSTM_OK;
 }
 

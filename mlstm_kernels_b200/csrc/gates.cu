@@ -145,7 +145,7 @@ gates_kernel(const T* __restrict__ vecI, const T* __restrict__ vecF, const float
 }
 
 // Per-token reductions for the gate gradients:
-//   acc_t = sum_d (q dq - k dk),  kdk_t = sum_d k dk
+//   qdq_t = sum_d q dq,  kdk_t = sum_d k dk
 // mlstm_kernels/torch/chunkwise/triton_xl_chunk/chunkwise_gates.py:68-95. One warp per token.
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -158,29 +158,35 @@ gate_grad_rows_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
   const size_t base = tok * DHQK;
   float a = 0.f, b = 0.f;
   for (int d = lane; d < DHQK; d += 32) {
-    const float kk = to_f32(k[base + d]) * to_f32(dk[base + d]);
-    a += to_f32(q[base + d]) * to_f32(dq[base + d]) - kk;
-    b += kk;
+    a += to_f32(q[base + d]) * to_f32(dq[base + d]);
+    b += to_f32(k[base + d]) * to_f32(dk[base + d]);
   }
   a = warp_sum(a); b = warp_sum(b);
   if (lane == 0) { acc[tok] = a; kdk[tok] = b; }
 }
 
-// deltaF_t = sigmoid(-f_t) * sum_{t' >= t over the whole sequence} acc_t' ; deltaI_t = kdk_t (* sigmoid(-i_t)).
+// deltaF_t = sigmoid(-f_t) * sum_{t' >= t over the whole sequence} (qdq_t' - kdk_t') ; deltaI_t = kdk_t (* sigmoid(-i_t)).
+// qdq / kdk may arrive as `nparts` partial sums (one per 128-wide head-dim tile), `part_stride` floats apart;
+// they are added in a fixed order, so the result does not depend on scheduling.
 // One CTA per (batch, head); each thread owns a contiguous token range, block scan over the range sums.
 constexpr int kScanThreads = 1024;
 template <typename T>
 __global__ void __launch_bounds__(kScanThreads)
-gate_grad_scan_kernel(const T* __restrict__ vecI, const T* __restrict__ vecF, const float* __restrict__ acc,
+gate_grad_scan_kernel(const T* __restrict__ vecI, const T* __restrict__ vecF, const float* __restrict__ qdq,
                       const float* __restrict__ kdk, float* __restrict__ dI, float* __restrict__ dF,
-                      int S, int variant) {
+                      int S, int variant, int nparts, size_t part_stride) {
   __shared__ float s_part[kScanThreads];
   const int bh = blockIdx.x, t = threadIdx.x;
   const size_t base = (size_t)bh * S;
   const int seg = (S + kScanThreads - 1) / kScanThreads;
   const int s0 = min(S, t * seg), s1 = min(S, (t + 1) * seg);
+  auto parts = [&](const float* src, size_t idx) {
+    float t = 0.f;
+    for (int pp = 0; pp < nparts; ++pp) t += src[pp * part_stride + idx];
+    return t;
+  };
   float sum = 0.f;
-  for (int s = s0; s < s1; ++s) sum += acc[base + s];
+  for (int s = s0; s < s1; ++s) sum += parts(qdq, base + s) - parts(kdk, base + s);
   s_part[t] = sum;
   __syncthreads();
   // suffix sums over threads (exclusive): sum of the ranges to the right
@@ -192,9 +198,9 @@ gate_grad_scan_kernel(const T* __restrict__ vecI, const T* __restrict__ vecF, co
   }
   float run = (t + 1 < kScanThreads) ? s_part[t + 1] : 0.f;
   for (int s = s1 - 1; s >= s0; --s) {
-    run += acc[base + s];
+    float di = parts(kdk, base + s);
+    run += parts(qdq, base + s) - di;
     dF[base + s] = run * sigmoid_f(-to_f32(vecF[base + s]));
-    float di = kdk[base + s];
     if (variant != MLSTM_EXP) di *= sigmoid_f(-to_f32(vecI[base + s]));
     dI[base + s] = di;
   }
@@ -231,8 +237,7 @@ int launch_gate_grad_rows_t(const void* q, const void* k, const void* dq, const 
   return MLSTM_OK;
 }
 
-int launch_gate_grad_scan(int gate_dtype, const void* i, const void* f, const float* acc, const float* kdk, float* dI,
-                          float* dF, const ChunkwiseDims& d, cudaStream_t st);
+
 
 int launch_gate_grads(int dtype, int gate_dtype, const void* q, const void* k, const void* dq, const void* dk,
                       const void* i, const void* f, float* acc, float* kdk, float* dI, float* dF,
@@ -245,24 +250,25 @@ int launch_gate_grads(int dtype, int gate_dtype, const void* q, const void* k, c
     case MLSTM_F16: rc = launch_gate_grad_rows_t<__half>(q, k, dq, dk, acc, kdk, d, st); break;
   }
   if (rc != MLSTM_OK) return rc;
-  return launch_gate_grad_scan(gate_dtype, i, f, acc, kdk, dI, dF, d, st);
+  return launch_gate_grad_scan(gate_dtype, i, f, acc, kdk, 1, dI, dF, d, st);
 }
 
-// Scan-only entry: acc / kdk were already produced (in f32, before rounding) by the backward kernels.
-int launch_gate_grad_scan(int dtype, const void* i, const void* f, const float* acc, const float* kdk, float* dI,
-                          float* dF, const ChunkwiseDims& d, cudaStream_t st) {
+// Scan-only entry: the row sums were already produced (in f32, before rounding) by the backward kernels.
+int launch_gate_grad_scan(int dtype, const void* i, const void* f, const float* qdq, const float* kdk, int nparts,
+                          float* dI, float* dF, const ChunkwiseDims& d, cudaStream_t st) {
+  const size_t stride = (size_t)d.B * d.NH * d.S;
   switch (dtype) {
     case MLSTM_F32:
-      gate_grad_scan_kernel<float><<<d.B * d.NH, kScanThreads, 0, st>>>((const float*)i, (const float*)f, acc, kdk,
-                                                                        dI, dF, d.S, d.variant);
+      gate_grad_scan_kernel<float><<<d.B * d.NH, kScanThreads, 0, st>>>((const float*)i, (const float*)f, qdq, kdk,
+                                                                        dI, dF, d.S, d.variant, nparts, stride);
       break;
     case MLSTM_BF16:
       gate_grad_scan_kernel<__nv_bfloat16><<<d.B * d.NH, kScanThreads, 0, st>>>(
-          (const __nv_bfloat16*)i, (const __nv_bfloat16*)f, acc, kdk, dI, dF, d.S, d.variant);
+          (const __nv_bfloat16*)i, (const __nv_bfloat16*)f, qdq, kdk, dI, dF, d.S, d.variant, nparts, stride);
       break;
     case MLSTM_F16:
-      gate_grad_scan_kernel<__half><<<d.B * d.NH, kScanThreads, 0, st>>>((const __half*)i, (const __half*)f, acc, kdk,
-                                                                         dI, dF, d.S, d.variant);
+      gate_grad_scan_kernel<__half><<<d.B * d.NH, kScanThreads, 0, st>>>((const __half*)i, (const __half*)f, qdq, kdk,
+                                                                         dI, dF, d.S, d.variant, nparts, stride);
       break;
     default: return MLSTM_ERR_DTYPE;
   }

@@ -10,8 +10,8 @@ int launch_gates(int dtype, const void* i, const void* f, const float* m_initial
 int launch_gate_grads(int dtype, int gate_dtype, const void* q, const void* k, const void* dq, const void* dk, const void* i,
                       const void* f, float* acc, float* kdk, float* dI, float* dF, const ChunkwiseDims& d,
                       cudaStream_t st);
-int launch_gate_grad_scan(int dtype, const void* i, const void* f, const float* acc, const float* kdk, float* dI,
-                          float* dF, const ChunkwiseDims& d, cudaStream_t st);
+int launch_gate_grad_scan(int dtype, const void* i, const void* f, const float* qdq, const float* kdk, int nparts,
+                          float* dI, float* dF, const ChunkwiseDims& d, cudaStream_t st);
 
 // chunkwise_simt.cu : portable CUDA-core kernels, any shape, any element type
 int simt_recurrent_fw(int dtype, int state_dtype, const void* k, const void* v, const GateBuffers& gb,
@@ -37,8 +37,8 @@ int sm100_parallel_fw(const void* q, const void* k, const void* v, const GateBuf
 int sm100_recurrent_bw(const void* q, const void* dh, const GateBuffers& gb, const float* dc_last, void* dc_states,
                        float* dc_initial, const ChunkwiseDims& d, cudaStream_t st);
 int sm100_parallel_bw(const void* q, const void* k, const void* v, const void* dh, const GateBuffers& gb,
-                      const void* c_states, const void* dc_states, void* dq, void* dk, void* dv, float* acc,
-                      float* kdk, const ChunkwiseDims& d, cudaStream_t st);
+                      const void* c_states, const void* dc_states, void* dq, void* dk, void* dv, float* qdq_parts,
+                      float* kdk_parts, const ChunkwiseDims& d, cudaStream_t st);
 
 int sm100_device_status(int reset, int* status);
 
