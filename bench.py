@@ -264,6 +264,14 @@ def run_b200(args):
     clocks = sampler.stop() if rank == 0 else None
     value = world * flops_fwbw / (ms * 1e-3) / 1e12
 
+    if args.quick:
+        if rank == 0:
+            print(json.dumps({"metric": "chunkwise_fwbw_tflops_64k_tokens", "value": value, "unit": "TFLOP/s",
+                              "ms_per_step": ms, "config": {"workload": w["name"]}, "quick": True}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
     # ---- end to end through the public API with host buffers ----
     e2e_steps = max(2, min(args.steps, 5))
     ms_e2e = timed(step_e2e, e2e_steps, 1)
@@ -399,9 +407,17 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary measurements")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--batch", type=int, default=None, help="override the batch size B of the workload (profiling)")
+    ap.add_argument("--quick", action="store_true",
+                    help="profiling mode: timed region only (no end-to-end leg, no per-kernel pass, no extras, no CPU leg)")
     args = ap.parse_args()
-    if args.warmup < 3 and args.impl == "b200":
+    if args.warmup < 3 and args.impl == "b200" and not args.quick:
         args.warmup = 3
+    if args.batch is not None:
+        WORKLOAD["B"] = args.batch
+        WORKLOAD["name"] = WORKLOAD["name"].replace("_B8_", f"_B{args.batch}_")
+    if args.quick:
+        args.no_extra = args.no_cpu = True
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -55,6 +55,8 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   __shared__ uint64_t bar_full[2], bar_empty[2], bar_scaled[2], bar_acc_full[2], bar_acc_free[2], bar_nsum[2];
   __shared__ uint32_t s_tmem;
+  __shared__ float s_scale[2][CL];  // per-row scale of the left tile, staged by the producer warp
+  __shared__ float s_g[4];          // decay of the chunk, ring of four
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int e0 = blockIdx.x * 128, d0 = blockIdx.y * 128, bh = blockIdx.z;
@@ -76,26 +78,38 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
   const uint32_t tmem = s_tmem;
 
   if (warp == 0) {
-    // ---------------- TMA producer ----------------
-    if (lane == 0) {
-      int issued = 0;
-      for (int s = 0; s < NC; ++s) {
-        const int st = s & 1;
-        if (!mbar_wait(&bar_empty[st], ((s >> 1) & 1) ^ 1, &g_sm100_status, 101)) break;
-        const int ck = BWD ? NC - 1 - s : s;
-        const int row0 = bh * p.S + ck * CL;
+    // ---------------- TMA producer (whole warp: also stages the per-row scales and the chunk decay) ----------------
+    int issued = 0;
+    for (int s = 0; s < NC; ++s) {
+      const int st = s & 1;
+      int ok = 1;
+      if (lane == 0) ok = mbar_wait(&bar_empty[st], ((s >> 1) & 1) ^ 1, &g_sm100_status, 101) ? 1 : 0;
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      const int ck = BWD ? NC - 1 - s : s;
+      const int row0 = bh * p.S + ck * CL;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int r = lane + 32 * u;
+        float sc = p.lscale[(size_t)row0 + r] * p.lmul;
+        if (BWD) sc *= p.rscale[(size_t)row0 + r];
+        s_scale[st][r] = sc;
+      }
+      if (lane == 0) s_g[s & 3] = p.gbar[(size_t)bh * NC + ck];
+      __syncwarp();
+      if (lane == 0) {
         uint8_t* sl = smem + st * REC_STAGE_BYTES;
         mbar_expect_tx(&bar_full[st], REC_STAGE_BYTES);
         tma_load_2d(sl, &mapL, &bar_full[st], d0, row0);
         tma_load_2d(sl + 16384, &mapL, &bar_full[st], d0 + 64, row0);
         tma_load_2d(sl + 32768, &mapR, &bar_full[st], e0, row0);
         tma_load_2d(sl + 49152, &mapR, &bar_full[st], e0 + 64, row0);
-        issued = s + 1;
       }
-      if (issued < NC && issued > 0) {  // error path: let the copies in flight land before the CTA retires
-        int dummy = 1;
-        for (int s = max(0, issued - 2); s < issued; ++s) mbar_wait(&bar_full[s & 1], (s >> 1) & 1, &dummy, 1);
-      }
+      issued = s + 1;
+    }
+    if (lane == 0 && issued < NC && issued > 0) {  // error path: let the copies in flight land before the CTA retires
+      int dummy = 1;
+      for (int s = max(0, issued - 2); s < issued; ++s) mbar_wait(&bar_full[s & 1], (s >> 1) & 1, &dummy, 1);
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
@@ -147,8 +161,7 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
       const int buf = s & 1;
       if (!mbar_wait(&bar_acc_full[buf], (s >> 1) & 1, &g_sm100_status, 104)) return false;
       tc_fence_after_sync();
-      const int ck = BWD ? NC - 1 - s : s;
-      const float g = p.gbar[(size_t)bh * NC + ck];
+      const float g = s_g[s & 3];
       const uint32_t ta = tmem + ((uint32_t)(quarter * 32) << 16) + buf * 128 + half * 64;
       uint32_t r0[32], r1[32];
       tmem_ld32(ta, r0);
@@ -170,8 +183,6 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
     bool ok = true;
     for (int s = 0; s < NC; ++s) {
       const int st = s & 1;
-      const int ck = BWD ? NC - 1 - s : s;
-      const size_t tok0 = (size_t)bh * p.S + (size_t)ck * CL;
       if (!mbar_wait(&bar_full[st], (s >> 1) & 1, &g_sm100_status, 105)) { ok = false; break; }
       // scale the rows of the left tile in place (two 64-column boxes of 128 rows x 128 B, 128-byte swizzle)
       uint8_t* sl = smem + st * REC_STAGE_BYTES;
@@ -183,8 +194,7 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
         const int r = (ct >> 3) + 32 * (u & 3);
-        float sc = p.lscale[tok0 + r] * p.lmul;
-        if (BWD) sc *= p.rscale[tok0 + r];
+        const float sc = s_scale[st][r];
         uint4* ptr = reinterpret_cast<uint4*>(sl + (u >> 2) * 16384 + r * 128 + (ct & 7) * 16);
         uint4 v = *ptr;
         uint32_t w[4] = {v.x, v.y, v.z, v.w};
@@ -216,7 +226,7 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
           float colsum = 0.f;   // fixed summation order: the result does not depend on scheduling
 #pragma unroll 8
           for (int g = 0; g < 32; ++g) colsum += npart[g * 128 + ct];
-          nval = fmaf(p.gbar[(size_t)bh * NC + ck], nval, colsum);
+          nval = fmaf(s_g[s & 3], nval, colsum);
           p.n_states[((size_t)bh * (NC + 1) + s + 1) * p.DHQK + d0 + ct] = nval;
         }
       }
