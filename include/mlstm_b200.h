@@ -84,7 +84,8 @@ int mlstm_b200_chunkwise_has_tcgen05(int S, int DHQK, int DHHV, int L, int dtype
  * case and implementation choice. */
 int mlstm_b200_chunkwise_state_dtype(int S, int DHQK, int DHHV, int L, int dtype, int impl);
 
-/* Scratch bytes the forward (backward = 0) or backward (backward = 1) call needs. */
+/* Scratch bytes the forward (backward = 0), the backward (backward = 1) or the segment summary
+ * (backward = 2) call needs. */
 size_t mlstm_b200_chunkwise_workspace_bytes(int B, int NH, int S, int DHQK, int DHHV, int L,
                                             int dtype, int variant, int impl, int backward);
 
@@ -133,6 +134,33 @@ int mlstm_b200_chunkwise_bw(const void* q, const void* k, const void* v, const v
                             void* workspace, size_t workspace_bytes,
                             int B, int NH, int S, int DHQK, int DHHV, int L,
                             int dtype, int gate_dtype, int variant, int impl, float eps, void* stream);
+
+/*
+ * Sequence-parallel prefill: a long sequence is split into contiguous segments, one per GPU.
+ * The reference has no multi-device code; these two entry points implement its state-passing
+ * contract (chaining segments through c_initial / n_initial / m_initial and the returned last
+ * states: tests/torch/conftest.py:82-175, mlstm_kernels/torch/kernel_wrappers.py:109-151) so that
+ * the segments' recurrences can run concurrently.
+ *
+ * mlstm_b200_chunkwise_summary: gates + inter-chunk recurrence of ONE segment started from the
+ *   empty state (C = 0, n = 0, m = -inf).  Outputs the segment's contribution c_last, n_last
+ *   (n_last may be NULL for MLSTM_SIG_NONORM), m_last (B,NH) and g_total (B,NH) = sum of
+ *   logsigmoid(f) over the segment.  No per-chunk states, no H.
+ * mlstm_b200_state_combine: joins the state entering a segment with that segment's summary,
+ *   m_out = max(g_total + m_in, m_loc), X_out = exp(g_total + m_in - m_out) X_in + exp(m_loc - m_out) X_loc
+ *   (m terms are zero for the sigmoid input gate).  c_in / n_in / m_in may be NULL (zero state, m = 0).
+ *   The result equals what the single-device recurrence holds at the segment's end
+ *   (mlstm_kernels/triton/chunkwise/xl_chunk/fw_kernel_recurrent.py:175-196 applied per segment).
+ */
+int mlstm_b200_chunkwise_summary(const void* k, const void* v, const void* i, const void* f,
+                                 float* c_last, float* n_last, float* m_last, float* g_total,
+                                 void* workspace, size_t workspace_bytes,
+                                 int B, int NH, int S, int DHQK, int DHHV, int L,
+                                 int dtype, int gate_dtype, int variant, int impl, void* stream);
+int mlstm_b200_state_combine(const float* c_in, const float* n_in, const float* m_in,
+                             const float* c_loc, const float* n_loc, const float* m_loc, const float* g_total,
+                             float* c_out, float* n_out, float* m_out,
+                             int B, int NH, int DHQK, int DHHV, int variant, void* stream);
 
 /*
  * One recurrent decode step.  Replaces mlstm_recurrent_step__triton_fw

@@ -26,18 +26,31 @@ def select_chunk_size(sequence_length: int, target_chunk_size: int) -> int:
     are processed as one chunk; otherwise the target chunk size must divide the sequence length."""
     if sequence_length % 16 != 0:
         raise ValueError("Sequence length must be divisible by 16.")
-    if sequence_length < 128:
-        if not _is_pow2(sequence_length):
-            raise ValueError("Sequence length must be a power of 2.")
-        return sequence_length
     if target_chunk_size is None:
         target_chunk_size = 128
+    if sequence_length < 128:
+        if _is_pow2(sequence_length):
+            return sequence_length
+        if _is_pow2(target_chunk_size) and target_chunk_size >= 16 and sequence_length % target_chunk_size == 0:
+            return target_chunk_size  # more permissive than the reference, which rejects this case
+        raise ValueError("Sequence length must be a power of 2.")
     if not _is_pow2(target_chunk_size) or target_chunk_size < 16:
         raise ValueError(f"Chunk size {target_chunk_size} must be a power of 2 >= 16.")
     if sequence_length % target_chunk_size != 0:
         raise ValueError(
             f"Sequence length must be divisible by the target chunk size {target_chunk_size}.")
     return target_chunk_size
+
+
+def kernel_chunk_size(q: torch.Tensor, v: torch.Tensor, chunk_size: int, impl: str = "auto") -> int:
+    """Chunk size the kernels run with.  Chunk sizes above 128 run as chunks of 128 on the tcgen05 path
+    (H does not depend on the chunk size; the reference does the same for its inter-chunk kernel:
+    chunk_size_inter = min(128, chunk_size), mlstm_kernels/triton/chunkwise/kernel_param_heuristics.py:96-121)."""
+    if chunk_size > 128 and impl != "simt" and q.is_cuda:
+        lib = _lib.load()
+        if lib.mlstm_b200_chunkwise_has_tcgen05(q.shape[2], q.shape[3], v.shape[3], 128, _lib.dtype_code(q.dtype)):
+            return 128
+    return chunk_size
 
 
 def _f32c(t):
@@ -134,7 +147,7 @@ def _make_fwbw(autocast_kernel_dtype: torch.dtype, variant: int):
         @custom_fwd(device_type="cuda", cast_inputs=autocast_kernel_dtype)
         def forward(ctx, q, k, v, i, f, c_initial, n_initial, m_initial, return_last_states, eps, chunk_size, impl):
             B, NH, S, DHQK = q.shape
-            L = select_chunk_size(S, chunk_size)
+            L = kernel_chunk_size(q, v, select_chunk_size(S, chunk_size), impl)
             out = chunkwise_fw_raw(q, k, v, i, f, c_initial, n_initial, m_initial, chunk_size=L, eps=eps,
                                    variant=variant, impl=impl, want_last=return_last_states)
             ctx.save_for_backward(q, k, v, i, f, m_initial, out["C_states"], out["n_out"])

@@ -89,6 +89,24 @@ static FwLayout carve_fw(void* ws, int BNH, int S, int NC, float* m_out) {
   return l;
 }
 
+struct SumLayout { GateBuffers gb; float* m_states; size_t bytes; };
+static SumLayout carve_summary(void* ws, int BNH, int S, int NC) {
+  Carver c(ws);
+  SumLayout l{};
+  const size_t tok = (size_t)BNH * S;
+  l.gb.vecB = c.take<float>(tok);
+  l.gb.iota = c.take<float>(tok);
+  l.gb.m_tok = c.take<float>(tok);
+  l.gb.abar = c.take<float>(tok);
+  l.gb.bbar = c.take<float>(tok);
+  l.gb.gbar = c.take<float>((size_t)BNH * NC);
+  l.gb.scratch = c.take<float>((size_t)BNH * NC * 2);
+  l.gb.inv_den = nullptr;
+  l.m_states = c.take<float>((size_t)BNH * (NC + 1));
+  l.bytes = align_up(c.off, 256);
+  return l;
+}
+
 struct BwLayout { GateBuffers gb; float* m_states; float* acc; float* kdk; void* dc_states; size_t bytes; };
 static BwLayout carve_bw(void* ws, int BNH, int S, int NC, int DHQK, int DHHV, size_t state_elem) {
   Carver c(ws);
@@ -189,6 +207,7 @@ size_t mlstm_b200_chunkwise_workspace_bytes(int B, int NH, int S, int DHQK, int 
   (void)variant;
   if (check_dims(B, NH, S, DHQK, DHHV, L) != MLSTM_OK) return 0;
   const int NC = S / L;
+  if (backward == 2) return carve_summary(nullptr, B * NH, S, NC).bytes;
   if (!backward) return carve_fw(nullptr, B * NH, S, NC, nullptr).bytes;
   const size_t se = dtype_size(mlstm_b200_chunkwise_state_dtype(S, DHQK, DHHV, L, dtype, impl));
   return carve_bw(nullptr, B * NH, S, NC, DHQK, DHHV, se).bytes;
@@ -271,6 +290,50 @@ int mlstm_b200_chunkwise_bw(const void* q, const void* k, const void* v, const v
     if ((rc = launch_gate_grads(dtype, gate_dtype, q, k, dq, dk, i, f, lay.acc, lay.kdk, di, df, d, st)) != MLSTM_OK) return rc;
   }
   return MLSTM_OK;
+}
+
+int mlstm_b200_chunkwise_summary(const void* k, const void* v, const void* i, const void* f, float* c_last,
+                                 float* n_last, float* m_last, float* g_total, void* workspace,
+                                 size_t workspace_bytes, int B, int NH, int S, int DHQK, int DHHV, int L, int dtype,
+                                 int gate_dtype, int variant, int impl, void* stream) {
+  int rc = check_dims(B, NH, S, DHQK, DHHV, L);
+  if (rc != MLSTM_OK) return rc;
+  if (dtype != MLSTM_F32 && dtype != MLSTM_BF16 && dtype != MLSTM_F16) return MLSTM_ERR_DTYPE;
+  if (gate_dtype != MLSTM_F32 && gate_dtype != MLSTM_BF16 && gate_dtype != MLSTM_F16) return MLSTM_ERR_DTYPE;
+  if (variant < MLSTM_EXP || variant > MLSTM_SIG_NONORM) return MLSTM_ERR_UNSUPPORTED;
+  if (!k || !v || !i || !f || !c_last || !m_last || !g_total || !workspace) return MLSTM_ERR_NULL;
+  if (variant != MLSTM_SIG_NONORM && !n_last) return MLSTM_ERR_NULL;
+  const void* ptrs[] = {k, v, i, f, c_last, n_last, m_last, g_total, workspace};
+  for (const void* p : ptrs) if (p && !aligned16(p)) return MLSTM_ERR_ALIGN;
+  bool use_sm100 = false;
+  if ((rc = resolve_impl(impl, S, DHQK, DHHV, L, dtype, &use_sm100)) != MLSTM_OK) return rc;
+  ChunkwiseDims d{B, NH, S, DHQK, DHHV, L, S / L, variant, 1e-6f, 1.0f / sqrtf((float)DHQK)};
+  SumLayout lay = carve_summary(workspace, B * NH, S, d.NC);
+  if (workspace_bytes < lay.bytes) return MLSTM_ERR_WORKSPACE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // the segment starts from the empty state: C = 0, n = 0, m = -inf
+  if ((rc = launch_gates(gate_dtype, i, f, nullptr, nullptr, lay.gb, lay.m_states, d, st, -INFINITY, g_total)) != MLSTM_OK) return rc;
+  if (use_sm100) {
+    if ((rc = sm100_recurrent_fw(k, v, lay.gb, nullptr, nullptr, nullptr, nullptr, c_last, n_last, d, st)) != MLSTM_OK) return rc;
+  } else {
+    if ((rc = simt_recurrent_fw(dtype, MLSTM_F32, k, v, lay.gb, nullptr, nullptr, nullptr, nullptr, c_last, n_last, d, st)) != MLSTM_OK) return rc;
+  }
+  MLSTM_CUDA_CHECK(cudaMemcpy2DAsync(m_last, sizeof(float), lay.m_states + d.NC, sizeof(float) * (d.NC + 1),
+                                     sizeof(float), (size_t)B * NH, cudaMemcpyDeviceToDevice, st));
+  return MLSTM_OK;
+}
+
+int mlstm_b200_state_combine(const float* c_in, const float* n_in, const float* m_in, const float* c_loc,
+                             const float* n_loc, const float* m_loc, const float* g_total, float* c_out,
+                             float* n_out, float* m_out, int B, int NH, int DHQK, int DHHV, int variant,
+                             void* stream) {
+  if (B <= 0 || NH <= 0 || DHQK <= 0 || DHHV <= 0) return MLSTM_ERR_SHAPE;
+  if (variant < MLSTM_EXP || variant > MLSTM_SIG_NONORM) return MLSTM_ERR_UNSUPPORTED;
+  if (!c_loc || !g_total || !c_out) return MLSTM_ERR_NULL;
+  if (variant == MLSTM_EXP && (!m_loc || !m_out)) return MLSTM_ERR_NULL;
+  if (n_out && !n_loc) return MLSTM_ERR_NULL;
+  return launch_state_combine(c_in, n_in, m_in, c_loc, n_loc, m_loc, g_total, c_out, n_out, m_out, B * NH, DHQK,
+                              DHHV, variant, static_cast<cudaStream_t>(stream));
 }
 
 int mlstm_b200_step(const void* q, const void* k, const void* v, const void* i, const void* f, const void* c,

@@ -32,7 +32,7 @@ rec_kernel(const T* __restrict__ left, const T* __restrict__ right, const float*
   __shared__ float Rs[KSL][TILE + 1];
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
   const int e0 = blockIdx.x * TILE, d0 = blockIdx.y * TILE, bh = blockIdx.z;
-  const bool do_n = (!BWD) && (blockIdx.x == 0) && (n_states != nullptr);
+  const bool do_n = (!BWD) && (blockIdx.x == 0) && (n_states != nullptr || n_final != nullptr);
 
   float C[4][4];
 #pragma unroll
@@ -46,15 +46,17 @@ rec_kernel(const T* __restrict__ left, const T* __restrict__ right, const float*
   if (do_n && tid < TILE && d0 + tid < DHQK && n_init) nval = n_init[(size_t)bh * DHQK + d0 + tid];
 
   auto store_state = [&](int slot) {
-    TS* cs = c_states + ((size_t)bh * (NC + 1) + slot) * DHQK * DHHV;
+    if (c_states != nullptr) {
+      TS* cs = c_states + ((size_t)bh * (NC + 1) + slot) * DHQK * DHHV;
 #pragma unroll
-    for (int a = 0; a < 4; ++a)
+      for (int a = 0; a < 4; ++a)
 #pragma unroll
-      for (int b = 0; b < 4; ++b) {
-        const int d = d0 + ty * 4 + a, e = e0 + tx * 4 + b;
-        if (d < DHQK && e < DHHV) cs[(size_t)d * DHHV + e] = from_f32<TS>(C[a][b]);
-      }
-    if (do_n && tid < TILE && d0 + tid < DHQK) n_states[((size_t)bh * (NC + 1) + slot) * DHQK + d0 + tid] = nval;
+        for (int b = 0; b < 4; ++b) {
+          const int d = d0 + ty * 4 + a, e = e0 + tx * 4 + b;
+          if (d < DHQK && e < DHHV) cs[(size_t)d * DHHV + e] = from_f32<TS>(C[a][b]);
+        }
+    }
+    if (do_n && n_states != nullptr && tid < TILE && d0 + tid < DHQK) n_states[((size_t)bh * (NC + 1) + slot) * DHQK + d0 + tid] = nval;
   };
 
   for (int s = 0; s < NC; ++s) {

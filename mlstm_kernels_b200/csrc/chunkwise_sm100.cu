@@ -61,7 +61,7 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int e0 = blockIdx.x * 128, d0 = blockIdx.y * 128, bh = blockIdx.z;
   const int NC = p.NC;
-  const bool do_n = (!BWD) && blockIdx.x == 0 && p.n_states != nullptr;
+  const bool do_n = (!BWD) && blockIdx.x == 0 && (p.n_states != nullptr || p.n_final != nullptr);
 
   if (tid == 0) {
     for (int s = 0; s < 2; ++s) {
@@ -148,6 +148,7 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
     if (do_n && ct < 128 && p.n_init) nval = p.n_init[(size_t)bh * p.DHQK + d0 + ct];
 
     auto store_c = [&](int slot) {
+      if (p.c_states == nullptr) return;
       uint4* dst = reinterpret_cast<uint4*>(p.c_states + (((size_t)bh * (NC + 1) + slot) * p.DHQK + d) * p.DHHV + ecol);
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
@@ -179,7 +180,7 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
 
     // slot written before step s: forward s, backward NC - s
     store_c(BWD ? NC : 0);
-    if (do_n && ct < 128) p.n_states[((size_t)bh * (NC + 1)) * p.DHQK + d0 + ct] = nval;
+    if (do_n && p.n_states != nullptr && ct < 128) p.n_states[((size_t)bh * (NC + 1)) * p.DHQK + d0 + ct] = nval;
     bool ok = true;
     for (int s = 0; s < NC; ++s) {
       const int st = s & 1;
@@ -227,7 +228,7 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
 #pragma unroll 8
           for (int g = 0; g < 32; ++g) colsum += npart[g * 128 + ct];
           nval = fmaf(s_g[s & 3], nval, colsum);
-          p.n_states[((size_t)bh * (NC + 1) + s + 1) * p.DHQK + d0 + ct] = nval;
+          if (p.n_states != nullptr) p.n_states[((size_t)bh * (NC + 1) + s + 1) * p.DHQK + d0 + ct] = nval;
         }
       }
       if (s > 0) {
@@ -596,7 +597,7 @@ int sm100_recurrent_fw(const void* k, const void* v, const GateBuffers& gb, cons
                        const ChunkwiseDims& d, cudaStream_t st) {
   PhaseScope ps(PH_REC_FW, st);
   RecParams rp{gb.abar, nullptr, 1.f, gb.gbar, c_initial, n_initial, (__nv_bfloat16*)c_states,
-               d.variant == MLSTM_SIG_NONORM ? nullptr : n_states, c_last, n_last, d.S, d.NC, d.DHQK, d.DHHV};
+               d.variant == MLSTM_SIG_NONORM ? nullptr : n_states, c_last, d.variant == MLSTM_SIG_NONORM ? nullptr : n_last, d.S, d.NC, d.DHQK, d.DHHV};
   return launch_rec<false>(k, v, rp, d, st);
 }
 

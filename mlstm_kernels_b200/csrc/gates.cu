@@ -6,6 +6,8 @@
 // Follows mlstm_kernels/torch/chunkwise/triton_xl_chunk/chunkwise_gates.py:15-65 (vecB, vecA),
 // mlstm_kernels/triton/chunkwise/xl_chunk/fw_kernel_recurrent.py:150-176 (m recursion) and
 // mlstm_kernels/torch/chunkwise/native/fw.py:178-195 (per-token max state).
+#include <algorithm>
+
 #include "common.cuh"
 #include "launch.cuh"
 
@@ -17,7 +19,7 @@ template <typename T>
 __global__ void __launch_bounds__(kGateThreads)
 gates_kernel(const T* __restrict__ vecI, const T* __restrict__ vecF, const float* __restrict__ m_initial,
              const float* __restrict__ n_out, GateBuffers gb, float* __restrict__ m_states,
-             int S, int L, int NC, int variant, float eps) {
+             int S, int L, int NC, int variant, float eps, float m_default, float* __restrict__ g_sum) {
   const int bh = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = kGateThreads / 32;
   const bool siging = variant != MLSTM_EXP;
@@ -82,7 +84,7 @@ gates_kernel(const T* __restrict__ vecI, const T* __restrict__ vecF, const float
       sG[t] = G; sA[t] = A;
       __syncthreads();
       if (t == 0) {
-        float m = m_initial ? m_initial[bh] : 0.f;
+        float m = m_initial ? m_initial[bh] : m_default;
         for (int u = 0; u < kGateThreads; ++u) { sMin[u] = m; m = fmaxf(m + sG[u], sA[u]); }
       }
       __syncthreads();
@@ -103,6 +105,11 @@ gates_kernel(const T* __restrict__ vecI, const T* __restrict__ vecF, const float
         if (k == NC - 1) ms[NC] = 0.f;
       }
     }
+  }
+  if (g_sum != nullptr && threadIdx.x == 0) {  // total log forget gate of the sequence (for chaining segments)
+    float G = 0.f;
+    for (int k = 0; k < NC; ++k) G += g_arr[k];
+    g_sum[bh] = G;
   }
   __syncthreads();
 
@@ -209,20 +216,21 @@ gate_grad_scan_kernel(const T* __restrict__ vecI, const T* __restrict__ vecF, co
 // ---- launchers ----------------------------------------------------------------------------------
 template <typename T>
 int launch_gates_t(const void* i, const void* f, const float* m_initial, const float* n_out, const GateBuffers& gb,
-                   float* m_states, const ChunkwiseDims& d, cudaStream_t st) {
+                   float* m_states, const ChunkwiseDims& d, cudaStream_t st, float m_default, float* g_sum) {
   PhaseScope ps(PH_GATES, st);
   gates_kernel<T><<<d.B * d.NH, kGateThreads, 0, st>>>((const T*)i, (const T*)f, m_initial, n_out, gb, m_states,
-                                                     d.S, d.L, d.NC, d.variant, d.eps);
+                                                     d.S, d.L, d.NC, d.variant, d.eps, m_default, g_sum);
   MLSTM_LAUNCH_CHECK();
   return MLSTM_OK;
 }
 
 int launch_gates(int dtype, const void* i, const void* f, const float* m_initial, const float* n_out,
-                 const GateBuffers& gb, float* m_states, const ChunkwiseDims& d, cudaStream_t st) {
+                 const GateBuffers& gb, float* m_states, const ChunkwiseDims& d, cudaStream_t st, float m_default,
+                 float* g_sum) {
   switch (dtype) {
-    case MLSTM_F32: return launch_gates_t<float>(i, f, m_initial, n_out, gb, m_states, d, st);
-    case MLSTM_BF16: return launch_gates_t<__nv_bfloat16>(i, f, m_initial, n_out, gb, m_states, d, st);
-    case MLSTM_F16: return launch_gates_t<__half>(i, f, m_initial, n_out, gb, m_states, d, st);
+    case MLSTM_F32: return launch_gates_t<float>(i, f, m_initial, n_out, gb, m_states, d, st, m_default, g_sum);
+    case MLSTM_BF16: return launch_gates_t<__nv_bfloat16>(i, f, m_initial, n_out, gb, m_states, d, st, m_default, g_sum);
+    case MLSTM_F16: return launch_gates_t<__half>(i, f, m_initial, n_out, gb, m_states, d, st, m_default, g_sum);
   }
   return MLSTM_ERR_DTYPE;
 }
@@ -251,6 +259,49 @@ int launch_gate_grads(int dtype, int gate_dtype, const void* q, const void* k, c
   }
   if (rc != MLSTM_OK) return rc;
   return launch_gate_grad_scan(gate_dtype, i, f, acc, kdk, 1, dI, dF, d, st);
+}
+
+// Joins the state a sequence segment produced from the EMPTY state (C = 0, n = 0, m = -inf) onto the state that
+// enters the segment:  m_out = max(G + m_in, m_loc),  X_out = exp(G + m_in - m_out) X_in + exp(m_loc - m_out) X_loc
+// for X in {C, n}; G = total log forget gate of the segment.  Same recursion as the per-chunk update
+// (mlstm_kernels/triton/chunkwise/xl_chunk/fw_kernel_recurrent.py:175-196) applied to a whole segment.
+__global__ void __launch_bounds__(256)
+state_combine_kernel(const float* __restrict__ c_in, const float* __restrict__ n_in, const float* __restrict__ m_in,
+                     const float* __restrict__ c_loc, const float* __restrict__ n_loc, const float* __restrict__ m_loc,
+                     const float* __restrict__ g_total, float* __restrict__ c_out, float* __restrict__ n_out,
+                     float* __restrict__ m_out, int DHQK, int DHHV, int variant) {
+  const int bh = blockIdx.y;
+  float a, b, mo = 0.f;
+  if (variant == MLSTM_EXP) {
+    const float mi = m_in ? m_in[bh] : 0.f, ml = m_loc[bh], G = g_total[bh];
+    mo = fmaxf(G + mi, ml);
+    a = expf(G + mi - mo);
+    b = expf(ml - mo);
+  } else {
+    a = expf(g_total[bh]);
+    b = 1.f;
+  }
+  const size_t nC = (size_t)DHQK * DHHV;
+  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < nC; e += (size_t)gridDim.x * blockDim.x) {
+    const size_t idx = (size_t)bh * nC + e;
+    c_out[idx] = a * (c_in ? c_in[idx] : 0.f) + b * c_loc[idx];
+    if (e < (size_t)DHQK && n_out != nullptr) {
+      const size_t ni = (size_t)bh * DHQK + e;
+      n_out[ni] = a * (n_in ? n_in[ni] : 0.f) + b * n_loc[ni];
+    }
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0 && m_out != nullptr) m_out[bh] = mo;
+}
+
+int launch_state_combine(const float* c_in, const float* n_in, const float* m_in, const float* c_loc,
+                         const float* n_loc, const float* m_loc, const float* g_total, float* c_out, float* n_out,
+                         float* m_out, int BNH, int DHQK, int DHHV, int variant, cudaStream_t st) {
+  const size_t nC = (size_t)DHQK * DHHV;
+  dim3 grid((unsigned)std::min<size_t>((nC + 255) / 256, 64), BNH);
+  state_combine_kernel<<<grid, 256, 0, st>>>(c_in, n_in, m_in, c_loc, n_loc, m_loc, g_total, c_out, n_out, m_out, DHQK,
+                                            DHHV, variant);
+  MLSTM_LAUNCH_CHECK();
+  return MLSTM_OK;
 }
 
 // Scan-only entry: the row sums were already produced (in f32, before rounding) by the backward kernels.

@@ -6,7 +6,11 @@ namespace mlstm {
 
 // gates.cu
 int launch_gates(int dtype, const void* i, const void* f, const float* m_initial, const float* n_out,
-                 const GateBuffers& gb, float* m_states, const ChunkwiseDims& d, cudaStream_t st);
+                 const GateBuffers& gb, float* m_states, const ChunkwiseDims& d, cudaStream_t st,
+                 float m_default = 0.f, float* g_sum = nullptr);
+int launch_state_combine(const float* c_in, const float* n_in, const float* m_in, const float* c_loc,
+                         const float* n_loc, const float* m_loc, const float* g_total, float* c_out, float* n_out,
+                         float* m_out, int BNH, int DHQK, int DHHV, int variant, cudaStream_t st);
 int launch_gate_grads(int dtype, int gate_dtype, const void* q, const void* k, const void* dq, const void* dk, const void* i,
                       const void* f, float* acc, float* kdk, float* dI, float* dF, const ChunkwiseDims& d,
                       cudaStream_t st);

@@ -1,0 +1,172 @@
+"""Multi-GPU use of the chunkwise kernels: one process per GPU, `torch.distributed` for the plumbing.
+
+Two modes (the reference itself is single-device; both build on its state-passing contract,
+c_initial / n_initial / m_initial in, last states out: mlstm_kernels/torch/kernel_wrappers.py:109-151):
+
+* batch x heads sharding: every (batch, head) pair is an independent unit in all kernels, so the units
+  are split contiguously over the ranks and no data-path collective is needed (`shard_range`,
+  `shard_batch_heads`).
+* sequence-parallel prefill of one long sequence (`mlstm_chunkwise_sequence_parallel`): rank r holds the
+  r-th contiguous segment of the sequence.  "scan" mode: (1) all ranks compute, concurrently, the state
+  their segment produces from the empty state; (2) the boundary state travels along the chain
+  rank 0 -> 1 -> ... with one point-to-point message per boundary (NCCL send/recv, i.e. NVLink between
+  GPUs of a node), each rank folding its summary onto the incoming state; (3) all ranks run the full
+  forward of their segment, concurrently, from the true incoming state.  "chain" mode is the plain
+  serial hand-off (segment r starts when r-1 has finished its recurrence).  Both reproduce the
+  single-GPU (C, n, m) path.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+from .chunkwise import chunkwise_fw_raw, kernel_chunk_size, select_chunk_size
+
+
+def shard_range(total: int, world: int, rank: int) -> tuple[int, int]:
+    """Contiguous [start, stop) of `total` units owned by `rank`; sizes differ by at most one."""
+    if world <= 0 or not (0 <= rank < world):
+        raise ValueError(f"bad rank {rank} for world size {world}")
+    base, rem = divmod(total, world)
+    start = rank * base + min(rank, rem)
+    return start, start + base + (1 if rank < rem else 0)
+
+
+def shard_batch_heads(tensors, world: int, rank: int):
+    """Slice the (B, NH, ...) tensors to this rank's share of the B*NH independent units.
+    Returns tensors of shape (1, units, ...) (views when the inputs are contiguous)."""
+    B, NH = tensors[0].shape[:2]
+    start, stop = shard_range(B * NH, world, rank)
+    return [t.reshape(1, B * NH, *t.shape[2:])[:, start:stop] for t in tensors]
+
+
+def _variant(siging: bool, normalize: bool) -> int:
+    return _lib.EXP if not siging else (_lib.SIG if normalize else _lib.SIG_NONORM)
+
+
+def segment_summary(k, v, i, f, *, chunk_size: int, variant: int, impl: str = "auto"):
+    """State (C, n, m) and total log forget gate G that one segment produces from the empty state."""
+    _lib.require_cuda(k, v, i, f)
+    lib = _lib.load()
+    B, NH, S, DHQK = k.shape
+    DHHV = v.shape[-1]
+    dt, gdt, im = _lib.dtype_code(k.dtype), _lib.dtype_code(i.dtype), _lib.IMPL[impl]
+    k, v, i, f = (t.contiguous() for t in (k, v, i, f.to(i.dtype)))
+    dev = k.device
+    c = torch.empty((B, NH, DHQK, DHHV), dtype=torch.float32, device=dev)
+    n = torch.zeros((B, NH, DHQK), dtype=torch.float32, device=dev)
+    m = torch.empty((B, NH, 1), dtype=torch.float32, device=dev)
+    g = torch.empty((B, NH), dtype=torch.float32, device=dev)
+    ws_bytes = lib.mlstm_b200_chunkwise_workspace_bytes(B, NH, S, DHQK, DHHV, chunk_size, dt, variant, im, 2)
+    ws = torch.empty((max(ws_bytes, 256),), dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        rc = lib.mlstm_b200_chunkwise_summary(
+            _lib.ptr(k), _lib.ptr(v), _lib.ptr(i), _lib.ptr(f), _lib.ptr(c),
+            None if variant == _lib.SIG_NONORM else _lib.ptr(n), _lib.ptr(m), _lib.ptr(g), _lib.ptr(ws), ws_bytes,
+            B, NH, S, DHQK, DHHV, chunk_size, dt, gdt, variant, im, _lib.stream_handle(dev))
+    _lib.check(rc, "mlstm_b200_chunkwise_summary")
+    return c, n, m, g
+
+
+def state_combine(state_in, summary, *, variant: int):
+    """Fold a segment summary (C_loc, n_loc, m_loc, G) onto the state (C, n, m) entering the segment."""
+    c_in, n_in, m_in = state_in
+    c_loc, n_loc, m_loc, g = summary
+    lib = _lib.load()
+    B, NH, DHQK, DHHV = c_loc.shape
+    dev = c_loc.device
+    c_out, n_out, m_out = torch.empty_like(c_loc), torch.zeros_like(n_loc), torch.zeros_like(m_loc)
+    f32 = lambda t: None if t is None else t.to(torch.float32).contiguous()  # noqa: E731
+    c_in, n_in, m_in = f32(c_in), f32(n_in), f32(m_in)
+    with torch.cuda.device(dev):
+        rc = lib.mlstm_b200_state_combine(
+            _lib.ptr(c_in), _lib.ptr(n_in), _lib.ptr(m_in), _lib.ptr(c_loc), _lib.ptr(n_loc), _lib.ptr(m_loc),
+            _lib.ptr(g), _lib.ptr(c_out), None if variant == _lib.SIG_NONORM else _lib.ptr(n_out), _lib.ptr(m_out),
+            B, NH, DHQK, DHHV, variant, _lib.stream_handle(dev))
+    _lib.check(rc, "mlstm_b200_state_combine")
+    return c_out, n_out, m_out
+
+
+def _segment_forward(q, k, v, i, f, state_in, *, chunk_size, eps, variant, impl, want_last):
+    c0, n0, m0 = state_in
+    out = chunkwise_fw_raw(q, k, v, i, f, c0, n0, m0 if variant == _lib.EXP else None, chunk_size=chunk_size,
+                           eps=eps, variant=variant, impl=impl, want_last=want_last)
+    return out["H"], (out["C_last"], out["n_last"], out["m_last"])
+
+
+def _send_state(state, dst, group):
+    for t in state:
+        dist.send(t.contiguous(), dst=dst, group=group)
+
+
+def _recv_state(like, src, group):
+    out = tuple(torch.empty_like(t) for t in like)
+    for t in out:
+        dist.recv(t, src=src, group=group)
+    return out
+
+
+def mlstm_chunkwise_sequence_parallel(
+    q: torch.Tensor,  # (B, NH, S_local, DHQK)  this rank's contiguous segment of the sequence
+    k: torch.Tensor,
+    v: torch.Tensor,  # (B, NH, S_local, DHHV)
+    i: torch.Tensor,  # (B, NH, S_local)
+    f: torch.Tensor,
+    c_initial: torch.Tensor = None,  # state entering the WHOLE sequence (used by rank 0)
+    n_initial: torch.Tensor = None,
+    m_initial: torch.Tensor = None,
+    return_last_states: bool = False,
+    eps: float = 1e-6,
+    chunk_size: int = 128,
+    siging: bool = False,
+    normalize: bool = True,
+    mode: str = "scan",
+    group=None,
+    impl: str = "auto",
+):
+    """Forward (prefill) of one long sequence whose segments live on the ranks of `group`.
+    Returns this rank's H (B, NH, S_local, DHHV) and, if requested, the state after the LAST segment
+    (identical on every rank).  Ranks are ordered along the sequence: global rank order of the group."""
+    if mode not in ("scan", "chain"):
+        raise ValueError(f"unknown mode {mode}")
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    variant = _variant(siging, normalize)
+    B, NH, S, DHQK = q.shape
+    DHHV = v.shape[-1]
+    L = kernel_chunk_size(q, v, select_chunk_size(S, chunk_size), impl)
+    dev = q.device
+    ranks = dist.get_process_group_ranks(group) if group is not None else list(range(world))
+    prev_rank = ranks[rank - 1] if rank > 0 else None
+    next_rank = ranks[rank + 1] if rank < world - 1 else None
+
+    zeros = (torch.zeros((B, NH, DHQK, DHHV), dtype=torch.float32, device=dev),
+             torch.zeros((B, NH, DHQK), dtype=torch.float32, device=dev),
+             torch.zeros((B, NH, 1), dtype=torch.float32, device=dev))
+    f32 = lambda t, z: z if t is None else t.to(torch.float32).contiguous()  # noqa: E731
+    first_state = (f32(c_initial, zeros[0]), f32(n_initial, zeros[1]), f32(m_initial, zeros[2]))
+
+    if mode == "chain":
+        state_in = first_state if rank == 0 else _recv_state(zeros, prev_rank, group)
+        h, last = _segment_forward(q, k, v, i, f, state_in, chunk_size=L, eps=eps, variant=variant, impl=impl,
+                                   want_last=True)
+        if next_rank is not None:
+            _send_state(last, next_rank, group)
+    else:
+        summary = segment_summary(k, v, i, f, chunk_size=L, variant=variant, impl=impl)
+        state_in = first_state if rank == 0 else _recv_state(zeros, prev_rank, group)
+        last = state_combine(state_in, summary, variant=variant)
+        if next_rank is not None:
+            _send_state(last, next_rank, group)
+        h, _ = _segment_forward(q, k, v, i, f, state_in, chunk_size=L, eps=eps, variant=variant, impl=impl,
+                                want_last=False)
+    if not return_last_states:
+        return h
+    last = tuple(t.contiguous() for t in last)
+    for t in last:
+        dist.broadcast(t, src=ranks[world - 1], group=group)
+    if siging:
+        return h, (last[0], last[1])
+    return h, last

@@ -1,0 +1,79 @@
+"""torchrun worker of tests/test_sequence_parallel_gpu.py: sequence-parallel prefill over the local GPUs,
+compared on rank 0 with the single-GPU pass over the whole sequence.  Also usable by hand:
+
+    python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 tests/run_sequence_parallel.py
+"""
+
+import argparse
+import os
+import sys
+import time
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+import mlstm_kernels_b200 as mk  # noqa: E402
+from inputs import max_rel_err  # noqa: E402
+from mlstm_kernels_b200 import sharding  # noqa: E402
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--mode", default="scan")
+    ap.add_argument("--out", default="")
+    ap.add_argument("--S", type=int, default=16384)
+    ap.add_argument("--NH", type=int, default=8)
+    ap.add_argument("--DHQK", type=int, default=256)
+    ap.add_argument("--DHHV", type=int, default=512)
+    ap.add_argument("--chunk", type=int, default=256)
+    ap.add_argument("--reps", type=int, default=3)
+    args = ap.parse_args()
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dev = torch.device("cuda", local)
+    g = torch.Generator().manual_seed(0)  # every rank draws the same full sequence, keeps its own segment
+    shape = (1, args.NH, args.S)
+    q = torch.randn(*shape, args.DHQK, generator=g).bfloat16()
+    k = torch.randn(*shape, args.DHQK, generator=g).bfloat16()
+    v = torch.randn(*shape, args.DHHV, generator=g).bfloat16()
+    i = torch.randn(*shape, generator=g).bfloat16()
+    f = (3 + torch.randn(*shape, generator=g)).bfloat16()
+    seg = args.S // world
+    sl = slice(rank * seg, (rank + 1) * seg)
+    loc = [t[:, :, sl].contiguous().to(dev) for t in (q, k, v, i, f)]
+    ms = None
+    for rep in range(args.reps):
+        dist.barrier(); torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        h, last = sharding.mlstm_chunkwise_sequence_parallel(*loc, return_last_states=True, chunk_size=args.chunk,
+                                                             mode=args.mode)
+        torch.cuda.synchronize(); dist.barrier()
+        ms = (time.perf_counter() - t0) * 1e3
+    hs = [torch.empty_like(h) for _ in range(world)]
+    dist.all_gather(hs, h)
+    if rank == 0:
+        full = [t.to(dev) for t in (q, k, v, i, f)]
+        for rep in range(args.reps):
+            torch.cuda.synchronize(); t0 = time.perf_counter()
+            h1, last1 = mk.mlstm_chunkwise__b200_xl_chunk(*full, return_last_states=True, chunk_size=args.chunk)
+            torch.cuda.synchronize(); ms1 = (time.perf_counter() - t0) * 1e3
+        err = dict(err_h=max_rel_err(torch.cat(hs, 2).double().cpu().numpy(), h1.double().cpu().numpy()),
+                   err_c=max_rel_err(last[0].double().cpu().numpy(), last1[0].double().cpu().numpy()),
+                   err_n=max_rel_err(last[1].double().cpu().numpy(), last1[1].double().cpu().numpy()),
+                   err_m=max_rel_err(last[2].double().cpu().numpy(), last1[2].double().cpu().numpy()))
+        print(f"mode={args.mode} world={world} S={args.S}: sequence-parallel {ms:.3f} ms, single GPU {ms1:.3f} ms, "
+              + " ".join(f"{k_}={v_:.2e}" for k_, v_ in err.items()))
+        if args.out:
+            np.savez(os.path.join(args.out, "result.npz"), ms_sp=ms, ms_single=ms1, **err)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -176,3 +176,20 @@ def test_autocast_casts_inputs():
     with torch.autocast("cuda", dtype=torch.bfloat16):
         h = mk.mlstm_chunkwise__b200_xl_chunk(q, k, v, i, f, autocast_kernel_dtype=torch.bfloat16)
     assert h.dtype == torch.bfloat16
+
+
+@pytest.mark.parametrize("variant", ["exp", "sig"])
+def test_long_prefill_geometry_chunk256(variant):
+    """Head geometry of the long-sequence prefill configuration (NH=8, 256/512, chunk 256), shortened
+    sequence.  Chunk sizes above 128 run as chunks of 128 on the tcgen05 path, so the oracle is run at the
+    chunk size the kernel used; H is also compared with the oracle at chunk 256 (H does not depend on it)."""
+    inp = case_inputs(13, 1, 8, 1024, 256, 512)
+    siging = variant != "exp"
+    q, k, v = (to_dev(inp[n], torch.bfloat16) for n in "qkv")
+    Lk = mk.kernel_chunk_size(q, v, 256)
+    assert Lk == 128
+    got = run_cuda_fwbw(inp, 256, dtype=torch.bfloat16, siging=siging)
+    ref = run_oracle_fwbw(inp, Lk, dtype=torch.bfloat16, siging=siging)
+    compare(got, ref, TOL_BF16, TOL_BF16, keys_fw=FW_KEYS if not siging else ("H", "C_last", "n_last"))
+    ref256 = run_oracle_fwbw(inp, 256, dtype=torch.bfloat16, siging=siging)
+    assert max_rel_err(got["H"], ref256["H"]) < TOL_BF16

@@ -1,0 +1,115 @@
+"""Host-side logic of the multi-GPU modes, run as two gloo ranks on CPU.  The CUDA entry points are
+replaced by the numpy oracle here (the kernels themselves are covered by the GPU tests); what is tested
+is the partitioning, the point-to-point state hand-off along the chain and the combine arithmetic."""
+
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from inputs import make_chunkwise_inputs, max_rel_err
+from mlstm_kernels_b200 import sharding
+from oracle import mlstm_oracle as O
+
+
+def test_shard_range_partitions_units():
+    for total in (1, 7, 64, 128, 2048):
+        for world in (1, 2, 4, 8):
+            spans = [sharding.shard_range(total, world, r) for r in range(world)]
+            assert spans[0][0] == 0 and spans[-1][1] == total
+            assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+            sizes = [b - a for a, b in spans]
+            assert max(sizes) - min(sizes) <= 1
+    with pytest.raises(ValueError):
+        sharding.shard_range(8, 2, 2)
+
+
+def test_shard_batch_heads_slices_units():
+    q = torch.arange(2 * 4 * 3 * 5, dtype=torch.float32).reshape(2, 4, 3, 5)
+    i = torch.arange(2 * 4 * 3, dtype=torch.float32).reshape(2, 4, 3)
+    parts = [sharding.shard_batch_heads([q, i], 4, r) for r in range(4)]
+    assert torch.equal(torch.cat([p[0] for p in parts], 1).reshape(2, 4, 3, 5), q)
+    assert torch.equal(torch.cat([p[1] for p in parts], 1).reshape(2, 4, 3), i)
+
+
+# ---- oracle-backed stand-ins for the CUDA entry points --------------------------------------------
+def _np(t):
+    return None if t is None else t.detach().double().numpy()
+
+
+def fake_segment_summary(k, v, i, f, *, chunk_size, variant, impl="auto"):
+    B, NH, S, DHQK = k.shape
+    siging = variant != 0
+    fw = O.chunkwise_fw(np.zeros_like(_np(k)), _np(k), _np(v), _np(i), _np(f), None, None,
+                        None if siging else np.full((B, NH, 1), -np.inf), chunk_size=chunk_size, siging=siging)
+    g = O.logsigmoid(_np(f)).sum(-1)
+    t = lambda x: torch.from_numpy(np.ascontiguousarray(x)).float()  # noqa: E731
+    return t(fw["C_last"]), t(fw["n_last"]), t(fw["m_last"]), t(g)
+
+
+def fake_state_combine(state_in, summary, *, variant):
+    c_in, n_in, m_in = (x.double() for x in state_in)
+    c_loc, n_loc, m_loc, g = (x.double() for x in summary)
+    if variant == 0:
+        m_out = torch.maximum(g[..., None] + m_in, m_loc)
+        a, b = torch.exp(g[..., None] + m_in - m_out), torch.exp(m_loc - m_out)
+    else:
+        m_out = torch.zeros_like(m_loc)
+        a, b = torch.exp(g[..., None]), torch.ones_like(m_loc)
+    return ((a[..., None] * c_in + b[..., None] * c_loc).float(), (a * n_in + b * n_loc).float(), m_out.float())
+
+
+def fake_segment_forward(q, k, v, i, f, state_in, *, chunk_size, eps, variant, impl, want_last):
+    siging = variant != 0
+    fw = O.chunkwise_fw(_np(q), _np(k), _np(v), _np(i), _np(f), _np(state_in[0]), _np(state_in[1]),
+                        None if siging else _np(state_in[2]), chunk_size=chunk_size, eps=eps, siging=siging,
+                        normalize=variant != 2)
+    t = lambda x: torch.from_numpy(np.ascontiguousarray(x)).float()  # noqa: E731
+    return t(fw["H"]), (t(fw["C_last"]), t(fw["n_last"]), t(fw["m_last"]))
+
+
+CASE = dict(seed=17, B=1, NH=2, S=256, DHQK=16, DHHV=32, f_offset=1.0)
+
+
+def _worker(rank, world, port, mode, siging, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    sharding.segment_summary = fake_segment_summary
+    sharding.state_combine = fake_state_combine
+    sharding._segment_forward = fake_segment_forward
+    inp = make_chunkwise_inputs(CASE)
+    seg = CASE["S"] // world
+    sl = slice(rank * seg, (rank + 1) * seg)
+    q, k, v, i, f = (torch.from_numpy(inp[n][:, :, sl].copy()) for n in "qkvif")
+    h, last = sharding.mlstm_chunkwise_sequence_parallel(q, k, v, i, f, return_last_states=True, chunk_size=32,
+                                                         siging=siging, mode=mode)
+    np.savez(os.path.join(out_dir, f"r{rank}.npz"), h=h.numpy(), **{f"s{j}": t.numpy() for j, t in enumerate(last)})
+    dist.destroy_process_group()
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+@pytest.mark.parametrize("mode", ["scan", "chain"])
+@pytest.mark.parametrize("siging", [False, True])
+def test_sequence_parallel_two_ranks_gloo(tmp_path, mode, siging):
+    world = 2
+    mp.spawn(_worker, args=(world, _free_port(), mode, siging, str(tmp_path)), nprocs=world, join=True)
+    inp = make_chunkwise_inputs(CASE)
+    full = O.chunkwise_fw(inp["q"], inp["k"], inp["v"], inp["i"], inp["f"], chunk_size=32, siging=siging)
+    outs = [dict(np.load(tmp_path / f"r{r}.npz")) for r in range(world)]
+    h = np.concatenate([o["h"] for o in outs], axis=2)
+    assert max_rel_err(h, full["H"]) < 1e-5
+    for o in outs:  # the final state is broadcast to every rank
+        assert max_rel_err(o["s0"], full["C_last"]) < 1e-5
+        assert max_rel_err(o["s1"], full["n_last"]) < 1e-5
+        if not siging:
+            assert max_rel_err(o["s2"], full["m_last"]) < 1e-6
