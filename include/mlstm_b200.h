@@ -116,6 +116,33 @@ int mlstm_b200_chunkwise_fw(const void* q, const void* k, const void* v, const v
                             int dtype, int gate_dtype, int variant, int impl, float eps, void* stream);
 
 /*
+ * mlstm_b200_chunkwise_fw for callers that cannot allocate device memory.  No counterpart in the
+ * reference (its launchers allocate freely through torch).
+ *
+ * Meant for hosts where cudaMalloc is not an option once they run: runtimes that give all free GPU
+ * memory to their own pool at start-up (a later driver allocation then fails), or loops that forbid
+ * allocator calls for latency reasons.  Arguments and results are those of mlstm_b200_chunkwise_fw
+ * without `workspace`: the scratch lives in a fixed array of mlstm_b200_static_scratch_bytes() bytes
+ * (8 MiB) in device global memory that belongs to the library; every GPU that loads the library holds
+ * it until the process exits.  The call itself allocates nothing.
+ *   - Limit: the case must need no more scratch than that (roughly B*NH*S <= 500,000); larger cases
+ *     are rejected with MLSTM_ERR_WORKSPACE before anything is launched.
+ *   - The first call on each device looks up the array's device address (a short host-side set-up,
+ *     done with that device current); make that first call before any stream capture begins.
+ *   - All calls on a device share the one array, which keeps whatever the previous call left in it.
+ *     The forward overwrites every word it later reads, so nothing needs clearing; but two calls
+ *     whose kernels overlap on the GPU (different streams, or threads) race on it - serialise them.
+ */
+size_t mlstm_b200_static_scratch_bytes(void);
+int mlstm_b200_chunkwise_fw_static(const void* q, const void* k, const void* v, const void* i, const void* f,
+                                   const float* c_initial, const float* n_initial, const float* m_initial,
+                                   void* h, float* n_out, float* m_out,
+                                   void* c_states, float* n_states, float* m_states,
+                                   float* c_last, float* n_last, float* m_last,
+                                   int B, int NH, int S, int DHQK, int DHHV, int L,
+                                   int dtype, int gate_dtype, int variant, int impl, float eps, void* stream);
+
+/*
  * Chunkwise backward (the hand-derived one that ignores the gradient through the
  * denominator).  Replaces mlstm_chunkwise_bw
  * (mlstm_kernels/torch/chunkwise/triton_xl_chunk/bw.py:27-227: bw_recurrent.py:13-120,

@@ -38,6 +38,9 @@ SIGNATURES = {
     "mlstm_b200_chunkwise_workspace_bytes": (_sz, [_i] * 10),
     "mlstm_b200_chunkwise_fw": (_i, [_vp] * 5 + [_fp] * 3 + [_vp, _fp, _fp] + [_vp, _fp, _fp] + [_fp] * 3
                                 + [_vp, _sz] + [_i] * 6 + [_i, _i, _i, _i, _f, _vp]),
+    "mlstm_b200_static_scratch_bytes": (_sz, []),
+    "mlstm_b200_chunkwise_fw_static": (_i, [_vp] * 5 + [_fp] * 3 + [_vp, _fp, _fp] + [_vp, _fp, _fp] + [_fp] * 3
+                                       + [_i] * 6 + [_i, _i, _i, _i, _f, _vp]),
     "mlstm_b200_chunkwise_bw": (_i, [_vp] * 5 + [_fp, _vp, _fp, _vp, _fp] + [_vp] * 3 + [_fp] * 3
                                 + [_vp, _sz] + [_i] * 6 + [_i, _i, _i, _i, _f, _vp]),
     "mlstm_b200_chunkwise_summary": (_i, [_vp] * 4 + [_fp] * 4 + [_vp, _sz] + [_i] * 6 + [_i, _i, _i, _i, _vp]),
