@@ -321,6 +321,8 @@ def run_b200(args):
         ms_sig = timed_local(torch, sig_step, 5, 3)
         extra["fwbw_mLSTMsig"] = dict(ms=ms_sig, tflops=flops_fwbw / (ms_sig * 1e-3) / 1e12)
         extra["step_decode"] = bench_step(torch, mk, dev, peaks)
+        if args.triton_ref:
+            extra["reference_triton_same_gpu"] = bench_triton_reference(torch, devin, leaf, L, flops_fw, flops_fwbw)
     if world > 1:
         dist.barrier()
 
@@ -345,6 +347,59 @@ def run_b200(args):
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def bench_triton_reference(torch, devin, leaf, L, flops_fw, flops_fwbw):
+    """Optional leg (--triton-ref): the reference's own Triton kernels, JIT-compiled by the box's Triton, on the
+    same GPU, inputs and timing loop.  Needs the reference package to be importable (e.g. pip-installed with
+    --target baseline/_ref); reports the error text otherwise."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if os.path.isdir(ref_dir) and ref_dir not in sys.path:
+        sys.path.insert(0, ref_dir)
+    out = {}
+    try:
+        from mlstm_kernels.torch.chunkwise.triton_xl_chunk import mlstm_chunkwise__xl_chunk
+        from mlstm_kernels.torch.chunkwise.triton_xl_chunk_siging import mlstm_siging_chunkwise__xl_chunk
+    except Exception as e:  # noqa: BLE001
+        return {"unavailable": f"{type(e).__name__}: {e}"[:300]}
+
+    def make(fn, **kw):
+        def step():
+            for t in leaf.values():
+                t.grad = None
+            H = fn(leaf["q"], leaf["k"], leaf["v"], leaf["i"], leaf["f"], chunk_size=L, **kw)
+            H.backward(devin["dH"])
+        return step
+
+    def fw_only():
+        with torch.no_grad():
+            mlstm_chunkwise__xl_chunk(devin["q"], devin["k"], devin["v"], devin["i"], devin["f"], chunk_size=L)
+
+    for name, fn, fl in (("fwbw_mLSTMexp", make(mlstm_chunkwise__xl_chunk), flops_fwbw),
+                         ("fw_mLSTMexp", fw_only, flops_fw),
+                         ("fwbw_mLSTMsig", make(mlstm_siging_chunkwise__xl_chunk, normalize=True), flops_fwbw)):
+        try:
+            ms = timed_local(torch, fn, 5, 3)
+            out[name] = dict(ms=ms, tflops=fl / (ms * 1e-3) / 1e12)
+        except Exception as e:  # noqa: BLE001
+            out[name] = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
+    try:
+        from mlstm_kernels.torch.recurrent.triton_step import mlstm_recurrent_step__triton
+        NH, DHQK, DHHV = 8, 256, 512
+        dev = devin["q"].device
+        for B in (1, 8, 64, 256):
+            c = torch.randn(B, NH, DHQK, DHHV, device=dev) * 0.1
+            n = torch.randn(B, NH, DHQK, device=dev).abs()
+            m = torch.randn(B, NH, 1, device=dev)
+            q = torch.randn(B, NH, DHQK, device=dev).bfloat16(); k = torch.randn_like(q)
+            v = torch.randn(B, NH, DHHV, device=dev).bfloat16()
+            i = torch.randn(B, NH, 1, device=dev).bfloat16(); f = (3 + torch.randn(B, NH, 1, device=dev)).bfloat16()
+            fn = lambda: mlstm_recurrent_step__triton(q, k, v, i, f, c, n, m)  # noqa: E731
+            ms = timed_local(torch, fn, 200 if B <= 64 else 50, 10)
+            out[f"step_B{B}"] = dict(us_per_step=ms * 1e3)
+    except Exception as e:  # noqa: BLE001
+        out["step"] = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
+    return out
 
 
 def timed_local(torch, fn, steps, warmup):
@@ -407,6 +462,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary measurements")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--triton-ref", action="store_true",
+                    help="also time the reference's Triton kernels on this GPU (needs the reference importable)")
     ap.add_argument("--batch", type=int, default=None, help="override the batch size B of the workload (profiling)")
     ap.add_argument("--quick", action="store_true",
                     help="profiling mode: timed region only (no end-to-end leg, no per-kernel pass, no extras, no CPU leg)")
