@@ -6,7 +6,7 @@
 //                    (gated left)^T x right contraction on the tensor cores into a double-buffered TMEM
 //                    accumulator, decay + accumulate of the running state in registers, bf16 state store.
 //                    mlstm_kernels/triton/chunkwise/xl_chunk/fw_kernel_recurrent.py:14-230, bw_kernel_recurrent.py:15-181
-//   par_sm100<MODE>  intra-chunk kernel for H, deltaV, deltaK, deltaQ.  Per (batch, head, chunk, 128-wide output tile):
+//   par_body         intra-chunk kernel (par_fw_sm100, par_bw_sm100) for H, deltaV, deltaK, deltaQ.  Per (batch, head, chunk, 128-wide output tile):
 //                    score = A B^T (TMEM) -> gate matrix applied by the CUDA cores, bf16 result written back to
 //                    TMEM and used as the A operand of score x X; the inter-chunk term A x state is accumulated
 //                    into the same TMEM tile first and row-scaled in place.  The L x L gate matrix never
@@ -271,10 +271,11 @@ enum { PM_H = 0, PM_DV = 1, PM_DK = 2, PM_DQ = 3 };
 struct ParParams {
   const float *vecB, *iota, *m_tok, *abar, *bbar, *inv_den;  // per token, f32
   const float* n_states;                                     // H only
-  __nv_bfloat16* out;
-  float* n_out;    // H only
-  float* rowdot;   // DQ: sum_d q dq, DK: sum_d k dk; one partial per output tile: [DO/128][tokens]
-  int S, NC, DI, DO, DHQK, DHHV, variant;
+  __nv_bfloat16 *out_h, *out_dv, *out_dk, *out_dq;
+  float* n_out;               // H only
+  float *rowdot_q, *rowdot_k; // sum_d q dq (from DQ), sum_d k dk (from DK); one partial per output tile: [DHQK/128][tokens]
+  size_t ntok;                // B * NH * S
+  int S, NC, DHQK, DHHV, variant;
   float eps, qk_scale;
 };
 
@@ -282,87 +283,98 @@ constexpr int PAR_THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2..9 element-
 constexpr int PAR_STAGE = 49152;  // A slice 16 KB + B slice 16 KB + state slice 16 KB (or a 32 KB 128 x 128 tile)
 constexpr int PAR_SMEM = 2 * PAR_STAGE + 1024;
 
-template <int MODE>
-__global__ void __launch_bounds__(PAR_THREADS, 2)
-par_sm100(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
-          const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapSt,
-          const __grid_constant__ CUtensorMap mapE, ParParams p) {
-  constexpr bool LOWER = (MODE == PM_H || MODE == PM_DQ);
-  constexpr bool ST_MN = (MODE == PM_H || MODE == PM_DV);  // state operand N-contiguous in shared memory
-  constexpr bool HAS_E = (MODE == PM_DQ || MODE == PM_DK);  // extra tile for the gate-gradient row sums
+// Shared-memory control block of one intra-chunk CTA (the operand ring lives in dynamic shared memory).
+struct ParShared {
+  uint64_t bar_full[2], bar_empty[2], bar_sfull, bar_gated, bar_hfull, bar_dot, bar_pair[4];
+  uint32_t tmem;
+  float s_colA[CL], s_colF[CL];  // per-column terms of the gate matrix (see par_body)
+  float s_part[2][CL];           // per-row partial sums exchanged between the two warps of a row
+  float s_qn[2][CL];
+  float s_n[512];
+};
+
+// One body for the four modes; `mode` is uniform over the CTA, so every branch on it is uniform (a single copy of the
+// code keeps the instruction cache warm when CTAs of different modes share an SM).
+// Gate factor of element (r, c), written with separable exponent terms:
+//   lower (H, DQ), valid c <= r:  rowF_r * exp(rowA_r + colA_c),  rowA = b_r - m_r,     colA = iota_c - b_c, rowF = s [* 1/(den_r+eps)]
+//   upper (DV, DK), valid c >= r: rowF_r * colF_c * exp(...),     rowA = iota_r - b_r,  colA = b_c - m_c,    rowF = s, colF = 1/(den_c+eps)
+__device__ __forceinline__ void
+par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const CUtensorMap* mapX,
+         const CUtensorMap* mapSt, const CUtensorMap* mapE, const ParParams& p, ParShared& sh, const int o_tile,
+         const int ck, const int bh) {
+  const bool LOWER = (mode == PM_H || mode == PM_DQ);
+  const bool ST_MN = (mode == PM_H || mode == PM_DV);  // state operand N-contiguous in shared memory
+  const bool HAS_E = (mode == PM_DQ || mode == PM_DK);  // extra tile for the gate-gradient row sums
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  __shared__ uint64_t bar_full[2], bar_empty[2], bar_sfull, bar_gated, bar_hfull, bar_dot, bar_pair[4];
-  __shared__ uint32_t s_tmem;
-  __shared__ float s_b[CL], s_iota[CL], s_m[CL], s_inv[CL];
-  __shared__ float s_part[2][CL];   // per-row partial sums exchanged between the two warps of a row
-  __shared__ float s_qn[2][CL];
-  __shared__ float s_n[512];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int o0 = blockIdx.x * 128, ck = blockIdx.y, bh = blockIdx.z;
-  const int NC = p.NC, ND = p.DI / 64;
+  const int o0 = o_tile * 128;
+  const int DI = (mode == PM_H || mode == PM_DV) ? p.DHQK : p.DHHV;   // contraction dim of the score product
+  const int DO = (mode == PM_H || mode == PM_DV) ? p.DHHV : p.DHQK;   // output width
+  const int NC = p.NC, ND = DI / 64;
   const int row0 = bh * p.S + ck * CL;
-  const bool use_n = (MODE == PM_H) && p.variant != MLSTM_SIG_NONORM && p.n_states != nullptr;
+  const bool use_n = (mode == PM_H) && p.variant != MLSTM_SIG_NONORM && p.n_states != nullptr;
 
   if (tid == 0) {
-    for (int s = 0; s < 2; ++s) { mbar_init(&bar_full[s], 1); mbar_init(&bar_empty[s], use_n ? 9 : 1); }
-    mbar_init(&bar_sfull, 1); mbar_init(&bar_gated, 256); mbar_init(&bar_hfull, 1); mbar_init(&bar_dot, 256);
-    for (int s = 0; s < 4; ++s) mbar_init(&bar_pair[s], 64);
+    for (int s = 0; s < 2; ++s) { mbar_init(&sh.bar_full[s], 1); mbar_init(&sh.bar_empty[s], use_n ? 9 : 1); }
+    mbar_init(&sh.bar_sfull, 1); mbar_init(&sh.bar_gated, 256); mbar_init(&sh.bar_hfull, 1); mbar_init(&sh.bar_dot, 256);
+    for (int s = 0; s < 4; ++s) mbar_init(&sh.bar_pair[s], 64);
     fence_barrier_init();
-    tma_prefetch_desc(&mapA); tma_prefetch_desc(&mapB); tma_prefetch_desc(&mapX); tma_prefetch_desc(&mapSt);
+    tma_prefetch_desc(mapA); tma_prefetch_desc(mapB); tma_prefetch_desc(mapX); tma_prefetch_desc(mapSt);
+    if (HAS_E) tma_prefetch_desc(mapE);
   }
-  if (warp == 1) { tmem_alloc(&s_tmem, 256); tmem_relinquish(); }
+  if (warp == 1) { tmem_alloc(&sh.tmem, 256); tmem_relinquish(); }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  const uint32_t tmem = s_tmem;
+  const uint32_t tmem = sh.tmem;
   const uint32_t tS = tmem, tAcc = tmem + 128;
   const int n_loads = ND + 1 + (HAS_E ? 1 : 0);
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
-      const int slot = (MODE == PM_H || MODE == PM_DQ) ? ck : ck + 1;
+      const int slot = LOWER ? ck : ck + 1;
       const int srow = (bh * (NC + 1) + slot) * p.DHQK;
       int issued = 0;
       for (int it = 0; it < n_loads; ++it) {
         const int st = it & 1;
-        if (!mbar_wait(&bar_empty[st], ((it >> 1) & 1) ^ 1, &g_sm100_status, 201)) break;
+        if (!mbar_wait(&sh.bar_empty[st], ((it >> 1) & 1) ^ 1, &g_sm100_status, 201)) break;
         uint8_t* sb = smem + st * PAR_STAGE;
         if (it < ND) {
-          mbar_expect_tx(&bar_full[st], PAR_STAGE);
-          tma_load_2d(sb, &mapA, &bar_full[st], 64 * it, row0);
-          tma_load_2d(sb + 16384, &mapB, &bar_full[st], 64 * it, row0);
+          mbar_expect_tx(&sh.bar_full[st], PAR_STAGE);
+          tma_load_2d(sb, mapA, &sh.bar_full[st], 64 * it, row0);
+          tma_load_2d(sb + 16384, mapB, &sh.bar_full[st], 64 * it, row0);
           if (ST_MN) {
-            tma_load_2d(sb + 32768, &mapSt, &bar_full[st], o0, srow + 64 * it);
-            tma_load_2d(sb + 32768 + 8192, &mapSt, &bar_full[st], o0 + 64, srow + 64 * it);
+            tma_load_2d(sb + 32768, mapSt, &sh.bar_full[st], o0, srow + 64 * it);
+            tma_load_2d(sb + 32768 + 8192, mapSt, &sh.bar_full[st], o0 + 64, srow + 64 * it);
           } else {
-            tma_load_2d(sb + 32768, &mapSt, &bar_full[st], 64 * it, srow + o0);
+            tma_load_2d(sb + 32768, mapSt, &sh.bar_full[st], 64 * it, srow + o0);
           }
         } else {
-          const CUtensorMap* m = (it == ND) ? &mapX : &mapE;
-          mbar_expect_tx(&bar_full[st], 32768);
-          tma_load_2d(sb, m, &bar_full[st], o0, row0);
-          tma_load_2d(sb + 16384, m, &bar_full[st], o0 + 64, row0);
+          const CUtensorMap* m = (it == ND) ? mapX : mapE;
+          mbar_expect_tx(&sh.bar_full[st], 32768);
+          tma_load_2d(sb, m, &sh.bar_full[st], o0, row0);
+          tma_load_2d(sb + 16384, m, &sh.bar_full[st], o0 + 64, row0);
         }
         issued = it + 1;
       }
       if (issued < n_loads && issued > 0) {  // error path: let the copies in flight land before the CTA retires
         int dummy = 1;
-        for (int it = max(0, issued - 2); it < issued; ++it) mbar_wait(&bar_full[it & 1], (it >> 1) & 1, &dummy, 1);
+        for (int it = max(0, issued - 2); it < issued; ++it) mbar_wait(&sh.bar_full[it & 1], (it >> 1) & 1, &dummy, 1);
       }
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);
-      constexpr uint32_t idesc_st = umma_idesc_bf16(128, 128, 0, ST_MN ? 1 : 0);
+      const uint32_t idesc_st = ST_MN ? umma_idesc_bf16(128, 128, 0, 1) : umma_idesc_bf16(128, 128, 0, 0);
       constexpr uint32_t idesc_x = umma_idesc_bf16(128, 128, 0, 1);
       bool ok = true;
       for (int it = 0; it < ND; ++it) {
         const int st = it & 1;
-        if (!mbar_wait(&bar_full[st], (it >> 1) & 1, &g_sm100_status, 202)) { ok = false; break; }
+        if (!mbar_wait(&sh.bar_full[st], (it >> 1) & 1, &g_sm100_status, 202)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t sa = smem_u32(smem + st * PAR_STAGE), sb = sa + 16384, ss = sa + 32768;
 #pragma unroll
@@ -374,20 +386,20 @@ par_sm100(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
           const uint64_t bdesc = ST_MN ? umma_desc_sw128(ss + kk * 2048, 8192, 1024) : umma_desc_sw128(ss + kk * 32, 16, 1024);
           umma_ss(tAcc, umma_desc_sw128(sa + kk * 32, 16, 1024), bdesc, idesc_st, (it > 0 || kk > 0) ? 1u : 0u);
         }
-        umma_commit(&bar_empty[st]);
+        umma_commit(&sh.bar_empty[st]);
       }
       if (ok) {
-        umma_commit(&bar_sfull);
+        umma_commit(&sh.bar_sfull);
         const int stx = ND & 1;
-        ok = mbar_wait(&bar_full[stx], (ND >> 1) & 1, &g_sm100_status, 203) &&
-             mbar_wait(&bar_gated, 0, &g_sm100_status, 204);
+        ok = mbar_wait(&sh.bar_full[stx], (ND >> 1) & 1, &g_sm100_status, 203) &&
+             mbar_wait(&sh.bar_gated, 0, &g_sm100_status, 204);
         if (ok) {
           tc_fence_after_sync();
           const uint32_t sx = smem_u32(smem + stx * PAR_STAGE);
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk)
             umma_ts(tAcc, tS + kk * 8, umma_desc_sw128(sx + kk * 2048, 16384, 1024), idesc_x, 1u);
-          umma_commit(&bar_hfull);
+          umma_commit(&sh.bar_hfull);
         }
       }
     }
@@ -397,15 +409,20 @@ par_sm100(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
     const int r = quarter * 32 + lane;
     const size_t tok = (size_t)row0 + r;
     const float b_r = p.vecB[tok], iota_r = p.iota[tok], m_r = p.m_tok[tok];
-    const float inv_r = (MODE == PM_H) ? 1.f : p.inv_den[tok];
-    if (half == 0) { s_b[r] = b_r; s_iota[r] = iota_r; s_m[r] = m_r; s_inv[r] = inv_r; }
+    const float inv_r = (mode == PM_H) ? 1.f : p.inv_den[tok];
+    const float rowA = LOWER ? (b_r - m_r) : (iota_r - b_r);
+    const float rowF = (mode == PM_DQ) ? p.qk_scale * inv_r : p.qk_scale;
+    if (half == 0) {
+      sh.s_colA[r] = LOWER ? (iota_r - b_r) : (b_r - m_r);
+      sh.s_colF[r] = LOWER ? 1.f : inv_r;
+    }
     float rowscale;
-    if (MODE == PM_H) rowscale = p.qk_scale * p.bbar[tok];
-    else if (MODE == PM_DQ) rowscale = p.qk_scale * p.bbar[tok] * inv_r;
+    if (mode == PM_H) rowscale = p.qk_scale * p.bbar[tok];
+    else if (mode == PM_DQ) rowscale = p.qk_scale * p.bbar[tok] * inv_r;
     else rowscale = p.abar[tok];
     if (use_n) {
       const float* nsrc = p.n_states + ((size_t)bh * (NC + 1) + ck) * p.DHQK;
-      for (int dd = tid - 64; dd < p.DHQK; dd += 256) s_n[dd] = nsrc[dd];
+      for (int dd = tid - 64; dd < p.DHQK; dd += 256) sh.s_n[dd] = nsrc[dd];
     }
     asm volatile("bar.sync 1, 256;" ::: "memory");  // gate vectors and n visible to the element-wise warps
 
@@ -416,14 +433,14 @@ par_sm100(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
     if (use_n) {
       for (int it = 0; it < ND && ok; ++it) {
         const int st = it & 1;
-        if (!mbar_wait(&bar_full[st], (it >> 1) & 1, &g_sm100_status, 207)) { ok = false; break; }
+        if (!mbar_wait(&sh.bar_full[st], (it >> 1) & 1, &g_sm100_status, 207)) { ok = false; break; }
         const uint8_t* rowp = smem + st * PAR_STAGE + r * 128;
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc) {
           const int lc = half * 4 + cc;                      // logical 16-byte chunk of the 64-column slice
           const uint4 v = *reinterpret_cast<const uint4*>(rowp + ((lc ^ (r & 7)) << 4));
           const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-          const float* nn = s_n + it * 64 + lc * 8;
+          const float* nn = sh.s_n + it * 64 + lc * 8;
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const __nv_bfloat162 h2 = *reinterpret_cast<const __nv_bfloat162*>(&w[e]);
@@ -432,14 +449,14 @@ par_sm100(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
           }
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(&bar_empty[st]);
+        if (lane == 0) mbar_arrive(&sh.bar_empty[st]);
       }
-      s_qn[half][r] = qn;
+      sh.s_qn[half][r] = qn;
     }
 
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     float rowsum = 0.f;
-    ok = ok && mbar_wait(&bar_sfull, 0, &g_sm100_status, 205);
+    ok = ok && mbar_wait(&sh.bar_sfull, 0, &g_sm100_status, 205);
     if (ok) {
       tc_fence_after_sync();
       // row-scale the inter-chunk term in place
@@ -455,7 +472,6 @@ par_sm100(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
       // gate the score tile; the bf16 result goes back to tensor memory as the A operand of the second product.
       // Both warps of a quarter first read their chunks, then (after a warp-pair sync) write: the bf16 words of
       // chunk cq land on columns [16 cq, 16 cq + 16), which the partner warp may still have to read.
-      const float f_r = (MODE == PM_DQ) ? p.qk_scale * inv_r : p.qk_scale;
       uint32_t pk[2][16];
 #pragma unroll
       for (int u = 0; u < 2; ++u) {
@@ -469,18 +485,15 @@ par_sm100(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
           uint32_t v[32];
           tmem_ld32(tS + lane_base + c0, v);
           tmem_wait_ld();
+          const bool diag = (cq == quarter);   // only the diagonal chunk needs the causal mask
 #pragma unroll
           for (int c = 0; c < 16; ++c) {
             float g2[2];
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-              const int col = c0 + 2 * c + h;
-              float val = 0.f;
-              if (LOWER) {
-                if (col <= r) val = __uint_as_float(v[2 * c + h]) * f_r * __expf((b_r - s_b[col]) + s_iota[col] - m_r);
-              } else {
-                if (col >= r) val = __uint_as_float(v[2 * c + h]) * (p.qk_scale * s_inv[col]) * __expf((s_b[col] - b_r) + iota_r - s_m[col]);
-              }
+              const int cl = 2 * c + h;        // column inside the chunk; row inside the chunk is `lane`
+              float val = __uint_as_float(v[cl]) * rowF * sh.s_colF[c0 + cl] * __expf(rowA + sh.s_colA[c0 + cl]);
+              if (diag && (LOWER ? (cl > lane) : (cl < lane))) val = 0.f;
               g2[h] = val;
               rowsum += val;
             }
@@ -490,38 +503,39 @@ par_sm100(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
       }
       // pair sync (bounded): both warps of the quarter have finished reading the score tile
       tc_fence_before_sync();
-      mbar_arrive(&bar_pair[quarter]);
-      ok = mbar_wait(&bar_pair[quarter], 0, &g_sm100_status, 210);
+      mbar_arrive(&sh.bar_pair[quarter]);
+      ok = mbar_wait(&sh.bar_pair[quarter], 0, &g_sm100_status, 210);
       if (ok) {
         tc_fence_after_sync();
 #pragma unroll
         for (int u = 0; u < 2; ++u) tmem_st16(tS + lane_base + (half + 2 * u) * 16, pk[u]);
-        s_part[half][r] = rowsum;
+        sh.s_part[half][r] = rowsum;
         tmem_wait_st();
         tc_fence_before_sync();
-        mbar_arrive(&bar_gated);
-        ok = mbar_wait(&bar_hfull, 0, &g_sm100_status, 206);
+        mbar_arrive(&sh.bar_gated);
+        ok = mbar_wait(&sh.bar_hfull, 0, &g_sm100_status, 206);
       }
     }
     if (ok) {
       tc_fence_after_sync();
       float inv = 1.f;
-      if (MODE == PM_H) {
+      if (mode == PM_H) {
         float den = 1.f;
-        const float nn = (s_part[0][r] + s_part[1][r]) + rowscale * (use_n ? (s_qn[0][r] + s_qn[1][r]) : 0.f);
+        const float nn = (sh.s_part[0][r] + sh.s_part[1][r]) + rowscale * (use_n ? (sh.s_qn[0][r] + sh.s_qn[1][r]) : 0.f);
         if (p.variant == MLSTM_EXP) den = fmaxf(fabsf(nn), __expf(-m_r));
         else if (p.variant == MLSTM_SIG) den = fmaxf(fabsf(nn), 1.f);
         if (p.variant != MLSTM_SIG_NONORM) inv = 1.f / (den + p.eps);
-        if (blockIdx.x == 0 && half == 0) p.n_out[tok] = den;
+        if (o_tile == 0 && half == 0) p.n_out[tok] = den;
       }
-      const uint8_t* erow = nullptr;
+      const uint8_t* erow = smem;
       if (HAS_E) {
         const int ste = (ND + 1) & 1;
-        ok = mbar_wait(&bar_full[ste], ((ND + 1) >> 1) & 1, &g_sm100_status, 208);
+        ok = mbar_wait(&sh.bar_full[ste], ((ND + 1) >> 1) & 1, &g_sm100_status, 208);
         erow = smem + ste * PAR_STAGE + r * 128;
       }
       float dot = 0.f;
-      __nv_bfloat16* orow = p.out + tok * p.DO + o0;
+      __nv_bfloat16* outp = (mode == PM_H) ? p.out_h : (mode == PM_DV) ? p.out_dv : (mode == PM_DK) ? p.out_dk : p.out_dq;
+      __nv_bfloat16* orow = outp + tok * DO + o0;
       if (ok) {
 #pragma unroll 1
         for (int cq = half; cq < 4; cq += 2) {
@@ -552,10 +566,10 @@ par_sm100(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
           }
         }
         if (HAS_E) {
-          s_qn[half][r] = dot;
-          mbar_arrive(&bar_dot);
-          if (half == 0 && mbar_wait(&bar_dot, 0, &g_sm100_status, 209))
-            p.rowdot[(size_t)blockIdx.x * ((size_t)gridDim.z * p.S) + tok] = s_qn[0][r] + s_qn[1][r];
+          sh.s_qn[half][r] = dot;
+          mbar_arrive(&sh.bar_dot);
+          if (half == 0 && mbar_wait(&sh.bar_dot, 0, &g_sm100_status, 209))
+            ((mode == PM_DQ) ? p.rowdot_q : p.rowdot_k)[(size_t)o_tile * p.ntok + tok] = sh.s_qn[0][r] + sh.s_qn[1][r];
         }
       }
     }
@@ -563,6 +577,33 @@ par_sm100(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem, 256);
+}
+
+__global__ void __launch_bounds__(PAR_THREADS, 2)
+par_fw_sm100(const __grid_constant__ CUtensorMap mQ, const __grid_constant__ CUtensorMap mK,
+             const __grid_constant__ CUtensorMap mV, const __grid_constant__ CUtensorMap mC,
+             const __grid_constant__ ParParams p) {
+  __shared__ ParShared sh;
+  par_body(PM_H, &mQ, &mK, &mV, &mC, &mV, p, sh, blockIdx.x, blockIdx.y, blockIdx.z);
+}
+
+// deltaV, deltaK and deltaQ of one chunk in ONE launch: blockIdx.x enumerates the 128-wide output tiles of the three
+// results, so the CTAs that read the same q, k, v, deltaH and state tiles of a chunk are scheduled next to each other
+// and share them through L2 instead of re-reading them from HBM in three separate launches.
+__global__ void __launch_bounds__(PAR_THREADS, 2)
+par_bw_sm100(const __grid_constant__ CUtensorMap mQ, const __grid_constant__ CUtensorMap mK,
+             const __grid_constant__ CUtensorMap mV, const __grid_constant__ CUtensorMap mDH,
+             const __grid_constant__ CUtensorMap mC_k, const __grid_constant__ CUtensorMap mdC_mn,
+             const __grid_constant__ CUtensorMap mdC_k, const __grid_constant__ ParParams p) {
+  __shared__ ParShared sh;
+  const int t_dv = p.DHHV / 128, t_dk = p.DHQK / 128;
+  const int x = blockIdx.x;
+  int mode, tile;
+  const CUtensorMap *a, *b, *xm, *stm, *e;
+  if (x < t_dv) { mode = PM_DV; tile = x; a = &mK; b = &mQ; xm = &mDH; stm = &mdC_mn; e = &mDH; }
+  else if (x < t_dv + t_dk) { mode = PM_DK; tile = x - t_dv; a = &mV; b = &mDH; xm = &mQ; stm = &mdC_k; e = &mK; }
+  else { mode = PM_DQ; tile = x - t_dv - t_dk; a = &mDH; b = &mV; xm = &mK; stm = &mC_k; e = &mQ; }
+  par_body(mode, a, b, xm, stm, e, p, sh, tile, blockIdx.y, blockIdx.z);
 }
 
 // =====================================================================================================
@@ -609,21 +650,11 @@ int sm100_recurrent_bw(const void* q, const void* dh, const GateBuffers& gb, con
   return launch_rec<true>(q, dh, rp, d, st);
 }
 
-template <int MODE>
-static int launch_par(const CUtensorMap& mA, const CUtensorMap& mB, const CUtensorMap& mX, const CUtensorMap& mSt,
-                      const CUtensorMap& mE, const ParParams& pp, const ChunkwiseDims& d, cudaStream_t st) {
-  auto kern = par_sm100<MODE>;
-  MLSTM_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PAR_SMEM));
-  dim3 grid(pp.DO / 128, d.NC, d.B * d.NH);
-  kern<<<grid, PAR_THREADS, PAR_SMEM, st>>>(mA, mB, mX, mSt, mE, pp);
-  MLSTM_LAUNCH_CHECK();
-  return MLSTM_OK;
-}
-
 static ParParams base_params(const GateBuffers& gb, const ChunkwiseDims& d) {
   ParParams pp{};
   pp.vecB = gb.vecB; pp.iota = gb.iota; pp.m_tok = gb.m_tok; pp.abar = gb.abar; pp.bbar = gb.bbar;
   pp.inv_den = gb.inv_den;
+  pp.ntok = (size_t)d.B * d.NH * d.S;
   pp.S = d.S; pp.NC = d.NC; pp.DHQK = d.DHQK; pp.DHHV = d.DHHV; pp.variant = d.variant; pp.eps = d.eps;
   pp.qk_scale = d.qk_scale;
   return pp;
@@ -637,9 +668,12 @@ int sm100_parallel_fw(const void* q, const void* k, const void* v, const GateBuf
       !state_map(&mC, c_states, d, 64))
     return MLSTM_ERR_CUDA;
   ParParams pp = base_params(gb, d);
-  pp.n_states = n_states; pp.out = (__nv_bfloat16*)h; pp.n_out = n_out;
-  pp.DI = d.DHQK; pp.DO = d.DHHV;
-  return launch_par<PM_H>(mQ, mK, mV, mC, mV, pp, d, st);
+  pp.n_states = n_states; pp.out_h = (__nv_bfloat16*)h; pp.n_out = n_out;
+  MLSTM_CUDA_CHECK(cudaFuncSetAttribute(par_fw_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, PAR_SMEM));
+  dim3 grid(d.DHHV / 128, d.NC, d.B * d.NH);
+  par_fw_sm100<<<grid, PAR_THREADS, PAR_SMEM, st>>>(mQ, mK, mV, mC, pp);
+  MLSTM_LAUNCH_CHECK();
+  return MLSTM_OK;
 }
 
 int sm100_parallel_bw(const void* q, const void* k, const void* v, const void* dh, const GateBuffers& gb,
@@ -651,14 +685,13 @@ int sm100_parallel_bw(const void* q, const void* k, const void* v, const void* d
       !tok_map(&mDH, dh, d, d.DHHV) || !state_map(&mC_k, c_states, d, 128) || !state_map(&mdC_mn, dc_states, d, 64) ||
       !state_map(&mdC_k, dc_states, d, 128))
     return MLSTM_ERR_CUDA;
-  int rc;
   ParParams pp = base_params(gb, d);
-  pp.DI = d.DHQK; pp.DO = d.DHHV; pp.out = (__nv_bfloat16*)dv;
-  if ((rc = launch_par<PM_DV>(mK, mQ, mDH, mdC_mn, mDH, pp, d, st)) != MLSTM_OK) return rc;
-  pp.DI = d.DHHV; pp.DO = d.DHQK; pp.out = (__nv_bfloat16*)dk; pp.rowdot = kdk_parts;
-  if ((rc = launch_par<PM_DK>(mV, mDH, mQ, mdC_k, mK, pp, d, st)) != MLSTM_OK) return rc;
-  pp.out = (__nv_bfloat16*)dq; pp.rowdot = qdq_parts;
-  if ((rc = launch_par<PM_DQ>(mDH, mV, mK, mC_k, mQ, pp, d, st)) != MLSTM_OK) return rc;
+  pp.out_dv = (__nv_bfloat16*)dv; pp.out_dk = (__nv_bfloat16*)dk; pp.out_dq = (__nv_bfloat16*)dq;
+  pp.rowdot_q = qdq_parts; pp.rowdot_k = kdk_parts;
+  MLSTM_CUDA_CHECK(cudaFuncSetAttribute(par_bw_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, PAR_SMEM));
+  dim3 grid(d.DHHV / 128 + 2 * (d.DHQK / 128), d.NC, d.B * d.NH);
+  par_bw_sm100<<<grid, PAR_THREADS, PAR_SMEM, st>>>(mQ, mK, mV, mDH, mC_k, mdC_mn, mdC_k, pp);
+  MLSTM_LAUNCH_CHECK();
   return MLSTM_OK;
 }
 
