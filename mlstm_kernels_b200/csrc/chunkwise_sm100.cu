@@ -43,20 +43,23 @@ struct RecParams {
   int S, NC, DHQK, DHHV;
 };
 
-constexpr int REC_THREADS = 320;                 // warp 0 TMA, warp 1 MMA, warps 2..9 element-wise
+constexpr int REC_THREADS = 576;                 // warp 0 TMA, warp 1 MMA, warps 2..9 gate the left tile, warps 10..17 own the state
 constexpr int REC_STAGE_BYTES = 65536;           // left tile 32 KB + right tile 32 KB
-constexpr int REC_NPART_BYTES = 2 * 32 * 128 * 4;   // per-stage partial column sums of the gated left tile
-constexpr int REC_SMEM = 2 * REC_STAGE_BYTES + REC_NPART_BYTES + 1024;
+constexpr int REC_NPART_BYTES = 2 * 32 * 128 * 4;   // double-buffered partial column sums of the gated left tile
+constexpr int REC_STAGES = 2;                    // operand ring depth
+constexpr int REC_OUT_BYTES = 2 * 32768;         // double-buffered bf16 state tile staged for the TMA store
+constexpr int REC_SMEM = REC_STAGES * REC_STAGE_BYTES + REC_NPART_BYTES + REC_OUT_BYTES + 1024;
 
 template <bool BWD>
 __global__ void __launch_bounds__(REC_THREADS, 1)
-rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUtensorMap mapR, RecParams p) {
+rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUtensorMap mapR,
+          const __grid_constant__ CUtensorMap mapS, RecParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  __shared__ uint64_t bar_full[2], bar_empty[2], bar_scaled[2], bar_acc_full[2], bar_acc_free[2], bar_nsum[2];
+  __shared__ uint64_t bar_full[REC_STAGES], bar_empty[REC_STAGES], bar_scaled[REC_STAGES], bar_acc_full[2], bar_acc_free[2], bar_nsum[2], bar_out_full[2], bar_out_free[2];
   __shared__ uint32_t s_tmem;
-  __shared__ float s_scale[2][CL];  // per-row scale of the left tile, staged by the producer warp
-  __shared__ float s_g[4];          // decay of the chunk, ring of four
+  __shared__ float s_scale[REC_STAGES][CL];  // per-row scale of the left tile, staged by the producer warp
+  __shared__ float s_g[8];          // decay of the chunk, ring of eight (outlives the operand ring)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int e0 = blockIdx.x * 128, d0 = blockIdx.y * 128, bh = blockIdx.z;
@@ -64,12 +67,15 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
   const bool do_n = (!BWD) && blockIdx.x == 0 && (p.n_states != nullptr || p.n_final != nullptr);
 
   if (tid == 0) {
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < REC_STAGES; ++s) {
       mbar_init(&bar_full[s], 1); mbar_init(&bar_empty[s], 1); mbar_init(&bar_scaled[s], 256);
+    }
+    for (int s = 0; s < 2; ++s) {
       mbar_init(&bar_acc_full[s], 1); mbar_init(&bar_acc_free[s], 256); mbar_init(&bar_nsum[s], 256);
+      mbar_init(&bar_out_full[s], 256); mbar_init(&bar_out_free[s], 1);
     }
     fence_barrier_init();
-    tma_prefetch_desc(&mapL); tma_prefetch_desc(&mapR);
+    tma_prefetch_desc(&mapL); tma_prefetch_desc(&mapR); tma_prefetch_desc(&mapS);
   }
   if (warp == 1) { tmem_alloc(&s_tmem, 256); tmem_relinquish(); }
   tc_fence_before_sync();
@@ -79,23 +85,37 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
 
   if (warp == 0) {
     // ---------------- TMA producer (whole warp: also stages the per-row scales and the chunk decay) ----------------
+    // The scales of chunk s+1 are fetched from global memory before the wait for the stage of chunk s, so their
+    // latency never sits between a stage becoming free and the next TMA issue.
+    auto fetch = [&](int s, float (&sc)[4], float& g) {
+      const int ck = BWD ? NC - 1 - s : s;
+      const size_t row0 = (size_t)bh * p.S + (size_t)ck * CL;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int r = lane + 32 * u;
+        sc[u] = p.lscale[row0 + r] * p.lmul;
+        if (BWD) sc[u] *= p.rscale[row0 + r];
+      }
+      g = p.gbar[(size_t)bh * NC + ck];
+    };
     int issued = 0;
+    float sc_next[4], g_next = 0.f;
+    if (NC > 0) fetch(0, sc_next, g_next);
     for (int s = 0; s < NC; ++s) {
-      const int st = s & 1;
+      const int st = s % REC_STAGES;
+      float sc[4], g = g_next;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) sc[u] = sc_next[u];
+      if (s + 1 < NC) fetch(s + 1, sc_next, g_next);
       int ok = 1;
-      if (lane == 0) ok = mbar_wait(&bar_empty[st], ((s >> 1) & 1) ^ 1, &g_sm100_status, 101) ? 1 : 0;
+      if (lane == 0) ok = mbar_wait(&bar_empty[st], ((s / REC_STAGES) & 1) ^ 1, &g_sm100_status, 101) ? 1 : 0;
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
       const int ck = BWD ? NC - 1 - s : s;
       const int row0 = bh * p.S + ck * CL;
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int r = lane + 32 * u;
-        float sc = p.lscale[(size_t)row0 + r] * p.lmul;
-        if (BWD) sc *= p.rscale[(size_t)row0 + r];
-        s_scale[st][r] = sc;
-      }
-      if (lane == 0) s_g[s & 3] = p.gbar[(size_t)bh * NC + ck];
+      for (int u = 0; u < 4; ++u) s_scale[st][lane + 32 * u] = sc[u];
+      if (lane == 0) s_g[s & 7] = g;
       __syncwarp();
       if (lane == 0) {
         uint8_t* sl = smem + st * REC_STAGE_BYTES;
@@ -109,15 +129,16 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
     }
     if (lane == 0 && issued < NC && issued > 0) {  // error path: let the copies in flight land before the CTA retires
       int dummy = 1;
-      for (int s = max(0, issued - 2); s < issued; ++s) mbar_wait(&bar_full[s & 1], (s >> 1) & 1, &dummy, 1);
+      for (int s = max(0, issued - REC_STAGES); s < issued; ++s)
+        mbar_wait(&bar_full[s % REC_STAGES], (s / REC_STAGES) & 1, &dummy, 1);
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc_bf16(128, 128, 1, 1);
       for (int s = 0; s < NC; ++s) {
-        const int st = s & 1, buf = s & 1;
-        if (!mbar_wait(&bar_scaled[st], (s >> 1) & 1, &g_sm100_status, 102)) break;
+        const int st = s % REC_STAGES, buf = s & 1;
+        if (!mbar_wait(&bar_scaled[st], (s / REC_STAGES) & 1, &g_sm100_status, 102)) break;
         if (!mbar_wait(&bar_acc_free[buf], ((s >> 1) & 1) ^ 1, &g_sm100_status, 103)) break;
         tc_fence_after_sync();
         const uint32_t sl = smem_u32(smem + st * REC_STAGE_BYTES), sr = sl + 32768;
@@ -129,63 +150,17 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
         umma_commit(&bar_acc_full[buf]);
       }
     }
-  } else {
-    // ---------------- element-wise warps: gate the left tile, fold the accumulator into the running state ----
+  } else if (warp < 10) {
+    // ---------------- gating warps: scale the rows of the left tile in place; column sums give n ----------------
     const int ct = tid - 64;                       // 0..255
-    const int quarter = warp & 3, half = (warp - 2) >> 2;
-    const int row = quarter * 32 + lane;           // state row (d) owned for the accumulator
-    const int d = d0 + row, ecol = e0 + half * 64;
-    float C[64];
-    if (p.c_init) {
-      const float4* src = reinterpret_cast<const float4*>(p.c_init + ((size_t)bh * p.DHQK + d) * p.DHHV + ecol);
-#pragma unroll
-      for (int c = 0; c < 16; ++c) { float4 v = src[c]; C[4 * c] = v.x; C[4 * c + 1] = v.y; C[4 * c + 2] = v.z; C[4 * c + 3] = v.w; }
-    } else {
-#pragma unroll
-      for (int c = 0; c < 64; ++c) C[c] = 0.f;
-    }
     float nval = 0.f;
     if (do_n && ct < 128 && p.n_init) nval = p.n_init[(size_t)bh * p.DHQK + d0 + ct];
-
-    auto store_c = [&](int slot) {
-      if (p.c_states == nullptr) return;
-      uint4* dst = reinterpret_cast<uint4*>(p.c_states + (((size_t)bh * (NC + 1) + slot) * p.DHQK + d) * p.DHHV + ecol);
-#pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        uint4 v;
-        v.x = pack_bf16(C[8 * c], C[8 * c + 1]); v.y = pack_bf16(C[8 * c + 2], C[8 * c + 3]);
-        v.z = pack_bf16(C[8 * c + 4], C[8 * c + 5]); v.w = pack_bf16(C[8 * c + 6], C[8 * c + 7]);
-        dst[c] = v;
-      }
-    };
-    auto epilogue = [&](int s) -> bool {   // fold the product of chunk step s into the running state
-      const int buf = s & 1;
-      if (!mbar_wait(&bar_acc_full[buf], (s >> 1) & 1, &g_sm100_status, 104)) return false;
-      tc_fence_after_sync();
-      const float g = s_g[s & 3];
-      const uint32_t ta = tmem + ((uint32_t)(quarter * 32) << 16) + buf * 128 + half * 64;
-      uint32_t r0[32], r1[32];
-      tmem_ld32(ta, r0);
-      tmem_ld32(ta + 32, r1);
-      tmem_wait_ld();
-      tc_fence_before_sync();
-      mbar_arrive(&bar_acc_free[buf]);
-#pragma unroll
-      for (int c = 0; c < 32; ++c) {
-        C[c] = fmaf(g, C[c], __uint_as_float(r0[c]));
-        C[32 + c] = fmaf(g, C[32 + c], __uint_as_float(r1[c]));
-      }
-      return true;
-    };
-
-    // slot written before step s: forward s, backward NC - s
-    store_c(BWD ? NC : 0);
     if (do_n && p.n_states != nullptr && ct < 128) p.n_states[((size_t)bh * (NC + 1)) * p.DHQK + d0 + ct] = nval;
     bool ok = true;
     for (int s = 0; s < NC; ++s) {
-      const int st = s & 1;
-      if (!mbar_wait(&bar_full[st], (s >> 1) & 1, &g_sm100_status, 105)) { ok = false; break; }
-      // scale the rows of the left tile in place (two 64-column boxes of 128 rows x 128 B, 128-byte swizzle)
+      const int st = s % REC_STAGES, nb = s & 1;
+      if (!mbar_wait(&bar_full[st], (s / REC_STAGES) & 1, &g_sm100_status, 105)) { ok = false; break; }
+      // two 64-column boxes of 128 rows x 128 B, 128-byte swizzle: the scale depends on the row only
       uint8_t* sl = smem + st * REC_STAGE_BYTES;
       float ns[2][8];
 #pragma unroll
@@ -208,7 +183,7 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
         }
         *ptr = make_uint4(w[0], w[1], w[2], w[3]);
       }
-      float* npart = reinterpret_cast<float*>(smem + 2 * REC_STAGE_BYTES) + st * (32 * 128);
+      float* npart = reinterpret_cast<float*>(smem + REC_STAGES * REC_STAGE_BYTES) + nb * (32 * 128);
       if (do_n) {
         const int lc = (ct & 7) ^ ((ct >> 3) & 7);   // logical 16-byte column chunk behind the swizzle
 #pragma unroll
@@ -221,37 +196,93 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
       fence_proxy_async_smem();
       mbar_arrive(&bar_scaled[st]);
       if (do_n) {   // n does not need the tensor cores: n_{s+1} = gbar n_s + column sums of the gated left tile
-        mbar_arrive(&bar_nsum[st]);
-        if (!mbar_wait(&bar_nsum[st], (s >> 1) & 1, &g_sm100_status, 106)) { ok = false; break; }
+        mbar_arrive(&bar_nsum[nb]);
+        if (!mbar_wait(&bar_nsum[nb], (s >> 1) & 1, &g_sm100_status, 106)) { ok = false; break; }
         if (ct < 128) {
           float colsum = 0.f;   // fixed summation order: the result does not depend on scheduling
 #pragma unroll 8
           for (int g = 0; g < 32; ++g) colsum += npart[g * 128 + ct];
-          nval = fmaf(s_g[s & 3], nval, colsum);
+          nval = fmaf(s_g[s & 7], nval, colsum);
           if (p.n_states != nullptr) p.n_states[((size_t)bh * (NC + 1) + s + 1) * p.DHQK + d0 + ct] = nval;
         }
       }
-      if (s > 0) {
-        if (!epilogue(s - 1)) { ok = false; break; }
-        store_c(BWD ? NC - s : s);
-      }
     }
-    if (ok && NC > 0) ok = epilogue(NC - 1);
-    if (ok) {
-      store_c(BWD ? 0 : NC);
-      if (p.c_final) {
-        float4* fd = reinterpret_cast<float4*>(p.c_final + ((size_t)bh * p.DHQK + d) * p.DHHV + ecol);
+    if (ok && do_n && p.n_final && ct < 128) p.n_final[(size_t)bh * p.DHQK + d0 + ct] = nval;
+  } else {
+    // ---------------- state warps: fold each chunk's product into the running state, store it ----------------
+    const int quarter = warp & 3, half = (warp - 10) >> 2;
+    const int row = quarter * 32 + lane;           // state row (d)
+    const int d = d0 + row, ecol = e0 + half * 64;
+    float C[64];
+    if (p.c_init) {
+      const float4* src = reinterpret_cast<const float4*>(p.c_init + ((size_t)bh * p.DHQK + d) * p.DHHV + ecol);
 #pragma unroll
-        for (int c = 0; c < 16; ++c) fd[c] = make_float4(C[4 * c], C[4 * c + 1], C[4 * c + 2], C[4 * c + 3]);
+      for (int c = 0; c < 16; ++c) { float4 v = src[c]; C[4 * c] = v.x; C[4 * c + 1] = v.y; C[4 * c + 2] = v.z; C[4 * c + 3] = v.w; }
+    } else {
+#pragma unroll
+      for (int c = 0; c < 64; ++c) C[c] = 0.f;
+    }
+    // The bf16 state tile goes to shared memory in the 128-byte-swizzled box layout and leaves with one TMA store
+    // per 64-column box (coalesced, asynchronous); two staging buffers, one store group in flight.
+    uint8_t* stage_base = smem + REC_STAGES * REC_STAGE_BYTES + REC_NPART_BYTES;
+    const bool elected = (warp == 10 && lane == 0);
+    int n_out = 0;   // tiles written so far
+    auto store_c = [&](int slot) -> bool {
+      if (p.c_states == nullptr) return true;
+      const int ob = n_out & 1;
+      if (n_out >= 2 && !mbar_wait(&bar_out_free[ob], ((n_out >> 1) - 1) & 1, &g_sm100_status, 107)) return false;
+      uint8_t* rowp = stage_base + ob * 32768 + half * 16384 + row * 128;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        uint4 v;
+        v.x = pack_bf16(C[8 * c], C[8 * c + 1]); v.y = pack_bf16(C[8 * c + 2], C[8 * c + 3]);
+        v.z = pack_bf16(C[8 * c + 4], C[8 * c + 5]); v.w = pack_bf16(C[8 * c + 6], C[8 * c + 7]);
+        *reinterpret_cast<uint4*>(rowp + ((c ^ (row & 7)) << 4)) = v;
       }
-      if (do_n && p.n_final && ct < 128) p.n_final[(size_t)bh * p.DHQK + d0 + ct] = nval;
+      fence_proxy_async_smem();
+      mbar_arrive(&bar_out_full[ob]);
+      if (elected) {
+        if (!mbar_wait(&bar_out_full[ob], (n_out >> 1) & 1, &g_sm100_status, 108)) return false;
+        const int y = (bh * (NC + 1) + slot) * p.DHQK + d0;
+        tma_store_2d(&mapS, stage_base + ob * 32768, e0, y);
+        tma_store_2d(&mapS, stage_base + ob * 32768 + 16384, e0 + 64, y);
+        tma_store_commit();
+        asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");   // the previous tile has left its buffer
+        if (n_out >= 1) mbar_arrive(&bar_out_free[ob ^ 1]);
+      }
+      ++n_out;
+      return true;
+    };
+    bool ok = store_c(BWD ? NC : 0);   // slot written before step s: forward s, backward NC - s
+    for (int s = 0; s < NC && ok; ++s) {
+      const int buf = s & 1;
+      if (!mbar_wait(&bar_acc_full[buf], (s >> 1) & 1, &g_sm100_status, 104)) { ok = false; break; }
+      tc_fence_after_sync();
+      const float g = s_g[s & 7];
+      const uint32_t ta = tmem + ((uint32_t)(quarter * 32) << 16) + buf * 128 + half * 64;
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        uint32_t rr[16];
+        tmem_ld16(ta + q4 * 16, rr);
+        tmem_wait_ld();
+#pragma unroll
+        for (int c = 0; c < 16; ++c) C[q4 * 16 + c] = fmaf(g, C[q4 * 16 + c], __uint_as_float(rr[c]));
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&bar_acc_free[buf]);
+      ok = store_c(BWD ? NC - 1 - s : s + 1);
+    }
+    if (elected) tma_store_wait_all();   // all state tiles have been written before the CTA retires
+    if (ok && p.c_final) {
+      float4* fd = reinterpret_cast<float4*>(p.c_final + ((size_t)bh * p.DHQK + d) * p.DHHV + ecol);
+#pragma unroll
+      for (int c = 0; c < 16; ++c) fd[c] = make_float4(C[4 * c], C[4 * c + 1], C[4 * c + 2], C[4 * c + 3]);
     }
   }
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem, 256);
 }
-
 
 // =====================================================================================================
 // Intra-chunk kernel.  Output tile rows r = tokens of one chunk, 128 output columns.
@@ -623,12 +654,14 @@ static bool state_map(CUtensorMap* m, const void* base, const ChunkwiseDims& d, 
 
 template <bool BWD>
 static int launch_rec(const void* left, const void* right, const RecParams& rp, const ChunkwiseDims& d, cudaStream_t st) {
-  CUtensorMap mL, mR;
+  CUtensorMap mL, mR, mS;
   if (!tok_map(&mL, left, d, d.DHQK) || !tok_map(&mR, right, d, d.DHHV)) return MLSTM_ERR_CUDA;
+  // store map over the per-chunk states; when no states are wanted (segment summary) the map is never used
+  if (!state_map(&mS, rp.c_states ? (const void*)rp.c_states : left, d, 128)) return MLSTM_ERR_CUDA;
   auto kern = rec_sm100<BWD>;
   MLSTM_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, REC_SMEM));
   dim3 grid(d.DHHV / 128, d.DHQK / 128, d.B * d.NH);
-  kern<<<grid, REC_THREADS, REC_SMEM, st>>>(mL, mR, rp);
+  kern<<<grid, REC_THREADS, REC_SMEM, st>>>(mL, mR, mS, rp);
   MLSTM_LAUNCH_CHECK();
   return MLSTM_OK;
 }
