@@ -316,7 +316,7 @@ constexpr int PAR_SMEM = 2 * PAR_STAGE + 1024;
 
 // Shared-memory control block of one intra-chunk CTA (the operand ring lives in dynamic shared memory).
 struct ParShared {
-  uint64_t bar_full[2], bar_empty[2], bar_sfull, bar_gated, bar_hfull, bar_dot, bar_pair[4];
+  uint64_t bar_full[2], bar_empty[2], bar_sfull, bar_gated, bar_hfull, bar_dot, bar_pair[4], bar_out;
   uint32_t tmem;
   float s_colA[CL], s_colF[CL];  // per-column terms of the gate matrix (see par_body)
   float s_part[2][CL];           // per-row partial sums exchanged between the two warps of a row
@@ -331,8 +331,8 @@ struct ParShared {
 //   upper (DV, DK), valid c >= r: rowF_r * colF_c * exp(...),     rowA = iota_r - b_r,  colA = b_c - m_c,    rowF = s, colF = 1/(den_c+eps)
 __device__ __forceinline__ void
 par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const CUtensorMap* mapX,
-         const CUtensorMap* mapSt, const CUtensorMap* mapE, const ParParams& p, ParShared& sh, const int o_tile,
-         const int ck, const int bh) {
+         const CUtensorMap* mapSt, const CUtensorMap* mapE, const CUtensorMap* mapO, const ParParams& p,
+         ParShared& sh, const int o_tile, const int ck, const int bh) {
   const bool LOWER = (mode == PM_H || mode == PM_DQ);
   const bool ST_MN = (mode == PM_H || mode == PM_DV);  // state operand N-contiguous in shared memory
   const bool HAS_E = (mode == PM_DQ || mode == PM_DK);  // extra tile for the gate-gradient row sums
@@ -351,7 +351,9 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
     for (int s = 0; s < 2; ++s) { mbar_init(&sh.bar_full[s], 1); mbar_init(&sh.bar_empty[s], use_n ? 9 : 1); }
     mbar_init(&sh.bar_sfull, 1); mbar_init(&sh.bar_gated, 256); mbar_init(&sh.bar_hfull, 1); mbar_init(&sh.bar_dot, 256);
     for (int s = 0; s < 4; ++s) mbar_init(&sh.bar_pair[s], 64);
+    mbar_init(&sh.bar_out, 256);
     fence_barrier_init();
+    tma_prefetch_desc(mapO);
     tma_prefetch_desc(mapA); tma_prefetch_desc(mapB); tma_prefetch_desc(mapX); tma_prefetch_desc(mapSt);
     if (HAS_E) tma_prefetch_desc(mapE);
   }
@@ -565,23 +567,24 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
         erow = smem + ste * PAR_STAGE + r * 128;
       }
       float dot = 0.f;
-      __nv_bfloat16* outp = (mode == PM_H) ? p.out_h : (mode == PM_DV) ? p.out_dv : (mode == PM_DK) ? p.out_dk : p.out_dq;
-      __nv_bfloat16* orow = outp + tok * DO + o0;
+      // the output tile is staged (bf16, 128-byte-swizzled boxes) in the ring stage the X tile occupied - every MMA
+      // that read the ring has completed - and leaves the SM with two TMA stores
+      uint8_t* ostage = smem + (ND & 1) * PAR_STAGE;
       if (ok) {
 #pragma unroll 1
         for (int cq = half; cq < 4; cq += 2) {
           uint32_t v[32];
           tmem_ld32(tAcc + lane_base + cq * 32, v);
           tmem_wait_ld();
-          uint4* dst = reinterpret_cast<uint4*>(orow + cq * 32);
+          uint8_t* orow = ostage + (cq >> 1) * 16384 + r * 128;
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             float x[8];
 #pragma unroll
             for (int e = 0; e < 8; ++e) x[e] = __uint_as_float(v[8 * c + e]) * inv;
+            const int sw = (((cq & 1) * 4 + c) ^ (r & 7)) << 4;   // 16-byte chunk (cq*4 + c) of the row, swizzled
             if (HAS_E) {
-              // logical 16-byte chunk (cq*4 + c) of the 128-column row: box (cq >> 1), chunk ((cq & 1) * 4 + c)
-              const uint4 ev = *reinterpret_cast<const uint4*>(erow + (cq >> 1) * 16384 + ((((cq & 1) * 4 + c) ^ (r & 7)) << 4));
+              const uint4 ev = *reinterpret_cast<const uint4*>(erow + (cq >> 1) * 16384 + sw);
               const uint32_t w[4] = {ev.x, ev.y, ev.z, ev.w};
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
@@ -593,8 +596,16 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
             uint4 o;
             o.x = pack_bf16(x[0], x[1]); o.y = pack_bf16(x[2], x[3]);
             o.z = pack_bf16(x[4], x[5]); o.w = pack_bf16(x[6], x[7]);
-            dst[c] = o;
+            *reinterpret_cast<uint4*>(orow + sw) = o;
           }
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(&sh.bar_out);
+        if (warp == 2 && lane == 0 && mbar_wait(&sh.bar_out, 0, &g_sm100_status, 211)) {
+          tma_store_2d(mapO, ostage, o0, row0);
+          tma_store_2d(mapO, ostage + 16384, o0 + 64, row0);
+          tma_store_commit();
+          tma_store_wait_all();
         }
         if (HAS_E) {
           sh.s_qn[half][r] = dot;
@@ -613,9 +624,9 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
 __global__ void __launch_bounds__(PAR_THREADS, 2)
 par_fw_sm100(const __grid_constant__ CUtensorMap mQ, const __grid_constant__ CUtensorMap mK,
              const __grid_constant__ CUtensorMap mV, const __grid_constant__ CUtensorMap mC,
-             const __grid_constant__ ParParams p) {
+             const __grid_constant__ CUtensorMap mH, const __grid_constant__ ParParams p) {
   __shared__ ParShared sh;
-  par_body(PM_H, &mQ, &mK, &mV, &mC, &mV, p, sh, blockIdx.x, blockIdx.y, blockIdx.z);
+  par_body(PM_H, &mQ, &mK, &mV, &mC, &mV, &mH, p, sh, blockIdx.x, blockIdx.y, blockIdx.z);
 }
 
 // deltaV, deltaK and deltaQ of one chunk in ONE launch: blockIdx.x enumerates the 128-wide output tiles of the three
@@ -625,16 +636,18 @@ __global__ void __launch_bounds__(PAR_THREADS, 2)
 par_bw_sm100(const __grid_constant__ CUtensorMap mQ, const __grid_constant__ CUtensorMap mK,
              const __grid_constant__ CUtensorMap mV, const __grid_constant__ CUtensorMap mDH,
              const __grid_constant__ CUtensorMap mC_k, const __grid_constant__ CUtensorMap mdC_mn,
-             const __grid_constant__ CUtensorMap mdC_k, const __grid_constant__ ParParams p) {
+             const __grid_constant__ CUtensorMap mdC_k, const __grid_constant__ CUtensorMap mDV,
+             const __grid_constant__ CUtensorMap mDK, const __grid_constant__ CUtensorMap mDQ,
+             const __grid_constant__ ParParams p) {
   __shared__ ParShared sh;
   const int t_dv = p.DHHV / 128, t_dk = p.DHQK / 128;
   const int x = blockIdx.x;
   int mode, tile;
-  const CUtensorMap *a, *b, *xm, *stm, *e;
-  if (x < t_dv) { mode = PM_DV; tile = x; a = &mK; b = &mQ; xm = &mDH; stm = &mdC_mn; e = &mDH; }
-  else if (x < t_dv + t_dk) { mode = PM_DK; tile = x - t_dv; a = &mV; b = &mDH; xm = &mQ; stm = &mdC_k; e = &mK; }
-  else { mode = PM_DQ; tile = x - t_dv - t_dk; a = &mDH; b = &mV; xm = &mK; stm = &mC_k; e = &mQ; }
-  par_body(mode, a, b, xm, stm, e, p, sh, tile, blockIdx.y, blockIdx.z);
+  const CUtensorMap *a, *b, *xm, *stm, *e, *o;
+  if (x < t_dv) { mode = PM_DV; tile = x; a = &mK; b = &mQ; xm = &mDH; stm = &mdC_mn; e = &mDH; o = &mDV; }
+  else if (x < t_dv + t_dk) { mode = PM_DK; tile = x - t_dv; a = &mV; b = &mDH; xm = &mQ; stm = &mdC_k; e = &mK; o = &mDK; }
+  else { mode = PM_DQ; tile = x - t_dv - t_dk; a = &mDH; b = &mV; xm = &mK; stm = &mC_k; e = &mQ; o = &mDQ; }
+  par_body(mode, a, b, xm, stm, e, o, p, sh, tile, blockIdx.y, blockIdx.z);
 }
 
 // =====================================================================================================
@@ -696,15 +709,15 @@ static ParParams base_params(const GateBuffers& gb, const ChunkwiseDims& d) {
 int sm100_parallel_fw(const void* q, const void* k, const void* v, const GateBuffers& gb, const void* c_states,
                       const float* n_states, void* h, float* n_out, const ChunkwiseDims& d, cudaStream_t st) {
   PhaseScope ps(PH_PAR_FW, st);
-  CUtensorMap mQ, mK, mV, mC;
+  CUtensorMap mQ, mK, mV, mC, mH;
   if (!tok_map(&mQ, q, d, d.DHQK) || !tok_map(&mK, k, d, d.DHQK) || !tok_map(&mV, v, d, d.DHHV) ||
-      !state_map(&mC, c_states, d, 64))
+      !state_map(&mC, c_states, d, 64) || !tok_map(&mH, h, d, d.DHHV))
     return MLSTM_ERR_CUDA;
   ParParams pp = base_params(gb, d);
   pp.n_states = n_states; pp.out_h = (__nv_bfloat16*)h; pp.n_out = n_out;
   MLSTM_CUDA_CHECK(cudaFuncSetAttribute(par_fw_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, PAR_SMEM));
   dim3 grid(d.DHHV / 128, d.NC, d.B * d.NH);
-  par_fw_sm100<<<grid, PAR_THREADS, PAR_SMEM, st>>>(mQ, mK, mV, mC, pp);
+  par_fw_sm100<<<grid, PAR_THREADS, PAR_SMEM, st>>>(mQ, mK, mV, mC, mH, pp);
   MLSTM_LAUNCH_CHECK();
   return MLSTM_OK;
 }
@@ -713,17 +726,18 @@ int sm100_parallel_bw(const void* q, const void* k, const void* v, const void* d
                       const void* c_states, const void* dc_states, void* dq, void* dk, void* dv, float* qdq_parts,
                       float* kdk_parts, const ChunkwiseDims& d, cudaStream_t st) {
   PhaseScope ps(PH_PAR_BW, st);
-  CUtensorMap mQ, mK, mV, mDH, mC_k, mdC_mn, mdC_k;
+  CUtensorMap mQ, mK, mV, mDH, mC_k, mdC_mn, mdC_k, mDV, mDK, mDQ;
   if (!tok_map(&mQ, q, d, d.DHQK) || !tok_map(&mK, k, d, d.DHQK) || !tok_map(&mV, v, d, d.DHHV) ||
       !tok_map(&mDH, dh, d, d.DHHV) || !state_map(&mC_k, c_states, d, 128) || !state_map(&mdC_mn, dc_states, d, 64) ||
-      !state_map(&mdC_k, dc_states, d, 128))
+      !state_map(&mdC_k, dc_states, d, 128) || !tok_map(&mDV, dv, d, d.DHHV) || !tok_map(&mDK, dk, d, d.DHQK) ||
+      !tok_map(&mDQ, dq, d, d.DHQK))
     return MLSTM_ERR_CUDA;
   ParParams pp = base_params(gb, d);
   pp.out_dv = (__nv_bfloat16*)dv; pp.out_dk = (__nv_bfloat16*)dk; pp.out_dq = (__nv_bfloat16*)dq;
   pp.rowdot_q = qdq_parts; pp.rowdot_k = kdk_parts;
   MLSTM_CUDA_CHECK(cudaFuncSetAttribute(par_bw_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, PAR_SMEM));
   dim3 grid(d.DHHV / 128 + 2 * (d.DHQK / 128), d.NC, d.B * d.NH);
-  par_bw_sm100<<<grid, PAR_THREADS, PAR_SMEM, st>>>(mQ, mK, mV, mDH, mC_k, mdC_mn, mdC_k, pp);
+  par_bw_sm100<<<grid, PAR_THREADS, PAR_SMEM, st>>>(mQ, mK, mV, mDH, mC_k, mdC_mn, mdC_k, mDV, mDK, mDQ, pp);
   MLSTM_LAUNCH_CHECK();
   return MLSTM_OK;
 }
