@@ -35,6 +35,14 @@ WORKLOAD = dict(name="c2_chunkwise_fwbw_mLSTMexp_B8_S8192_NH16_DHQK256_DHHV256_L
 CPU_SAMPLE = dict(B=1, NH=16)
 
 
+# measured with ncu at NH=16, 256/256, chunk 128, bf16 (profiles/chunkwise_fwbw_tcgen05_ncu_full_B2_S8192.md)
+NCU_DRAM_BYTES_PER_CHUNK = {"recurrent_fw": 254758, "parallel_fw": 389478, "recurrent_bw": 242731, "parallel_bw": 715320}
+
+
+def impl_used_is_tcgen05(_lib, S, DHQK, DHHV, L):
+    return bool(_lib.load().mlstm_b200_chunkwise_has_tcgen05(S, DHQK, DHHV, L, _lib.BF16))
+
+
 def fw_flops(B, NH, S, DHQK, DHHV, L):
     return B * NH * S * (4 * DHQK * DHHV + L * (DHQK + DHHV))
 
@@ -317,10 +325,12 @@ def run_b200(args):
             if name in pf:
                 kernels[name]["tflops"] = pf[name] / (tot / cnt * 1e-3) / 1e12
     dom = max((n for n in kernels if n in pf), key=lambda n: kernels[n]["ms"] * kernels[n]["launches_per_step"])
+    # DRAM bytes per launch of the dominant kernel: ncu dram__bytes_read.sum + dram__bytes_write.sum per chunk of 128
+    # tokens, captured on a quarter batch (see profiles/), times the chunks of this launch (traffic is
+    # proportional to the number of chunks)
     traffic = None
-    tpath = os.path.join(ROOT, "profiles", "roofline_traffic.json")
-    if os.path.exists(tpath):
-        traffic = json.load(open(tpath)).get(dom)
+    if impl_used_is_tcgen05(_lib, S, DHQK, DHHV, L) and (DHQK, DHHV, L) == (256, 256, 128) and dom in NCU_DRAM_BYTES_PER_CHUNK:
+        traffic = NCU_DRAM_BYTES_PER_CHUNK[dom] * B * NH * (S // L)
     impl_used = "tcgen05" if _lib.load().mlstm_b200_chunkwise_has_tcgen05(S, DHQK, DHHV, L, _lib.BF16) else "simt"
     roofline = {"bound": "tensor", "kernel": dom, "achieved": kernels[dom]["tflops"], "peak": peaks["tflops"],
                 "unit": "TFLOP/s", "frac": kernels[dom]["tflops"] / peaks["tflops"], "traffic": traffic,
