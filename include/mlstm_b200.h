@@ -35,8 +35,9 @@ enum { MLSTM_F32 = 0, MLSTM_BF16 = 1, MLSTM_F16 = 2 };
 enum { MLSTM_EXP = 0, MLSTM_SIG = 1, MLSTM_SIG_NONORM = 2 };
 
 /* which implementation to run: AUTO picks the tcgen05/TMA kernels whenever the
- * shape allows and the portable CUDA-core kernels otherwise */
-enum { MLSTM_IMPL_AUTO = 0, MLSTM_IMPL_SIMT = 1, MLSTM_IMPL_TCGEN05 = 2 };
+ * shape allows and the portable CUDA-core kernels otherwise; TCGEN05_FUSED forces the forward kernel that keeps
+ * the inter-chunk state on chip (backward is the same as TCGEN05) */
+enum { MLSTM_IMPL_AUTO = 0, MLSTM_IMPL_SIMT = 1, MLSTM_IMPL_TCGEN05 = 2, MLSTM_IMPL_TCGEN05_FUSED = 3 };
 
 enum {
   MLSTM_OK = 0,

@@ -15,7 +15,7 @@ LIB_PATH = os.path.join(_PKG, "libmlstm_b200.so")
 
 F32, BF16, F16 = 0, 1, 2
 EXP, SIG, SIG_NONORM = 0, 1, 2
-IMPL = {"auto": 0, "simt": 1, "tcgen05": 2}
+IMPL = {"auto": 0, "simt": 1, "tcgen05": 2, "tcgen05_fused": 3}
 
 _DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
 _CODE_DTYPE = {v: k for k, v in _DTYPE_CODE.items()}

@@ -1,6 +1,7 @@
 // extern "C" entry points of libmlstm_b200.so: argument validation, workspace carving, dispatch.
 #include <atomic>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <vector>
@@ -43,6 +44,9 @@ PhaseScope::~PhaseScope() {
   if (slot < (int)g_prof_recs.size()) cudaEventRecord(g_prof_recs[slot].b, st);
 }
 
+// AUTO picks the fused forward unless MLSTM_B200_FUSED_FW=0 is set in the environment
+static const bool g_fused_auto = []() { const char* e = getenv("MLSTM_B200_FUSED_FW"); return !(e && e[0] == '0'); }();
+
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 static int check_dims(int B, int NH, int S, int DHQK, int DHHV, int L) {
@@ -56,7 +60,7 @@ static int resolve_impl(int impl, int S, int DHQK, int DHHV, int L, int dtype, b
   const bool ok = sm100_supported(S, DHQK, DHHV, L, dtype);
   if (impl == MLSTM_IMPL_AUTO) { *use_sm100 = ok; return MLSTM_OK; }
   if (impl == MLSTM_IMPL_SIMT) { *use_sm100 = false; return MLSTM_OK; }
-  if (impl == MLSTM_IMPL_TCGEN05) { *use_sm100 = true; return ok ? MLSTM_OK : MLSTM_ERR_UNSUPPORTED; }
+  if (impl == MLSTM_IMPL_TCGEN05 || impl == MLSTM_IMPL_TCGEN05_FUSED) { *use_sm100 = true; return ok ? MLSTM_OK : MLSTM_ERR_UNSUPPORTED; }
   return MLSTM_ERR_UNSUPPORTED;
 }
 
@@ -238,7 +242,13 @@ int mlstm_b200_chunkwise_fw(const void* q, const void* k, const void* v, const v
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 
   if ((rc = launch_gates(gate_dtype, i, f, variant == MLSTM_EXP ? m_initial : nullptr, nullptr, lay.gb, m_states, d, st)) != MLSTM_OK) return rc;
-  if (use_sm100) {
+  const bool fused_ok = use_sm100 && sm100_fused_fw_supported(B, NH, S, DHQK, DHHV, L, dtype);
+  if (impl == MLSTM_IMPL_TCGEN05_FUSED && !(use_sm100 && dtype == MLSTM_BF16 && DHQK == 256)) return MLSTM_ERR_UNSUPPORTED;
+  if (use_sm100 && (impl == MLSTM_IMPL_TCGEN05_FUSED || (impl == MLSTM_IMPL_AUTO && fused_ok && g_fused_auto))) {
+    if ((rc = sm100_fused_fw(q, k, v, lay.gb, c_initial, n_initial, h, n_out, c_states,
+                             variant == MLSTM_SIG_NONORM ? nullptr : n_states, c_last,
+                             variant == MLSTM_SIG_NONORM ? nullptr : n_last, d, st)) != MLSTM_OK) return rc;
+  } else if (use_sm100) {
     if ((rc = sm100_recurrent_fw(k, v, lay.gb, c_initial, n_initial, c_states, n_states, c_last, n_last, d, st)) != MLSTM_OK) return rc;
     if ((rc = sm100_parallel_fw(q, k, v, lay.gb, c_states, n_states, h, n_out, d, st)) != MLSTM_OK) return rc;
   } else {

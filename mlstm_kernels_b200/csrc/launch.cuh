@@ -46,6 +46,12 @@ int sm100_parallel_bw(const void* q, const void* k, const void* v, const void* d
 
 int sm100_device_status(int reset, int* status);
 
+// chunkwise_fused_sm100.cu : forward with the inter-chunk state kept on chip
+bool sm100_fused_fw_supported(int B, int NH, int S, int DHQK, int DHHV, int L, int dtype);
+int sm100_fused_fw(const void* q, const void* k, const void* v, const GateBuffers& gb, const float* c_initial,
+                   const float* n_initial, void* h, float* n_out, void* c_states, float* n_states, float* c_last,
+                   float* n_last, const ChunkwiseDims& d, cudaStream_t st);
+
 // step.cu
 int launch_step(const void* q, const void* k, const void* v, const void* i, const void* f, const void* c,
                 const void* n, const void* m, void* h, void* c_new, void* n_new, void* m_new, int B, int NH, int DHQK,

@@ -193,3 +193,20 @@ def test_long_prefill_geometry_chunk256(variant):
     compare(got, ref, TOL_BF16, TOL_BF16, keys_fw=FW_KEYS if not siging else ("H", "C_last", "n_last"))
     ref256 = run_oracle_fwbw(inp, 256, dtype=torch.bfloat16, siging=siging)
     assert max_rel_err(got["H"], ref256["H"]) < TOL_BF16
+
+
+@pytest.mark.parametrize("variant", ["exp", "sig", "sig_nonorm"])
+@pytest.mark.parametrize("shape,init", [((1, 2, 256, 256, 256, 128), False), ((2, 2, 1024, 256, 256, 128), True),
+                                        ((1, 1, 512, 256, 512, 128), True)])
+def test_fused_forward_keeps_state_on_chip(variant, shape, init):
+    """The forward kernel that keeps the inter-chunk state in tensor memory: same results as the oracle (bf16
+    tolerance) and as the two-kernel tcgen05 path, including the per-chunk states the backward consumes."""
+    B, NH, S, DHQK, DHHV, L = shape
+    inp = case_inputs(14, B, NH, S, DHQK, DHHV, init=init, dC_last=init)
+    siging, normalize = variant != "exp", variant != "sig_nonorm"
+    got = run_cuda_fwbw(inp, L, dtype=torch.bfloat16, siging=siging, normalize=normalize, impl="tcgen05_fused")
+    two = run_cuda_fwbw(inp, L, dtype=torch.bfloat16, siging=siging, normalize=normalize, impl="tcgen05")
+    ref = run_oracle_fwbw(inp, L, dtype=torch.bfloat16, siging=siging, normalize=normalize)
+    keys = FW_KEYS if not siging else (("H", "C_last", "n_last") if normalize else ("H", "C_last"))
+    compare(got, ref, TOL_BF16, TOL_BF16, keys_fw=keys)
+    compare(got, two, 1e-2, 1e-2, keys_fw=keys)
