@@ -144,6 +144,17 @@ def cpu_port_step(inp, L):
 
 
 def time_cpu_port(steps, warmup):
+    """Times the CPU port with all host cores (launchers such as torchrun export OMP_NUM_THREADS=1; the BLAS
+    thread pool is raised again here)."""
+    try:
+        from threadpoolctl import threadpool_limits
+        with threadpool_limits(limits=os.cpu_count() or 1):
+            return _time_cpu_port(steps, warmup)
+    except ImportError:
+        return _time_cpu_port(steps, warmup)
+
+
+def _time_cpu_port(steps, warmup):
     w = WORKLOAD
     B, NH = CPU_SAMPLE["B"], CPU_SAMPLE["NH"]
     inp = make_inputs_np(B, NH, w["S"], w["DHQK"], w["DHHV"], seed=1)
@@ -354,6 +365,8 @@ def run_b200(args):
         ms_sig = timed_local(torch, sig_step, 5, 3)
         extra["fwbw_mLSTMsig"] = dict(ms=ms_sig, tflops=flops_fwbw / (ms_sig * 1e-3) / 1e12)
         extra["step_decode"] = bench_step(torch, mk, dev, peaks)
+        extra["consttoken_sweep_65536_tokens"] = bench_sweep(torch, mk, dev, peaks)
+        extra["long_prefill_B1_NH8_S131072_256_512_cs256"] = bench_long_prefill(torch, mk, dev, peaks)
         if args.triton_ref:
             extra["reference_triton_same_gpu"] = bench_triton_reference(torch, devin, leaf, L, flops_fw, flops_fwbw)
     if world > 1:
@@ -433,6 +446,53 @@ def bench_triton_reference(torch, devin, leaf, L, flops_fw, flops_fwbw):
     except Exception as e:  # noqa: BLE001
         out["step"] = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
     return out
+
+
+def bench_sweep(torch, mk, dev, peaks):
+    """The baseline's constant-token sweep (65,536 tokens, NH=16, 256/256, chunk 128, bf16): forward and
+    forward+backward for mLSTMexp at every (B, S) point."""
+    NH, DHQK, DHHV, L = 16, 256, 256, 128
+    out = {}
+    for B, S in ((128, 512), (64, 1024), (32, 2048), (16, 4096), (8, 8192), (4, 16384)):
+        g = torch.Generator(device=dev).manual_seed(S)
+        mk_t = lambda *sh: torch.randn(*sh, device=dev, generator=g).bfloat16()  # noqa: E731
+        q, k, v = mk_t(B, NH, S, DHQK), mk_t(B, NH, S, DHQK), mk_t(B, NH, S, DHHV)
+        i, f = mk_t(B, NH, S), (3 + torch.randn(B, NH, S, device=dev, generator=g)).bfloat16()
+        dH = mk_t(B, NH, S, DHHV)
+        leaf = [t.clone().requires_grad_(True) for t in (q, k, v, i, f)]
+
+        def fw():
+            with torch.no_grad():
+                mk.mlstm_chunkwise__b200_xl_chunk(q, k, v, i, f, chunk_size=L)
+
+        def fwbw():
+            for t in leaf:
+                t.grad = None
+            mk.mlstm_chunkwise__b200_xl_chunk(*leaf, chunk_size=L).backward(dH)
+        ms_fw, ms_fwbw = timed_local(torch, fw, 5, 3), timed_local(torch, fwbw, 5, 3)
+        ffw = fw_flops(B, NH, S, DHQK, DHHV, L)
+        ffb = ffw + bw_flops(B, NH, S, DHQK, DHHV, L)
+        out[f"B{B}_S{S}"] = dict(fw_ms=ms_fw, fw_tflops=ffw / ms_fw / 1e9, fw_frac_of_peak=ffw / ms_fw / 1e9 / peaks["tflops"],
+                                 fwbw_ms=ms_fwbw, fwbw_tflops=ffb / ms_fwbw / 1e9,
+                                 fwbw_frac_of_peak=ffb / ms_fwbw / 1e9 / peaks["tflops"])
+        del q, k, v, i, f, dH, leaf
+    return out
+
+
+def bench_long_prefill(torch, mk, dev, peaks):
+    """Single-GPU forward of the long-sequence configuration (the sequence-parallel runs compare with this)."""
+    B, NH, S, DHQK, DHHV, L = 1, 8, 131072, 256, 512, 256
+    g = torch.Generator(device=dev).manual_seed(7)
+    mk_t = lambda *sh: torch.randn(*sh, device=dev, generator=g).bfloat16()  # noqa: E731
+    q, k, v = mk_t(B, NH, S, DHQK), mk_t(B, NH, S, DHQK), mk_t(B, NH, S, DHHV)
+    i, f = mk_t(B, NH, S), (3 + torch.randn(B, NH, S, device=dev, generator=g)).bfloat16()
+
+    def fw():
+        with torch.no_grad():
+            mk.mlstm_chunkwise__b200_xl_chunk(q, k, v, i, f, return_last_states=True, chunk_size=L)
+    ms = timed_local(torch, fw, 5, 3)
+    fl = fw_flops(B, NH, S, DHQK, DHHV, L)
+    return dict(ms=ms, tflops=fl / ms / 1e9, frac_of_peak=fl / ms / 1e9 / peaks["tflops"], tokens_per_s=S / (ms * 1e-3))
 
 
 def timed_local(torch, fn, steps, warmup):
