@@ -25,6 +25,11 @@ import sys
 import threading
 import time
 
+# torchrun exports OMP_NUM_THREADS=1 for every rank; the CPU baseline legs must use all host cores, so undo that
+# before numpy / torch load their BLAS and OpenMP runtimes.
+if os.environ.get("OMP_NUM_THREADS") == "1":
+    os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
+
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.join(ROOT, "tests"))
