@@ -14,6 +14,9 @@
 //                    fw_kernel_parallel.py:14-289, bw_kernel_parallel_dV.py, bw_kernel_parallel_dK.py, bw_kernel_parallel_dQ.py
 // Operands arrive by TMA (128-byte swizzle, no multicast) through a two-stage mbarrier ring; one warp produces,
 // one thread issues the MMAs, the remaining warps do the element-wise work.  Every wait is bounded.
+#include <algorithm>
+#include <cstdlib>
+
 #include "common.cuh"
 #include "launch.cuh"
 #include "sm100.cuh"
