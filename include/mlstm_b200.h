@@ -164,6 +164,21 @@ int mlstm_b200_chunkwise_bw(const void* q, const void* k, const void* v, const v
                             int dtype, int gate_dtype, int variant, int impl, float eps, void* stream);
 
 /*
+ * Same as mlstm_b200_chunkwise_bw when the forward call of the same problem has just run and its scratch buffer
+ * `fw_workspace` (and its m_out output) are still intact: the gate pre-pass (logsigmoid, cumulative sums, max-state
+ * recursion) is not repeated, its per-token vectors are read back from that buffer.  The reference keeps no such
+ * cache (it recomputes vecB / vecA in mlstm_kernels/torch/chunkwise/triton_xl_chunk/bw.py:116-118).
+ */
+int mlstm_b200_chunkwise_bw_cached(const void* q, const void* k, const void* v, const void* i, const void* f,
+                                   const float* m_initial, const void* c_states, const float* n_out,
+                                   const float* m_out, const void* fw_workspace, size_t fw_workspace_bytes,
+                                   const void* dh, const float* dc_last,
+                                   void* dq, void* dk, void* dv, float* di, float* df, float* dc_initial,
+                                   void* workspace, size_t workspace_bytes,
+                                   int B, int NH, int S, int DHQK, int DHHV, int L,
+                                   int dtype, int gate_dtype, int variant, int impl, float eps, void* stream);
+
+/*
  * Sequence-parallel prefill: a long sequence is split into contiguous segments, one per GPU.
  * The reference has no multi-device code; these two entry points implement its state-passing
  * contract (chaining segments through c_initial / n_initial / m_initial and the returned last

@@ -43,6 +43,8 @@ SIGNATURES = {
                                        + [_i] * 6 + [_i, _i, _i, _i, _f, _vp]),
     "mlstm_b200_chunkwise_bw": (_i, [_vp] * 5 + [_fp, _vp, _fp, _vp, _fp] + [_vp] * 3 + [_fp] * 3
                                 + [_vp, _sz] + [_i] * 6 + [_i, _i, _i, _i, _f, _vp]),
+    "mlstm_b200_chunkwise_bw_cached": (_i, [_vp] * 5 + [_fp, _vp, _fp, _fp, _vp, _sz, _vp, _fp] + [_vp] * 3 + [_fp] * 3
+                                       + [_vp, _sz] + [_i] * 6 + [_i, _i, _i, _i, _f, _vp]),
     "mlstm_b200_chunkwise_summary": (_i, [_vp] * 4 + [_fp] * 4 + [_vp, _sz] + [_i] * 6 + [_i, _i, _i, _i, _vp]),
     "mlstm_b200_state_combine": (_i, [_fp] * 10 + [_i] * 5 + [_vp]),
     "mlstm_b200_step": (_i, [_vp] * 12 + [_i] * 6 + [_f, _vp]),

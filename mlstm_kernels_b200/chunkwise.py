@@ -43,10 +43,11 @@ def select_chunk_size(sequence_length: int, target_chunk_size: int) -> int:
 
 
 def kernel_chunk_size(q: torch.Tensor, v: torch.Tensor, chunk_size: int, impl: str = "auto") -> int:
-    """Chunk size the kernels run with.  Chunk sizes above 128 run as chunks of 128 on the tcgen05 path
+    """Chunk size the kernels run with.  Where the tcgen05 path applies (bf16, head dims multiples of 128, sequence a
+    multiple of 128) every requested chunk size runs as chunks of 128
     (H does not depend on the chunk size; the reference does the same for its inter-chunk kernel:
     chunk_size_inter = min(128, chunk_size), mlstm_kernels/triton/chunkwise/kernel_param_heuristics.py:96-121)."""
-    if chunk_size > 128 and impl != "simt" and q.is_cuda:
+    if chunk_size != 128 and q.shape[2] % 128 == 0 and impl != "simt" and q.is_cuda:
         lib = _lib.load()
         if lib.mlstm_b200_chunkwise_has_tcgen05(q.shape[2], q.shape[3], v.shape[3], 128, _lib.dtype_code(q.dtype)):
             return 128
@@ -103,12 +104,13 @@ def chunkwise_fw_raw(q, k, v, i, f, c_initial=None, n_initial=None, m_initial=No
             _lib.stream_handle(dev))
     _lib.check(rc, "mlstm_b200_chunkwise_fw")
     return dict(H=h, n_out=n_out, m_out=m_out, C_states=c_states, n_states=n_states, m_states=m_states,
-                C_last=c_last, n_last=n_last, m_last=m_last)
+                C_last=c_last, n_last=n_last, m_last=m_last, workspace=ws)
 
 
 def chunkwise_bw_raw(q, k, v, i, f, m_initial, c_states, n_out, dh, dc_last=None, *, chunk_size: int, eps: float,
-                     variant: int, impl: str = "auto", want_dc_initial: bool = False):
-    """Run the backward kernels.  Returns (dq, dk, dv, di, df, dc_initial)."""
+                     variant: int, impl: str = "auto", want_dc_initial: bool = False, m_out=None, fw_workspace=None):
+    """Run the backward kernels.  Returns (dq, dk, dv, di, df, dc_initial).  With `m_out` and `fw_workspace` (both
+    as returned by chunkwise_fw_raw for the same inputs) the gate pre-pass is not repeated."""
     _lib.require_cuda(q, k, v, i, f, dh)
     lib = _lib.load()
     B, NH, S, DHQK = q.shape
@@ -131,12 +133,21 @@ def chunkwise_bw_raw(q, k, v, i, f, m_initial, c_states, n_out, dh, dc_last=None
     ws_bytes = lib.mlstm_b200_chunkwise_workspace_bytes(B, NH, S, DHQK, DHHV, L, dt, variant, im, 1)
     ws = torch.empty((max(ws_bytes, 256),), dtype=torch.uint8, device=dev)
     with torch.cuda.device(dev):
-        rc = lib.mlstm_b200_chunkwise_bw(
-            _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(i), _lib.ptr(f),
-            _lib.ptr(m0), _lib.ptr(c_states), _lib.ptr(n_out), _lib.ptr(dh), _lib.ptr(dcl),
-            _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(di), _lib.ptr(df), _lib.ptr(dc0),
-            _lib.ptr(ws), ws_bytes, B, NH, S, DHQK, DHHV, L, dt, gdt, variant, im, float(eps),
-            _lib.stream_handle(dev))
+        if fw_workspace is not None and m_out is not None:
+            rc = lib.mlstm_b200_chunkwise_bw_cached(
+                _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(i), _lib.ptr(f),
+                _lib.ptr(m0), _lib.ptr(c_states), _lib.ptr(n_out), _lib.ptr(m_out), _lib.ptr(fw_workspace),
+                fw_workspace.numel(), _lib.ptr(dh), _lib.ptr(dcl),
+                _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(di), _lib.ptr(df), _lib.ptr(dc0),
+                _lib.ptr(ws), ws_bytes, B, NH, S, DHQK, DHHV, L, dt, gdt, variant, im, float(eps),
+                _lib.stream_handle(dev))
+        else:
+            rc = lib.mlstm_b200_chunkwise_bw(
+                _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(i), _lib.ptr(f),
+                _lib.ptr(m0), _lib.ptr(c_states), _lib.ptr(n_out), _lib.ptr(dh), _lib.ptr(dcl),
+                _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(di), _lib.ptr(df), _lib.ptr(dc0),
+                _lib.ptr(ws), ws_bytes, B, NH, S, DHQK, DHHV, L, dt, gdt, variant, im, float(eps),
+                _lib.stream_handle(dev))
     _lib.check(rc, "mlstm_b200_chunkwise_bw")
     return dq, dk, dv, di, df, dc0
 
@@ -150,7 +161,9 @@ def _make_fwbw(autocast_kernel_dtype: torch.dtype, variant: int):
             L = kernel_chunk_size(q, v, select_chunk_size(S, chunk_size), impl)
             out = chunkwise_fw_raw(q, k, v, i, f, c_initial, n_initial, m_initial, chunk_size=L, eps=eps,
                                    variant=variant, impl=impl, want_last=return_last_states)
-            ctx.save_for_backward(q, k, v, i, f, m_initial, out["C_states"], out["n_out"])
+            # the forward's gate vectors (its scratch buffer and m_out) are kept for the backward: 24 B per token
+            ctx.save_for_backward(q, k, v, i, f, m_initial, out["C_states"], out["n_out"], out["m_out"],
+                                  out["workspace"])
             ctx.cfg = (L, eps, impl, c_initial is not None, n_initial is not None, m_initial is not None,
                        None if c_initial is None else c_initial.dtype,
                        None if n_initial is None else n_initial.dtype)
@@ -162,11 +175,11 @@ def _make_fwbw(autocast_kernel_dtype: torch.dtype, variant: int):
         @staticmethod
         @custom_bwd(device_type="cuda")
         def backward(ctx, dH, dC_last, dN_last, dM_last):
-            q, k, v, i, f, m_initial, c_states, n_out = ctx.saved_tensors
+            q, k, v, i, f, m_initial, c_states, n_out, m_out, fw_ws = ctx.saved_tensors
             L, eps, impl, has_c0, has_n0, has_m0, c0_dtype, n0_dtype = ctx.cfg
             dq, dk, dv, di, df, dc0 = chunkwise_bw_raw(
                 q, k, v, i, f, m_initial, c_states, n_out, dH, dC_last, chunk_size=L, eps=eps, variant=variant,
-                impl=impl, want_dc_initial=has_c0)
+                impl=impl, want_dc_initial=has_c0, m_out=m_out, fw_workspace=fw_ws)
             B, NH, S, DHQK = q.shape
             dn0 = torch.zeros((B, NH, DHQK), dtype=n0_dtype, device=q.device) if has_n0 else None
             dm0 = torch.zeros_like(m_initial) if has_m0 else None

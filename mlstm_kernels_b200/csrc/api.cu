@@ -263,11 +263,16 @@ int mlstm_b200_chunkwise_fw(const void* q, const void* k, const void* v, const v
   return MLSTM_OK;
 }
 
-int mlstm_b200_chunkwise_bw(const void* q, const void* k, const void* v, const void* i, const void* f,
-                            const float* m_initial, const void* c_states, const float* n_out, const void* dh,
-                            const float* dc_last, void* dq, void* dk, void* dv, float* di, float* df,
-                            float* dc_initial, void* workspace, size_t workspace_bytes, int B, int NH, int S, int DHQK,
-                            int DHHV, int L, int dtype, int gate_dtype, int variant, int impl, float eps, void* stream) {
+}  // extern "C"
+
+// Backward body.  With `fw_workspace` (the scratch buffer the forward call of the same problem left behind, still
+// intact) and `m_out` the gate pre-pass is not run again: its vectors are read from that buffer.
+static int bw_impl(const void* q, const void* k, const void* v, const void* i, const void* f,
+                   const float* m_initial, const void* c_states, const float* n_out, const void* dh,
+                   const float* dc_last, void* dq, void* dk, void* dv, float* di, float* df,
+                   float* dc_initial, void* workspace, size_t workspace_bytes, int B, int NH, int S, int DHQK,
+                   int DHHV, int L, int dtype, int gate_dtype, int variant, int impl, float eps, void* stream,
+                   const void* fw_workspace, size_t fw_workspace_bytes, const float* m_out) {
   int rc = check_dims(B, NH, S, DHQK, DHHV, L);
   if (rc != MLSTM_OK) return rc;
   if (dtype != MLSTM_F32 && dtype != MLSTM_BF16 && dtype != MLSTM_F16) return MLSTM_ERR_DTYPE;
@@ -287,7 +292,17 @@ int mlstm_b200_chunkwise_bw(const void* q, const void* k, const void* v, const v
   if (workspace_bytes < lay.bytes) return MLSTM_ERR_WORKSPACE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 
-  if ((rc = launch_gates(gate_dtype, i, f, variant == MLSTM_EXP ? m_initial : nullptr, n_out, lay.gb, lay.m_states, d, st)) != MLSTM_OK) return rc;
+  if (fw_workspace != nullptr) {
+    if (!m_out || !aligned16(fw_workspace) || !aligned16(m_out)) return MLSTM_ERR_NULL;
+    FwLayout fl = carve_fw(const_cast<void*>(fw_workspace), B * NH, S, d.NC, const_cast<float*>(m_out));
+    if (fw_workspace_bytes < fl.bytes) return MLSTM_ERR_WORKSPACE;
+    float* inv_den = lay.gb.inv_den;
+    lay.gb = fl.gb;
+    lay.gb.inv_den = inv_den;
+    if ((rc = launch_inv_den(n_out, inv_den, (size_t)B * NH * S, variant, eps, st)) != MLSTM_OK) return rc;
+  } else {
+    if ((rc = launch_gates(gate_dtype, i, f, variant == MLSTM_EXP ? m_initial : nullptr, n_out, lay.gb, lay.m_states, d, st)) != MLSTM_OK) return rc;
+  }
   if (use_sm100) {
     if ((rc = sm100_recurrent_bw(q, dh, lay.gb, dc_last, lay.dc_states, dc_initial, d, st)) != MLSTM_OK) return rc;
     if ((rc = sm100_parallel_bw(q, k, v, dh, lay.gb, c_states, lay.dc_states, dq, dk, dv, lay.acc, lay.kdk, d, st)) != MLSTM_OK) return rc;
@@ -301,6 +316,31 @@ int mlstm_b200_chunkwise_bw(const void* q, const void* k, const void* v, const v
     if ((rc = launch_gate_grads(dtype, gate_dtype, q, k, dq, dk, i, f, lay.acc, lay.kdk, di, df, d, st)) != MLSTM_OK) return rc;
   }
   return MLSTM_OK;
+}
+
+extern "C" {
+
+int mlstm_b200_chunkwise_bw(const void* q, const void* k, const void* v, const void* i, const void* f,
+                            const float* m_initial, const void* c_states, const float* n_out, const void* dh,
+                            const float* dc_last, void* dq, void* dk, void* dv, float* di, float* df,
+                            float* dc_initial, void* workspace, size_t workspace_bytes, int B, int NH, int S, int DHQK,
+                            int DHHV, int L, int dtype, int gate_dtype, int variant, int impl, float eps, void* stream) {
+  return bw_impl(q, k, v, i, f, m_initial, c_states, n_out, dh, dc_last, dq, dk, dv, di, df, dc_initial, workspace,
+                 workspace_bytes, B, NH, S, DHQK, DHHV, L, dtype, gate_dtype, variant, impl, eps, stream, nullptr, 0,
+                 nullptr);
+}
+
+int mlstm_b200_chunkwise_bw_cached(const void* q, const void* k, const void* v, const void* i, const void* f,
+                                   const float* m_initial, const void* c_states, const float* n_out,
+                                   const float* m_out, const void* fw_workspace, size_t fw_workspace_bytes,
+                                   const void* dh, const float* dc_last, void* dq, void* dk, void* dv, float* di,
+                                   float* df, float* dc_initial, void* workspace, size_t workspace_bytes, int B,
+                                   int NH, int S, int DHQK, int DHHV, int L, int dtype, int gate_dtype, int variant,
+                                   int impl, float eps, void* stream) {
+  if (!fw_workspace || !m_out) return MLSTM_ERR_NULL;
+  return bw_impl(q, k, v, i, f, m_initial, c_states, n_out, dh, dc_last, dq, dk, dv, di, df, dc_initial, workspace,
+                 workspace_bytes, B, NH, S, DHQK, DHHV, L, dtype, gate_dtype, variant, impl, eps, stream, fw_workspace,
+                 fw_workspace_bytes, m_out);
 }
 
 int mlstm_b200_chunkwise_summary(const void* k, const void* v, const void* i, const void* f, float* c_last,

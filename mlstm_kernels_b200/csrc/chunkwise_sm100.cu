@@ -46,7 +46,7 @@ struct RecParams {
   int S, NC, DHQK, DHHV;
 };
 
-constexpr int REC_THREADS = 576;                 // warp 0 TMA, warp 1 MMA, warps 2..9 gate the left tile, warps 10..17 own the state
+constexpr int REC_THREADS = 608;                 // warp 0 TMA, 1 MMA, 2..9 gate the left tile, 10..17 own the state, 18 stores it
 constexpr int REC_STAGE_BYTES = 65536;           // left tile 32 KB + right tile 32 KB
 constexpr int REC_NPART_BYTES = 2 * 32 * 128 * 4;   // double-buffered partial column sums of the gated left tile
 constexpr int REC_STAGES = 2;                    // operand ring depth
@@ -211,6 +211,23 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
       }
     }
     if (ok && do_n && p.n_final && ct < 128) p.n_final[(size_t)bh * p.DHQK + d0 + ct] = nval;
+  } else if (warp == 18) {
+    // ---------------- store warp: one TMA store per 64-column box of each staged state tile ----------------
+    if (lane == 0 && p.c_states != nullptr) {
+      uint8_t* stage_base = smem + REC_STAGES * REC_STAGE_BYTES + REC_NPART_BYTES;
+      for (int n = 0; n <= NC; ++n) {
+        const int ob = n & 1;
+        if (!mbar_wait(&bar_out_full[ob], (n >> 1) & 1, &g_sm100_status, 108)) break;
+        const int slot = BWD ? NC - n : n;
+        const int y = (bh * (NC + 1) + slot) * p.DHQK + d0;
+        tma_store_2d(&mapS, stage_base + ob * 32768, e0, y);
+        tma_store_2d(&mapS, stage_base + ob * 32768 + 16384, e0 + 64, y);
+        tma_store_commit();
+        asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");   // the previous tile has left its buffer
+        if (n >= 1) mbar_arrive(&bar_out_free[ob ^ 1]);
+      }
+      tma_store_wait_all();   // all state tiles have been written before the CTA retires
+    }
   } else {
     // ---------------- state warps: fold each chunk's product into the running state, store it ----------------
     const int quarter = warp & 3, half = (warp - 10) >> 2;
@@ -228,9 +245,9 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
     // The bf16 state tile goes to shared memory in the 128-byte-swizzled box layout and leaves with one TMA store
     // per 64-column box (coalesced, asynchronous); two staging buffers, one store group in flight.
     uint8_t* stage_base = smem + REC_STAGES * REC_STAGE_BYTES + REC_NPART_BYTES;
-    const bool elected = (warp == 10 && lane == 0);
     int n_out = 0;   // tiles written so far
     auto store_c = [&](int slot) -> bool {
+      (void)slot;
       if (p.c_states == nullptr) return true;
       const int ob = n_out & 1;
       if (n_out >= 2 && !mbar_wait(&bar_out_free[ob], ((n_out >> 1) - 1) & 1, &g_sm100_status, 107)) return false;
@@ -243,16 +260,7 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
         *reinterpret_cast<uint4*>(rowp + ((c ^ (row & 7)) << 4)) = v;
       }
       fence_proxy_async_smem();
-      mbar_arrive(&bar_out_full[ob]);
-      if (elected) {
-        if (!mbar_wait(&bar_out_full[ob], (n_out >> 1) & 1, &g_sm100_status, 108)) return false;
-        const int y = (bh * (NC + 1) + slot) * p.DHQK + d0;
-        tma_store_2d(&mapS, stage_base + ob * 32768, e0, y);
-        tma_store_2d(&mapS, stage_base + ob * 32768 + 16384, e0 + 64, y);
-        tma_store_commit();
-        asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");   // the previous tile has left its buffer
-        if (n_out >= 1) mbar_arrive(&bar_out_free[ob ^ 1]);
-      }
+      mbar_arrive(&bar_out_full[ob]);   // the store warp ships the tile
       ++n_out;
       return true;
     };
@@ -275,7 +283,6 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
       mbar_arrive(&bar_acc_free[buf]);
       ok = store_c(BWD ? NC - 1 - s : s + 1);
     }
-    if (elected) tma_store_wait_all();   // all state tiles have been written before the CTA retires
     if (ok && p.c_final) {
       float4* fd = reinterpret_cast<float4*>(p.c_final + ((size_t)bh * p.DHQK + d) * p.DHHV + ecol);
 #pragma unroll

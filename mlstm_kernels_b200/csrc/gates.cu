@@ -15,137 +15,143 @@ namespace mlstm {
 
 constexpr int kGateThreads = 256;
 
+// The pre-pass runs as three launches so that the per-chunk work (1 and 3) spreads over the whole GPU and only
+// the scan over chunks (2) is serial per (batch, head):
+//   gates_chunk_kernel  b_j, a_j, g_k, max_j a_j           one warp per chunk
+//   gates_scan_kernel   m_k, gbar_k, total G               one CTA per (batch, head)
+//   gates_token_kernel  m_i, abar_j, bbar_i, 1/(den+eps)   one warp per chunk
 template <typename T>
 __global__ void __launch_bounds__(kGateThreads)
-gates_kernel(const T* __restrict__ vecI, const T* __restrict__ vecF, const float* __restrict__ m_initial,
-             const float* __restrict__ n_out, GateBuffers gb, float* __restrict__ m_states,
-             int S, int L, int NC, int variant, float eps, float m_default, float* __restrict__ g_sum) {
-  const int bh = blockIdx.x;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = kGateThreads / 32;
+gates_chunk_kernel(const T* __restrict__ vecI, const T* __restrict__ vecF, GateBuffers gb, int S, int L, int NC,
+                   int variant) {
+  const int bh = blockIdx.y;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int k = blockIdx.x * (kGateThreads / 32) + warp;
+  if (k >= NC) return;
   const bool siging = variant != MLSTM_EXP;
-  const size_t tok0 = (size_t)bh * S;
   float* g_arr = gb.scratch + (size_t)bh * 2 * NC;
   float* amax_arr = g_arr + NC;
-
-  // ---- phase 1: b_j, a_j, g_k, max_j a_j per chunk (one warp per chunk) ----
-  for (int k = warp; k < NC; k += nwarps) {
-    const size_t base = tok0 + (size_t)k * L;
-    float carry = 0.f;
-    for (int j0 = 0; j0 < L; j0 += 32) {
-      const int j = j0 + lane;
-      float x = (j < L) ? logsigmoid_f(to_f32(vecF[base + j])) : 0.f;
+  const size_t base = (size_t)bh * S + (size_t)k * L;
+  float carry = 0.f;
+  for (int j0 = 0; j0 < L; j0 += 32) {
+    const int j = j0 + lane;
+    float x = (j < L) ? logsigmoid_f(to_f32(vecF[base + j])) : 0.f;
 #pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        float y = __shfl_up_sync(0xffffffffu, x, o);
-        if (lane >= o) x += y;
-      }
-      x += carry;
-      if (j < L) gb.vecB[base + j] = x;
-      carry = __shfl_sync(0xffffffffu, x, 31);
+    for (int o = 1; o < 32; o <<= 1) {
+      float y = __shfl_up_sync(0xffffffffu, x, o);
+      if (lane >= o) x += y;
     }
-    const float g = carry;
-    // a_j = sum_{t>j} lf_t + iota_j as a reverse scan that never includes position j
-    float suffix = 0.f, amax = -INFINITY;
-    for (int j0 = ((L - 1) / 32) * 32; j0 >= 0; j0 -= 32) {
-      const int j = j0 + lane;
-      float x = (j < L) ? logsigmoid_f(to_f32(vecF[base + j])) : 0.f;
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        float y = __shfl_down_sync(0xffffffffu, x, o);
-        if (lane + o < 32) x += y;
-      }
-      float excl = __shfl_down_sync(0xffffffffu, x, 1);
-      if (lane == 31) excl = 0.f;
-      excl += suffix;
-      suffix += __shfl_sync(0xffffffffu, x, 0);
-      if (j < L) {
-        const float iv = to_f32(vecI[base + j]);
-        const float iota = siging ? logsigmoid_f(iv) : iv;
-        const float a = excl + iota;
-        gb.iota[base + j] = iota;
-        gb.abar[base + j] = a;  // finalised in phase 3
-        amax = fmaxf(amax, a);
-      }
-    }
-    amax = warp_max(amax);
-    if (lane == 0) { g_arr[k] = g; amax_arr[k] = amax; }
+    x += carry;
+    if (j < L) gb.vecB[base + j] = x;
+    carry = __shfl_sync(0xffffffffu, x, 31);
   }
-  __syncthreads();
+  const float g = carry;
+  // a_j = sum_{t>j} lf_t + iota_j as a reverse scan that never includes position j
+  float suffix = 0.f, amax = -INFINITY;
+  for (int j0 = ((L - 1) / 32) * 32; j0 >= 0; j0 -= 32) {
+    const int j = j0 + lane;
+    float x = (j < L) ? logsigmoid_f(to_f32(vecF[base + j])) : 0.f;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      float y = __shfl_down_sync(0xffffffffu, x, o);
+      if (lane + o < 32) x += y;
+    }
+    float excl = __shfl_down_sync(0xffffffffu, x, 1);
+    if (lane == 31) excl = 0.f;
+    excl += suffix;
+    suffix += __shfl_sync(0xffffffffu, x, 0);
+    if (j < L) {
+      const float iv = to_f32(vecI[base + j]);
+      const float iota = siging ? logsigmoid_f(iv) : iv;
+      const float a = excl + iota;
+      gb.iota[base + j] = iota;
+      gb.abar[base + j] = a;  // finalised by gates_token_kernel
+      amax = fmaxf(amax, a);
+    }
+  }
+  amax = warp_max(amax);
+  if (lane == 0) { g_arr[k] = g; amax_arr[k] = amax; }
+}
 
-  // ---- phase 2: m_{k+1} = max(g_k + m_k, amax_k) as a scan over maps x -> max(x + G, A) ----
+// m_{k+1} = max(g_k + m_k, amax_k) as a block scan over the maps x -> max(x + G, A)
+__global__ void __launch_bounds__(kGateThreads)
+gates_scan_kernel(const float* __restrict__ m_initial, GateBuffers gb, float* __restrict__ m_states, int NC,
+                  int variant, float m_default, float* __restrict__ g_sum) {
   __shared__ float sG[kGateThreads], sA[kGateThreads], sMin[kGateThreads];
-  {
-    const int t = threadIdx.x;
-    const int seg = (NC + kGateThreads - 1) / kGateThreads;
-    const int k0 = min(NC, t * seg), k1 = min(NC, (t + 1) * seg);
-    if (!siging) {
-      float G = 0.f, A = -INFINITY;
-      for (int k = k0; k < k1; ++k) { A = fmaxf(A + g_arr[k], amax_arr[k]); G += g_arr[k]; }
-      sG[t] = G; sA[t] = A;
-      __syncthreads();
-      if (t == 0) {
-        float m = m_initial ? m_initial[bh] : m_default;
-        for (int u = 0; u < kGateThreads; ++u) { sMin[u] = m; m = fmaxf(m + sG[u], sA[u]); }
-      }
-      __syncthreads();
-      float m = sMin[t];
-      float* ms = m_states + (size_t)bh * (NC + 1);
-      for (int k = k0; k < k1; ++k) {
-        ms[k] = m;
-        const float mn = fmaxf(g_arr[k] + m, amax_arr[k]);
-        gb.gbar[(size_t)bh * NC + k] = expf(g_arr[k] + m - mn);
-        m = mn;
-        if (k == NC - 1) ms[NC] = m;
-      }
-    } else {
-      float* ms = m_states + (size_t)bh * (NC + 1);
-      for (int k = k0; k < k1; ++k) {
-        ms[k] = 0.f;
-        gb.gbar[(size_t)bh * NC + k] = expf(g_arr[k]);
-        if (k == NC - 1) ms[NC] = 0.f;
-      }
-    }
-  }
-  if (g_sum != nullptr && threadIdx.x == 0) {  // total log forget gate of the sequence (for chaining segments)
-    float G = 0.f;
-    for (int k = 0; k < NC; ++k) G += g_arr[k];
-    g_sum[bh] = G;
+  const int bh = blockIdx.x, t = threadIdx.x;
+  const bool siging = variant != MLSTM_EXP;
+  const float* g_arr = gb.scratch + (size_t)bh * 2 * NC;
+  const float* amax_arr = g_arr + NC;
+  const int seg = (NC + kGateThreads - 1) / kGateThreads;
+  const int k0 = min(NC, t * seg), k1 = min(NC, (t + 1) * seg);
+  float* ms = m_states + (size_t)bh * (NC + 1);
+  float G = 0.f, A = -INFINITY;
+  for (int k = k0; k < k1; ++k) { A = fmaxf(A + g_arr[k], amax_arr[k]); G += g_arr[k]; }
+  sG[t] = G; sA[t] = A;
+  __syncthreads();
+  if (t == 0) {
+    float m = m_initial ? m_initial[bh] : m_default;
+    float Gt = 0.f;
+    for (int u = 0; u < kGateThreads; ++u) { sMin[u] = m; m = fmaxf(m + sG[u], sA[u]); Gt += sG[u]; }
+    if (g_sum != nullptr) g_sum[bh] = Gt;   // total log forget gate of the sequence (for chaining segments)
   }
   __syncthreads();
+  if (!siging) {
+    float m = sMin[t];
+    for (int k = k0; k < k1; ++k) {
+      ms[k] = m;
+      const float mn = fmaxf(g_arr[k] + m, amax_arr[k]);
+      gb.gbar[(size_t)bh * NC + k] = expf(g_arr[k] + m - mn);
+      m = mn;
+      if (k == NC - 1) ms[NC] = m;
+    }
+  } else {
+    for (int k = k0; k < k1; ++k) {
+      ms[k] = 0.f;
+      gb.gbar[(size_t)bh * NC + k] = expf(g_arr[k]);
+      if (k == NC - 1) ms[NC] = 0.f;
+    }
+  }
+}
 
-  // ---- phase 3: per-token stabiliser and the three exponentiated gate vectors ----
-  for (int k = warp; k < NC; k += nwarps) {
-    const size_t base = tok0 + (size_t)k * L;
-    const float m_prev = m_states[(size_t)bh * (NC + 1) + k];
-    const float m_next = m_states[(size_t)bh * (NC + 1) + k + 1];
-    float carry = -INFINITY;
-    for (int j0 = 0; j0 < L; j0 += 32) {
-      const int j = j0 + lane;
-      float b = 0.f, x = -INFINITY;
-      if (j < L) { b = gb.vecB[base + j]; x = gb.iota[base + j] - b; }
+__global__ void __launch_bounds__(kGateThreads)
+gates_token_kernel(const float* __restrict__ n_out, GateBuffers gb, const float* __restrict__ m_states, int S, int L,
+                   int NC, int variant, float eps) {
+  const int bh = blockIdx.y;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int k = blockIdx.x * (kGateThreads / 32) + warp;
+  if (k >= NC) return;
+  const bool siging = variant != MLSTM_EXP;
+  const size_t base = (size_t)bh * S + (size_t)k * L;
+  const float m_prev = m_states[(size_t)bh * (NC + 1) + k];
+  const float m_next = m_states[(size_t)bh * (NC + 1) + k + 1];
+  float carry = -INFINITY;
+  for (int j0 = 0; j0 < L; j0 += 32) {
+    const int j = j0 + lane;
+    float b = 0.f, x = -INFINITY;
+    if (j < L) { b = gb.vecB[base + j]; x = gb.iota[base + j] - b; }
 #pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        float y = __shfl_up_sync(0xffffffffu, x, o);
-        if (lane >= o) x = fmaxf(x, y);
+    for (int o = 1; o < 32; o <<= 1) {
+      float y = __shfl_up_sync(0xffffffffu, x, o);
+      if (lane >= o) x = fmaxf(x, y);
+    }
+    x = fmaxf(x, carry);
+    carry = __shfl_sync(0xffffffffu, x, 31);
+    if (j < L) {
+      float m_i, bbar, abar;
+      const float a = gb.abar[base + j];
+      if (siging) {
+        m_i = 0.f; bbar = expf(b); abar = expf(a);
+      } else {
+        m_i = fmaxf(b + m_prev, b + x);
+        bbar = expf(b + m_prev - m_i);
+        abar = expf(a - m_next);
       }
-      x = fmaxf(x, carry);
-      carry = __shfl_sync(0xffffffffu, x, 31);
-      if (j < L) {
-        float m_i, bbar, abar;
-        const float a = gb.abar[base + j];
-        if (siging) {
-          m_i = 0.f; bbar = expf(b); abar = expf(a);
-        } else {
-          m_i = fmaxf(b + m_prev, b + x);
-          bbar = expf(b + m_prev - m_i);
-          abar = expf(a - m_next);
-        }
-        gb.m_tok[base + j] = m_i;
-        gb.bbar[base + j] = bbar;
-        gb.abar[base + j] = abar;
-        if (gb.inv_den) {
-          gb.inv_den[base + j] = (variant == MLSTM_SIG_NONORM || n_out == nullptr) ? 1.f : 1.f / (n_out[base + j] + eps);
-        }
+      gb.m_tok[base + j] = m_i;
+      gb.bbar[base + j] = bbar;
+      gb.abar[base + j] = abar;
+      if (gb.inv_den) {
+        gb.inv_den[base + j] = (variant == MLSTM_SIG_NONORM || n_out == nullptr) ? 1.f : 1.f / (n_out[base + j] + eps);
       }
     }
   }
@@ -218,8 +224,12 @@ template <typename T>
 int launch_gates_t(const void* i, const void* f, const float* m_initial, const float* n_out, const GateBuffers& gb,
                    float* m_states, const ChunkwiseDims& d, cudaStream_t st, float m_default, float* g_sum) {
   PhaseScope ps(PH_GATES, st);
-  gates_kernel<T><<<d.B * d.NH, kGateThreads, 0, st>>>((const T*)i, (const T*)f, m_initial, n_out, gb, m_states,
-                                                     d.S, d.L, d.NC, d.variant, d.eps, m_default, g_sum);
+  const dim3 grid(ceil_div(d.NC, kGateThreads / 32), d.B * d.NH);
+  gates_chunk_kernel<T><<<grid, kGateThreads, 0, st>>>((const T*)i, (const T*)f, gb, d.S, d.L, d.NC, d.variant);
+  MLSTM_LAUNCH_CHECK();
+  gates_scan_kernel<<<d.B * d.NH, kGateThreads, 0, st>>>(m_initial, gb, m_states, d.NC, d.variant, m_default, g_sum);
+  MLSTM_LAUNCH_CHECK();
+  gates_token_kernel<<<grid, kGateThreads, 0, st>>>(n_out, gb, m_states, d.S, d.L, d.NC, d.variant, d.eps);
   MLSTM_LAUNCH_CHECK();
   return MLSTM_OK;
 }
@@ -300,6 +310,20 @@ int launch_state_combine(const float* c_in, const float* n_in, const float* m_in
   dim3 grid((unsigned)std::min<size_t>((nC + 255) / 256, 64), BNH);
   state_combine_kernel<<<grid, 256, 0, st>>>(c_in, n_in, m_in, c_loc, n_loc, m_loc, g_total, c_out, n_out, m_out, DHQK,
                                             DHHV, variant);
+  MLSTM_LAUNCH_CHECK();
+  return MLSTM_OK;
+}
+
+// inv_den_t = 1 / (n_out_t + eps), or 1 where the variant has no normaliser
+__global__ void __launch_bounds__(256)
+inv_den_kernel(const float* __restrict__ n_out, float* __restrict__ inv_den, size_t ntok, int variant, float eps) {
+  const size_t t = (size_t)blockIdx.x * 256 + threadIdx.x;
+  if (t < ntok) inv_den[t] = (variant == MLSTM_SIG_NONORM || n_out == nullptr) ? 1.f : 1.f / (n_out[t] + eps);
+}
+
+int launch_inv_den(const float* n_out, float* inv_den, size_t ntok, int variant, float eps, cudaStream_t st) {
+  PhaseScope ps(PH_GATES, st);
+  inv_den_kernel<<<(unsigned)((ntok + 255) / 256), 256, 0, st>>>(n_out, inv_den, ntok, variant, eps);
   MLSTM_LAUNCH_CHECK();
   return MLSTM_OK;
 }

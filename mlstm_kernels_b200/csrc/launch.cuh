@@ -8,6 +8,7 @@ namespace mlstm {
 int launch_gates(int dtype, const void* i, const void* f, const float* m_initial, const float* n_out,
                  const GateBuffers& gb, float* m_states, const ChunkwiseDims& d, cudaStream_t st,
                  float m_default = 0.f, float* g_sum = nullptr);
+int launch_inv_den(const float* n_out, float* inv_den, size_t ntok, int variant, float eps, cudaStream_t st);
 int launch_state_combine(const float* c_in, const float* n_in, const float* m_in, const float* c_loc,
                          const float* n_loc, const float* m_loc, const float* g_total, float* c_out, float* n_out,
                          float* m_out, int BNH, int DHQK, int DHHV, int variant, cudaStream_t st);
