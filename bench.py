@@ -41,7 +41,7 @@ CPU_SAMPLE = dict(B=1, NH=16)
 
 
 # measured with ncu at NH=16, 256/256, chunk 128, bf16 (profiles/chunkwise_fwbw_tcgen05_ncu_full_B2_S8192.md)
-NCU_DRAM_BYTES_PER_CHUNK = {"recurrent_fw": 254758, "parallel_fw": 389478, "recurrent_bw": 242731, "parallel_bw": 715320}
+NCU_DRAM_BYTES_PER_CHUNK = {"recurrent_fw": 252488, "parallel_fw": 389250, "recurrent_bw": 242392, "parallel_bw": 717646}
 
 
 def impl_used_is_tcgen05(_lib, S, DHQK, DHHV, L):
