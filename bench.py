@@ -40,7 +40,8 @@ WORKLOAD = dict(name="c2_chunkwise_fwbw_mLSTMexp_B8_S8192_NH16_DHQK256_DHHV256_L
 CPU_SAMPLE = dict(B=1, NH=16)
 
 
-# measured with ncu at NH=16, 256/256, chunk 128, bf16 (profiles/chunkwise_fwbw_tcgen05_ncu_full_B2_S8192.md)
+# measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum) at NH=16, 256/256, chunk 128, bf16 on a quarter
+# batch, divided by its 2048 chunks; the ncu summaries are kept under profiles/
 NCU_DRAM_BYTES_PER_CHUNK = {"recurrent_fw": 252488, "parallel_fw": 389250, "recurrent_bw": 242392, "parallel_bw": 717646}
 
 
