@@ -47,26 +47,34 @@ struct RecParams {
 };
 
 constexpr int REC_THREADS = 608;                 // warp 0 TMA, 1 MMA, 2..9 gate the left tile, 10..17 own the state, 18 stores it
-constexpr int REC_STAGE_BYTES = 65536;           // left tile 32 KB + right tile 32 KB
+constexpr int REC_HALF = 64;                     // tokens per ring stage: half a chunk
+constexpr int REC_STAGE_BYTES = 32768;           // 64 tokens: left tile 16 KB + right tile 16 KB
+constexpr int REC_STAGES = 5;                    // operand ring depth (two and a half chunks in flight)
 constexpr int REC_NPART_BYTES = 2 * 32 * 128 * 4;   // double-buffered partial column sums of the gated left tile
-constexpr int REC_STAGES = 2;                    // operand ring depth
-constexpr int REC_OUT_BYTES = 2 * 32768;         // double-buffered bf16 state tile staged for the TMA store
-constexpr int REC_SMEM = REC_STAGES * REC_STAGE_BYTES + REC_NPART_BYTES + REC_OUT_BYTES + 1024;
+constexpr int REC_OUT_BYTES = 32768;             // bf16 state tile staged for the TMA store
+constexpr int rec_smem_bytes(bool bwd) {   // the backward recurrence has no n and needs no partial sums
+  return REC_STAGES * REC_STAGE_BYTES + (bwd ? 0 : REC_NPART_BYTES) + REC_OUT_BYTES + 1024;
+}
 
+// One ring stage holds 64 tokens of the left and of the right operand (boxes of 64 rows x 64 columns, 8 KB each:
+// left columns d0.., d0+64.., right columns e0.., e0+64..).  A chunk is two stages; the product of a chunk is
+// accumulated over both before the state warps fold it in.  The ring is deeper than one chunk so that the load of
+// chunk s+2 is already in flight while chunk s is being gated and multiplied.
 template <bool BWD>
 __global__ void __launch_bounds__(REC_THREADS, 1)
 rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUtensorMap mapR,
           const __grid_constant__ CUtensorMap mapS, RecParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  __shared__ uint64_t bar_full[REC_STAGES], bar_empty[REC_STAGES], bar_scaled[REC_STAGES], bar_acc_full[2], bar_acc_free[2], bar_nsum[2], bar_out_full[2], bar_out_free[2];
+  __shared__ uint64_t bar_full[REC_STAGES], bar_empty[REC_STAGES], bar_scaled[REC_STAGES], bar_acc_full[2], bar_acc_free[2], bar_nsum[2], bar_out_full, bar_out_free;
   __shared__ uint32_t s_tmem;
-  __shared__ float s_scale[REC_STAGES][CL];  // per-row scale of the left tile, staged by the producer warp
+  // per-row scale factors of the left tile, copied with the stage (backward: two factors per row)
+  __shared__ __align__(16) float s_scale[REC_STAGES][REC_HALF], s_scale2[BWD ? REC_STAGES : 1][REC_HALF];
   __shared__ float s_g[8];          // decay of the chunk, ring of eight (outlives the operand ring)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int e0 = blockIdx.x * 128, d0 = blockIdx.y * 128, bh = blockIdx.z;
-  const int NC = p.NC;
+  const int NC = p.NC, NH2 = 2 * p.NC;   // ring steps: two per chunk
   const bool do_n = (!BWD) && blockIdx.x == 0 && (p.n_states != nullptr || p.n_final != nullptr);
 
   if (tid == 0) {
@@ -75,8 +83,8 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&bar_acc_full[s], 1); mbar_init(&bar_acc_free[s], 256); mbar_init(&bar_nsum[s], 256);
-      mbar_init(&bar_out_full[s], 256); mbar_init(&bar_out_free[s], 1);
     }
+    mbar_init(&bar_out_full, 256); mbar_init(&bar_out_free, 1);
     fence_barrier_init();
     tma_prefetch_desc(&mapL); tma_prefetch_desc(&mapR); tma_prefetch_desc(&mapS);
   }
@@ -87,70 +95,62 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
   const uint32_t tmem = s_tmem;
 
   if (warp == 0) {
-    // ---------------- TMA producer (whole warp: also stages the per-row scales and the chunk decay) ----------------
-    // The scales of chunk s+1 are fetched from global memory before the wait for the stage of chunk s, so their
-    // latency never sits between a stage becoming free and the next TMA issue.
-    auto fetch = [&](int s, float (&sc)[4], float& g) {
-      const int ck = BWD ? NC - 1 - s : s;
-      const size_t row0 = (size_t)bh * p.S + (size_t)ck * CL;
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int r = lane + 32 * u;
-        sc[u] = p.lscale[row0 + r] * p.lmul;
-        if (BWD) sc[u] *= p.rscale[row0 + r];
-      }
-      g = p.gbar[(size_t)bh * NC + ck];
+    // ---------------- TMA producer ----------------
+    // The per-row scale vectors travel with the stage (bulk copies on the same barrier).  The decay of a chunk is a
+    // single float: the warp keeps the values of 32 consecutive steps in its lanes and fetches the next 32 a whole
+    // block ahead, so no global-memory latency sits between a stage becoming free and the next issue.
+    auto load_g = [&](int blk) -> float {
+      const int s = blk * 32 + lane;
+      return s < NC ? p.gbar[(size_t)bh * NC + (BWD ? NC - 1 - s : s)] : 0.f;
     };
+    float g_blk = load_g(0), g_nxt = load_g(1);
     int issued = 0;
-    float sc_next[4], g_next = 0.f;
-    if (NC > 0) fetch(0, sc_next, g_next);
-    for (int s = 0; s < NC; ++s) {
-      const int st = s % REC_STAGES;
-      float sc[4], g = g_next;
-#pragma unroll
-      for (int u = 0; u < 4; ++u) sc[u] = sc_next[u];
-      if (s + 1 < NC) fetch(s + 1, sc_next, g_next);
+    for (int h = 0; h < NH2; ++h) {
+      const int st = h % REC_STAGES, s = h >> 1;
+      if ((h & 1) == 0) {
+        if (s > 0 && (s & 31) == 0) { g_blk = g_nxt; g_nxt = load_g((s >> 5) + 1); }
+        const float g = __shfl_sync(0xffffffffu, g_blk, s & 31);
+        if (lane == 0) s_g[s & 7] = g;   // read two or more barrier hand-overs later (MMA commit -> state warps)
+      }
       int ok = 1;
-      if (lane == 0) ok = mbar_wait(&bar_empty[st], ((s / REC_STAGES) & 1) ^ 1, &g_sm100_status, 101) ? 1 : 0;
+      if (lane == 0) ok = mbar_wait(&bar_empty[st], ((h / REC_STAGES) & 1) ^ 1, &g_sm100_status, 101) ? 1 : 0;
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
-      const int ck = BWD ? NC - 1 - s : s;
-      const int row0 = bh * p.S + ck * CL;
-#pragma unroll
-      for (int u = 0; u < 4; ++u) s_scale[st][lane + 32 * u] = sc[u];
-      if (lane == 0) s_g[s & 7] = g;
-      __syncwarp();
       if (lane == 0) {
+        const int ck = BWD ? NC - 1 - s : s;
+        const int row0 = bh * p.S + ck * CL + (h & 1) * REC_HALF;
         uint8_t* sl = smem + st * REC_STAGE_BYTES;
-        mbar_expect_tx(&bar_full[st], REC_STAGE_BYTES);
+        mbar_expect_tx(&bar_full[st], REC_STAGE_BYTES + (BWD ? 2 : 1) * REC_HALF * 4);
+        bulk_load(s_scale[st], p.lscale + row0, REC_HALF * 4, &bar_full[st]);
+        if (BWD) bulk_load(s_scale2[st], p.rscale + row0, REC_HALF * 4, &bar_full[st]);
         tma_load_2d(sl, &mapL, &bar_full[st], d0, row0);
-        tma_load_2d(sl + 16384, &mapL, &bar_full[st], d0 + 64, row0);
-        tma_load_2d(sl + 32768, &mapR, &bar_full[st], e0, row0);
-        tma_load_2d(sl + 49152, &mapR, &bar_full[st], e0 + 64, row0);
+        tma_load_2d(sl + 8192, &mapL, &bar_full[st], d0 + 64, row0);
+        tma_load_2d(sl + 16384, &mapR, &bar_full[st], e0, row0);
+        tma_load_2d(sl + 24576, &mapR, &bar_full[st], e0 + 64, row0);
       }
-      issued = s + 1;
+      issued = h + 1;
     }
-    if (lane == 0 && issued < NC && issued > 0) {  // error path: let the copies in flight land before the CTA retires
+    if (lane == 0 && issued < NH2 && issued > 0) {  // error path: let the copies in flight land before the CTA retires
       int dummy = 1;
-      for (int s = max(0, issued - REC_STAGES); s < issued; ++s)
-        mbar_wait(&bar_full[s % REC_STAGES], (s / REC_STAGES) & 1, &dummy, 1);
+      for (int h = max(0, issued - REC_STAGES); h < issued; ++h)
+        mbar_wait(&bar_full[h % REC_STAGES], (h / REC_STAGES) & 1, &dummy, 1);
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc_bf16(128, 128, 1, 1);
-      for (int s = 0; s < NC; ++s) {
-        const int st = s % REC_STAGES, buf = s & 1;
-        if (!mbar_wait(&bar_scaled[st], (s / REC_STAGES) & 1, &g_sm100_status, 102)) break;
-        if (!mbar_wait(&bar_acc_free[buf], ((s >> 1) & 1) ^ 1, &g_sm100_status, 103)) break;
+      for (int h = 0; h < NH2; ++h) {
+        const int st = h % REC_STAGES, s = h >> 1, buf = s & 1;
+        if (!mbar_wait(&bar_scaled[st], (h / REC_STAGES) & 1, &g_sm100_status, 102)) break;
+        if ((h & 1) == 0 && !mbar_wait(&bar_acc_free[buf], ((s >> 1) & 1) ^ 1, &g_sm100_status, 103)) break;
         tc_fence_after_sync();
-        const uint32_t sl = smem_u32(smem + st * REC_STAGE_BYTES), sr = sl + 32768;
+        const uint32_t sl = smem_u32(smem + st * REC_STAGE_BYTES), sr = sl + 16384;
 #pragma unroll
-        for (int kk = 0; kk < CL / 16; ++kk)
-          umma_ss(tmem + buf * 128, umma_desc_sw128(sl + kk * 2048, 16384, 1024),
-                  umma_desc_sw128(sr + kk * 2048, 16384, 1024), idesc, kk > 0);
+        for (int kk = 0; kk < REC_HALF / 16; ++kk)
+          umma_ss(tmem + buf * 128, umma_desc_sw128(sl + kk * 2048, 8192, 1024),
+                  umma_desc_sw128(sr + kk * 2048, 8192, 1024), idesc, ((h & 1) || kk > 0) ? 1u : 0u);
         umma_commit(&bar_empty[st]);
-        umma_commit(&bar_acc_full[buf]);
+        if (h & 1) umma_commit(&bar_acc_full[buf]);
       }
     }
   } else if (warp < 10) {
@@ -160,34 +160,37 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
     if (do_n && ct < 128 && p.n_init) nval = p.n_init[(size_t)bh * p.DHQK + d0 + ct];
     if (do_n && p.n_states != nullptr && ct < 128) p.n_states[((size_t)bh * (NC + 1)) * p.DHQK + d0 + ct] = nval;
     bool ok = true;
-    for (int s = 0; s < NC; ++s) {
-      const int st = s % REC_STAGES, nb = s & 1;
-      if (!mbar_wait(&bar_full[st], (s / REC_STAGES) & 1, &g_sm100_status, 105)) { ok = false; break; }
-      // two 64-column boxes of 128 rows x 128 B, 128-byte swizzle: the scale depends on the row only
+    float ns[2][8];
+    for (int h = 0; h < NH2; ++h) {
+      const int st = h % REC_STAGES, s = h >> 1, nb = s & 1;
+      if (!mbar_wait(&bar_full[st], (h / REC_STAGES) & 1, &g_sm100_status, 105)) { ok = false; break; }
+      // two 64-column boxes of 64 rows x 128 B, 128-byte swizzle: the scale depends on the row only
       uint8_t* sl = smem + st * REC_STAGE_BYTES;
-      float ns[2][8];
+      if ((h & 1) == 0) {
 #pragma unroll
-      for (int b = 0; b < 2; ++b)
+        for (int b = 0; b < 2; ++b)
 #pragma unroll
-        for (int e = 0; e < 8; ++e) ns[b][e] = 0.f;
+          for (int e = 0; e < 8; ++e) ns[b][e] = 0.f;
+      }
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const int r = (ct >> 3) + 32 * (u & 3);
-        const float sc = s_scale[st][r];
-        uint4* ptr = reinterpret_cast<uint4*>(sl + (u >> 2) * 16384 + r * 128 + (ct & 7) * 16);
+      for (int u = 0; u < 4; ++u) {
+        const int r = (ct >> 3) + 32 * (u & 1);
+        float sc = s_scale[st][r] * p.lmul;
+        if (BWD) sc *= s_scale2[st][r];
+        uint4* ptr = reinterpret_cast<uint4*>(sl + (u >> 1) * 8192 + r * 128 + (ct & 7) * 16);
         uint4 v = *ptr;
         uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           __nv_bfloat162 h2 = *reinterpret_cast<__nv_bfloat162*>(&w[e]);
           const float lo = __low2float(h2) * sc, hi = __high2float(h2) * sc;
-          ns[u >> 2][2 * e] += lo; ns[u >> 2][2 * e + 1] += hi;
+          ns[u >> 1][2 * e] += lo; ns[u >> 1][2 * e + 1] += hi;
           w[e] = pack_bf16(lo, hi);
         }
         *ptr = make_uint4(w[0], w[1], w[2], w[3]);
       }
       float* npart = reinterpret_cast<float*>(smem + REC_STAGES * REC_STAGE_BYTES) + nb * (32 * 128);
-      if (do_n) {
+      if (do_n && (h & 1)) {
         const int lc = (ct & 7) ^ ((ct >> 3) & 7);   // logical 16-byte column chunk behind the swizzle
 #pragma unroll
         for (int b = 0; b < 2; ++b) {
@@ -198,7 +201,7 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
       }
       fence_proxy_async_smem();
       mbar_arrive(&bar_scaled[st]);
-      if (do_n) {   // n does not need the tensor cores: n_{s+1} = gbar n_s + column sums of the gated left tile
+      if (do_n && (h & 1)) {   // n does not need the tensor cores: n_{s+1} = gbar n_s + column sums of the gated left tile
         mbar_arrive(&bar_nsum[nb]);
         if (!mbar_wait(&bar_nsum[nb], (s >> 1) & 1, &g_sm100_status, 106)) { ok = false; break; }
         if (ct < 128) {
@@ -214,17 +217,16 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
   } else if (warp == 18) {
     // ---------------- store warp: one TMA store per 64-column box of each staged state tile ----------------
     if (lane == 0 && p.c_states != nullptr) {
-      uint8_t* stage_base = smem + REC_STAGES * REC_STAGE_BYTES + REC_NPART_BYTES;
+      uint8_t* stage_base = smem + REC_STAGES * REC_STAGE_BYTES + (BWD ? 0 : REC_NPART_BYTES);
       for (int n = 0; n <= NC; ++n) {
-        const int ob = n & 1;
-        if (!mbar_wait(&bar_out_full[ob], (n >> 1) & 1, &g_sm100_status, 108)) break;
+        if (!mbar_wait(&bar_out_full, n & 1, &g_sm100_status, 108)) break;
         const int slot = BWD ? NC - n : n;
         const int y = (bh * (NC + 1) + slot) * p.DHQK + d0;
-        tma_store_2d(&mapS, stage_base + ob * 32768, e0, y);
-        tma_store_2d(&mapS, stage_base + ob * 32768 + 16384, e0 + 64, y);
+        tma_store_2d(&mapS, stage_base, e0, y);
+        tma_store_2d(&mapS, stage_base + 16384, e0 + 64, y);
         tma_store_commit();
-        asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");   // the previous tile has left its buffer
-        if (n >= 1) mbar_arrive(&bar_out_free[ob ^ 1]);
+        tma_store_wait_read();          // the tile has left the staging buffer
+        mbar_arrive(&bar_out_free);
       }
       tma_store_wait_all();   // all state tiles have been written before the CTA retires
     }
@@ -243,15 +245,14 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
       for (int c = 0; c < 64; ++c) C[c] = 0.f;
     }
     // The bf16 state tile goes to shared memory in the 128-byte-swizzled box layout and leaves with one TMA store
-    // per 64-column box (coalesced, asynchronous); two staging buffers, one store group in flight.
-    uint8_t* stage_base = smem + REC_STAGES * REC_STAGE_BYTES + REC_NPART_BYTES;
+    // per 64-column box (coalesced, asynchronous).  One staging buffer: the store of a tile has read it long before
+    // the next tile is ready (a chunk takes longer than the read), so the wait below rarely blocks.
+    uint8_t* stage_base = smem + REC_STAGES * REC_STAGE_BYTES + (BWD ? 0 : REC_NPART_BYTES);
     int n_out = 0;   // tiles written so far
-    auto store_c = [&](int slot) -> bool {
-      (void)slot;
+    auto store_c = [&]() -> bool {
       if (p.c_states == nullptr) return true;
-      const int ob = n_out & 1;
-      if (n_out >= 2 && !mbar_wait(&bar_out_free[ob], ((n_out >> 1) - 1) & 1, &g_sm100_status, 107)) return false;
-      uint8_t* rowp = stage_base + ob * 32768 + half * 16384 + row * 128;
+      if (n_out >= 1 && !mbar_wait(&bar_out_free, (n_out - 1) & 1, &g_sm100_status, 107)) return false;
+      uint8_t* rowp = stage_base + half * 16384 + row * 128;
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
         uint4 v;
@@ -260,11 +261,11 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
         *reinterpret_cast<uint4*>(rowp + ((c ^ (row & 7)) << 4)) = v;
       }
       fence_proxy_async_smem();
-      mbar_arrive(&bar_out_full[ob]);   // the store warp ships the tile
+      mbar_arrive(&bar_out_full);   // the store warp ships the tile
       ++n_out;
       return true;
     };
-    bool ok = store_c(BWD ? NC : 0);   // slot written before step s: forward s, backward NC - s
+    bool ok = store_c();   // the state before the first step (slot 0 forward, slot NC backward)
     for (int s = 0; s < NC && ok; ++s) {
       const int buf = s & 1;
       if (!mbar_wait(&bar_acc_full[buf], (s >> 1) & 1, &g_sm100_status, 104)) { ok = false; break; }
@@ -281,7 +282,7 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
       }
       tc_fence_before_sync();
       mbar_arrive(&bar_acc_free[buf]);
-      ok = store_c(BWD ? NC - 1 - s : s + 1);
+      ok = store_c();
     }
     if (ok && p.c_final) {
       float4* fd = reinterpret_cast<float4*>(p.c_final + ((size_t)bh * p.DHQK + d) * p.DHHV + ecol);
@@ -678,13 +679,17 @@ static bool state_map(CUtensorMap* m, const void* base, const ChunkwiseDims& d, 
 template <bool BWD>
 static int launch_rec(const void* left, const void* right, const RecParams& rp, const ChunkwiseDims& d, cudaStream_t st) {
   CUtensorMap mL, mR, mS;
-  if (!tok_map(&mL, left, d, d.DHQK) || !tok_map(&mR, right, d, d.DHHV)) return MLSTM_ERR_CUDA;
+  // recurrence operands arrive in half-chunk boxes (64 tokens x 64 columns)
+  const uint64_t ntok = (uint64_t)d.B * d.NH * d.S;
+  if (!sm100_host::make_map_bf16(&mL, left, ntok, (uint64_t)d.DHQK, REC_HALF, 64) ||
+      !sm100_host::make_map_bf16(&mR, right, ntok, (uint64_t)d.DHHV, REC_HALF, 64))
+    return MLSTM_ERR_CUDA;
   // store map over the per-chunk states; when no states are wanted (segment summary) the map is never used
   if (!state_map(&mS, rp.c_states ? (const void*)rp.c_states : left, d, 128)) return MLSTM_ERR_CUDA;
   auto kern = rec_sm100<BWD>;
-  MLSTM_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, REC_SMEM));
+  MLSTM_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, rec_smem_bytes(BWD)));
   dim3 grid(d.DHHV / 128, d.DHQK / 128, d.B * d.NH);
-  kern<<<grid, REC_THREADS, REC_SMEM, st>>>(mL, mR, mS, rp);
+  kern<<<grid, REC_THREADS, rec_smem_bytes(BWD), st>>>(mL, mR, mS, rp);
   MLSTM_LAUNCH_CHECK();
   return MLSTM_OK;
 }
