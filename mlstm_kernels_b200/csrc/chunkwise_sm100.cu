@@ -329,7 +329,7 @@ constexpr int PAR_SMEM = 2 * PAR_STAGE + 1024;
 struct ParShared {
   uint64_t bar_full[2], bar_empty[2], bar_sfull, bar_gated, bar_hfull, bar_dot, bar_pair[4], bar_out;
   uint32_t tmem;
-  float s_colA[CL], s_colF[CL];  // per-column terms of the gate matrix (see par_body)
+  __align__(16) float s_colE[CL];  // per-column term of the gate exponent, base 2 (see par_body)
   float s_part[2][CL];           // per-row partial sums exchanged between the two warps of a row
   float s_qn[2][CL];
   float s_n[512];
@@ -337,9 +337,10 @@ struct ParShared {
 
 // One body for the four modes; `mode` is uniform over the CTA, so every branch on it is uniform (a single copy of the
 // code keeps the instruction cache warm when CTAs of different modes share an SM).
-// Gate factor of element (r, c), written with separable exponent terms:
-//   lower (H, DQ), valid c <= r:  rowF_r * exp(rowA_r + colA_c),  rowA = b_r - m_r,     colA = iota_c - b_c, rowF = s [* 1/(den_r+eps)]
-//   upper (DV, DK), valid c >= r: rowF_r * colF_c * exp(...),     rowA = iota_r - b_r,  colA = b_c - m_c,    rowF = s, colF = 1/(den_c+eps)
+// Gate factor of element (r, c): 2^(rowE_r + colE_c), every positive factor folded into the exponent:
+//   lower (H, DQ), valid c <= r:  rowE = (b_r - m_r) log2e + log2(s [/(den_r+eps)]),   colE = (iota_c - b_c) log2e
+//   upper (DV, DK), valid c >= r: rowE = (iota_r - b_r) log2e + log2(s),               colE = (b_c - m_c) log2e - log2(den_c+eps)
+// so one element costs an add, an ex2 and a multiply.
 __device__ __forceinline__ void
 par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const CUtensorMap* mapX,
          const CUtensorMap* mapSt, const CUtensorMap* mapE, const CUtensorMap* mapO, const ParParams& p,
@@ -454,12 +455,10 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
     const size_t tok = (size_t)row0 + r;
     const float b_r = p.vecB[tok], iota_r = p.iota[tok], m_r = p.m_tok[tok];
     const float inv_r = (mode == PM_H) ? 1.f : p.inv_den[tok];
-    const float rowA = LOWER ? (b_r - m_r) : (iota_r - b_r);
-    const float rowF = (mode == PM_DQ) ? p.qk_scale * inv_r : p.qk_scale;
-    if (half == 0) {
-      sh.s_colA[r] = LOWER ? (iota_r - b_r) : (b_r - m_r);
-      sh.s_colF[r] = LOWER ? 1.f : inv_r;
-    }
+    constexpr float kLog2e = 1.4426950408889634f;
+    const float rowE = (LOWER ? (b_r - m_r) : (iota_r - b_r)) * kLog2e +
+                       __log2f((mode == PM_DQ) ? p.qk_scale * inv_r : p.qk_scale);
+    if (half == 0) sh.s_colE[r] = LOWER ? (iota_r - b_r) * kLog2e : (b_r - m_r) * kLog2e + __log2f(inv_r);
     float rowscale;
     if (mode == PM_H) rowscale = p.qk_scale * p.bbar[tok];
     else if (mode == PM_DQ) rowscale = p.qk_scale * p.bbar[tok] * inv_r;
@@ -503,15 +502,22 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
     ok = ok && mbar_wait(&sh.bar_sfull, 0, &g_sm100_status, 205);
     if (ok) {
       tc_fence_after_sync();
+      // Tensor memory is read 16 columns at a time, the next load in flight while the current one is processed.
       // row-scale the inter-chunk term in place
 #pragma unroll 1
       for (int cq = half; cq < 4; cq += 2) {
-        uint32_t v[32];
-        tmem_ld32(tAcc + lane_base + cq * 32, v);
-        tmem_wait_ld();
+        uint32_t va[16], vb[16];
+        const uint32_t ta = tAcc + lane_base + cq * 32;
+        tmem_ld16(ta, va);
+        tmem_wait_ld(va);
+        tmem_ld16(ta + 16, vb);
 #pragma unroll
-        for (int c = 0; c < 32; ++c) v[c] = __float_as_uint(__uint_as_float(v[c]) * rowscale);
-        tmem_st32(tAcc + lane_base + cq * 32, v);
+        for (int c = 0; c < 16; ++c) va[c] = __float_as_uint(__uint_as_float(va[c]) * rowscale);
+        tmem_wait_ld(vb);
+        tmem_st16(ta, va);
+#pragma unroll
+        for (int c = 0; c < 16; ++c) vb[c] = __float_as_uint(__uint_as_float(vb[c]) * rowscale);
+        tmem_st16(ta + 16, vb);
       }
       // gate the score tile; the bf16 result goes back to tensor memory as the A operand of the second product.
       // Both warps of a quarter first read their chunks, then (after a warp-pair sync) write: the bf16 words of
@@ -526,22 +532,32 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
 #pragma unroll
           for (int c = 0; c < 16; ++c) pk[u][c] = 0u;
         } else {
-          uint32_t v[32];
-          tmem_ld32(tS + lane_base + c0, v);
-          tmem_wait_ld();
           const bool diag = (cq == quarter);   // only the diagonal chunk needs the causal mask
+          uint32_t va[16], vb[16];
+          tmem_ld16(tS + lane_base + c0, va);
+          tmem_wait_ld(va);
+          tmem_ld16(tS + lane_base + c0 + 16, vb);
 #pragma unroll
-          for (int c = 0; c < 16; ++c) {
-            float g2[2];
+          for (int hh = 0; hh < 2; ++hh) {
+            if (hh == 1) tmem_wait_ld(vb);
+            const uint32_t (&v)[16] = hh ? vb : va;
+            const float4* ce = reinterpret_cast<const float4*>(sh.s_colE + c0 + 16 * hh);
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              const int cl = 2 * c + h;        // column inside the chunk; row inside the chunk is `lane`
-              float val = __uint_as_float(v[cl]) * rowF * sh.s_colF[c0 + cl] * __expf(rowA + sh.s_colA[c0 + cl]);
-              if (diag && (LOWER ? (cl > lane) : (cl < lane))) val = 0.f;
-              g2[h] = val;
-              rowsum += val;
+            for (int c4 = 0; c4 < 4; ++c4) {
+              const float4 e4 = ce[c4];
+              const float ee[4] = {e4.x, e4.y, e4.z, e4.w};
+              float g4[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int cl = 16 * hh + 4 * c4 + e;   // column inside the chunk; row inside the chunk is `lane`
+                float val = __uint_as_float(v[4 * c4 + e]) * ex2_approx(rowE + ee[e]);
+                if (diag && (LOWER ? (cl > lane) : (cl < lane))) val = 0.f;
+                g4[e] = val;
+                rowsum += val;
+              }
+              pk[u][8 * hh + 2 * c4] = pack_bf16(g4[0], g4[1]);
+              pk[u][8 * hh + 2 * c4 + 1] = pack_bf16(g4[2], g4[3]);
             }
-            pk[u][c] = pack_bf16(g2[0], g2[1]);
           }
         }
       }
