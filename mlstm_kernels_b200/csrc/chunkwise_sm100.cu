@@ -593,22 +593,28 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
         ok = mbar_wait(&sh.bar_full[ste], ((ND + 1) >> 1) & 1, &g_sm100_status, 208);
         erow = smem + ste * PAR_STAGE + r * 128;
       }
-      float dot = 0.f;
-      // the output tile is staged (bf16, 128-byte-swizzled boxes) in the ring stage the X tile occupied - every MMA
-      // that read the ring has completed - and leaves the SM with two TMA stores
+      float dot4[4] = {0.f, 0.f, 0.f, 0.f};   // four partial sums: no 64-long chain of dependent FMAs
+      // The output tile is staged (bf16, two boxes of 128 rows x 128 bytes, 16-byte pieces XOR-swizzled by the row)
+      // in the ring stage the X tile occupied - every MMA that read the ring has completed - and is then written out
+      // by all element-wise warps together, each warp instruction covering two full 256-byte rows of the tile.  Plain
+      // stores are posted, so the CTA retires without waiting for them.
       uint8_t* ostage = smem + (ND & 1) * PAR_STAGE;
       if (ok) {
 #pragma unroll 1
         for (int cq = half; cq < 4; cq += 2) {
-          uint32_t v[32];
-          tmem_ld32(tAcc + lane_base + cq * 32, v);
-          tmem_wait_ld();
+          uint32_t va[16], vb[16];
+          const uint32_t ta = tAcc + lane_base + cq * 32;
+          tmem_ld16(ta, va);
+          tmem_wait_ld(va);
+          tmem_ld16(ta + 16, vb);
           uint8_t* orow = ostage + (cq >> 1) * 16384 + r * 128;
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
+            if (c == 2) tmem_wait_ld(vb);
+            const uint32_t (&v)[16] = (c < 2) ? va : vb;
             float x[8];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) x[e] = __uint_as_float(v[8 * c + e]) * inv;
+            for (int e = 0; e < 8; ++e) x[e] = __uint_as_float(v[8 * (c & 1) + e]) * inv;
             const int sw = (((cq & 1) * 4 + c) ^ (r & 7)) << 4;   // 16-byte chunk (cq*4 + c) of the row, swizzled
             if (HAS_E) {
               const uint4 ev = *reinterpret_cast<const uint4*>(erow + (cq >> 1) * 16384 + sw);
@@ -616,8 +622,8 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
                 const __nv_bfloat162 h2 = *reinterpret_cast<const __nv_bfloat162*>(&w[e]);
-                dot = fmaf(__low2float(h2), x[2 * e], dot);
-                dot = fmaf(__high2float(h2), x[2 * e + 1], dot);
+                dot4[e] = fmaf(__low2float(h2), x[2 * e], dot4[e]);
+                dot4[e] = fmaf(__high2float(h2), x[2 * e + 1], dot4[e]);
               }
             }
             uint4 o;
@@ -626,13 +632,18 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
             *reinterpret_cast<uint4*>(orow + sw) = o;
           }
         }
-        fence_proxy_async_smem();
+        const float dot = (dot4[0] + dot4[1]) + (dot4[2] + dot4[3]);
         mbar_arrive(&sh.bar_out);
-        if (warp == 2 && lane == 0 && mbar_wait(&sh.bar_out, 0, &g_sm100_status, 211)) {
-          tma_store_2d(mapO, ostage, o0, row0);
-          tma_store_2d(mapO, ostage + 16384, o0 + 64, row0);
-          tma_store_commit();
-          tma_store_wait_all();
+        if (mbar_wait(&sh.bar_out, 0, &g_sm100_status, 211)) {
+          __nv_bfloat16* outp = (mode == PM_H) ? p.out_h : (mode == PM_DV) ? p.out_dv : (mode == PM_DK) ? p.out_dk : p.out_dq;
+          uint8_t* gbase = reinterpret_cast<uint8_t*>(outp + (size_t)row0 * DO + o0);
+          const int ew = warp - 2, j = lane & 15;          // 16-byte piece j of the 256-byte tile row
+#pragma unroll
+          for (int i2 = 0; i2 < 8; ++i2) {
+            const int orow_i = 16 * i2 + 2 * ew + (lane >> 4);
+            const uint4 o = *reinterpret_cast<const uint4*>(ostage + (j >> 3) * 16384 + orow_i * 128 + (((j & 7) ^ (orow_i & 7)) << 4));
+            *reinterpret_cast<uint4*>(gbase + (size_t)orow_i * DO * 2 + j * 16) = o;
+          }
         }
         if (HAS_E) {
           sh.s_qn[half][r] = dot;
