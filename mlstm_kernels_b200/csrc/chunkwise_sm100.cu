@@ -322,12 +322,14 @@ struct ParParams {
 };
 
 constexpr int PAR_THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2..9 element-wise
-constexpr int PAR_STAGE = 49152;  // A slice 16 KB + B slice 16 KB + state slice 16 KB (or a 32 KB 128 x 128 tile)
-constexpr int PAR_SMEM = 2 * PAR_STAGE + 1024;
+constexpr int PAR_STAGE = 32768;  // two 16 KB boxes: (A, B) slice pair, (A, state) slice pair, or a 128 x 128 tile
+constexpr int PAR_NST = 3;        // ring depth
+constexpr int PAR_SMEM = PAR_NST * PAR_STAGE + 1024;
 
 // Shared-memory control block of one intra-chunk CTA (the operand ring lives in dynamic shared memory).
 struct ParShared {
-  uint64_t bar_full[2], bar_empty[2], bar_sfull, bar_gated, bar_hfull, bar_dot, bar_pair[4], bar_out;
+  uint64_t bar_full[PAR_NST], bar_empty[PAR_NST], bar_qdone[PAR_NST], bar_sfull, bar_afull, bar_gated, bar_hfull, bar_dot,
+      bar_pair[4], bar_out;
   uint32_t tmem;
   __align__(16) float s_colE[CL];  // per-column term of the gate exponent, base 2 (see par_body)
   float s_part[2][CL];           // per-row partial sums exchanged between the two warps of a row
@@ -360,8 +362,10 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
   const bool use_n = (mode == PM_H) && p.variant != MLSTM_SIG_NONORM && p.n_states != nullptr;
 
   if (tid == 0) {
-    for (int s = 0; s < 2; ++s) { mbar_init(&sh.bar_full[s], 1); mbar_init(&sh.bar_empty[s], use_n ? 9 : 1); }
-    mbar_init(&sh.bar_sfull, 1); mbar_init(&sh.bar_gated, 256); mbar_init(&sh.bar_hfull, 1); mbar_init(&sh.bar_dot, 256);
+    for (int s = 0; s < PAR_NST; ++s) {
+      mbar_init(&sh.bar_full[s], 1); mbar_init(&sh.bar_empty[s], 1); mbar_init(&sh.bar_qdone[s], 8);
+    }
+    mbar_init(&sh.bar_sfull, 1); mbar_init(&sh.bar_afull, 1); mbar_init(&sh.bar_gated, 256); mbar_init(&sh.bar_hfull, 1); mbar_init(&sh.bar_dot, 256);
     for (int s = 0; s < 4; ++s) mbar_init(&sh.bar_pair[s], 64);
     mbar_init(&sh.bar_out, 256);
     fence_barrier_init();
@@ -375,7 +379,10 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
   tc_fence_after_sync();
   const uint32_t tmem = sh.tmem;
   const uint32_t tS = tmem, tAcc = tmem + 128;
-  const int n_loads = ND + 1 + (HAS_E ? 1 : 0);
+  // Ring loads, in order: ND (A, B) slice pairs for the score product, ND (A, state) slice pairs for the inter-chunk
+  // product (A comes from L2 the second time), the X tile, the E tile.  The score is complete - and the element-wise
+  // warps start gating - while the second group is still arriving.
+  const int n_loads = 2 * ND + 1 + (HAS_E ? 1 : 0);
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -383,31 +390,38 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
       const int slot = LOWER ? ck : ck + 1;
       const int srow = (bh * (NC + 1) + slot) * p.DHQK;
       int issued = 0;
-      for (int it = 0; it < n_loads; ++it) {
-        const int st = it & 1;
-        if (!mbar_wait(&sh.bar_empty[st], ((it >> 1) & 1) ^ 1, &g_sm100_status, 201)) break;
+      for (int ld = 0; ld < n_loads; ++ld) {
+        const int st = ld % PAR_NST, use = ld / PAR_NST;
+        if (!mbar_wait(&sh.bar_empty[st], (use & 1) ^ 1, &g_sm100_status, 201)) break;
+        // the element-wise warps read the A box of a score pair (q . n): the stage is reused only after they are done
+        if (use_n && ld >= PAR_NST && ld - PAR_NST < ND &&
+            !mbar_wait(&sh.bar_qdone[st], ((use - 1) & 1), &g_sm100_status, 212))
+          break;
         uint8_t* sb = smem + st * PAR_STAGE;
-        if (it < ND) {
-          mbar_expect_tx(&sh.bar_full[st], PAR_STAGE);
+        mbar_expect_tx(&sh.bar_full[st], PAR_STAGE);
+        if (ld < ND) {
+          tma_load_2d(sb, mapA, &sh.bar_full[st], 64 * ld, row0);
+          tma_load_2d(sb + 16384, mapB, &sh.bar_full[st], 64 * ld, row0);
+        } else if (ld < 2 * ND) {
+          const int it = ld - ND;
           tma_load_2d(sb, mapA, &sh.bar_full[st], 64 * it, row0);
-          tma_load_2d(sb + 16384, mapB, &sh.bar_full[st], 64 * it, row0);
           if (ST_MN) {
-            tma_load_2d(sb + 32768, mapSt, &sh.bar_full[st], o0, srow + 64 * it);
-            tma_load_2d(sb + 32768 + 8192, mapSt, &sh.bar_full[st], o0 + 64, srow + 64 * it);
+            tma_load_2d(sb + 16384, mapSt, &sh.bar_full[st], o0, srow + 64 * it);
+            tma_load_2d(sb + 16384 + 8192, mapSt, &sh.bar_full[st], o0 + 64, srow + 64 * it);
           } else {
-            tma_load_2d(sb + 32768, mapSt, &sh.bar_full[st], 64 * it, srow + o0);
+            tma_load_2d(sb + 16384, mapSt, &sh.bar_full[st], 64 * it, srow + o0);
           }
         } else {
-          const CUtensorMap* m = (it == ND) ? mapX : mapE;
-          mbar_expect_tx(&sh.bar_full[st], 32768);
+          const CUtensorMap* m = (ld == 2 * ND) ? mapX : mapE;
           tma_load_2d(sb, m, &sh.bar_full[st], o0, row0);
           tma_load_2d(sb + 16384, m, &sh.bar_full[st], o0 + 64, row0);
         }
-        issued = it + 1;
+        issued = ld + 1;
       }
       if (issued < n_loads && issued > 0) {  // error path: let the copies in flight land before the CTA retires
         int dummy = 1;
-        for (int it = max(0, issued - 2); it < issued; ++it) mbar_wait(&sh.bar_full[it & 1], (it >> 1) & 1, &dummy, 1);
+        for (int ld = max(0, issued - PAR_NST); ld < issued; ++ld)
+          mbar_wait(&sh.bar_full[ld % PAR_NST], (ld / PAR_NST) & 1, &dummy, 1);
       }
     }
   } else if (warp == 1) {
@@ -417,26 +431,34 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
       const uint32_t idesc_st = ST_MN ? umma_idesc_bf16(128, 128, 0, 1) : umma_idesc_bf16(128, 128, 0, 0);
       constexpr uint32_t idesc_x = umma_idesc_bf16(128, 128, 0, 1);
       bool ok = true;
-      for (int it = 0; it < ND; ++it) {
-        const int st = it & 1;
-        if (!mbar_wait(&sh.bar_full[st], (it >> 1) & 1, &g_sm100_status, 202)) { ok = false; break; }
+      for (int ld = 0; ld < ND; ++ld) {            // score: S = A . B^T
+        const int st = ld % PAR_NST;
+        if (!mbar_wait(&sh.bar_full[st], (ld / PAR_NST) & 1, &g_sm100_status, 202)) { ok = false; break; }
         tc_fence_after_sync();
-        const uint32_t sa = smem_u32(smem + st * PAR_STAGE), sb = sa + 16384, ss = sa + 32768;
+        const uint32_t sa = smem_u32(smem + st * PAR_STAGE), sb = sa + 16384;
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
           umma_ss(tS, umma_desc_sw128(sa + kk * 32, 16, 1024), umma_desc_sw128(sb + kk * 32, 16, 1024), idesc_s,
-                  (it > 0 || kk > 0) ? 1u : 0u);
+                  (ld > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(&sh.bar_empty[st]);
+      }
+      if (ok) umma_commit(&sh.bar_sfull);
+      for (int ld = ND; ld < 2 * ND && ok; ++ld) {  // inter-chunk term: Acc = A . State
+        const int st = ld % PAR_NST;
+        if (!mbar_wait(&sh.bar_full[st], (ld / PAR_NST) & 1, &g_sm100_status, 213)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t sa = smem_u32(smem + st * PAR_STAGE), ss = sa + 16384;
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
           const uint64_t bdesc = ST_MN ? umma_desc_sw128(ss + kk * 2048, 8192, 1024) : umma_desc_sw128(ss + kk * 32, 16, 1024);
-          umma_ss(tAcc, umma_desc_sw128(sa + kk * 32, 16, 1024), bdesc, idesc_st, (it > 0 || kk > 0) ? 1u : 0u);
+          umma_ss(tAcc, umma_desc_sw128(sa + kk * 32, 16, 1024), bdesc, idesc_st, (ld > ND || kk > 0) ? 1u : 0u);
         }
         umma_commit(&sh.bar_empty[st]);
       }
       if (ok) {
-        umma_commit(&sh.bar_sfull);
-        const int stx = ND & 1;
-        ok = mbar_wait(&sh.bar_full[stx], (ND >> 1) & 1, &g_sm100_status, 203) &&
+        umma_commit(&sh.bar_afull);
+        const int ldx = 2 * ND, stx = ldx % PAR_NST;
+        ok = mbar_wait(&sh.bar_full[stx], (ldx / PAR_NST) & 1, &g_sm100_status, 203) &&
              mbar_wait(&sh.bar_gated, 0, &g_sm100_status, 204);
         if (ok) {
           tc_fence_after_sync();
@@ -475,8 +497,8 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
     float qn = 0.f;
     if (use_n) {
       for (int it = 0; it < ND && ok; ++it) {
-        const int st = it & 1;
-        if (!mbar_wait(&sh.bar_full[st], (it >> 1) & 1, &g_sm100_status, 207)) { ok = false; break; }
+        const int st = it % PAR_NST;
+        if (!mbar_wait(&sh.bar_full[st], (it / PAR_NST) & 1, &g_sm100_status, 207)) { ok = false; break; }
         const uint8_t* rowp = smem + st * PAR_STAGE + r * 128;
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc) {
@@ -492,7 +514,7 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
           }
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(&sh.bar_empty[st]);
+        if (lane == 0) mbar_arrive(&sh.bar_qdone[st]);
       }
       sh.s_qn[half][r] = qn;
     }
@@ -503,22 +525,6 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
     if (ok) {
       tc_fence_after_sync();
       // Tensor memory is read 16 columns at a time, the next load in flight while the current one is processed.
-      // row-scale the inter-chunk term in place
-#pragma unroll 1
-      for (int cq = half; cq < 4; cq += 2) {
-        uint32_t va[16], vb[16];
-        const uint32_t ta = tAcc + lane_base + cq * 32;
-        tmem_ld16(ta, va);
-        tmem_wait_ld(va);
-        tmem_ld16(ta + 16, vb);
-#pragma unroll
-        for (int c = 0; c < 16; ++c) va[c] = __float_as_uint(__uint_as_float(va[c]) * rowscale);
-        tmem_wait_ld(vb);
-        tmem_st16(ta, va);
-#pragma unroll
-        for (int c = 0; c < 16; ++c) vb[c] = __float_as_uint(__uint_as_float(vb[c]) * rowscale);
-        tmem_st16(ta + 16, vb);
-      }
       // gate the score tile; the bf16 result goes back to tensor memory as the A operand of the second product.
       // Both warps of a quarter first read their chunks, then (after a warp-pair sync) write: the bf16 words of
       // chunk cq land on columns [16 cq, 16 cq + 16), which the partner warp may still have to read.
@@ -570,6 +576,26 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
 #pragma unroll
         for (int u = 0; u < 2; ++u) tmem_st16(tS + lane_base + (half + 2 * u) * 16, pk[u]);
         sh.s_part[half][r] = rowsum;
+        // the inter-chunk product has usually landed by now: row-scale it in place
+        ok = mbar_wait(&sh.bar_afull, 0, &g_sm100_status, 214);
+      }
+      if (ok) {
+        tc_fence_after_sync();
+#pragma unroll 1
+        for (int cq = half; cq < 4; cq += 2) {
+          uint32_t va[16], vb[16];
+          const uint32_t ta = tAcc + lane_base + cq * 32;
+          tmem_ld16(ta, va);
+          tmem_wait_ld(va);
+          tmem_ld16(ta + 16, vb);
+#pragma unroll
+          for (int c = 0; c < 16; ++c) va[c] = __float_as_uint(__uint_as_float(va[c]) * rowscale);
+          tmem_wait_ld(vb);
+          tmem_st16(ta, va);
+#pragma unroll
+          for (int c = 0; c < 16; ++c) vb[c] = __float_as_uint(__uint_as_float(vb[c]) * rowscale);
+          tmem_st16(ta + 16, vb);
+        }
         tmem_wait_st();
         tc_fence_before_sync();
         mbar_arrive(&sh.bar_gated);
@@ -589,8 +615,8 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
       }
       const uint8_t* erow = smem;
       if (HAS_E) {
-        const int ste = (ND + 1) & 1;
-        ok = mbar_wait(&sh.bar_full[ste], ((ND + 1) >> 1) & 1, &g_sm100_status, 208);
+        const int lde = 2 * ND + 1, ste = lde % PAR_NST;
+        ok = mbar_wait(&sh.bar_full[ste], (lde / PAR_NST) & 1, &g_sm100_status, 208);
         erow = smem + ste * PAR_STAGE + r * 128;
       }
       float dot4[4] = {0.f, 0.f, 0.f, 0.f};   // four partial sums: no 64-long chain of dependent FMAs
@@ -598,7 +624,7 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
       // in the ring stage the X tile occupied - every MMA that read the ring has completed - and is then written out
       // by all element-wise warps together, each warp instruction covering two full 256-byte rows of the tile.  Plain
       // stores are posted, so the CTA retires without waiting for them.
-      uint8_t* ostage = smem + (ND & 1) * PAR_STAGE;
+      uint8_t* ostage = smem + ((2 * ND) % PAR_NST) * PAR_STAGE;
       if (ok) {
 #pragma unroll 1
         for (int cq = half; cq < 4; cq += 2) {
