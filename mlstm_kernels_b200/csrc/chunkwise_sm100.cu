@@ -14,9 +14,6 @@
 //                    fw_kernel_parallel.py:14-289, bw_kernel_parallel_dV.py, bw_kernel_parallel_dK.py, bw_kernel_parallel_dQ.py
 // Operands arrive by TMA (128-byte swizzle, no multicast) through a two-stage mbarrier ring; one warp produces,
 // one thread issues the MMAs, the remaining warps do the element-wise work.  Every wait is bounded.
-#include <algorithm>
-#include <cstdlib>
-
 #include "common.cuh"
 #include "launch.cuh"
 #include "sm100.cuh"
@@ -306,7 +303,12 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
 //   DQ    dH   V    DHHV         lower  K    C_k^T      (rows d, cols e)    s*bbar_r/(den_r+e)  dQ
 // lower: c <= r, (i,j) = (r,c); upper: c >= r, (i,j) = (c,r);
 // gate = s * exp((b_i - b_j) + iota_j - m_i) [* 1/(den_i+eps) in the three backward modes].
-// grid (DO/128, NC, B*NH); 192 threads: warp 0 TMA, warp 1 MMA, warps 2..5 element-wise (thread = row).
+// grid (DO/128, NC, B*NH), two CTAs per SM; 320 threads: warp 0 TMA, warp 1 MMA, warps 2..9 element-wise (two warps
+// per 32-row quarter of the tile, each owning two 32-column chunks).
+// Time line of a CTA (measured with time stamps at the benchmark size, two CTAs sharing an SM): first slices land
+// after ~1.8 us, score complete ~3.3 us, gating until ~5.8 us with the inter-chunk product arriving underneath,
+// second product ~6.4 us, epilogue and stores until ~8.8 us.  The kernel is bound by this chain of dependent steps,
+// not by HBM or L2 (the same kernel with every operand resident in L2 runs at the same speed).
 // =====================================================================================================
 enum { PM_H = 0, PM_DV = 1, PM_DK = 2, PM_DQ = 3 };
 
@@ -345,7 +347,7 @@ struct ParShared {
 // so one element costs an add, an ex2 and a multiply.
 __device__ __forceinline__ void
 par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const CUtensorMap* mapX,
-         const CUtensorMap* mapSt, const CUtensorMap* mapE, const CUtensorMap* mapO, const ParParams& p,
+         const CUtensorMap* mapSt, const CUtensorMap* mapE, const ParParams& p,
          ParShared& sh, const int o_tile, const int ck, const int bh) {
   const bool LOWER = (mode == PM_H || mode == PM_DQ);
   const bool ST_MN = (mode == PM_H || mode == PM_DV);  // state operand N-contiguous in shared memory
@@ -369,7 +371,6 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
     for (int s = 0; s < 4; ++s) mbar_init(&sh.bar_pair[s], 64);
     mbar_init(&sh.bar_out, 256);
     fence_barrier_init();
-    tma_prefetch_desc(mapO);
     tma_prefetch_desc(mapA); tma_prefetch_desc(mapB); tma_prefetch_desc(mapX); tma_prefetch_desc(mapSt);
     if (HAS_E) tma_prefetch_desc(mapE);
   }
@@ -688,9 +689,9 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
 __global__ void __launch_bounds__(PAR_THREADS, 2)
 par_fw_sm100(const __grid_constant__ CUtensorMap mQ, const __grid_constant__ CUtensorMap mK,
              const __grid_constant__ CUtensorMap mV, const __grid_constant__ CUtensorMap mC,
-             const __grid_constant__ CUtensorMap mH, const __grid_constant__ ParParams p) {
+             const __grid_constant__ ParParams p) {
   __shared__ ParShared sh;
-  par_body(PM_H, &mQ, &mK, &mV, &mC, &mV, &mH, p, sh, blockIdx.x, blockIdx.y, blockIdx.z);
+  par_body(PM_H, &mQ, &mK, &mV, &mC, &mV, p, sh, blockIdx.x, blockIdx.y, blockIdx.z);
 }
 
 // deltaV, deltaK and deltaQ of one chunk in ONE launch: blockIdx.x enumerates the 128-wide output tiles of the three
@@ -700,18 +701,17 @@ __global__ void __launch_bounds__(PAR_THREADS, 2)
 par_bw_sm100(const __grid_constant__ CUtensorMap mQ, const __grid_constant__ CUtensorMap mK,
              const __grid_constant__ CUtensorMap mV, const __grid_constant__ CUtensorMap mDH,
              const __grid_constant__ CUtensorMap mC_k, const __grid_constant__ CUtensorMap mdC_mn,
-             const __grid_constant__ CUtensorMap mdC_k, const __grid_constant__ CUtensorMap mDV,
-             const __grid_constant__ CUtensorMap mDK, const __grid_constant__ CUtensorMap mDQ,
+             const __grid_constant__ CUtensorMap mdC_k,
              const __grid_constant__ ParParams p) {
   __shared__ ParShared sh;
   const int t_dv = p.DHHV / 128, t_dk = p.DHQK / 128;
   const int x = blockIdx.x;
   int mode, tile;
-  const CUtensorMap *a, *b, *xm, *stm, *e, *o;
-  if (x < t_dv) { mode = PM_DV; tile = x; a = &mK; b = &mQ; xm = &mDH; stm = &mdC_mn; e = &mDH; o = &mDV; }
-  else if (x < t_dv + t_dk) { mode = PM_DK; tile = x - t_dv; a = &mV; b = &mDH; xm = &mQ; stm = &mdC_k; e = &mK; o = &mDK; }
-  else { mode = PM_DQ; tile = x - t_dv - t_dk; a = &mDH; b = &mV; xm = &mK; stm = &mC_k; e = &mQ; o = &mDQ; }
-  par_body(mode, a, b, xm, stm, e, o, p, sh, tile, blockIdx.y, blockIdx.z);
+  const CUtensorMap *a, *b, *xm, *stm, *e;
+  if (x < t_dv) { mode = PM_DV; tile = x; a = &mK; b = &mQ; xm = &mDH; stm = &mdC_mn; e = &mDH; }
+  else if (x < t_dv + t_dk) { mode = PM_DK; tile = x - t_dv; a = &mV; b = &mDH; xm = &mQ; stm = &mdC_k; e = &mK; }
+  else { mode = PM_DQ; tile = x - t_dv - t_dk; a = &mDH; b = &mV; xm = &mK; stm = &mC_k; e = &mQ; }
+  par_body(mode, a, b, xm, stm, e, p, sh, tile, blockIdx.y, blockIdx.z);
 }
 
 // =====================================================================================================
@@ -777,15 +777,15 @@ static ParParams base_params(const GateBuffers& gb, const ChunkwiseDims& d) {
 int sm100_parallel_fw(const void* q, const void* k, const void* v, const GateBuffers& gb, const void* c_states,
                       const float* n_states, void* h, float* n_out, const ChunkwiseDims& d, cudaStream_t st) {
   PhaseScope ps(PH_PAR_FW, st);
-  CUtensorMap mQ, mK, mV, mC, mH;
+  CUtensorMap mQ, mK, mV, mC;
   if (!tok_map(&mQ, q, d, d.DHQK) || !tok_map(&mK, k, d, d.DHQK) || !tok_map(&mV, v, d, d.DHHV) ||
-      !state_map(&mC, c_states, d, 64) || !tok_map(&mH, h, d, d.DHHV))
+      !state_map(&mC, c_states, d, 64))
     return MLSTM_ERR_CUDA;
   ParParams pp = base_params(gb, d);
   pp.n_states = n_states; pp.out_h = (__nv_bfloat16*)h; pp.n_out = n_out;
   MLSTM_CUDA_CHECK(cudaFuncSetAttribute(par_fw_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, PAR_SMEM));
   dim3 grid(d.DHHV / 128, d.NC, d.B * d.NH);
-  par_fw_sm100<<<grid, PAR_THREADS, PAR_SMEM, st>>>(mQ, mK, mV, mC, mH, pp);
+  par_fw_sm100<<<grid, PAR_THREADS, PAR_SMEM, st>>>(mQ, mK, mV, mC, pp);
   MLSTM_LAUNCH_CHECK();
   return MLSTM_OK;
 }
@@ -794,18 +794,17 @@ int sm100_parallel_bw(const void* q, const void* k, const void* v, const void* d
                       const void* c_states, const void* dc_states, void* dq, void* dk, void* dv, float* qdq_parts,
                       float* kdk_parts, const ChunkwiseDims& d, cudaStream_t st) {
   PhaseScope ps(PH_PAR_BW, st);
-  CUtensorMap mQ, mK, mV, mDH, mC_k, mdC_mn, mdC_k, mDV, mDK, mDQ;
+  CUtensorMap mQ, mK, mV, mDH, mC_k, mdC_mn, mdC_k;
   if (!tok_map(&mQ, q, d, d.DHQK) || !tok_map(&mK, k, d, d.DHQK) || !tok_map(&mV, v, d, d.DHHV) ||
       !tok_map(&mDH, dh, d, d.DHHV) || !state_map(&mC_k, c_states, d, 128) || !state_map(&mdC_mn, dc_states, d, 64) ||
-      !state_map(&mdC_k, dc_states, d, 128) || !tok_map(&mDV, dv, d, d.DHHV) || !tok_map(&mDK, dk, d, d.DHQK) ||
-      !tok_map(&mDQ, dq, d, d.DHQK))
+      !state_map(&mdC_k, dc_states, d, 128))
     return MLSTM_ERR_CUDA;
   ParParams pp = base_params(gb, d);
   pp.out_dv = (__nv_bfloat16*)dv; pp.out_dk = (__nv_bfloat16*)dk; pp.out_dq = (__nv_bfloat16*)dq;
   pp.rowdot_q = qdq_parts; pp.rowdot_k = kdk_parts;
   MLSTM_CUDA_CHECK(cudaFuncSetAttribute(par_bw_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, PAR_SMEM));
   dim3 grid(d.DHHV / 128 + 2 * (d.DHQK / 128), d.NC, d.B * d.NH);
-  par_bw_sm100<<<grid, PAR_THREADS, PAR_SMEM, st>>>(mQ, mK, mV, mDH, mC_k, mdC_mn, mdC_k, mDV, mDK, mDQ, pp);
+  par_bw_sm100<<<grid, PAR_THREADS, PAR_SMEM, st>>>(mQ, mK, mV, mDH, mC_k, mdC_mn, mdC_k, pp);
   MLSTM_LAUNCH_CHECK();
   return MLSTM_OK;
 }
