@@ -43,14 +43,15 @@ struct RecParams {
   int S, NC, DHQK, DHHV;
 };
 
-constexpr int REC_THREADS = 608;                 // warp 0 TMA, 1 MMA, 2..9 gate the left tile, 10..17 own the state, 18 stores it
+constexpr int REC_THREADS = 640;                 // warp 0 TMA, 1 MMA, 2..9 gate the left tile, 10..17 own the state, 18 stores it, 19 keeps n
 constexpr int REC_HALF = 64;                     // tokens per ring stage: half a chunk
 constexpr int REC_STAGE_BYTES = 32768;           // 64 tokens: left tile 16 KB + right tile 16 KB
-constexpr int REC_STAGES = 5;                    // operand ring depth (two and a half chunks in flight)
 constexpr int REC_NPART_BYTES = 2 * 32 * 128 * 4;   // double-buffered partial column sums of the gated left tile
-constexpr int REC_OUT_BYTES = 32768;             // bf16 state tile staged for the TMA store
-constexpr int rec_smem_bytes(bool bwd) {   // the backward recurrence has no n and needs no partial sums
-  return REC_STAGES * REC_STAGE_BYTES + (bwd ? 0 : REC_NPART_BYTES) + REC_OUT_BYTES + 1024;
+constexpr int REC_OUT_BYTES = 2 * 32768;         // double-buffered bf16 state tile staged for the TMA store
+// operand ring depth (two chunks in flight)
+constexpr int rec_stages(bool) { return 4; }
+constexpr int rec_smem_bytes(bool bwd) {
+  return rec_stages(bwd) * REC_STAGE_BYTES + (bwd ? 0 : REC_NPART_BYTES) + REC_OUT_BYTES + 1024;
 }
 
 // One ring stage holds 64 tokens of the left and of the right operand (boxes of 64 rows x 64 columns, 8 KB each:
@@ -63,7 +64,8 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
           const __grid_constant__ CUtensorMap mapS, RecParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  __shared__ uint64_t bar_full[REC_STAGES], bar_empty[REC_STAGES], bar_scaled[REC_STAGES], bar_acc_full[2], bar_acc_free[2], bar_nsum[2], bar_out_full, bar_out_free;
+  constexpr int REC_STAGES = rec_stages(BWD);
+  __shared__ uint64_t bar_full[REC_STAGES], bar_empty[REC_STAGES], bar_scaled[REC_STAGES], bar_acc_full[2], bar_acc_free[2], bar_nsum[2], bar_nread[2], bar_out_full[2], bar_out_free[2];
   __shared__ uint32_t s_tmem;
   // per-row scale factors of the left tile, copied with the stage (backward: two factors per row)
   __shared__ __align__(16) float s_scale[REC_STAGES][REC_HALF], s_scale2[BWD ? REC_STAGES : 1][REC_HALF];
@@ -79,9 +81,9 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
       mbar_init(&bar_full[s], 1); mbar_init(&bar_empty[s], 1); mbar_init(&bar_scaled[s], 256);
     }
     for (int s = 0; s < 2; ++s) {
-      mbar_init(&bar_acc_full[s], 1); mbar_init(&bar_acc_free[s], 256); mbar_init(&bar_nsum[s], 256);
+      mbar_init(&bar_acc_full[s], 1); mbar_init(&bar_acc_free[s], 256); mbar_init(&bar_nsum[s], 256); mbar_init(&bar_nread[s], 1);
+      mbar_init(&bar_out_full[s], 256); mbar_init(&bar_out_free[s], 1);
     }
-    mbar_init(&bar_out_full, 256); mbar_init(&bar_out_free, 1);
     fence_barrier_init();
     tma_prefetch_desc(&mapL); tma_prefetch_desc(&mapR); tma_prefetch_desc(&mapS);
   }
@@ -153,9 +155,6 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
   } else if (warp < 10) {
     // ---------------- gating warps: scale the rows of the left tile in place; column sums give n ----------------
     const int ct = tid - 64;                       // 0..255
-    float nval = 0.f;
-    if (do_n && ct < 128 && p.n_init) nval = p.n_init[(size_t)bh * p.DHQK + d0 + ct];
-    if (do_n && p.n_states != nullptr && ct < 128) p.n_states[((size_t)bh * (NC + 1)) * p.DHQK + d0 + ct] = nval;
     bool ok = true;
     float ns[2][8];
     for (int h = 0; h < NH2; ++h) {
@@ -188,6 +187,8 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
       }
       float* npart = reinterpret_cast<float*>(smem + REC_STAGES * REC_STAGE_BYTES) + nb * (32 * 128);
       if (do_n && (h & 1)) {
+        // the n warp has read the partial sums of chunk s - 2 out of this buffer
+        if (s >= 2 && !mbar_wait(&bar_nread[nb], ((s >> 1) - 1) & 1, &g_sm100_status, 109)) { ok = false; break; }
         const int lc = (ct & 7) ^ ((ct >> 3) & 7);   // logical 16-byte column chunk behind the swizzle
 #pragma unroll
         for (int b = 0; b < 2; ++b) {
@@ -198,34 +199,50 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
       }
       fence_proxy_async_smem();
       mbar_arrive(&bar_scaled[st]);
-      if (do_n && (h & 1)) {   // n does not need the tensor cores: n_{s+1} = gbar n_s + column sums of the gated left tile
-        mbar_arrive(&bar_nsum[nb]);
-        if (!mbar_wait(&bar_nsum[nb], (s >> 1) & 1, &g_sm100_status, 106)) { ok = false; break; }
-        if (ct < 128) {
-          float colsum = 0.f;   // fixed summation order: the result does not depend on scheduling
-#pragma unroll 8
-          for (int g = 0; g < 32; ++g) colsum += npart[g * 128 + ct];
-          nval = fmaf(s_g[s & 7], nval, colsum);
-          if (p.n_states != nullptr) p.n_states[((size_t)bh * (NC + 1) + s + 1) * p.DHQK + d0 + ct] = nval;
-        }
-      }
+      if (do_n && (h & 1)) mbar_arrive(&bar_nsum[nb]);   // partial column sums of chunk s are complete (n warp)
     }
-    if (ok && do_n && p.n_final && ct < 128) p.n_final[(size_t)bh * p.DHQK + d0 + ct] = nval;
   } else if (warp == 18) {
     // ---------------- store warp: one TMA store per 64-column box of each staged state tile ----------------
     if (lane == 0 && p.c_states != nullptr) {
       uint8_t* stage_base = smem + REC_STAGES * REC_STAGE_BYTES + (BWD ? 0 : REC_NPART_BYTES);
       for (int n = 0; n <= NC; ++n) {
-        if (!mbar_wait(&bar_out_full, n & 1, &g_sm100_status, 108)) break;
+        const int ob = n & 1;
+        if (!mbar_wait(&bar_out_full[ob], (n >> 1) & 1, &g_sm100_status, 108)) break;
         const int slot = BWD ? NC - n : n;
         const int y = (bh * (NC + 1) + slot) * p.DHQK + d0;
-        tma_store_2d(&mapS, stage_base, e0, y);
-        tma_store_2d(&mapS, stage_base + 16384, e0 + 64, y);
+        tma_store_2d(&mapS, stage_base + ob * 32768, e0, y);
+        tma_store_2d(&mapS, stage_base + ob * 32768 + 16384, e0 + 64, y);
         tma_store_commit();
-        tma_store_wait_read();          // the tile has left the staging buffer
-        mbar_arrive(&bar_out_free);
+        asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");   // the previous tile has left its buffer
+        if (n >= 1) mbar_arrive(&bar_out_free[ob ^ 1]);
       }
       tma_store_wait_all();   // all state tiles have been written before the CTA retires
+    }
+  } else if (warp == 19) {
+    // ---------------- n warp: n_{s+1} = gbar n_s + column sums of the gated left tile (no tensor cores needed) ----
+    // Four columns per lane; the 32 partial sums of a column are added in a fixed order, so the result does not
+    // depend on scheduling.
+    if (do_n) {
+      float4 nv = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (p.n_init) nv = *reinterpret_cast<const float4*>(p.n_init + (size_t)bh * p.DHQK + d0 + 4 * lane);
+      if (p.n_states != nullptr)
+        *reinterpret_cast<float4*>(p.n_states + ((size_t)bh * (NC + 1)) * p.DHQK + d0 + 4 * lane) = nv;
+      bool ok = true;
+      for (int s = 0; s < NC; ++s) {
+        const int nb = s & 1;
+        if (!mbar_wait(&bar_nsum[nb], (s >> 1) & 1, &g_sm100_status, 106)) { ok = false; break; }
+        const float4* np4 = reinterpret_cast<const float4*>(smem + REC_STAGES * REC_STAGE_BYTES) + nb * (32 * 32) + lane;
+        float4 cs = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+        for (int g = 0; g < 32; ++g) { const float4 v = np4[g * 32]; cs.x += v.x; cs.y += v.y; cs.z += v.z; cs.w += v.w; }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar_nread[nb]);
+        const float g = s_g[s & 7];
+        nv.x = fmaf(g, nv.x, cs.x); nv.y = fmaf(g, nv.y, cs.y); nv.z = fmaf(g, nv.z, cs.z); nv.w = fmaf(g, nv.w, cs.w);
+        if (p.n_states != nullptr)
+          *reinterpret_cast<float4*>(p.n_states + ((size_t)bh * (NC + 1) + s + 1) * p.DHQK + d0 + 4 * lane) = nv;
+      }
+      if (ok && p.n_final) *reinterpret_cast<float4*>(p.n_final + (size_t)bh * p.DHQK + d0 + 4 * lane) = nv;
     }
   } else {
     // ---------------- state warps: fold each chunk's product into the running state, store it ----------------
@@ -242,14 +259,14 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
       for (int c = 0; c < 64; ++c) C[c] = 0.f;
     }
     // The bf16 state tile goes to shared memory in the 128-byte-swizzled box layout and leaves with one TMA store
-    // per 64-column box (coalesced, asynchronous).  One staging buffer: the store of a tile has read it long before
-    // the next tile is ready (a chunk takes longer than the read), so the wait below rarely blocks.
+    // per 64-column box (coalesced, asynchronous); two staging buffers, one store group in flight.
     uint8_t* stage_base = smem + REC_STAGES * REC_STAGE_BYTES + (BWD ? 0 : REC_NPART_BYTES);
     int n_out = 0;   // tiles written so far
     auto store_c = [&]() -> bool {
       if (p.c_states == nullptr) return true;
-      if (n_out >= 1 && !mbar_wait(&bar_out_free, (n_out - 1) & 1, &g_sm100_status, 107)) return false;
-      uint8_t* rowp = stage_base + half * 16384 + row * 128;
+      const int ob = n_out & 1;
+      if (n_out >= 2 && !mbar_wait(&bar_out_free[ob], ((n_out >> 1) - 1) & 1, &g_sm100_status, 107)) return false;
+      uint8_t* rowp = stage_base + ob * 32768 + half * 16384 + row * 128;
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
         uint4 v;
@@ -258,7 +275,7 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
         *reinterpret_cast<uint4*>(rowp + ((c ^ (row & 7)) << 4)) = v;
       }
       fence_proxy_async_smem();
-      mbar_arrive(&bar_out_full);   // the store warp ships the tile
+      mbar_arrive(&bar_out_full[ob]);   // the store warp ships the tile
       ++n_out;
       return true;
     };
