@@ -95,6 +95,25 @@ def test_bf16_vs_oracle(shape, variant, impl):
     compare(got, ref, TOL_BF16, TOL_BF16, keys_fw=keys)
 
 
+@pytest.mark.parametrize("shape", [(1, 1, 256, 512, 512, 128),    # widest qk head the tcgen05 path takes (8 slices)
+                                   (1, 1, 256, 128, 1024, 128),   # widest v head (8 output tiles per chunk)
+                                   (1, 2, 384, 128, 256, 128),    # odd number of chunks; 128/256 head geometry
+                                   (3, 5, 640, 256, 256, 128)])   # odd batch x heads, five chunks
+@pytest.mark.parametrize("variant", ["exp", "sig_nonorm"])
+def test_tcgen05_head_geometries(shape, variant):
+    """Edge geometries of the tcgen05 path (limits of the head dims it accepts, odd chunk and head counts) against
+    the oracle, with initial states and an incoming state gradient."""
+    B, NH, S, DHQK, DHHV, L = shape
+    inp = case_inputs(21, B, NH, S, DHQK, DHHV, init=True, dC_last=True)
+    siging, normalize = variant != "exp", variant != "sig_nonorm"
+    q, v = to_dev(inp["q"], torch.bfloat16), to_dev(inp["v"], torch.bfloat16)
+    assert mk.kernel_chunk_size(q, v, L) == 128
+    got = run_cuda_fwbw(inp, L, dtype=torch.bfloat16, siging=siging, normalize=normalize, impl="tcgen05")
+    ref = run_oracle_fwbw(inp, L, dtype=torch.bfloat16, siging=siging, normalize=normalize)
+    keys = FW_KEYS if not siging else ("H", "C_last")
+    compare(got, ref, TOL_BF16, TOL_BF16, keys_fw=keys)
+
+
 @pytest.mark.parametrize("variant", ["exp", "sig"])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_state_passing(variant, dtype):
