@@ -351,6 +351,8 @@ struct ParShared {
       bar_pair[4], bar_out;
   uint32_t tmem;
   __align__(16) float s_colE[CL];  // per-column term of the gate exponent, base 2 (see par_body)
+  __align__(16) float s_colF[CL];  // 2^(colE_c - colP of the column's 32-column block)
+  float s_colP[4];                 // largest colE of each 32-column block
   float s_part[2][CL];           // per-row partial sums exchanged between the two warps of a row
   float s_qn[2][CL];
   float s_n[512];
@@ -361,7 +363,13 @@ struct ParShared {
 // Gate factor of element (r, c): 2^(rowE_r + colE_c), every positive factor folded into the exponent:
 //   lower (H, DQ), valid c <= r:  rowE = (b_r - m_r) log2e + log2(s [/(den_r+eps)]),   colE = (iota_c - b_c) log2e
 //   upper (DV, DK), valid c >= r: rowE = (iota_r - b_r) log2e + log2(s),               colE = (b_c - m_c) log2e - log2(den_c+eps)
-// so one element costs an add, an ex2 and a multiply.
+// A 32 x 32 block off the diagonal is gated without a transcendental per element: with colP = the largest colE of
+// the block's columns, 2^(rowE_r + colE_c) = 2^(rowE_r + colP) * 2^(colE_c - colP); the column factors (one ex2 per
+// column and CTA) lie in (0, 1], and the row factor (one ex2 per row and block) cannot overflow because every
+// element of an off-diagonal block is a valid gate entry, bounded by s / (den + eps).  Where a column factor
+// underflows the exact value is below 2^-100 as well.  The diagonal block keeps the exact per-element form (its
+// masked columns may carry arbitrarily large colE).  The special-function unit (16 results per clock and SM) was
+// the limit of the gating phase before: the warps of the busiest row quarter share one SM sub-partition.
 __device__ __forceinline__ void
 par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const CUtensorMap* mapX,
          const CUtensorMap* mapSt, const CUtensorMap* mapE, const ParParams& p,
@@ -498,7 +506,16 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
     constexpr float kLog2e = 1.4426950408889634f;
     const float rowE = (LOWER ? (b_r - m_r) : (iota_r - b_r)) * kLog2e +
                        __log2f((mode == PM_DQ) ? p.qk_scale * inv_r : p.qk_scale);
-    if (half == 0) sh.s_colE[r] = LOWER ? (iota_r - b_r) * kLog2e : (b_r - m_r) * kLog2e + __log2f(inv_r);
+    if (half == 0) {   // this thread's row in its role as a column of the gate matrix
+      const float colE = LOWER ? (iota_r - b_r) * kLog2e : (b_r - m_r) * kLog2e + __log2f(inv_r);
+      float colP = colE;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) colP = fmaxf(colP, __shfl_xor_sync(0xffffffffu, colP, o));
+      if (!(colP > -3.0e38f)) colP = 0.f;   // a block whose columns are all switched off
+      sh.s_colE[r] = colE;
+      sh.s_colF[r] = ex2_approx(colE - colP);
+      if (lane == 0) sh.s_colP[quarter] = colP;
+    }
     float rowscale;
     if (mode == PM_H) rowscale = p.qk_scale * p.bbar[tok];
     else if (mode == PM_DQ) rowscale = p.qk_scale * p.bbar[tok] * inv_r;
@@ -565,22 +582,36 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
           for (int hh = 0; hh < 2; ++hh) {
             if (hh == 1) tmem_wait_ld(vb);
             const uint32_t (&v)[16] = hh ? vb : va;
-            const float4* ce = reinterpret_cast<const float4*>(sh.s_colE + c0 + 16 * hh);
+            if (diag) {
+              const float4* ce = reinterpret_cast<const float4*>(sh.s_colE + c0 + 16 * hh);
 #pragma unroll
-            for (int c4 = 0; c4 < 4; ++c4) {
-              const float4 e4 = ce[c4];
-              const float ee[4] = {e4.x, e4.y, e4.z, e4.w};
-              float g4[4];
+              for (int c4 = 0; c4 < 4; ++c4) {
+                const float4 e4 = ce[c4];
+                const float ee[4] = {e4.x, e4.y, e4.z, e4.w};
+                float g4[4];
 #pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const int cl = 16 * hh + 4 * c4 + e;   // column inside the chunk; row inside the chunk is `lane`
-                float val = __uint_as_float(v[4 * c4 + e]) * ex2_approx(rowE + ee[e]);
-                if (diag && (LOWER ? (cl > lane) : (cl < lane))) val = 0.f;
-                g4[e] = val;
-                rowsum += val;
+                for (int e = 0; e < 4; ++e) {
+                  const int cl = 16 * hh + 4 * c4 + e;   // column inside the chunk; row inside the chunk is `lane`
+                  float val = __uint_as_float(v[4 * c4 + e]) * ex2_approx(rowE + ee[e]);
+                  if (LOWER ? (cl > lane) : (cl < lane)) val = 0.f;
+                  g4[e] = val;
+                  rowsum += val;
+                }
+                pk[u][8 * hh + 2 * c4] = pack_bf16(g4[0], g4[1]);
+                pk[u][8 * hh + 2 * c4 + 1] = pack_bf16(g4[2], g4[3]);
               }
-              pk[u][8 * hh + 2 * c4] = pack_bf16(g4[0], g4[1]);
-              pk[u][8 * hh + 2 * c4 + 1] = pack_bf16(g4[2], g4[3]);
+            } else {
+              const float rf = ex2_approx(rowE + sh.s_colP[cq]);
+              const float4* cf = reinterpret_cast<const float4*>(sh.s_colF + c0 + 16 * hh);
+#pragma unroll
+              for (int c4 = 0; c4 < 4; ++c4) {
+                const float4 f4 = cf[c4];
+                const float g0 = __uint_as_float(v[4 * c4]) * (rf * f4.x), g1 = __uint_as_float(v[4 * c4 + 1]) * (rf * f4.y);
+                const float g2 = __uint_as_float(v[4 * c4 + 2]) * (rf * f4.z), g3 = __uint_as_float(v[4 * c4 + 3]) * (rf * f4.w);
+                rowsum += (g0 + g1) + (g2 + g3);
+                pk[u][8 * hh + 2 * c4] = pack_bf16(g0, g1);
+                pk[u][8 * hh + 2 * c4 + 1] = pack_bf16(g2, g3);
+              }
             }
           }
         }
