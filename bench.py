@@ -488,6 +488,7 @@ def bench_sweep(torch, mk, dev, peaks):
 def bench_long_prefill(torch, mk, dev, peaks):
     """Single-GPU forward of the long-sequence configuration (the sequence-parallel runs compare with this)."""
     B, NH, S, DHQK, DHHV, L = 1, 8, 131072, 256, 512, 256
+    torch.cuda.empty_cache()   # the sweep before this leaves the caching allocator fragmented
     g = torch.Generator(device=dev).manual_seed(7)
     mk_t = lambda *sh: torch.randn(*sh, device=dev, generator=g).bfloat16()  # noqa: E731
     q, k, v = mk_t(B, NH, S, DHQK), mk_t(B, NH, S, DHQK), mk_t(B, NH, S, DHHV)
