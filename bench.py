@@ -551,6 +551,27 @@ def bench_step(torch, mk, dev, peaks):
         gbs = nbytes / (us * 1e-6) / 1e9
         out[f"B{B}"] = dict(us_per_step=us, tokens_per_s=B / (us * 1e-6), gbs=gbs, frac_of_hbm=gbs / peaks["hbm"],
                             note="includes Python launch overhead per step" if B <= 8 else "")
+        if B <= 8:
+            # the same chain of steps captured once in a CUDA graph and replayed: device time without the host loop
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                run(2)
+            torch.cuda.current_stream().wait_stream(side)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                run(T)
+            graph.replay()
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(16):
+                graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            us_g = e0.elapsed_time(e1) / (16 * T) * 1e3
+            out[f"B{B}"].update(us_per_step_cuda_graph=us_g, tokens_per_s_cuda_graph=B / (us_g * 1e-6),
+                                gbs_cuda_graph=nbytes / (us_g * 1e-6) / 1e9,
+                                note_cuda_graph="both state buffers of this batch size fit the 126 MB L2")
     return out
 
 

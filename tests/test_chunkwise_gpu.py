@@ -229,3 +229,35 @@ def test_fused_forward_keeps_state_on_chip(variant, shape, init):
     keys = FW_KEYS if not siging else (("H", "C_last", "n_last") if normalize else ("H", "C_last"))
     compare(got, ref, TOL_BF16, TOL_BF16, keys_fw=keys)
     compare(got, two, 1e-2, 1e-2, keys_fw=keys)
+
+
+def test_forward_backward_capture_in_cuda_graph():
+    """The kernels enqueue on the current stream without host synchronisation, so a forward + backward can be captured
+    in a CUDA graph and replayed (the reference's callers compile and capture their models)."""
+    inp = case_inputs(31, 2, 2, 512, 256, 256)
+    q, k, v = (to_dev(inp[n], torch.bfloat16) for n in "qkv")
+    i, f = (to_dev(inp[n], torch.float32) for n in "if")
+    dh = to_dev(inp["dH"], torch.float32)
+
+    def step():
+        # leaves and the gradient seed are created inside the step, on the stream it runs on: autograd would otherwise
+        # synchronise with the stream that created them, which a capture does not allow
+        leaves = [t.detach().requires_grad_(True) for t in (q, k, v, i, f)]
+        h = mk.mlstm_chunkwise__b200_xl_chunk(*leaves, chunk_size=128)
+        grads = torch.autograd.grad((h.float() * dh).sum(), leaves)
+        return (h.detach(),) + grads
+
+    eager = [t.clone() for t in step()]
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):       # warm-up on a side stream, as graph capture requires
+        step()
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        outs = step()
+    for _ in range(2):
+        graph.replay()
+    torch.cuda.synchronize()
+    for a, b in zip(eager, outs):
+        assert torch.equal(a, b)
