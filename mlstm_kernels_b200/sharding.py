@@ -14,6 +14,11 @@ c_initial / n_initial / m_initial in, last states out: mlstm_kernels/torch/kerne
   forward of their segment, concurrently, from the true incoming state.  "chain" mode is the plain
   serial hand-off (segment r starts when r-1 has finished its recurrence).  Both reproduce the
   single-GPU (C, n, m) path.
+  The call is differentiable: the backward runs the chain the other way.  Rank r receives, from rank r+1, the
+  gradient of the state it handed over and the sum of (q . dq - k . dk) over all later tokens of each head
+  (the forget-gate gradient of a token is sigmoid(-f) times that sum over all tokens from it to the end of the
+  WHOLE sequence: mlstm_kernels/torch/chunkwise/triton_xl_chunk/chunkwise_gates.py:75-95), runs the backward of its
+  segment, and passes both on to rank r-1.
 """
 
 from __future__ import annotations
@@ -22,7 +27,7 @@ import torch
 import torch.distributed as dist
 
 from . import _lib
-from .chunkwise import chunkwise_fw_raw, kernel_chunk_size, select_chunk_size
+from .chunkwise import chunkwise_bw_raw, chunkwise_fw_raw, kernel_chunk_size, select_chunk_size
 
 
 def shard_range(total: int, world: int, rank: int) -> tuple[int, int]:
@@ -89,11 +94,92 @@ def state_combine(state_in, summary, *, variant: int):
     return c_out, n_out, m_out
 
 
-def _segment_forward(q, k, v, i, f, state_in, *, chunk_size, eps, variant, impl, want_last):
+def _segment_forward_saved(q, k, v, i, f, state_in, *, chunk_size, eps, variant, impl):
+    """Forward of one segment that also returns what its backward needs."""
     c0, n0, m0 = state_in
     out = chunkwise_fw_raw(q, k, v, i, f, c0, n0, m0 if variant == _lib.EXP else None, chunk_size=chunk_size,
-                           eps=eps, variant=variant, impl=impl, want_last=want_last)
-    return out["H"], (out["C_last"], out["n_last"], out["m_last"])
+                           eps=eps, variant=variant, impl=impl, want_last=True)
+    saved = dict(m_initial=m0 if variant == _lib.EXP else None, c_states=out["C_states"], n_out=out["n_out"],
+                 m_out=out["m_out"], workspace=out["workspace"])
+    return out["H"], (out["C_last"], out["n_last"], out["m_last"]), saved
+
+
+def _segment_backward(q, k, v, i, f, saved, dh, dc_last, *, chunk_size, eps, variant, impl):
+    """Backward of one segment: (dq, dk, dv, di, df, gradient of the state the segment received)."""
+    return chunkwise_bw_raw(q, k, v, i, f, saved["m_initial"], saved["c_states"], saved["n_out"], dh, dc_last,
+                            chunk_size=chunk_size, eps=eps, variant=variant, impl=impl, want_dc_initial=True,
+                            m_out=saved["m_out"], fw_workspace=saved["workspace"])
+
+
+def _segment_gate_sum(q, k, f, dq, dk, df_local):
+    """Sum over the segment's tokens of (q . dq - k . dk), per (batch, head).
+    The kernels form these sums in f32 from their f32 accumulators and return them inside the forget-gate gradient:
+    df_local[t] = sigmoid(-f[t]) * (sum over tokens t' >= t of the segment), so token 0 carries the whole sum.  The sum
+    of the rounded dq, dk outputs is not used unless sigmoid(-f[0]) underflows: q . dq and k . dk nearly cancel, and the
+    rounding of bf16 outputs would dominate their difference."""
+    s0 = torch.sigmoid(-f[..., 0].float())
+    from_df = df_local[..., 0].float() / s0.clamp_min(1e-30)
+    fallback = (q.float() * dq.float() - k.float() * dk.float()).sum(dim=(-1, -2))
+    return torch.where(s0 > 1e-30, from_df, fallback)
+
+
+class _SequenceParallelFn(torch.autograd.Function):
+    """Differentiable sequence-parallel forward; see the module docstring for the backward chain."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, i, f, first_state, opts):
+        group, ranks, rank, world = opts["group"], opts["ranks"], opts["rank"], opts["world"]
+        L, eps, variant, impl, mode = opts["L"], opts["eps"], opts["variant"], opts["impl"], opts["mode"]
+        prev_rank = ranks[rank - 1] if rank > 0 else None
+        next_rank = ranks[rank + 1] if rank < world - 1 else None
+        like = first_state
+        if mode == "chain":
+            state_in = first_state if rank == 0 else _recv_state(like, prev_rank, group)
+            h, last, saved = _segment_forward_saved(q, k, v, i, f, state_in, chunk_size=L, eps=eps, variant=variant,
+                                                    impl=impl)
+            if next_rank is not None:
+                _send_state(last, next_rank, group)
+        else:
+            summary = segment_summary(k, v, i, f, chunk_size=L, variant=variant, impl=impl)
+            state_in = first_state if rank == 0 else _recv_state(like, prev_rank, group)
+            last = state_combine(state_in, summary, variant=variant)
+            if next_rank is not None:
+                _send_state(last, next_rank, group)
+            h, _, saved = _segment_forward_saved(q, k, v, i, f, state_in, chunk_size=L, eps=eps, variant=variant,
+                                                 impl=impl)
+        ctx.opts, ctx.saved = opts, saved
+        ctx.save_for_backward(q, k, v, i, f)
+        ctx.mark_non_differentiable(*last)
+        return (h,) + tuple(last)
+
+    @staticmethod
+    def backward(ctx, dh, *_unused):
+        q, k, v, i, f = ctx.saved_tensors
+        opts = ctx.opts
+        group, ranks, rank, world = opts["group"], opts["ranks"], opts["rank"], opts["world"]
+        prev_rank = ranks[rank - 1] if rank > 0 else None
+        next_rank = ranks[rank + 1] if rank < world - 1 else None
+        B, NH, S, DHQK = q.shape
+        DHHV = v.shape[-1]
+        dc_last, tail = None, None
+        if next_rank is not None:   # gradient of the state handed to rank r+1, and the sum over all later tokens
+            dc_last = torch.empty((B, NH, DHQK, DHHV), dtype=torch.float32, device=q.device)
+            tail = torch.empty((B, NH), dtype=torch.float32, device=q.device)
+            dist.recv(dc_last, src=next_rank, group=group)
+            dist.recv(tail, src=next_rank, group=group)
+        dq, dk, dv, di, df, dc0 = _segment_backward(q, k, v, i, f, ctx.saved, dh.contiguous(), dc_last,
+                                                    chunk_size=opts["L"], eps=opts["eps"], variant=opts["variant"],
+                                                    impl=opts["impl"])
+        if prev_rank is not None:
+            total = _segment_gate_sum(q, k, f, dq, dk, df)
+            if tail is not None:
+                total = total + tail
+        if tail is not None:
+            df = df + torch.sigmoid(-f.float()) * tail[..., None]
+        if prev_rank is not None:
+            dist.send(dc0.contiguous(), dst=prev_rank, group=group)
+            dist.send(total.contiguous(), dst=prev_rank, group=group)
+        return dq, dk, dv, di.to(i.dtype), df.to(f.dtype), None, None
 
 
 def _send_state(state, dst, group):
@@ -128,7 +214,9 @@ def mlstm_chunkwise_sequence_parallel(
 ):
     """Forward (prefill) of one long sequence whose segments live on the ranks of `group`.
     Returns this rank's H (B, NH, S_local, DHHV) and, if requested, the state after the LAST segment
-    (identical on every rank).  Ranks are ordered along the sequence: global rank order of the group."""
+    (identical on every rank).  Ranks are ordered along the sequence: global rank order of the group.
+    Differentiable with respect to q, k, v, i, f (every rank must then run the backward: it is a chain of
+    point-to-point messages from the last rank to the first)."""
     if mode not in ("scan", "chain"):
         raise ValueError(f"unknown mode {mode}")
     world = dist.get_world_size(group)
@@ -139,29 +227,15 @@ def mlstm_chunkwise_sequence_parallel(
     L = kernel_chunk_size(q, v, select_chunk_size(S, chunk_size), impl)
     dev = q.device
     ranks = dist.get_process_group_ranks(group) if group is not None else list(range(world))
-    prev_rank = ranks[rank - 1] if rank > 0 else None
-    next_rank = ranks[rank + 1] if rank < world - 1 else None
-
     zeros = (torch.zeros((B, NH, DHQK, DHHV), dtype=torch.float32, device=dev),
              torch.zeros((B, NH, DHQK), dtype=torch.float32, device=dev),
              torch.zeros((B, NH, 1), dtype=torch.float32, device=dev))
     f32 = lambda t, z: z if t is None else t.to(torch.float32).contiguous()  # noqa: E731
     first_state = (f32(c_initial, zeros[0]), f32(n_initial, zeros[1]), f32(m_initial, zeros[2]))
 
-    if mode == "chain":
-        state_in = first_state if rank == 0 else _recv_state(zeros, prev_rank, group)
-        h, last = _segment_forward(q, k, v, i, f, state_in, chunk_size=L, eps=eps, variant=variant, impl=impl,
-                                   want_last=True)
-        if next_rank is not None:
-            _send_state(last, next_rank, group)
-    else:
-        summary = segment_summary(k, v, i, f, chunk_size=L, variant=variant, impl=impl)
-        state_in = first_state if rank == 0 else _recv_state(zeros, prev_rank, group)
-        last = state_combine(state_in, summary, variant=variant)
-        if next_rank is not None:
-            _send_state(last, next_rank, group)
-        h, _ = _segment_forward(q, k, v, i, f, state_in, chunk_size=L, eps=eps, variant=variant, impl=impl,
-                                want_last=False)
+    opts = dict(group=group, ranks=ranks, rank=rank, world=world, L=L, eps=eps, variant=variant, impl=impl, mode=mode)
+    out = _SequenceParallelFn.apply(q, k, v, i, f, first_state, opts)
+    h, last = out[0], out[1:]
     if not return_last_states:
         return h
     last = tuple(t.contiguous() for t in last)

@@ -57,16 +57,31 @@ def main():
         ms = (time.perf_counter() - t0) * 1e3
     hs = [torch.empty_like(h) for _ in range(world)]
     dist.all_gather(hs, h)
+    # backward through the sequence-parallel call: a chain of messages from the last rank to the first
+    dh_full = torch.randn(1, args.NH, args.S, args.DHHV, generator=g).bfloat16()
+    leaves = [t.detach().clone().requires_grad_(True) for t in loc]
+    h_b = sharding.mlstm_chunkwise_sequence_parallel(*leaves, chunk_size=args.chunk, mode=args.mode)
+    h_b.backward(dh_full[:, :, sl].contiguous().to(dev))
+    torch.cuda.synchronize()
+    gathered = []
+    for t in leaves:
+        parts = [torch.empty_like(t.grad) for _ in range(world)]
+        dist.all_gather(parts, t.grad.contiguous())
+        gathered.append(torch.cat(parts, 2))
     if rank == 0:
         full = [t.to(dev) for t in (q, k, v, i, f)]
         for rep in range(args.reps):
             torch.cuda.synchronize(); t0 = time.perf_counter()
             h1, last1 = mk.mlstm_chunkwise__b200_xl_chunk(*full, return_last_states=True, chunk_size=args.chunk)
             torch.cuda.synchronize(); ms1 = (time.perf_counter() - t0) * 1e3
+        full_leaves = [t.detach().clone().requires_grad_(True) for t in full]
+        mk.mlstm_chunkwise__b200_xl_chunk(*full_leaves, chunk_size=args.chunk).backward(dh_full.to(dev))
+        err_g = {"err_d" + n: max_rel_err(a.double().cpu().numpy(), b.grad.double().cpu().numpy())
+                 for n, a, b in zip("qkvif", gathered, full_leaves)}
         err = dict(err_h=max_rel_err(torch.cat(hs, 2).double().cpu().numpy(), h1.double().cpu().numpy()),
                    err_c=max_rel_err(last[0].double().cpu().numpy(), last1[0].double().cpu().numpy()),
                    err_n=max_rel_err(last[1].double().cpu().numpy(), last1[1].double().cpu().numpy()),
-                   err_m=max_rel_err(last[2].double().cpu().numpy(), last1[2].double().cpu().numpy()))
+                   err_m=max_rel_err(last[2].double().cpu().numpy(), last1[2].double().cpu().numpy()), **err_g)
         print(f"mode={args.mode} world={world} S={args.S}: sequence-parallel {ms:.3f} ms, single GPU {ms1:.3f} ms, "
               + " ".join(f"{k_}={v_:.2e}" for k_, v_ in err.items()))
         if args.out:

@@ -42,8 +42,8 @@ def test_scan_mode_emulated_on_one_gpu(dtype, L, dims, siging):
         sl = slice(r * seg, (r + 1) * seg)
         summ = sharding.segment_summary(k[:, :, sl], v[:, :, sl], i[:, :, sl], f[:, :, sl], chunk_size=Lk,
                                         variant=variant)
-        h, _ = sharding._segment_forward(q[:, :, sl], k[:, :, sl], v[:, :, sl], i[:, :, sl], f[:, :, sl], state,
-                                         chunk_size=Lk, eps=1e-6, variant=variant, impl="auto", want_last=False)
+        h, _, _ = sharding._segment_forward_saved(q[:, :, sl], k[:, :, sl], v[:, :, sl], i[:, :, sl], f[:, :, sl],
+                                                  state, chunk_size=Lk, eps=1e-6, variant=variant, impl="auto")
         state = sharding.state_combine(state, summ, variant=variant)
         hs.append(h)
     tol_h = 1e-5 if dtype == torch.float32 else 2e-2
@@ -58,6 +58,47 @@ def test_scan_mode_emulated_on_one_gpu(dtype, L, dims, siging):
     assert max_rel_err(npy(state[0]), ref["C_last"]) < (1e-4 if dtype == torch.float32 else 2e-2)
 
 
+@pytest.mark.parametrize("dtype,L,dims", [(torch.float32, 32, (16, 32)), (torch.bfloat16, 128, (256, 256))])
+@pytest.mark.parametrize("siging", [False, True])
+def test_backward_chain_emulated_on_one_gpu(dtype, L, dims, siging):
+    """The backward of the sequence-parallel mode, ranks emulated one after the other: segments are differentiated
+    from the last to the first, each receiving the gradient of the state it handed over and the sum of
+    (q . dq - k . dk) over all later tokens.  Compared with the single pass over the whole sequence."""
+    DHQK, DHHV = dims
+    P, S = 4, 4 * max(L, 128)
+    inp = case_inputs(33, 1, 2, S, DHQK, DHHV, f_offset=1.0)
+    q, k, v, i, f = (to_dev(inp[n], dtype) for n in "qkvif")
+    dh = to_dev(inp["dH"], dtype)
+    variant = _lib.SIG if siging else _lib.EXP
+    fn = mk.mlstm_siging_chunkwise__b200_xl_chunk if siging else mk.mlstm_chunkwise__b200_xl_chunk
+    leaves = [t.detach().clone().requires_grad_(True) for t in (q, k, v, i, f)]
+    fn(*leaves, chunk_size=L).backward(dh)
+    Lk = mk.kernel_chunk_size(q, v, L)
+    seg = S // P
+    state, saved = (None, None, None), []
+    for r in range(P):
+        sl = slice(r * seg, (r + 1) * seg)
+        _, state, sv = sharding._segment_forward_saved(q[:, :, sl], k[:, :, sl], v[:, :, sl], i[:, :, sl], f[:, :, sl],
+                                                       state, chunk_size=Lk, eps=1e-6, variant=variant, impl="auto")
+        saved.append(sv)
+    dc_last, tail, grads = None, None, [None] * P
+    for r in reversed(range(P)):
+        sl = slice(r * seg, (r + 1) * seg)
+        qs, ks, vs, is_, fs = (t[:, :, sl].contiguous() for t in (q, k, v, i, f))
+        dq, dk, dv, di, df, dc_last = sharding._segment_backward(qs, ks, vs, is_, fs, saved[r],
+                                                                 dh[:, :, sl].contiguous(), dc_last, chunk_size=Lk,
+                                                                 eps=1e-6, variant=variant, impl="auto")
+        own = sharding._segment_gate_sum(qs, ks, fs, dq, dk, df)
+        if tail is not None:
+            df = df + torch.sigmoid(-fs.float()) * tail[..., None]
+        tail = own if tail is None else own + tail
+        grads[r] = (dq, dk, dv, di, df)
+    tol = 1e-4 if dtype == torch.float32 else 2e-2
+    for j, name in enumerate("qkvif"):
+        got = torch.cat([g[j] for g in grads], 2)
+        assert max_rel_err(npy(got), npy(leaves[j].grad)) < tol, name
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least two GPUs")
 @pytest.mark.parametrize("mode", ["scan", "chain"])
 def test_sequence_parallel_torchrun(tmp_path, mode):
@@ -70,3 +111,5 @@ def test_sequence_parallel_torchrun(tmp_path, mode):
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
     res = dict(np.load(tmp_path / "result.npz"))
     assert res["err_h"] < 2e-2 and res["err_c"] < 1e-4 and res["err_n"] < 1e-4 and res["err_m"] < 1e-5
+    for n in "qkvif":   # backward chain against the single-GPU backward of the whole sequence
+        assert res["err_d" + n] < 2e-2, n

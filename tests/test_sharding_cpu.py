@@ -63,13 +63,21 @@ def fake_state_combine(state_in, summary, *, variant):
     return ((a[..., None] * c_in + b[..., None] * c_loc).float(), (a * n_in + b * n_loc).float(), m_out.float())
 
 
-def fake_segment_forward(q, k, v, i, f, state_in, *, chunk_size, eps, variant, impl, want_last):
+def fake_segment_forward_saved(q, k, v, i, f, state_in, *, chunk_size, eps, variant, impl):
     siging = variant != 0
     fw = O.chunkwise_fw(_np(q), _np(k), _np(v), _np(i), _np(f), _np(state_in[0]), _np(state_in[1]),
                         None if siging else _np(state_in[2]), chunk_size=chunk_size, eps=eps, siging=siging,
                         normalize=variant != 2)
     t = lambda x: torch.from_numpy(np.ascontiguousarray(x)).float()  # noqa: E731
-    return t(fw["H"]), (t(fw["C_last"]), t(fw["n_last"]), t(fw["m_last"]))
+    return t(fw["H"]), (t(fw["C_last"]), t(fw["n_last"]), t(fw["m_last"])), dict(fw=fw)
+
+
+def fake_segment_backward(q, k, v, i, f, saved, dh, dc_last, *, chunk_size, eps, variant, impl):
+    siging = variant != 0
+    bw = O.chunkwise_bw(_np(q), _np(k), _np(v), _np(i), _np(f), _np(dh), saved["fw"], _np(dc_last), True,
+                        chunk_size=chunk_size, eps=eps, siging=siging, normalize=variant != 2)
+    t = lambda x: torch.from_numpy(np.ascontiguousarray(x)).float()  # noqa: E731
+    return t(bw["dQ"]), t(bw["dK"]), t(bw["dV"]), t(bw["dI"]), t(bw["dF"]), t(bw["dC_initial"])
 
 
 CASE = dict(seed=17, B=1, NH=2, S=256, DHQK=16, DHHV=32, f_offset=1.0)
@@ -81,14 +89,18 @@ def _worker(rank, world, port, mode, siging, out_dir):
     dist.init_process_group("gloo", rank=rank, world_size=world)
     sharding.segment_summary = fake_segment_summary
     sharding.state_combine = fake_state_combine
-    sharding._segment_forward = fake_segment_forward
+    sharding._segment_forward_saved = fake_segment_forward_saved
+    sharding._segment_backward = fake_segment_backward
     inp = make_chunkwise_inputs(CASE)
     seg = CASE["S"] // world
     sl = slice(rank * seg, (rank + 1) * seg)
-    q, k, v, i, f = (torch.from_numpy(inp[n][:, :, sl].copy()) for n in "qkvif")
+    q, k, v, i, f = (torch.from_numpy(inp[n][:, :, sl].copy()).requires_grad_(True) for n in "qkvif")
     h, last = sharding.mlstm_chunkwise_sequence_parallel(q, k, v, i, f, return_last_states=True, chunk_size=32,
                                                          siging=siging, mode=mode)
-    np.savez(os.path.join(out_dir, f"r{rank}.npz"), h=h.numpy(), **{f"s{j}": t.numpy() for j, t in enumerate(last)})
+    (h * torch.from_numpy(inp["dH"][:, :, sl].copy())).sum().backward()   # chain of messages from the last rank back
+    np.savez(os.path.join(out_dir, f"r{rank}.npz"), h=h.detach().numpy(),
+             **{f"s{j}": t.numpy() for j, t in enumerate(last)},
+             **{"d" + n: t.grad.numpy() for n, t in zip("qkvif", (q, k, v, i, f))})
     dist.destroy_process_group()
 
 
@@ -104,7 +116,8 @@ def test_sequence_parallel_two_ranks_gloo(tmp_path, mode, siging):
     world = 2
     mp.spawn(_worker, args=(world, _free_port(), mode, siging, str(tmp_path)), nprocs=world, join=True)
     inp = make_chunkwise_inputs(CASE)
-    full = O.chunkwise_fw(inp["q"], inp["k"], inp["v"], inp["i"], inp["f"], chunk_size=32, siging=siging)
+    full, full_bw = O.chunkwise_fwbw(inp["q"], inp["k"], inp["v"], inp["i"], inp["f"], inp["dH"], chunk_size=32,
+                                     siging=siging)
     outs = [dict(np.load(tmp_path / f"r{r}.npz")) for r in range(world)]
     h = np.concatenate([o["h"] for o in outs], axis=2)
     assert max_rel_err(h, full["H"]) < 1e-5
@@ -113,3 +126,7 @@ def test_sequence_parallel_two_ranks_gloo(tmp_path, mode, siging):
         assert max_rel_err(o["s1"], full["n_last"]) < 1e-5
         if not siging:
             assert max_rel_err(o["s2"], full["m_last"]) < 1e-6
+    # gradients of the whole sequence, assembled from the ranks' segments
+    for n, key in (("q", "dQ"), ("k", "dK"), ("v", "dV"), ("i", "dI"), ("f", "dF")):
+        got = np.concatenate([o["d" + n] for o in outs], axis=2)
+        assert max_rel_err(got, full_bw[key]) < 1e-5, key
