@@ -347,7 +347,7 @@ constexpr int PAR_SMEM = PAR_NST * PAR_STAGE + 1024;
 
 // Shared-memory control block of one intra-chunk CTA (the operand ring lives in dynamic shared memory).
 struct ParShared {
-  uint64_t bar_full[PAR_NST], bar_empty[PAR_NST], bar_qdone[PAR_NST], bar_sfull, bar_afull, bar_gated, bar_hfull, bar_dot,
+  uint64_t bar_full[PAR_NST], bar_empty[PAR_NST], bar_qdone[PAR_NST], bar_sfull, bar_afull, bar_gated, bar_hfull, bar_accfree, bar_done, bar_dot,
       bar_pair[4], bar_out;
   uint32_t tmem;
   __align__(16) float s_colE[CL];  // per-column term of the gate exponent, base 2 (see par_body)
@@ -373,7 +373,7 @@ struct ParShared {
 __device__ __forceinline__ void
 par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const CUtensorMap* mapX,
          const CUtensorMap* mapSt, const CUtensorMap* mapE, const ParParams& p,
-         ParShared& sh, const int o_tile, const int ck, const int bh) {
+         ParShared& sh, const int o_tile0, const int nsub, const int ck, const int bh) {
   const bool LOWER = (mode == PM_H || mode == PM_DQ);
   const bool ST_MN = (mode == PM_H || mode == PM_DV);  // state operand N-contiguous in shared memory
   const bool HAS_E = (mode == PM_DQ || mode == PM_DK);  // extra tile for the gate-gradient row sums
@@ -381,7 +381,7 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int o0 = o_tile * 128;
+  const int o00 = o_tile0 * 128;   // first output column of the CTA's first tile
   const int DI = (mode == PM_H || mode == PM_DV) ? p.DHQK : p.DHHV;   // contraction dim of the score product
   const int DO = (mode == PM_H || mode == PM_DV) ? p.DHHV : p.DHQK;   // output width
   const int NC = p.NC, ND = DI / 64;
@@ -394,7 +394,7 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
     }
     mbar_init(&sh.bar_sfull, 1); mbar_init(&sh.bar_afull, 1); mbar_init(&sh.bar_gated, 256); mbar_init(&sh.bar_hfull, 1); mbar_init(&sh.bar_dot, 256);
     for (int s = 0; s < 4; ++s) mbar_init(&sh.bar_pair[s], 64);
-    mbar_init(&sh.bar_out, 256);
+    mbar_init(&sh.bar_out, 256); mbar_init(&sh.bar_accfree, 256); mbar_init(&sh.bar_done, 256);
     fence_barrier_init();
     tma_prefetch_desc(mapA); tma_prefetch_desc(mapB); tma_prefetch_desc(mapX); tma_prefetch_desc(mapSt);
     if (HAS_E) tma_prefetch_desc(mapE);
@@ -408,7 +408,22 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
   // Ring loads, in order: ND (A, B) slice pairs for the score product, ND (A, state) slice pairs for the inter-chunk
   // product (A comes from L2 the second time), the X tile, the E tile.  The score is complete - and the element-wise
   // warps start gating - while the second group is still arriving.
-  const int n_loads = 2 * ND + 1 + (HAS_E ? 1 : 0);
+  // A CTA produces `nsub` (1 or 2) neighbouring 128-column output tiles of the same chunk and mode.  The score tile
+  // and its gated form are the same for both, so the second tile only needs its own state slices, X and E tiles:
+  // the gated tile stays in tensor memory, the accumulator is reused once the first tile's epilogue has read it.
+  const int n0 = 2 * ND + 1 + (HAS_E ? 1 : 0);          // loads of the first tile
+  const int n1 = ND + 1 + (HAS_E ? 1 : 0);              // loads of the second tile
+  const int n_loads = n0 + (nsub > 1 ? n1 : 0);
+  enum { LK_SCORE = 0, LK_STATE = 1, LK_X = 2, LK_E = 3 };
+  auto load_kind = [&](int ld, int& sub, int& it) -> int {
+    sub = ld >= n0 ? 1 : 0;
+    const int l = ld - sub * n0;
+    if (sub == 0 && l < ND) { it = l; return LK_SCORE; }
+    const int ls = l - (sub == 0 ? ND : 0);
+    if (ls < ND) { it = ls; return LK_STATE; }
+    it = 0;
+    return ls == ND ? LK_X : LK_E;
+  };
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -416,20 +431,32 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
       const int slot = LOWER ? ck : ck + 1;
       const int srow = (bh * (NC + 1) + slot) * p.DHQK;
       int issued = 0;
+      int rel_mma[PAR_NST] = {0, 0, 0};   // uses of a stage handed back by an MMA commit so far (phase counter of bar_empty)
+      int rel_q[PAR_NST] = {0, 0, 0};     // score pairs of a stage read for q . n so far (phase counter of bar_qdone)
       for (int ld = 0; ld < n_loads; ++ld) {
-        const int st = ld % PAR_NST, use = ld / PAR_NST;
-        if (!mbar_wait(&sh.bar_empty[st], (use & 1) ^ 1, &g_sm100_status, 201)) break;
-        // the element-wise warps read the A box of a score pair (q . n): the stage is reused only after they are done
-        if (use_n && ld >= PAR_NST && ld - PAR_NST < ND &&
-            !mbar_wait(&sh.bar_qdone[st], ((use - 1) & 1), &g_sm100_status, 212))
-          break;
+        const int st = ld % PAR_NST;
+        int sub, it;
+        const int kind = load_kind(ld, sub, it);
+        if (ld >= PAR_NST) {   // the stage's previous occupant must be gone
+          int psub, pit;
+          const int pkind = load_kind(ld - PAR_NST, psub, pit);
+          bool okw;
+          if (pkind == LK_SCORE || pkind == LK_STATE) {
+            okw = mbar_wait(&sh.bar_empty[st], (rel_mma[st] - 1) & 1, &g_sm100_status, 201);
+            // the element-wise warps read the A box of a score pair (q . n)
+            if (okw && use_n && pkind == LK_SCORE) okw = mbar_wait(&sh.bar_qdone[st], (rel_q[st] - 1) & 1, &g_sm100_status, 212);
+          } else {             // X (the staging buffer of a tile) and E are handed back when the tile has been stored
+            okw = mbar_wait(&sh.bar_done, psub & 1, &g_sm100_status, 215);
+          }
+          if (!okw) break;
+        }
+        const int o0 = o00 + 128 * sub;
         uint8_t* sb = smem + st * PAR_STAGE;
         mbar_expect_tx(&sh.bar_full[st], PAR_STAGE);
-        if (ld < ND) {
-          tma_load_2d(sb, mapA, &sh.bar_full[st], 64 * ld, row0);
-          tma_load_2d(sb + 16384, mapB, &sh.bar_full[st], 64 * ld, row0);
-        } else if (ld < 2 * ND) {
-          const int it = ld - ND;
+        if (kind == LK_SCORE) {
+          tma_load_2d(sb, mapA, &sh.bar_full[st], 64 * it, row0);
+          tma_load_2d(sb + 16384, mapB, &sh.bar_full[st], 64 * it, row0);
+        } else if (kind == LK_STATE) {
           tma_load_2d(sb, mapA, &sh.bar_full[st], 64 * it, row0);
           if (ST_MN) {
             tma_load_2d(sb + 16384, mapSt, &sh.bar_full[st], o0, srow + 64 * it);
@@ -438,10 +465,12 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
             tma_load_2d(sb + 16384, mapSt, &sh.bar_full[st], 64 * it, srow + o0);
           }
         } else {
-          const CUtensorMap* m = (ld == 2 * ND) ? mapX : mapE;
+          const CUtensorMap* m = (kind == LK_X) ? mapX : mapE;
           tma_load_2d(sb, m, &sh.bar_full[st], o0, row0);
           tma_load_2d(sb + 16384, m, &sh.bar_full[st], o0 + 64, row0);
         }
+        if (kind == LK_SCORE || kind == LK_STATE) ++rel_mma[st];
+        if (kind == LK_SCORE) ++rel_q[st];
         issued = ld + 1;
       }
       if (issued < n_loads && issued > 0) {  // error path: let the copies in flight land before the CTA retires
@@ -469,31 +498,35 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
         umma_commit(&sh.bar_empty[st]);
       }
       if (ok) umma_commit(&sh.bar_sfull);
-      for (int ld = ND; ld < 2 * ND && ok; ++ld) {  // inter-chunk term: Acc = A . State
-        const int st = ld % PAR_NST;
-        if (!mbar_wait(&sh.bar_full[st], (ld / PAR_NST) & 1, &g_sm100_status, 213)) { ok = false; break; }
-        tc_fence_after_sync();
-        const uint32_t sa = smem_u32(smem + st * PAR_STAGE), ss = sa + 16384;
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {
-          const uint64_t bdesc = ST_MN ? umma_desc_sw128(ss + kk * 2048, 8192, 1024) : umma_desc_sw128(ss + kk * 32, 16, 1024);
-          umma_ss(tAcc, umma_desc_sw128(sa + kk * 32, 16, 1024), bdesc, idesc_st, (ld > ND || kk > 0) ? 1u : 0u);
-        }
-        umma_commit(&sh.bar_empty[st]);
-      }
-      if (ok) {
-        umma_commit(&sh.bar_afull);
-        const int ldx = 2 * ND, stx = ldx % PAR_NST;
-        ok = mbar_wait(&sh.bar_full[stx], (ldx / PAR_NST) & 1, &g_sm100_status, 203) &&
-             mbar_wait(&sh.bar_gated, 0, &g_sm100_status, 204);
-        if (ok) {
+      for (int sub = 0; sub < nsub && ok; ++sub) {
+        const int lbase = sub == 0 ? ND : n0;       // first state pair of this tile
+        // the accumulator tile is free once the previous tile's epilogue has read it
+        if (sub > 0 && !mbar_wait(&sh.bar_accfree, 0, &g_sm100_status, 216)) { ok = false; break; }
+        if (sub > 0) tc_fence_after_sync();
+        for (int it = 0; it < ND; ++it) {           // inter-chunk term: Acc = A . State
+          const int ld = lbase + it, st = ld % PAR_NST;
+          if (!mbar_wait(&sh.bar_full[st], (ld / PAR_NST) & 1, &g_sm100_status, 213)) { ok = false; break; }
           tc_fence_after_sync();
-          const uint32_t sx = smem_u32(smem + stx * PAR_STAGE);
+          const uint32_t sa = smem_u32(smem + st * PAR_STAGE), ss = sa + 16384;
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk)
-            umma_ts(tAcc, tS + kk * 8, umma_desc_sw128(sx + kk * 2048, 16384, 1024), idesc_x, 1u);
-          umma_commit(&sh.bar_hfull);
+          for (int kk = 0; kk < 4; ++kk) {
+            const uint64_t bdesc = ST_MN ? umma_desc_sw128(ss + kk * 2048, 8192, 1024) : umma_desc_sw128(ss + kk * 32, 16, 1024);
+            umma_ss(tAcc, umma_desc_sw128(sa + kk * 32, 16, 1024), bdesc, idesc_st, (it > 0 || kk > 0) ? 1u : 0u);
+          }
+          umma_commit(&sh.bar_empty[st]);
         }
+        if (!ok) break;
+        umma_commit(&sh.bar_afull);
+        const int ldx = lbase + ND, stx = ldx % PAR_NST;
+        ok = mbar_wait(&sh.bar_full[stx], (ldx / PAR_NST) & 1, &g_sm100_status, 203) &&
+             mbar_wait(&sh.bar_gated, sub & 1, &g_sm100_status, 204);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t sx = smem_u32(smem + stx * PAR_STAGE);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_ts(tAcc, tS + kk * 8, umma_desc_sw128(sx + kk * 2048, 16384, 1024), idesc_x, 1u);
+        umma_commit(&sh.bar_hfull);
       }
     }
   } else {
@@ -625,108 +658,116 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
 #pragma unroll
         for (int u = 0; u < 2; ++u) tmem_st16(tS + lane_base + (half + 2 * u) * 16, pk[u]);
         sh.s_part[half][r] = rowsum;
-        // the inter-chunk product has usually landed by now: row-scale it in place
-        ok = mbar_wait(&sh.bar_afull, 0, &g_sm100_status, 214);
-      }
-      if (ok) {
-        tc_fence_after_sync();
-#pragma unroll 1
-        for (int cq = half; cq < 4; cq += 2) {
-          uint32_t va[16], vb[16];
-          const uint32_t ta = tAcc + lane_base + cq * 32;
-          tmem_ld16(ta, va);
-          tmem_wait_ld(va);
-          tmem_ld16(ta + 16, vb);
-#pragma unroll
-          for (int c = 0; c < 16; ++c) va[c] = __float_as_uint(__uint_as_float(va[c]) * rowscale);
-          tmem_wait_ld(vb);
-          tmem_st16(ta, va);
-#pragma unroll
-          for (int c = 0; c < 16; ++c) vb[c] = __float_as_uint(__uint_as_float(vb[c]) * rowscale);
-          tmem_st16(ta + 16, vb);
-        }
         tmem_wait_st();
-        tc_fence_before_sync();
-        mbar_arrive(&sh.bar_gated);
-        ok = mbar_wait(&sh.bar_hfull, 0, &g_sm100_status, 206);
       }
     }
-    if (ok) {
+    // ---- per output tile: row-scale the inter-chunk product, second product, epilogue, store ----
+    float inv = 1.f;
+    for (int sub = 0; sub < nsub && ok; ++sub) {
+      const int o0 = o00 + 128 * sub;
+      // the inter-chunk product of this tile has usually landed by now: row-scale it in place
+      if (!mbar_wait(&sh.bar_afull, sub & 1, &g_sm100_status, 214)) { ok = false; break; }
       tc_fence_after_sync();
-      float inv = 1.f;
-      if (mode == PM_H) {
+#pragma unroll 1
+      for (int cq = half; cq < 4; cq += 2) {
+        uint32_t va[16], vb[16];
+        const uint32_t ta = tAcc + lane_base + cq * 32;
+        tmem_ld16(ta, va);
+        tmem_wait_ld(va);
+        tmem_ld16(ta + 16, vb);
+#pragma unroll
+        for (int c = 0; c < 16; ++c) va[c] = __float_as_uint(__uint_as_float(va[c]) * rowscale);
+        tmem_wait_ld(vb);
+        tmem_st16(ta, va);
+#pragma unroll
+        for (int c = 0; c < 16; ++c) vb[c] = __float_as_uint(__uint_as_float(vb[c]) * rowscale);
+        tmem_st16(ta + 16, vb);
+      }
+      tmem_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(&sh.bar_gated);   // (first tile: the gated score tile is in place as well)
+      if (!mbar_wait(&sh.bar_hfull, sub & 1, &g_sm100_status, 206)) { ok = false; break; }
+      tc_fence_after_sync();
+      if (sub == 0 && mode == PM_H) {
         float den = 1.f;
         const float nn = (sh.s_part[0][r] + sh.s_part[1][r]) + rowscale * (use_n ? (sh.s_qn[0][r] + sh.s_qn[1][r]) : 0.f);
         if (p.variant == MLSTM_EXP) den = fmaxf(fabsf(nn), __expf(-m_r));
         else if (p.variant == MLSTM_SIG) den = fmaxf(fabsf(nn), 1.f);
         if (p.variant != MLSTM_SIG_NONORM) inv = 1.f / (den + p.eps);
-        if (o_tile == 0 && half == 0) p.n_out[tok] = den;
+        if (o_tile0 == 0 && half == 0) p.n_out[tok] = den;
       }
+      const int ldx = (sub == 0 ? 2 * ND : n0 + ND);    // ring index of this tile's X load; E follows it
       const uint8_t* erow = smem;
       if (HAS_E) {
-        const int lde = 2 * ND + 1, ste = lde % PAR_NST;
-        ok = mbar_wait(&sh.bar_full[ste], (lde / PAR_NST) & 1, &g_sm100_status, 208);
+        const int lde = ldx + 1, ste = lde % PAR_NST;
+        if (!mbar_wait(&sh.bar_full[ste], (lde / PAR_NST) & 1, &g_sm100_status, 208)) { ok = false; break; }
         erow = smem + ste * PAR_STAGE + r * 128;
       }
       float dot4[4] = {0.f, 0.f, 0.f, 0.f};   // four partial sums: no 64-long chain of dependent FMAs
       // The output tile is staged (bf16, two boxes of 128 rows x 128 bytes, 16-byte pieces XOR-swizzled by the row)
-      // in the ring stage the X tile occupied - every MMA that read the ring has completed - and is then written out
+      // in the ring stage the X tile occupied - every MMA that read it has completed - and is then written out
       // by all element-wise warps together, each warp instruction covering two full 256-byte rows of the tile.  Plain
       // stores are posted, so the CTA retires without waiting for them.
-      uint8_t* ostage = smem + ((2 * ND) % PAR_NST) * PAR_STAGE;
-      if (ok) {
+      uint8_t* ostage = smem + (ldx % PAR_NST) * PAR_STAGE;
 #pragma unroll 1
-        for (int cq = half; cq < 4; cq += 2) {
-          uint32_t va[16], vb[16];
-          const uint32_t ta = tAcc + lane_base + cq * 32;
-          tmem_ld16(ta, va);
-          tmem_wait_ld(va);
-          tmem_ld16(ta + 16, vb);
-          uint8_t* orow = ostage + (cq >> 1) * 16384 + r * 128;
+      for (int cq = half; cq < 4; cq += 2) {
+        uint32_t va[16], vb[16];
+        const uint32_t ta = tAcc + lane_base + cq * 32;
+        tmem_ld16(ta, va);
+        tmem_wait_ld(va);
+        tmem_ld16(ta + 16, vb);
+        uint8_t* orow = ostage + (cq >> 1) * 16384 + r * 128;
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            if (c == 2) tmem_wait_ld(vb);
-            const uint32_t (&v)[16] = (c < 2) ? va : vb;
-            float x[8];
+        for (int c = 0; c < 4; ++c) {
+          if (c == 2) tmem_wait_ld(vb);
+          const uint32_t (&v)[16] = (c < 2) ? va : vb;
+          float x[8];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) x[e] = __uint_as_float(v[8 * (c & 1) + e]) * inv;
-            const int sw = (((cq & 1) * 4 + c) ^ (r & 7)) << 4;   // 16-byte chunk (cq*4 + c) of the row, swizzled
-            if (HAS_E) {
-              const uint4 ev = *reinterpret_cast<const uint4*>(erow + (cq >> 1) * 16384 + sw);
-              const uint32_t w[4] = {ev.x, ev.y, ev.z, ev.w};
+          for (int e = 0; e < 8; ++e) x[e] = __uint_as_float(v[8 * (c & 1) + e]) * inv;
+          const int sw = (((cq & 1) * 4 + c) ^ (r & 7)) << 4;   // 16-byte chunk (cq*4 + c) of the row, swizzled
+          if (HAS_E) {
+            const uint4 ev = *reinterpret_cast<const uint4*>(erow + (cq >> 1) * 16384 + sw);
+            const uint32_t w[4] = {ev.x, ev.y, ev.z, ev.w};
 #pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const __nv_bfloat162 h2 = *reinterpret_cast<const __nv_bfloat162*>(&w[e]);
-                dot4[e] = fmaf(__low2float(h2), x[2 * e], dot4[e]);
-                dot4[e] = fmaf(__high2float(h2), x[2 * e + 1], dot4[e]);
-              }
+            for (int e = 0; e < 4; ++e) {
+              const __nv_bfloat162 h2 = *reinterpret_cast<const __nv_bfloat162*>(&w[e]);
+              dot4[e] = fmaf(__low2float(h2), x[2 * e], dot4[e]);
+              dot4[e] = fmaf(__high2float(h2), x[2 * e + 1], dot4[e]);
             }
-            uint4 o;
-            o.x = pack_bf16(x[0], x[1]); o.y = pack_bf16(x[2], x[3]);
-            o.z = pack_bf16(x[4], x[5]); o.w = pack_bf16(x[6], x[7]);
-            *reinterpret_cast<uint4*>(orow + sw) = o;
           }
-        }
-        const float dot = (dot4[0] + dot4[1]) + (dot4[2] + dot4[3]);
-        mbar_arrive(&sh.bar_out);
-        if (mbar_wait(&sh.bar_out, 0, &g_sm100_status, 211)) {
-          __nv_bfloat16* outp = (mode == PM_H) ? p.out_h : (mode == PM_DV) ? p.out_dv : (mode == PM_DK) ? p.out_dk : p.out_dq;
-          uint8_t* gbase = reinterpret_cast<uint8_t*>(outp + (size_t)row0 * DO + o0);
-          const int ew = warp - 2, j = lane & 15;          // 16-byte piece j of the 256-byte tile row
-#pragma unroll
-          for (int i2 = 0; i2 < 8; ++i2) {
-            const int orow_i = 16 * i2 + 2 * ew + (lane >> 4);
-            const uint4 o = *reinterpret_cast<const uint4*>(ostage + (j >> 3) * 16384 + orow_i * 128 + (((j & 7) ^ (orow_i & 7)) << 4));
-            *reinterpret_cast<uint4*>(gbase + (size_t)orow_i * DO * 2 + j * 16) = o;
-          }
-        }
-        if (HAS_E) {
-          sh.s_qn[half][r] = dot;
-          mbar_arrive(&sh.bar_dot);
-          if (half == 0 && mbar_wait(&sh.bar_dot, 0, &g_sm100_status, 209))
-            ((mode == PM_DQ) ? p.rowdot_q : p.rowdot_k)[(size_t)o_tile * p.ntok + tok] = sh.s_qn[0][r] + sh.s_qn[1][r];
+          uint4 o;
+          o.x = pack_bf16(x[0], x[1]); o.y = pack_bf16(x[2], x[3]);
+          o.z = pack_bf16(x[4], x[5]); o.w = pack_bf16(x[6], x[7]);
+          *reinterpret_cast<uint4*>(orow + sw) = o;
         }
       }
+      if (sub + 1 < nsub) {   // the accumulator tile may be overwritten by the next tile's inter-chunk product
+        tc_fence_before_sync();
+        mbar_arrive(&sh.bar_accfree);
+      }
+      const float dot = (dot4[0] + dot4[1]) + (dot4[2] + dot4[3]);
+      mbar_arrive(&sh.bar_out);
+      if (!mbar_wait(&sh.bar_out, sub & 1, &g_sm100_status, 211)) { ok = false; break; }
+      {
+        __nv_bfloat16* outp = (mode == PM_H) ? p.out_h : (mode == PM_DV) ? p.out_dv : (mode == PM_DK) ? p.out_dk : p.out_dq;
+        uint8_t* gbase = reinterpret_cast<uint8_t*>(outp + (size_t)row0 * DO + o0);
+        const int ew = warp - 2, j = lane & 15;          // 16-byte piece j of the 256-byte tile row
+#pragma unroll
+        for (int i2 = 0; i2 < 8; ++i2) {
+          const int orow_i = 16 * i2 + 2 * ew + (lane >> 4);
+          const uint4 o = *reinterpret_cast<const uint4*>(ostage + (j >> 3) * 16384 + orow_i * 128 + (((j & 7) ^ (orow_i & 7)) << 4));
+          *reinterpret_cast<uint4*>(gbase + (size_t)orow_i * DO * 2 + j * 16) = o;
+        }
+      }
+      if (HAS_E) {
+        sh.s_qn[half][r] = dot;
+        mbar_arrive(&sh.bar_dot);
+        if (half == 0) {
+          if (!mbar_wait(&sh.bar_dot, sub & 1, &g_sm100_status, 209)) { ok = false; break; }
+          ((mode == PM_DQ) ? p.rowdot_q : p.rowdot_k)[(size_t)(o_tile0 + sub) * p.ntok + tok] = sh.s_qn[0][r] + sh.s_qn[1][r];
+        }
+      }
+      if (sub + 1 < nsub) mbar_arrive(&sh.bar_done);   // staging and E stages of this tile may be refilled
     }
   }
   tc_fence_before_sync();
@@ -739,7 +780,8 @@ par_fw_sm100(const __grid_constant__ CUtensorMap mQ, const __grid_constant__ CUt
              const __grid_constant__ CUtensorMap mV, const __grid_constant__ CUtensorMap mC,
              const __grid_constant__ ParParams p) {
   __shared__ ParShared sh;
-  par_body(PM_H, &mQ, &mK, &mV, &mC, &mV, p, sh, blockIdx.x, blockIdx.y, blockIdx.z);
+  const int T = p.DHHV / 128;                         // output tiles per chunk; a CTA takes two (the last one may take one)
+  par_body(PM_H, &mQ, &mK, &mV, &mC, &mV, p, sh, 2 * blockIdx.x, min(2, T - 2 * (int)blockIdx.x), blockIdx.y, blockIdx.z);
 }
 
 // deltaV, deltaK and deltaQ of one chunk in ONE launch: blockIdx.x enumerates the 128-wide output tiles of the three
@@ -752,14 +794,15 @@ par_bw_sm100(const __grid_constant__ CUtensorMap mQ, const __grid_constant__ CUt
              const __grid_constant__ CUtensorMap mdC_k,
              const __grid_constant__ ParParams p) {
   __shared__ ParShared sh;
-  const int t_dv = p.DHHV / 128, t_dk = p.DHQK / 128;
+  const int T_dv = p.DHHV / 128, T_dk = p.DHQK / 128;         // output tiles per chunk of dV, and of dK / dQ
+  const int c_dv = (T_dv + 1) / 2, c_dk = (T_dk + 1) / 2;     // CTAs: two tiles each (the last one may take one)
   const int x = blockIdx.x;
-  int mode, tile;
+  int mode, pair, T;
   const CUtensorMap *a, *b, *xm, *stm, *e;
-  if (x < t_dv) { mode = PM_DV; tile = x; a = &mK; b = &mQ; xm = &mDH; stm = &mdC_mn; e = &mDH; }
-  else if (x < t_dv + t_dk) { mode = PM_DK; tile = x - t_dv; a = &mV; b = &mDH; xm = &mQ; stm = &mdC_k; e = &mK; }
-  else { mode = PM_DQ; tile = x - t_dv - t_dk; a = &mDH; b = &mV; xm = &mK; stm = &mC_k; e = &mQ; }
-  par_body(mode, a, b, xm, stm, e, p, sh, tile, blockIdx.y, blockIdx.z);
+  if (x < c_dv) { mode = PM_DV; pair = x; T = T_dv; a = &mK; b = &mQ; xm = &mDH; stm = &mdC_mn; e = &mDH; }
+  else if (x < c_dv + c_dk) { mode = PM_DK; pair = x - c_dv; T = T_dk; a = &mV; b = &mDH; xm = &mQ; stm = &mdC_k; e = &mK; }
+  else { mode = PM_DQ; pair = x - c_dv - c_dk; T = T_dk; a = &mDH; b = &mV; xm = &mK; stm = &mC_k; e = &mQ; }
+  par_body(mode, a, b, xm, stm, e, p, sh, 2 * pair, min(2, T - 2 * pair), blockIdx.y, blockIdx.z);
 }
 
 // =====================================================================================================
@@ -832,7 +875,7 @@ int sm100_parallel_fw(const void* q, const void* k, const void* v, const GateBuf
   ParParams pp = base_params(gb, d);
   pp.n_states = n_states; pp.out_h = (__nv_bfloat16*)h; pp.n_out = n_out;
   MLSTM_CUDA_CHECK(cudaFuncSetAttribute(par_fw_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, PAR_SMEM));
-  dim3 grid(d.DHHV / 128, d.NC, d.B * d.NH);
+  dim3 grid((d.DHHV / 128 + 1) / 2, d.NC, d.B * d.NH);   // two output tiles per CTA
   par_fw_sm100<<<grid, PAR_THREADS, PAR_SMEM, st>>>(mQ, mK, mV, mC, pp);
   MLSTM_LAUNCH_CHECK();
   return MLSTM_OK;
@@ -851,7 +894,7 @@ int sm100_parallel_bw(const void* q, const void* k, const void* v, const void* d
   pp.out_dv = (__nv_bfloat16*)dv; pp.out_dk = (__nv_bfloat16*)dk; pp.out_dq = (__nv_bfloat16*)dq;
   pp.rowdot_q = qdq_parts; pp.rowdot_k = kdk_parts;
   MLSTM_CUDA_CHECK(cudaFuncSetAttribute(par_bw_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, PAR_SMEM));
-  dim3 grid(d.DHHV / 128 + 2 * (d.DHQK / 128), d.NC, d.B * d.NH);
+  dim3 grid((d.DHHV / 128 + 1) / 2 + 2 * ((d.DHQK / 128 + 1) / 2), d.NC, d.B * d.NH);   // two output tiles per CTA
   par_bw_sm100<<<grid, PAR_THREADS, PAR_SMEM, st>>>(mQ, mK, mV, mDH, mC_k, mdC_mn, mdC_k, pp);
   MLSTM_LAUNCH_CHECK();
   return MLSTM_OK;
