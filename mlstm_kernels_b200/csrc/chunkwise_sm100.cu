@@ -431,8 +431,11 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
       const int slot = LOWER ? ck : ck + 1;
       const int srow = (bh * (NC + 1) + slot) * p.DHQK;
       int issued = 0;
-      int rel_mma[PAR_NST] = {0, 0, 0};   // uses of a stage handed back by an MMA commit so far (phase counter of bar_empty)
-      int rel_q[PAR_NST] = {0, 0, 0};     // score pairs of a stage read for q . n so far (phase counter of bar_qdone)
+      // Per stage: uses handed back by an MMA commit so far (phase counter of bar_empty) and score pairs read for
+      // q . n so far (phase counter of bar_qdone).  Scalars picked by comparisons, not arrays: a dynamically indexed
+      // array would live in local memory, and with nearly all of L1 configured as shared memory every access to it
+      // is a round trip to L2 on the load-issue path.
+      int rm0 = 0, rm1 = 0, rm2 = 0, rq0 = 0, rq1 = 0, rq2 = 0;
       for (int ld = 0; ld < n_loads; ++ld) {
         const int st = ld % PAR_NST;
         int sub, it;
@@ -442,11 +445,17 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
           const int pkind = load_kind(ld - PAR_NST, psub, pit);
           bool okw;
           if (pkind == LK_SCORE || pkind == LK_STATE) {
-            okw = mbar_wait(&sh.bar_empty[st], (rel_mma[st] - 1) & 1, &g_sm100_status, 201);
+            const int rm = st == 0 ? rm0 : (st == 1 ? rm1 : rm2);
+            okw = mbar_wait(&sh.bar_empty[st], (rm - 1) & 1, &g_sm100_status, 201);
             // the element-wise warps read the A box of a score pair (q . n)
-            if (okw && use_n && pkind == LK_SCORE) okw = mbar_wait(&sh.bar_qdone[st], (rel_q[st] - 1) & 1, &g_sm100_status, 212);
-          } else {             // X (the staging buffer of a tile) and E are handed back when the tile has been stored
+            if (okw && use_n && pkind == LK_SCORE) {
+              const int rq = st == 0 ? rq0 : (st == 1 ? rq1 : rq2);
+              okw = mbar_wait(&sh.bar_qdone[st], (rq - 1) & 1, &g_sm100_status, 212);
+            }
+          } else if (pkind == LK_X) {   // the staging buffer of a tile is handed back when the tile has been stored
             okw = mbar_wait(&sh.bar_done, psub & 1, &g_sm100_status, 215);
+          } else {                      // E: when the tile's epilogue has read it (same point as the accumulator)
+            okw = mbar_wait(&sh.bar_accfree, psub & 1, &g_sm100_status, 217);
           }
           if (!okw) break;
         }
@@ -469,8 +478,8 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
           tma_load_2d(sb, m, &sh.bar_full[st], o0, row0);
           tma_load_2d(sb + 16384, m, &sh.bar_full[st], o0 + 64, row0);
         }
-        if (kind == LK_SCORE || kind == LK_STATE) ++rel_mma[st];
-        if (kind == LK_SCORE) ++rel_q[st];
+        if (kind == LK_SCORE || kind == LK_STATE) { rm0 += (st == 0); rm1 += (st == 1); rm2 += (st == 2); }
+        if (kind == LK_SCORE) { rq0 += (st == 0); rq1 += (st == 1); rq2 += (st == 2); }
         issued = ld + 1;
       }
       if (issued < n_loads && issued > 0) {  // error path: let the copies in flight land before the CTA retires
