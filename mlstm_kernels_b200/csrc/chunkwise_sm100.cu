@@ -750,8 +750,9 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
           *reinterpret_cast<uint4*>(orow + sw) = o;
         }
       }
-      if (sub + 1 < nsub) {   // the accumulator tile may be overwritten by the next tile's inter-chunk product
-        tc_fence_before_sync();
+      if (sub + 1 < nsub) {   // the accumulator tile may be overwritten by the next tile's inter-chunk product,
+        tc_fence_before_sync();   // and the E stage refilled (generic-proxy reads ordered before the TMA writes)
+        fence_proxy_async_smem();
         mbar_arrive(&sh.bar_accfree);
       }
       const float dot = (dot4[0] + dot4[1]) + (dot4[2] + dot4[3]);
@@ -776,7 +777,13 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
           ((mode == PM_DQ) ? p.rowdot_q : p.rowdot_k)[(size_t)(o_tile0 + sub) * p.ntok + tok] = sh.s_qn[0][r] + sh.s_qn[1][r];
         }
       }
-      if (sub + 1 < nsub) mbar_arrive(&sh.bar_done);   // staging and E stages of this tile may be refilled
+      if (sub + 1 < nsub) {
+        // The staging stage of this tile may be refilled.  The TMA engine writes shared memory through the async
+        // proxy: without this fence its data can be overtaken by this thread's own earlier (generic-proxy) staging
+        // writes to the same addresses.
+        fence_proxy_async_smem();
+        mbar_arrive(&sh.bar_done);
+      }
     }
   }
   tc_fence_before_sync();
