@@ -343,6 +343,7 @@ struct ParParams {
 constexpr int PAR_THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2..9 element-wise
 constexpr int PAR_STAGE = 32768;  // two 16 KB boxes: (A, B) slice pair, (A, state) slice pair, or a 128 x 128 tile
 constexpr int PAR_NST = 3;        // ring depth
+constexpr int PAR_MAXSUB = 4;     // output tiles one CTA produces at most
 constexpr int PAR_SMEM = PAR_NST * PAR_STAGE + 1024;
 
 // Shared-memory control block of one intra-chunk CTA (the operand ring lives in dynamic shared memory).
@@ -408,16 +409,16 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
   // Ring loads, in order: ND (A, B) slice pairs for the score product, ND (A, state) slice pairs for the inter-chunk
   // product (A comes from L2 the second time), the X tile, the E tile.  The score is complete - and the element-wise
   // warps start gating - while the second group is still arriving.
-  // A CTA produces `nsub` (1 or 2) neighbouring 128-column output tiles of the same chunk and mode.  The score tile
-  // and its gated form are the same for both, so the second tile only needs its own state slices, X and E tiles:
-  // the gated tile stays in tensor memory, the accumulator is reused once the first tile's epilogue has read it.
+  // A CTA produces `nsub` (1 .. PAR_MAXSUB) neighbouring 128-column output tiles of the same chunk and mode.  The
+  // score tile and its gated form are the same for all of them, so every tile after the first only needs its own
+  // state slices, X and E tiles: the gated tile stays in tensor memory, the accumulator is reused once the previous
+  // tile's epilogue has read it.
   const int n0 = 2 * ND + 1 + (HAS_E ? 1 : 0);          // loads of the first tile
-  const int n1 = ND + 1 + (HAS_E ? 1 : 0);              // loads of the second tile
-  const int n_loads = n0 + (nsub > 1 ? n1 : 0);
+  const int n1 = ND + 1 + (HAS_E ? 1 : 0);              // loads of every further tile
+  const int n_loads = n0 + (nsub - 1) * n1;
   enum { LK_SCORE = 0, LK_STATE = 1, LK_X = 2, LK_E = 3 };
-  auto load_kind = [&](int ld, int& sub, int& it) -> int {
-    sub = ld >= n0 ? 1 : 0;
-    const int l = ld - sub * n0;
+  // kind of the load at position l of tile `sub` (no divisions: this runs on the load-issue path)
+  auto load_kind = [&](int sub, int l, int& it) -> int {
     if (sub == 0 && l < ND) { it = l; return LK_SCORE; }
     const int ls = l - (sub == 0 ? ND : 0);
     if (ls < ND) { it = ls; return LK_STATE; }
@@ -436,13 +437,13 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
       // array would live in local memory, and with nearly all of L1 configured as shared memory every access to it
       // is a round trip to L2 on the load-issue path.
       int rm0 = 0, rm1 = 0, rm2 = 0, rq0 = 0, rq1 = 0, rq2 = 0;
+      int st = 0, sub = 0, l = 0;                        // stage, tile and position inside the tile of load `ld`
+      int pk1 = 0, pk2 = 0, pk3 = 0, ps1 = 0, ps2 = 0, ps3 = 0;   // kind and tile of the last three loads
       for (int ld = 0; ld < n_loads; ++ld) {
-        const int st = ld % PAR_NST;
-        int sub, it;
-        const int kind = load_kind(ld, sub, it);
-        if (ld >= PAR_NST) {   // the stage's previous occupant must be gone
-          int psub, pit;
-          const int pkind = load_kind(ld - PAR_NST, psub, pit);
+        int it;
+        const int kind = load_kind(sub, l, it);
+        if (ld >= PAR_NST) {   // the stage's previous occupant (three loads back) must be gone
+          const int pkind = pk3, psub = ps3;
           bool okw;
           if (pkind == LK_SCORE || pkind == LK_STATE) {
             const int rm = st == 0 ? rm0 : (st == 1 ? rm1 : rm2);
@@ -481,6 +482,9 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
         if (kind == LK_SCORE || kind == LK_STATE) { rm0 += (st == 0); rm1 += (st == 1); rm2 += (st == 2); }
         if (kind == LK_SCORE) { rq0 += (st == 0); rq1 += (st == 1); rq2 += (st == 2); }
         issued = ld + 1;
+        pk3 = pk2; pk2 = pk1; pk1 = kind; ps3 = ps2; ps2 = ps1; ps1 = sub;
+        st = st == PAR_NST - 1 ? 0 : st + 1;
+        if (++l == (sub == 0 ? n0 : n1)) { l = 0; ++sub; }
       }
       if (issued < n_loads && issued > 0) {  // error path: let the copies in flight land before the CTA retires
         int dummy = 1;
@@ -508,9 +512,9 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
       }
       if (ok) umma_commit(&sh.bar_sfull);
       for (int sub = 0; sub < nsub && ok; ++sub) {
-        const int lbase = sub == 0 ? ND : n0;       // first state pair of this tile
+        const int lbase = sub == 0 ? ND : n0 + (sub - 1) * n1;   // first state pair of this tile
         // the accumulator tile is free once the previous tile's epilogue has read it
-        if (sub > 0 && !mbar_wait(&sh.bar_accfree, 0, &g_sm100_status, 216)) { ok = false; break; }
+        if (sub > 0 && !mbar_wait(&sh.bar_accfree, (sub - 1) & 1, &g_sm100_status, 216)) { ok = false; break; }
         if (sub > 0) tc_fence_after_sync();
         for (int it = 0; it < ND; ++it) {           // inter-chunk term: Acc = A . State
           const int ld = lbase + it, st = ld % PAR_NST;
@@ -590,6 +594,7 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
             qn = fmaf(__high2float(h2), nn[2 * e + 1], qn);
           }
         }
+        fence_proxy_async_smem();   // generic-proxy reads ordered before the TMA refill of the stage
         __syncwarp();
         if (lane == 0) mbar_arrive(&sh.bar_qdone[st]);
       }
@@ -705,7 +710,7 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
         if (p.variant != MLSTM_SIG_NONORM) inv = 1.f / (den + p.eps);
         if (o_tile0 == 0 && half == 0) p.n_out[tok] = den;
       }
-      const int ldx = (sub == 0 ? 2 * ND : n0 + ND);    // ring index of this tile's X load; E follows it
+      const int ldx = (sub == 0 ? 2 * ND : n0 + (sub - 1) * n1 + ND);    // ring index of this tile's X load; E follows it
       const uint8_t* erow = smem;
       if (HAS_E) {
         const int lde = ldx + 1, ste = lde % PAR_NST;
@@ -796,8 +801,9 @@ par_fw_sm100(const __grid_constant__ CUtensorMap mQ, const __grid_constant__ CUt
              const __grid_constant__ CUtensorMap mV, const __grid_constant__ CUtensorMap mC,
              const __grid_constant__ ParParams p) {
   __shared__ ParShared sh;
-  const int T = p.DHHV / 128;                         // output tiles per chunk; a CTA takes two (the last one may take one)
-  par_body(PM_H, &mQ, &mK, &mV, &mC, &mV, p, sh, 2 * blockIdx.x, min(2, T - 2 * (int)blockIdx.x), blockIdx.y, blockIdx.z);
+  const int T = p.DHHV / 128;                         // output tiles per chunk; a CTA takes up to PAR_MAXSUB of them
+  const int t0 = PAR_MAXSUB * blockIdx.x;
+  par_body(PM_H, &mQ, &mK, &mV, &mC, &mV, p, sh, t0, min(PAR_MAXSUB, T - t0), blockIdx.y, blockIdx.z);
 }
 
 // deltaV, deltaK and deltaQ of one chunk in ONE launch: blockIdx.x enumerates the 128-wide output tiles of the three
@@ -811,14 +817,14 @@ par_bw_sm100(const __grid_constant__ CUtensorMap mQ, const __grid_constant__ CUt
              const __grid_constant__ ParParams p) {
   __shared__ ParShared sh;
   const int T_dv = p.DHHV / 128, T_dk = p.DHQK / 128;         // output tiles per chunk of dV, and of dK / dQ
-  const int c_dv = (T_dv + 1) / 2, c_dk = (T_dk + 1) / 2;     // CTAs: two tiles each (the last one may take one)
+  const int c_dv = (T_dv + PAR_MAXSUB - 1) / PAR_MAXSUB, c_dk = (T_dk + PAR_MAXSUB - 1) / PAR_MAXSUB;   // CTAs per mode
   const int x = blockIdx.x;
   int mode, pair, T;
   const CUtensorMap *a, *b, *xm, *stm, *e;
   if (x < c_dv) { mode = PM_DV; pair = x; T = T_dv; a = &mK; b = &mQ; xm = &mDH; stm = &mdC_mn; e = &mDH; }
   else if (x < c_dv + c_dk) { mode = PM_DK; pair = x - c_dv; T = T_dk; a = &mV; b = &mDH; xm = &mQ; stm = &mdC_k; e = &mK; }
   else { mode = PM_DQ; pair = x - c_dv - c_dk; T = T_dk; a = &mDH; b = &mV; xm = &mK; stm = &mC_k; e = &mQ; }
-  par_body(mode, a, b, xm, stm, e, p, sh, 2 * pair, min(2, T - 2 * pair), blockIdx.y, blockIdx.z);
+  par_body(mode, a, b, xm, stm, e, p, sh, PAR_MAXSUB * pair, min(PAR_MAXSUB, T - PAR_MAXSUB * pair), blockIdx.y, blockIdx.z);
 }
 
 // =====================================================================================================
@@ -891,7 +897,7 @@ int sm100_parallel_fw(const void* q, const void* k, const void* v, const GateBuf
   ParParams pp = base_params(gb, d);
   pp.n_states = n_states; pp.out_h = (__nv_bfloat16*)h; pp.n_out = n_out;
   MLSTM_CUDA_CHECK(cudaFuncSetAttribute(par_fw_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, PAR_SMEM));
-  dim3 grid((d.DHHV / 128 + 1) / 2, d.NC, d.B * d.NH);   // two output tiles per CTA
+  dim3 grid((d.DHHV / 128 + PAR_MAXSUB - 1) / PAR_MAXSUB, d.NC, d.B * d.NH);   // up to PAR_MAXSUB output tiles per CTA
   par_fw_sm100<<<grid, PAR_THREADS, PAR_SMEM, st>>>(mQ, mK, mV, mC, pp);
   MLSTM_LAUNCH_CHECK();
   return MLSTM_OK;
@@ -910,7 +916,8 @@ int sm100_parallel_bw(const void* q, const void* k, const void* v, const void* d
   pp.out_dv = (__nv_bfloat16*)dv; pp.out_dk = (__nv_bfloat16*)dk; pp.out_dq = (__nv_bfloat16*)dq;
   pp.rowdot_q = qdq_parts; pp.rowdot_k = kdk_parts;
   MLSTM_CUDA_CHECK(cudaFuncSetAttribute(par_bw_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, PAR_SMEM));
-  dim3 grid((d.DHHV / 128 + 1) / 2 + 2 * ((d.DHQK / 128 + 1) / 2), d.NC, d.B * d.NH);   // two output tiles per CTA
+  dim3 grid((d.DHHV / 128 + PAR_MAXSUB - 1) / PAR_MAXSUB + 2 * ((d.DHQK / 128 + PAR_MAXSUB - 1) / PAR_MAXSUB), d.NC,
+            d.B * d.NH);   // up to PAR_MAXSUB output tiles per CTA
   par_bw_sm100<<<grid, PAR_THREADS, PAR_SMEM, st>>>(mQ, mK, mV, mDH, mC_k, mdC_mn, mdC_k, pp);
   MLSTM_LAUNCH_CHECK();
   return MLSTM_OK;

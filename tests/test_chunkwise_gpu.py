@@ -98,7 +98,8 @@ def test_bf16_vs_oracle(shape, variant, impl):
 @pytest.mark.parametrize("shape", [(1, 1, 256, 512, 512, 128),    # widest qk head the tcgen05 path takes (8 slices)
                                    (1, 1, 256, 128, 1024, 128),   # widest v head (8 output tiles per chunk)
                                    (1, 2, 384, 128, 256, 128),    # odd number of chunks; 128/256 head geometry
-                                   (3, 5, 640, 256, 256, 128)])   # odd batch x heads, five chunks
+                                   (3, 5, 640, 256, 256, 128),    # odd batch x heads, five chunks
+                                   (1, 2, 256, 384, 640, 128)])   # three and five 128-column tiles per chunk
 @pytest.mark.parametrize("variant", ["exp", "sig_nonorm"])
 def test_tcgen05_head_geometries(shape, variant):
     """Edge geometries of the tcgen05 path (limits of the head dims it accepts, odd chunk and head counts) against
