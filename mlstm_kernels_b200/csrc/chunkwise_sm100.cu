@@ -445,7 +445,7 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
         if (ld >= PAR_NST) {   // the stage's previous occupant (three loads back) must be gone
           const int pkind = pk3, psub = ps3;
           bool okw;
-          if (pkind == LK_SCORE || pkind == LK_STATE) {
+          if (pkind == LK_SCORE || pkind == LK_STATE || (pkind == LK_X && HAS_E)) {
             const int rm = st == 0 ? rm0 : (st == 1 ? rm1 : rm2);
             okw = mbar_wait(&sh.bar_empty[st], (rm - 1) & 1, &g_sm100_status, 201);
             // the element-wise warps read the A box of a score pair (q . n)
@@ -453,10 +453,8 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
               const int rq = st == 0 ? rq0 : (st == 1 ? rq1 : rq2);
               okw = mbar_wait(&sh.bar_qdone[st], (rq - 1) & 1, &g_sm100_status, 212);
             }
-          } else if (pkind == LK_X) {   // the staging buffer of a tile is handed back when the tile has been stored
-            okw = mbar_wait(&sh.bar_done, psub & 1, &g_sm100_status, 215);
-          } else {                      // E: when the tile's epilogue has read it (same point as the accumulator)
-            okw = mbar_wait(&sh.bar_accfree, psub & 1, &g_sm100_status, 217);
+          } else {   // the staging buffer of a tile (its E stage, or its X stage in the modes without E) is handed
+            okw = mbar_wait(&sh.bar_done, psub & 1, &g_sm100_status, 215);   // back when the tile has been stored
           }
           if (!okw) break;
         }
@@ -479,7 +477,7 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
           tma_load_2d(sb, m, &sh.bar_full[st], o0, row0);
           tma_load_2d(sb + 16384, m, &sh.bar_full[st], o0 + 64, row0);
         }
-        if (kind == LK_SCORE || kind == LK_STATE) { rm0 += (st == 0); rm1 += (st == 1); rm2 += (st == 2); }
+        if (kind == LK_SCORE || kind == LK_STATE || (kind == LK_X && HAS_E)) { rm0 += (st == 0); rm1 += (st == 1); rm2 += (st == 2); }
         if (kind == LK_SCORE) { rq0 += (st == 0); rq1 += (st == 1); rq2 += (st == 2); }
         issued = ld + 1;
         pk3 = pk2; pk2 = pk1; pk1 = kind; ps3 = ps2; ps2 = ps1; ps1 = sub;
@@ -539,6 +537,7 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
           umma_ts(tAcc, tS + kk * 8, umma_desc_sw128(sx + kk * 2048, 16384, 1024), idesc_x, 1u);
+        if (HAS_E) umma_commit(&sh.bar_empty[stx]);   // the output is staged in the E stage: X's stage is free again
         umma_commit(&sh.bar_hfull);
       }
     }
@@ -719,10 +718,12 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
       }
       float dot4[4] = {0.f, 0.f, 0.f, 0.f};   // four partial sums: no 64-long chain of dependent FMAs
       // The output tile is staged (bf16, two boxes of 128 rows x 128 bytes, 16-byte pieces XOR-swizzled by the row)
-      // in the ring stage the X tile occupied - every MMA that read it has completed - and is then written out
-      // by all element-wise warps together, each warp instruction covering two full 256-byte rows of the tile.  Plain
-      // stores are posted, so the CTA retires without waiting for them.
-      uint8_t* ostage = smem + (ldx % PAR_NST) * PAR_STAGE;
+      // in the ring stage of the E tile - which arrives in exactly this layout, so a thread reads its E piece and
+      // writes its output piece to the same 16 bytes - or, in the modes without E, in the stage the X tile occupied
+      // (every MMA that read it has completed).  It is then written out by all element-wise warps together, each warp
+      // instruction covering two full 256-byte rows of the tile.  Plain stores are posted, so the CTA retires without
+      // waiting for them.
+      uint8_t* ostage = smem + ((ldx + (HAS_E ? 1 : 0)) % PAR_NST) * PAR_STAGE;
 #pragma unroll 1
       for (int cq = half; cq < 4; cq += 2) {
         uint32_t va[16], vb[16];
@@ -755,9 +756,8 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
           *reinterpret_cast<uint4*>(orow + sw) = o;
         }
       }
-      if (sub + 1 < nsub) {   // the accumulator tile may be overwritten by the next tile's inter-chunk product,
-        tc_fence_before_sync();   // and the E stage refilled (generic-proxy reads ordered before the TMA writes)
-        fence_proxy_async_smem();
+      if (sub + 1 < nsub) {   // the accumulator tile may be overwritten by the next tile's inter-chunk product
+        tc_fence_before_sync();
         mbar_arrive(&sh.bar_accfree);
       }
       const float dot = (dot4[0] + dot4[1]) + (dot4[2] + dot4[3]);
