@@ -42,7 +42,7 @@ CPU_SAMPLE = dict(B=1, NH=16)
 
 # measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum) at NH=16, 256/256, chunk 128, bf16 on a quarter
 # batch, divided by its 2048 chunks; the ncu summaries are kept under profiles/
-NCU_DRAM_BYTES_PER_CHUNK = {"recurrent_fw": 245443, "parallel_fw": 389698, "recurrent_bw": 242275, "parallel_bw": 717890}
+NCU_DRAM_BYTES_PER_CHUNK = {"recurrent_fw": 245839, "parallel_fw": 389908, "recurrent_bw": 242707, "parallel_bw": 718655}
 
 
 def impl_used_is_tcgen05(_lib, S, DHQK, DHHV, L):
