@@ -320,12 +320,14 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
 //   DQ    dH   V    DHHV         lower  K    C_k^T      (rows d, cols e)    s*bbar_r/(den_r+e)  dQ
 // lower: c <= r, (i,j) = (r,c); upper: c >= r, (i,j) = (c,r);
 // gate = s * exp((b_i - b_j) + iota_j - m_i) [* 1/(den_i+eps) in the three backward modes].
-// grid (DO/128, NC, B*NH), two CTAs per SM; 320 threads: warp 0 TMA, warp 1 MMA, warps 2..9 element-wise (two warps
-// per 32-row quarter of the tile, each owning two 32-column chunks).
-// Time line of a CTA (measured with time stamps at the benchmark size, two CTAs sharing an SM): first slices land
-// after ~1.8 us, score complete ~3.3 us, gating until ~5.8 us with the inter-chunk product arriving underneath,
-// second product ~6.4 us, epilogue and stores until ~8.8 us.  The kernel is bound by this chain of dependent steps,
-// not by HBM or L2 (the same kernel with every operand resident in L2 runs at the same speed).
+// grid (ceil(DO / 128 / PAR_MAXSUB), NC, B*NH), two CTAs per SM; 320 threads: warp 0 TMA, warp 1 MMA, warps 2..9
+// element-wise (two warps per 32-row quarter of the tile, each owning two 32-column chunks).  One CTA produces up to
+// PAR_MAXSUB neighbouring output tiles of its chunk and mode, one after the other, from a single score tile.
+// Time line of a CTA's first tile (measured with time stamps at the benchmark size, two CTAs sharing an SM): first
+// slices land after ~1.8 us, score complete ~3.3 us, gating until ~5 us with the inter-chunk product arriving
+// underneath (~5.5 us), second product ~6.4 us, epilogue and stores until ~8.8 us; every further tile takes ~5.5 us.
+// Within a tile the kernel is bound by this chain of dependent steps (the same kernel with every operand resident in
+// L2 runs at the same speed); the forward kernel as a whole runs at the HBM copy bandwidth.
 // =====================================================================================================
 enum { PM_H = 0, PM_DV = 1, PM_DK = 2, PM_DQ = 3 };
 
