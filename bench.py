@@ -349,6 +349,16 @@ def run_b200(args):
     if impl_used_is_tcgen05(_lib, S, DHQK, DHHV, L) and (DHQK, DHHV, L) == (256, 256, 128) and dom in NCU_DRAM_BYTES_PER_CHUNK:
         traffic = NCU_DRAM_BYTES_PER_CHUNK[dom] * B * NH * (S // L)
     impl_used = "tcgen05" if _lib.load().mlstm_b200_chunkwise_has_tcgen05(S, DHQK, DHHV, L, _lib.BF16) else "simt"
+    # the same kernels against the HBM roofline: algorithmic bytes per chunk (bf16 operands and states, outputs
+    # written once; the figures listed next to the ncu capture in profiles/) divided by the measured time
+    algo_bytes_per_chunk = {"recurrent_fw": 2 * L * (DHQK + DHHV) + 2 * DHQK * DHHV,
+                            "parallel_fw": 2 * L * (2 * DHQK + 2 * DHHV) + 2 * DHQK * DHHV,
+                            "recurrent_bw": 2 * L * (DHQK + DHHV) + 2 * DHQK * DHHV,
+                            "parallel_bw": 2 * L * (4 * DHQK + 3 * DHHV) + 4 * DHQK * DHHV}
+    for name, nbytes in algo_bytes_per_chunk.items():
+        if name in kernels:
+            gbs = nbytes * B * NH * (S // L) / (kernels[name]["ms"] * 1e-3) / 1e9
+            kernels[name].update(hbm_gbs=gbs, hbm_frac=gbs / peaks["hbm"])
     roofline = {"bound": "tensor", "kernel": dom, "achieved": kernels[dom]["tflops"], "peak": peaks["tflops"],
                 "unit": "TFLOP/s", "frac": kernels[dom]["tflops"] / peaks["tflops"], "traffic": traffic,
                 "peak_source": peaks["source"] + " (burst bf16 GEMM)", "impl": impl_used,
