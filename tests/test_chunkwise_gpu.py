@@ -14,6 +14,7 @@ import torch
 
 import mlstm_kernels_b200 as mk
 from inputs import CASES, make_chunkwise_inputs, max_rel_err, subsample
+from oracle import mlstm_oracle as O
 from util_gpu import case_inputs, npy, run_cuda_fwbw, run_oracle_fwbw, to_dev
 
 pytestmark = pytest.mark.gpu
@@ -262,3 +263,50 @@ def test_forward_backward_capture_in_cuda_graph():
     torch.cuda.synchronize()
     for a, b in zip(eager, outs):
         assert torch.equal(a, b)
+
+
+def test_benchmark_size_properties():
+    """At the benchmark size (B=8, S=8192, NH=16, 256/256, bf16: too large for the oracle) the kernels are checked
+    through properties that do not depend on the size: reruns are bit-identical (forward and all five gradients),
+    a (batch, head) slice computed alone gives bit-identical results (units are independent), the sequence processed
+    as two halves with state passing reproduces H and the final state, and a sub-block is checked against the oracle."""
+    B, NH, S, D, L = 8, 16, 8192, 256, 128
+    g = torch.Generator(device="cuda").manual_seed(5)
+    rnd = lambda *s: torch.randn(*s, device="cuda", generator=g)  # noqa: E731
+    q, k, v = (rnd(B, NH, S, D).bfloat16() for _ in range(3))
+    i, f = rnd(B, NH, S).bfloat16(), (3 + rnd(B, NH, S)).bfloat16()
+    dh = rnd(B, NH, S, D).bfloat16()
+
+    def fwbw(qq, kk, vv, ii, ff, dd):
+        leaves = [t.detach().clone().requires_grad_(True) for t in (qq, kk, vv, ii, ff)]
+        h, last = mk.mlstm_chunkwise__b200_xl_chunk(*leaves, return_last_states=True, chunk_size=L)
+        h.backward(dd)
+        return [h.detach()] + [t.grad for t in leaves], last
+
+    a, last_a = fwbw(q, k, v, i, f, dh)
+    b, _ = fwbw(q, k, v, i, f, dh)
+    for x, y in zip(a, b):
+        assert torch.equal(x, y)
+        assert torch.isfinite(x.float()).all()
+    # one (batch, head) unit on its own
+    sl = (slice(5, 6), slice(11, 12))
+    c, _ = fwbw(*(t[sl].contiguous() for t in (q, k, v, i, f, dh)))
+    for x, y in zip(a, c):
+        assert torch.equal(x[sl], y)
+    # two halves with state passing
+    hlf = S // 2
+    first = [t[:, :, :hlf].contiguous() for t in (q, k, v, i, f)]
+    second = [t[:, :, hlf:].contiguous() for t in (q, k, v, i, f)]
+    with torch.no_grad():
+        h1, st = mk.mlstm_chunkwise__b200_xl_chunk(*first, return_last_states=True, chunk_size=L)
+        h2, st2 = mk.mlstm_chunkwise__b200_xl_chunk(*second, c_initial=st[0], n_initial=st[1], m_initial=st[2],
+                                                    return_last_states=True, chunk_size=L)
+    assert torch.equal(torch.cat([h1, h2], 2), a[0])
+    for x, y in zip(st2, last_a):
+        assert max_rel_err(npy(x), npy(y)) < 1e-5
+    # the single unit against the oracle (forward and gradients)
+    unit = {n: npy(t[sl]) for n, t in zip(("q", "k", "v", "i", "f", "dH"), (q, k, v, i, f, dh))}
+    ref_fw, ref_bw = O.chunkwise_fwbw(unit["q"], unit["k"], unit["v"], unit["i"], unit["f"], unit["dH"], chunk_size=L)
+    assert max_rel_err(npy(c[0]), ref_fw["H"]) < TOL_BF16
+    for j, key in enumerate(("dQ", "dK", "dV", "dI", "dF"), start=1):
+        assert max_rel_err(npy(c[j]), ref_bw[key]) < TOL_BF16, key
