@@ -5,13 +5,17 @@
 
 One step = one chunkwise mLSTMexp forward+backward over one synthetic 65,536-token batch
 (B=8, S=8192, NH=16, DHQK=DHHV=256, chunk 128, bf16; seeded q,k,v,i ~ N(0,1), f = 3 + N(0,1),
-dH ~ N(0,1)).  With N > 1 (torchrun, one rank per GPU) every rank processes its own batch of the
-same size: batch x heads are independent units, there is no data-path collective (weak scaling).
+dH ~ N(0,1)), per-chunk states kept for the backward (recompute_states_in_bw=False; the recompute setting is
+timed next to it).  With N > 1 (torchrun, one rank per GPU) every rank processes its own batch of the same size:
+batch x heads are independent units, there is no data-path collective (weak scaling).  The same run also
+measures, under `extra`, the FIXED batch sharded over the N ranks (strong scaling), decode sharded over batch
+and the sequence-parallel prefill of one long sequence over the N ranks.
 
 Prints ONE JSON line.  `value` is TFLOP/s of algorithmic FLOPs with inputs resident in HBM;
 `e2e` is the same metric through the public API with host (pinned) buffers, host<->device copies
-inside the timed region.  `--impl reference` times the CPU restatement of the reference's native
-PyTorch path (the oracle) on the host cores on a bounded sample of the same workload.
+inside the timed region.  `--impl reference` times the reference's own native PyTorch chunkwise path
+(mlstm_chunkwise__native_custbw, fp32, CPU, all host threads) on a bounded sample of the same workload; when the
+reference package cannot be imported it falls back to the numpy restatement of that algorithm (the oracle).
 """
 
 from __future__ import annotations
@@ -33,20 +37,18 @@ if os.environ.get("OMP_NUM_THREADS") == "1":
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.join(ROOT, "tests"))
+REF_DIR = os.path.join(ROOT, "baseline", "_ref")
 
 WORKLOAD = dict(name="c2_chunkwise_fwbw_mLSTMexp_B8_S8192_NH16_DHQK256_DHHV256_L128_bf16",
                 B=8, S=8192, NH=16, DHQK=256, DHHV=256, L=128)
 # bounded CPU sample of the same workload: same S, head dims and chunk size, fewer (batch, head) units
 CPU_SAMPLE = dict(B=1, NH=16)
+METRIC = "chunkwise_fwbw_tflops_64k_tokens"
 
 
 # measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum) at NH=16, 256/256, chunk 128, bf16 on a quarter
 # batch, divided by its 2048 chunks; the ncu summaries are kept under profiles/
 NCU_DRAM_BYTES_PER_CHUNK = {"recurrent_fw": 245839, "parallel_fw": 389908, "recurrent_bw": 242707, "parallel_bw": 718655}
-
-
-def impl_used_is_tcgen05(_lib, S, DHQK, DHHV, L):
-    return bool(_lib.load().mlstm_b200_chunkwise_has_tcgen05(S, DHQK, DHHV, L, _lib.BF16))
 
 
 def fw_flops(B, NH, S, DHQK, DHHV, L):
@@ -65,6 +67,10 @@ def phase_flops(B, NH, S, DHQK, DHHV, L):
         "recurrent_bw": t * 2 * DHQK * DHHV,
         "parallel_bw": t * (6 * DHQK * DHHV + L * (3 * DHQK + 2 * DHHV)),
     }
+
+
+def step_bytes(B, NH, DHQK, DHHV):
+    return B * NH * (2 * DHQK * DHHV * 4 + 2 * DHQK * 4 + 8 + (2 * DHQK + 2 * DHHV) * 2 + 4)
 
 
 def measured_peaks():
@@ -128,6 +134,9 @@ class ClockSampler:
         return dict(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
 
 
+# =====================================================================================================
+# CPU legs: the reference's native PyTorch path (or, if it cannot be imported, the numpy port)
+# =====================================================================================================
 def make_inputs_np(B, NH, S, DHQK, DHHV, seed):
     import numpy as np
     rng = np.random.default_rng(seed)
@@ -142,58 +151,120 @@ def make_inputs_np(B, NH, S, DHQK, DHHV, seed):
     return out
 
 
-def cpu_port_step(inp, L):
-    """One forward+backward of the numpy restatement of the reference's native path (float32)."""
-    import numpy as np
-    from oracle import mlstm_oracle as O
-    O.chunkwise_fwbw(inp["q"], inp["k"], inp["v"], inp["i"], inp["f"], inp["dH"], chunk_size=L, dtype=np.float32)
-
-
-def time_cpu_port(steps, warmup):
-    """Times the CPU port with all host cores (launchers such as torchrun export OMP_NUM_THREADS=1; the BLAS
-    thread pool is raised again here)."""
+def import_reference_native():
+    """The reference's native chunkwise function from the installed copy under baseline/_ref (or any importable
+    mlstm_kernels).  Returns (function, None) or (None, reason)."""
+    if os.path.isdir(REF_DIR) and REF_DIR not in sys.path:
+        sys.path.insert(0, REF_DIR)
     try:
-        from threadpoolctl import threadpool_limits
-        with threadpool_limits(limits=os.cpu_count() or 1):
-            return _time_cpu_port(steps, warmup)
-    except ImportError:
-        return _time_cpu_port(steps, warmup)
+        from mlstm_kernels.torch.chunkwise.native.fwbw import mlstm_chunkwise__native_custbw
+        return mlstm_chunkwise__native_custbw, None
+    except Exception as e:  # noqa: BLE001
+        return None, f"{type(e).__name__}: {e}"[:200]
 
 
-def _time_cpu_port(steps, warmup):
+def time_cpu_reference(steps, warmup):
+    """(TFLOP/s, seconds per step, sample description, kind, threads) of the CPU leg."""
+    import numpy as np
     w = WORKLOAD
     B, NH = CPU_SAMPLE["B"], CPU_SAMPLE["NH"]
     inp = make_inputs_np(B, NH, w["S"], w["DHQK"], w["DHHV"], seed=1)
-    for _ in range(warmup):
-        cpu_port_step(inp, w["L"])
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        cpu_port_step(inp, w["L"])
-    dt = (time.perf_counter() - t0) / steps
+    cores = os.cpu_count() or 1
+    fn, why = import_reference_native()
+    if fn is not None:
+        import torch
+        torch.set_num_threads(cores)
+        t = {n: torch.from_numpy(x) for n, x in inp.items()}
+        leaves = [t[n].clone().requires_grad_(True) for n in "qkvif"]
+
+        def step():
+            for x in leaves:
+                x.grad = None
+            H = fn(*leaves, chunk_size=w["L"])
+            H.backward(t["dH"])
+        kind, threads = "reference", torch.get_num_threads()
+        what = "mlstm_chunkwise__native_custbw of the reference package (torch CPU, fp32)"
+    else:
+        from oracle import mlstm_oracle as O
+
+        def step():
+            O.chunkwise_fwbw(inp["q"], inp["k"], inp["v"], inp["i"], inp["f"], inp["dH"], chunk_size=w["L"],
+                             dtype=np.float32)
+        kind, threads = "port", cores
+        what = f"numpy restatement of the reference's native path (reference not importable: {why})"
+
+    def run():
+        for _ in range(warmup):
+            step()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            step()
+        return (time.perf_counter() - t0) / steps
+    try:
+        from threadpoolctl import threadpool_limits
+        with threadpool_limits(limits=cores):
+            dt = run()
+    except ImportError:
+        dt = run()
     fl = fw_flops(B, NH, w["S"], w["DHQK"], w["DHHV"], w["L"]) + bw_flops(B, NH, w["S"], w["DHQK"], w["DHHV"], w["L"])
-    sample = (f"B={B} NH={NH} of the workload's B={w['B']} NH={w['NH']} (same S={w['S']}, head dims, chunk size), "
-              f"float32, {steps} timed steps of {dt:.2f} s")
-    return fl / dt / 1e12, dt, sample
+    sample = (f"{what}; B={B} NH={NH} of the workload's B={w['B']} NH={w['NH']} (same S={w['S']}, head dims, chunk "
+              f"size), {steps} timed steps of {dt:.2f} s, rate-normalised")
+    return fl / dt / 1e12, dt, sample, kind, threads
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    cores = os.cpu_count() or 1
-    val, dt, sample = time_cpu_port(args.steps, args.warmup)
+    val, dt, sample, kind, threads = time_cpu_reference(args.steps, args.warmup)
     w = WORKLOAD
     line = {
-        "impl": "reference", "metric": "chunkwise_fwbw_tflops_64k_tokens", "value": val, "unit": "TFLOP/s",
+        "impl": "reference", "metric": METRIC, "value": val, "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": w["name"], "note": "CPU restatement (numpy, BLAS threads) of the reference's native "
-                   "PyTorch chunkwise path; each step is a bounded sample of the workload"},
-        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "config": {"workload": w["name"]},
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": threads, "kind": kind, "sample": sample},
         "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line))
+
+
+# =====================================================================================================
+# GPU arm
+# =====================================================================================================
+def timed_local(torch, fn, steps, warmup):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def timed_reps(torch, fn, reps=30, warmup=10, flush=False):
+    """The reference's timing protocol (mlstm_kernels/utils/benchmark/runtime.py:66-72,121-122): one CUDA-event pair
+    per repetition, median (and min) over the repetitions; with `flush` a 256 MB buffer is zeroed before every
+    repetition so that the L2 holds no input data."""
+    cache = torch.empty(int(256e6 // 4), dtype=torch.int, device="cuda") if flush else None
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
+    for a, b in ev:
+        if cache is not None:
+            cache.zero_()
+        a.record()
+        fn()
+        b.record()
+    torch.cuda.synchronize()
+    ts = [a.elapsed_time(b) for a, b in ev]
+    return dict(median_ms=statistics.median(ts), min_ms=min(ts), reps=reps, warmup=warmup,
+                l2_flush_256MB=bool(flush))
 
 
 def run_b200(args):
@@ -207,6 +278,7 @@ def run_b200(args):
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if world > 1:
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")   # point-to-point hand-offs only: no NVLink multicast binding
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
@@ -236,13 +308,21 @@ def run_b200(args):
         host[name] = t.bfloat16().pin_memory()
     devin = {n: t.to(dev) for n, t in host.items()}
     leaf = {n: devin[n].clone().requires_grad_(True) for n in "qkvif"}
+    RECOMPUTE = False   # the headline keeps the per-chunk states; the recompute setting is timed under `extra`
 
-    def step_resident():
-        for t in leaf.values():
-            t.grad = None
-        H = mk.mlstm_chunkwise__b200_xl_chunk(leaf["q"], leaf["k"], leaf["v"], leaf["i"], leaf["f"], chunk_size=L)
-        H.backward(devin["dH"])
-        return H
+    def make_step(fn=None, recompute=RECOMPUTE, **kw):
+        fn = fn or mk.mlstm_chunkwise__b200_xl_chunk
+
+        def step():
+            for t in leaf.values():
+                t.grad = None
+            H = fn(leaf["q"], leaf["k"], leaf["v"], leaf["i"], leaf["f"], chunk_size=L,
+                   recompute_states_in_bw=recompute, **kw)
+            H.backward(devin["dH"])
+            return H
+        return step
+
+    step_resident = make_step()
 
     def fw_only():
         with torch.no_grad():
@@ -271,7 +351,8 @@ def run_b200(args):
                 for t in d.values():
                     t.record_stream(s_cmp)
                 lf = {n: d[n].requires_grad_(True) for n in "qkvif"}
-                H = mk.mlstm_chunkwise__b200_xl_chunk(lf["q"], lf["k"], lf["v"], lf["i"], lf["f"], chunk_size=L)
+                H = mk.mlstm_chunkwise__b200_xl_chunk(lf["q"], lf["k"], lf["v"], lf["i"], lf["f"], chunk_size=L,
+                                                      recompute_states_in_bw=RECOMPUTE)
                 H.backward(d["dH"])
                 ev_c = torch.cuda.Event()
                 ev_c.record(s_cmp)
@@ -314,7 +395,7 @@ def run_b200(args):
 
     if args.quick:
         if rank == 0:
-            print(json.dumps({"metric": "chunkwise_fwbw_tflops_64k_tokens", "value": value, "unit": "TFLOP/s",
+            print(json.dumps({"metric": METRIC, "value": value, "unit": "TFLOP/s",
                               "ms_per_step": ms, "config": {"workload": w["name"]}, "quick": True}))
         if world > 1:
             dist.destroy_process_group()
@@ -327,80 +408,122 @@ def run_b200(args):
 
     # ---- per-kernel device time (CUDA events inside the library, on the launching stream) ----
     peaks = measured_peaks()
-    _lib.profile_enable(True)
-    prof_steps = max(2, min(args.steps, 5))
-    for _ in range(prof_steps):
-        step_resident()
-    torch.cuda.synchronize()
-    prof = _lib.profile_read()
-    _lib.profile_enable(False)
-    pf = phase_flops(B, NH, S, DHQK, DHHV, L)
-    kernels = {}
-    for name, (tot, cnt) in prof.items():
-        if cnt:
-            kernels[name] = dict(ms=tot / cnt, launches_per_step=cnt / prof_steps)
+    impl_used = "tcgen05" if _lib.load().mlstm_b200_chunkwise_has_tcgen05(S, DHQK, DHHV, L, _lib.BF16) else "simt"
+
+    def kernel_profile(step_fn, Bp, NHp, steps=5):
+        _lib.profile_enable(True)
+        for _ in range(steps):
+            step_fn()
+        torch.cuda.synchronize()
+        prof = _lib.profile_read()
+        _lib.profile_enable(False)
+        pf = phase_flops(Bp, NHp, S, DHQK, DHHV, L)
+        nchunks = Bp * NHp * (S // L)
+        # the same kernels against the HBM roofline: algorithmic bytes per chunk (bf16 operands and states, outputs
+        # written once; the figures listed next to the ncu capture in profiles/) divided by the measured time
+        algo = {"recurrent_fw": 2 * L * (DHQK + DHHV) + 2 * DHQK * DHHV,
+                "parallel_fw": 2 * L * (2 * DHQK + 2 * DHHV) + 2 * DHQK * DHHV,
+                "recurrent_bw": 2 * L * (DHQK + DHHV) + 2 * DHQK * DHHV,
+                "parallel_bw": 2 * L * (4 * DHQK + 3 * DHHV) + 4 * DHQK * DHHV}
+        kernels = {}
+        for name, (tot, cnt) in prof.items():
+            if not cnt:
+                continue
+            kernels[name] = dict(ms=tot / cnt, launches_per_step=cnt / steps)
             if name in pf:
                 kernels[name]["tflops"] = pf[name] / (tot / cnt * 1e-3) / 1e12
+                gbs = algo[name] * nchunks / (tot / cnt * 1e-3) / 1e9
+                kernels[name].update(hbm_gbs=gbs, hbm_frac=gbs / peaks["hbm"])
+        return kernels
+
+    kernels = kernel_profile(step_resident, B, NH, steps=max(2, min(args.steps, 5)))
+    pf = phase_flops(B, NH, S, DHQK, DHHV, L)
     dom = max((n for n in kernels if n in pf), key=lambda n: kernels[n]["ms"] * kernels[n]["launches_per_step"])
     # DRAM bytes per launch of the dominant kernel: ncu dram__bytes_read.sum + dram__bytes_write.sum per chunk of 128
     # tokens, captured on a quarter batch (see profiles/), times the chunks of this launch (traffic is
     # proportional to the number of chunks)
     traffic = None
-    if impl_used_is_tcgen05(_lib, S, DHQK, DHHV, L) and (DHQK, DHHV, L) == (256, 256, 128) and dom in NCU_DRAM_BYTES_PER_CHUNK:
+    if impl_used == "tcgen05" and (DHQK, DHHV, L) == (256, 256, 128) and dom in NCU_DRAM_BYTES_PER_CHUNK:
         traffic = NCU_DRAM_BYTES_PER_CHUNK[dom] * B * NH * (S // L)
-    impl_used = "tcgen05" if _lib.load().mlstm_b200_chunkwise_has_tcgen05(S, DHQK, DHHV, L, _lib.BF16) else "simt"
-    # the same kernels against the HBM roofline: algorithmic bytes per chunk (bf16 operands and states, outputs
-    # written once; the figures listed next to the ncu capture in profiles/) divided by the measured time
-    algo_bytes_per_chunk = {"recurrent_fw": 2 * L * (DHQK + DHHV) + 2 * DHQK * DHHV,
-                            "parallel_fw": 2 * L * (2 * DHQK + 2 * DHHV) + 2 * DHQK * DHHV,
-                            "recurrent_bw": 2 * L * (DHQK + DHHV) + 2 * DHQK * DHHV,
-                            "parallel_bw": 2 * L * (4 * DHQK + 3 * DHHV) + 4 * DHQK * DHHV}
-    for name, nbytes in algo_bytes_per_chunk.items():
-        if name in kernels:
-            gbs = nbytes * B * NH * (S // L) / (kernels[name]["ms"] * 1e-3) / 1e9
-            kernels[name].update(hbm_gbs=gbs, hbm_frac=gbs / peaks["hbm"])
     roofline = {"bound": "tensor", "kernel": dom, "achieved": kernels[dom]["tflops"], "peak": peaks["tflops"],
                 "unit": "TFLOP/s", "frac": kernels[dom]["tflops"] / peaks["tflops"], "traffic": traffic,
                 "peak_source": peaks["source"] + " (burst bf16 GEMM)", "impl": impl_used,
                 "whole_step_frac": (flops_fwbw / (ms * 1e-3) / 1e12) / peaks["tflops"],
                 "kernels": kernels}
 
-    # ---- secondary numbers (not the headline): forward only, mLSTMsig, decode step ----
     extra = {}
+    # ---- multi-GPU blocks (every rank takes part; at N=1 they are the single-GPU figures) ----
+    if not args.no_extra:
+        extra["strong_scaling_fixed_batch"] = bench_strong(torch, dist, mk, _lib, dev, devin, world, rank, L, barrier,
+                                                           max_over_ranks, kernel_profile, peaks)
+        extra["step_decode_sharded_B256"] = bench_step_sharded(torch, mk, dev, world, rank, barrier, max_over_ranks,
+                                                               peaks)
+        extra["sequence_parallel_prefill_B1_NH8_S131072_256_512_cs256"] = bench_sequence_parallel(
+            torch, dist, mk, dev, world, rank, barrier, max_over_ranks, peaks)
+
+    # ---- secondary single-GPU numbers (rank 0): forward only, recompute, mLSTMsig, protocol, decode, sweep ----
     if rank == 0 and not args.no_extra:
         ms_fw = timed_local(torch, fw_only, 5, 3)
         extra["fw_only"] = dict(ms=ms_fw, tflops=flops_fw / (ms_fw * 1e-3) / 1e12,
                                 frac_of_peak=flops_fw / (ms_fw * 1e-3) / 1e12 / peaks["tflops"])
 
-        def sig_step():
+        def memory(recompute):
+            """GB above the resident inputs: held between forward and backward, and at the peak of the step."""
             for t in leaf.values():
                 t.grad = None
-            H = mk.mlstm_siging_chunkwise__b200_xl_chunk(leaf["q"], leaf["k"], leaf["v"], leaf["i"], leaf["f"],
-                                                         chunk_size=L, normalize=True)
+            torch.cuda.synchronize()
+            torch.cuda.reset_peak_memory_stats()
+            base = torch.cuda.memory_allocated()
+            H = mk.mlstm_chunkwise__b200_xl_chunk(leaf["q"], leaf["k"], leaf["v"], leaf["i"], leaf["f"], chunk_size=L,
+                                                  recompute_states_in_bw=recompute)
+            torch.cuda.synchronize()
+            held = torch.cuda.memory_allocated() - base
             H.backward(devin["dH"])
+            torch.cuda.synchronize()
+            peak = torch.cuda.max_memory_allocated() - base
+            return dict(held_between_fw_and_bw_gb=held / 1e9, peak_gb=peak / 1e9)
+        rec_step = make_step(recompute=True)
+        ms_rec = timed_local(torch, rec_step, 5, 3)
+        ms_keep = timed_local(torch, step_resident, 5, 3)
+        extra["recompute_states_in_bw"] = {
+            "False (headline setting)": dict(ms=ms_keep, tflops=flops_fwbw / (ms_keep * 1e-3) / 1e12, **memory(False)),
+            "True (the reference's default)": dict(ms=ms_rec, tflops=flops_fwbw / (ms_rec * 1e-3) / 1e12,
+                                                   **memory(True)),
+            "note": "memory above the resident inputs (H and the input gradients included); timed back to back"}
+        sig_step = make_step(mk.mlstm_siging_chunkwise__b200_xl_chunk, normalize=True)
         ms_sig = timed_local(torch, sig_step, 5, 3)
         extra["fwbw_mLSTMsig"] = dict(ms=ms_sig, tflops=flops_fwbw / (ms_sig * 1e-3) / 1e12)
+        # the reference's own protocol: >= 10 warm-up, 30 repetitions, median; with and without its 256 MB L2 flush
+        extra["reference_protocol_fwbw"] = {
+            "no_flush": timed_reps(torch, step_resident, 30, 10, flush=False),
+            "l2_flush": timed_reps(torch, step_resident, 30, 10, flush=True)}
+        extra["reference_protocol_fw"] = {
+            "no_flush": timed_reps(torch, fw_only, 30, 10, flush=False),
+            "l2_flush": timed_reps(torch, fw_only, 30, 10, flush=True)}
         extra["step_decode"] = bench_step(torch, mk, dev, peaks)
         extra["consttoken_sweep_65536_tokens"] = bench_sweep(torch, mk, dev, peaks)
-        extra["long_prefill_B1_NH8_S131072_256_512_cs256"] = bench_long_prefill(torch, mk, dev, peaks)
-        if args.triton_ref:
+        if world == 1 and not args.no_triton_ref:
             extra["reference_triton_same_gpu"] = bench_triton_reference(torch, devin, leaf, L, flops_fw, flops_fwbw)
     if world > 1:
         dist.barrier()
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
-        val, dt, sample = time_cpu_port(5, 1)
-        cpu = {"value": val, "unit": "TFLOP/s", "cores": os.cpu_count() or 1, "kind": "port", "sample": sample}
+        val, dt, sample, kind, threads = time_cpu_reference(5, 1)
+        cpu = {"value": val, "unit": "TFLOP/s", "cores": threads, "kind": kind, "sample": sample}
 
     if rank == 0:
         line = {
-            "metric": "chunkwise_fwbw_tflops_64k_tokens", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": w["name"], "tokens_per_step_per_gpu": B * S,
-                       "tokens_per_s": world * B * S / (ms * 1e-3), "sharding": "batch x heads, no collective",
-                       "l2": "inputs (2.2 GB per step) larger than L2; no flush", "impl": impl_used},
+            "config": {"workload": w["name"]},
+            "run": {"tokens_per_step_per_gpu": B * S, "tokens_per_s": world * B * S / (ms * 1e-3),
+                    "sharding": "batch x heads, no collective; each rank runs its own batch (weak scaling); the fixed "
+                                "batch split over the ranks is under extra.strong_scaling_fixed_batch",
+                    "l2": "inputs (2.2 GB per step) larger than L2; no flush (a flushed variant is under "
+                          "extra.reference_protocol_fwbw)",
+                    "recompute_states_in_bw": RECOMPUTE, "impl": impl_used},
             "roofline": roofline, "cpu_baseline": cpu,
             "e2e": {"value": e2e_val, "unit": "TFLOP/s", "ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h},
@@ -411,13 +534,185 @@ def run_b200(args):
         dist.destroy_process_group()
 
 
+def bench_strong(torch, dist, mk, _lib, dev, devin, world, rank, L, barrier, max_over_ranks, kernel_profile, peaks):
+    """The FIXED benchmark batch (B=8 x NH=16 = 128 independent units) split contiguously over the ranks with
+    shard_batch_heads: rank r runs 128 / N units, no collective on the data path.  Throughput = FLOPs of the whole
+    batch / slowest rank's device time.  Every rank draws the same full batch (same seed) and slices its share."""
+    from mlstm_kernels_b200.sharding import shard_batch_heads, shard_range
+    w = WORKLOAD
+    B, S, NH, DHQK, DHHV = (w[x] for x in ("B", "S", "NH", "DHQK", "DHHV"))
+    g = torch.Generator(device=dev).manual_seed(11)
+    full = {}
+    for name, shape in (("q", (B, NH, S, DHQK)), ("k", (B, NH, S, DHQK)), ("v", (B, NH, S, DHHV)),
+                        ("i", (B, NH, S)), ("f", (B, NH, S)), ("dH", (B, NH, S, DHHV))):
+        t = torch.randn(shape, device=dev, generator=g)
+        full[name] = (t + 3.0 if name == "f" else t).bfloat16()
+    mine = dict(zip(full, shard_batch_heads(list(full.values()), world, rank)))
+    del full
+    lo, hi = shard_range(B * NH, world, rank)
+    leaves = [mine[n].contiguous().clone().requires_grad_(True) for n in "qkvif"]
+    dH = mine["dH"].contiguous()
+
+    def step():
+        for t in leaves:
+            t.grad = None
+        mk.mlstm_chunkwise__b200_xl_chunk(*leaves, chunk_size=L, recompute_states_in_bw=False).backward(dH)
+
+    for _ in range(3):
+        step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(10):
+        step()
+    e1.record()
+    barrier()
+    ms = max_over_ranks(e0.elapsed_time(e1) / 10)
+    fl = fw_flops(B, NH, S, DHQK, DHHV, L) + bw_flops(B, NH, S, DHQK, DHHV, L)
+    kern = kernel_profile(step, 1, hi - lo, steps=3)
+    return dict(ms_per_step=ms, tflops=fl / (ms * 1e-3) / 1e12, tokens_per_s=B * S / (ms * 1e-3), n_gpus=world,
+                units_total=B * NH, units_on_rank0=hi - lo, scaling="strong", collective="none",
+                frac_of_n_gpu_peak=fl / (ms * 1e-3) / 1e12 / (world * peaks["tflops"]),
+                kernels_rank0={k_: {x: v_[x] for x in ("ms", "tflops", "hbm_frac") if x in v_} for k_, v_ in kern.items()})
+
+
+def bench_step_sharded(torch, mk, dev, world, rank, barrier, max_over_ranks, peaks):
+    """Decode at NH=8, 256/512 with the batch B=256 sharded over the ranks (B / N sequences per rank, no collective):
+    tokens/s of the whole batch = 256 / slowest rank's time per step."""
+    from mlstm_kernels_b200.sharding import shard_range
+    NH, DHQK, DHHV, Btot = 8, 256, 512, 256
+    lo, hi = shard_range(Btot, world, rank)
+    Bm = hi - lo
+    g = torch.Generator(device=dev).manual_seed(100 + rank)
+    c = torch.randn(Bm, NH, DHQK, DHHV, device=dev, generator=g) * 0.1
+    n = torch.randn(Bm, NH, DHQK, device=dev, generator=g).abs()
+    m = torch.randn(Bm, NH, 1, device=dev, generator=g)
+    state = [(c, n, m), (torch.empty_like(c), torch.empty_like(n), torch.empty_like(m))]
+    T = 32
+    q, k = (torch.randn(T, Bm, NH, DHQK, device=dev, generator=g).bfloat16() for _ in range(2))
+    v = torch.randn(T, Bm, NH, DHHV, device=dev, generator=g).bfloat16()
+    i = torch.randn(T, Bm, NH, 1, device=dev, generator=g).bfloat16()
+    f = (3 + torch.randn(T, Bm, NH, 1, device=dev, generator=g)).bfloat16()
+    h = torch.empty(Bm, NH, DHHV, device=dev, dtype=torch.bfloat16)
+
+    toks = [(q[t], k[t], v[t], i[t], f[t]) for t in range(T)]
+
+    def run(nsteps):
+        for t in range(nsteps):
+            (ci, ni, mi), (co, no, mo) = state[t % 2], state[(t + 1) % 2]
+            qt, kt, vt, it, ft = toks[t % T]
+            mk.mlstm_recurrent_step__b200_fw(ci, ni, mi, qt, kt, vt, it, ft,
+                                             matC_new=co, vecN_new=no, scaM_new=mo, vecH_out=h)
+    nsteps = 256
+    run(16)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    run(nsteps)
+    e1.record()
+    barrier()
+    us = max_over_ranks(e0.elapsed_time(e1) / nsteps * 1e3)
+    gbs = step_bytes(Btot, NH, DHQK, DHHV) / (us * 1e-6) / 1e9
+    return dict(us_per_step=us, tokens_per_s=Btot / (us * 1e-6), batch_total=Btot, batch_per_rank=Bm, n_gpus=world,
+                gbs_all_gpus=gbs, frac_of_n_gpu_hbm=gbs / (world * peaks["hbm"]), scaling="strong", collective="none")
+
+
+def bench_sequence_parallel(torch, dist, mk, dev, world, rank, barrier, max_over_ranks, peaks):
+    """Prefill of ONE long sequence (B=1, NH=8, 256/512, S=131072, requested chunk 256) with its chunks split
+    contiguously over the ranks and the (C, n, m) boundary state handed from GPU to GPU (NCCL point-to-point, one
+    message per hop).  Every rank draws the whole sequence from the same seed, runs the single-GPU pass as the
+    reference result and its own segment through mlstm_chunkwise_sequence_parallel; times are device events, slowest
+    rank.  FLOPs are counted at the chunk size the kernels actually run (128)."""
+    from mlstm_kernels_b200.sharding import mlstm_chunkwise_sequence_parallel
+    B, NH, S, DHQK, DHHV, Lreq = 1, 8, 131072, 256, 512, 256
+    g = torch.Generator(device=dev).manual_seed(7)
+    mk_t = lambda *sh: torch.randn(*sh, device=dev, generator=g).bfloat16()  # noqa: E731
+    q, k, v = mk_t(B, NH, S, DHQK), mk_t(B, NH, S, DHQK), mk_t(B, NH, S, DHHV)
+    i, f = mk_t(B, NH, S), (3 + torch.randn(B, NH, S, device=dev, generator=g)).bfloat16()
+    dH = mk_t(B, NH, S, DHHV)
+    Lrun = mk.kernel_chunk_size(q, v, Lreq)
+    fl_fw = fw_flops(B, NH, S, DHQK, DHHV, Lrun)
+    fl_fwbw = fl_fw + bw_flops(B, NH, S, DHQK, DHHV, Lrun)
+
+    def single_fw():
+        with torch.no_grad():
+            return mk.mlstm_chunkwise__b200_xl_chunk(q, k, v, i, f, return_last_states=True, chunk_size=Lreq)
+    ms_single = timed_local(torch, single_fw, 5, 3)
+    out = dict(chunk_size_requested=Lreq, chunk_size_run=Lrun, n_gpus=world,
+               single_gpu=dict(fw_ms=ms_single, fw_tflops=fl_fw / ms_single / 1e9,
+                               fw_frac_of_peak=fl_fw / ms_single / 1e9 / peaks["tflops"],
+                               tokens_per_s=S / (ms_single * 1e-3)))
+    leaves = [t.clone().requires_grad_(True) for t in (q, k, v, i, f)]
+
+    def single_fwbw():
+        for t in leaves:
+            t.grad = None
+        mk.mlstm_chunkwise__b200_xl_chunk(*leaves, chunk_size=Lreq, recompute_states_in_bw=False).backward(dH)
+    ms_single_fwbw = timed_local(torch, single_fwbw, 3, 2)
+    out["single_gpu"].update(fwbw_ms=ms_single_fwbw, fwbw_tflops=fl_fwbw / ms_single_fwbw / 1e9)
+    if world == 1:
+        return out
+    h_ref, last_ref = single_fw()
+    grads_ref = [t.grad.clone() for t in leaves]
+    seg = S // world
+    sl = slice(rank * seg, (rank + 1) * seg)
+    mine = [t[:, :, sl].contiguous() for t in (q, k, v, i, f)]
+    dH_m = dH[:, :, sl].contiguous()
+
+    def max_err(a, b):
+        d = (a.float() - b.float()).abs().max() / b.float().abs().max().clamp_min(1e-30)
+        return max_over_ranks(float(d))
+
+    for mode in ("scan", "chain"):
+        def sp_fw():
+            with torch.no_grad():
+                return mlstm_chunkwise_sequence_parallel(*mine, return_last_states=True, chunk_size=Lreq, mode=mode)
+        for _ in range(2):
+            sp_fw()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(5):
+            h_sp, last_sp = sp_fw()
+        e1.record()
+        barrier()
+        ms = max_over_ranks(e0.elapsed_time(e1) / 5)
+        res = dict(fw_ms=ms, fw_tflops=fl_fw / ms / 1e9, tokens_per_s=S / (ms * 1e-3),
+                   speedup_vs_single_gpu=ms_single / ms,
+                   H_max_rel_err_vs_single_gpu=max_err(h_sp, h_ref[:, :, sl]),
+                   H_bit_identical=bool(max_over_ranks(0.0 if torch.equal(h_sp, h_ref[:, :, sl]) else 1.0) == 0.0),
+                   C_last_max_rel_err=max_err(last_sp[0], last_ref[0]),
+                   n_last_max_rel_err=max_err(last_sp[1], last_ref[1]),
+                   m_last_max_abs_err=max_over_ranks(float((last_sp[2] - last_ref[2]).abs().max())))
+        # forward + backward: the backward is the chain run right to left
+        lv = [t.clone().requires_grad_(True) for t in mine]
+
+        def sp_fwbw():
+            for t in lv:
+                t.grad = None
+            mlstm_chunkwise_sequence_parallel(*lv, chunk_size=Lreq, mode=mode).backward(dH_m)
+        sp_fwbw()
+        barrier()
+        e0.record()
+        for _ in range(3):
+            sp_fwbw()
+        e1.record()
+        barrier()
+        msb = max_over_ranks(e0.elapsed_time(e1) / 3)
+        res.update(fwbw_ms=msb, fwbw_tflops=fl_fwbw / msb / 1e9, fwbw_speedup_vs_single_gpu=ms_single_fwbw / msb)
+        for name, a, b in zip(("dQ", "dK", "dV", "dI", "dF"), lv, grads_ref):
+            res[f"{name}_max_rel_err_vs_single_gpu"] = max_err(a.grad, b[:, :, sl])
+        out[mode] = res
+    out["exchange"] = "(C, n, m) packed into one NCCL point-to-point message per hop (4.2 MB per head pair); NVLS off"
+    return out
+
+
 def bench_triton_reference(torch, devin, leaf, L, flops_fw, flops_fwbw):
-    """Optional leg (--triton-ref): the reference's own Triton kernels, JIT-compiled by the box's Triton, on the
-    same GPU, inputs and timing loop.  Needs the reference package to be importable (e.g. pip-installed with
-    --target baseline/_ref); reports the error text otherwise."""
-    ref_dir = os.path.join(ROOT, "baseline", "_ref")
-    if os.path.isdir(ref_dir) and ref_dir not in sys.path:
-        sys.path.insert(0, ref_dir)
+    """The reference's own Triton kernels, JIT-compiled by the machine's Triton, on the same GPU, inputs and timing
+    loop (the first calls, which compile, are excluded).  Needs the reference package to be importable (e.g.
+    pip-installed with --target baseline/_ref); reports the error text otherwise."""
+    if os.path.isdir(REF_DIR) and REF_DIR not in sys.path:
+        sys.path.insert(0, REF_DIR)
     out = {}
     try:
         from mlstm_kernels.torch.chunkwise.triton_xl_chunk import mlstm_chunkwise__xl_chunk
@@ -437,12 +732,19 @@ def bench_triton_reference(torch, devin, leaf, L, flops_fw, flops_fwbw):
         with torch.no_grad():
             mlstm_chunkwise__xl_chunk(devin["q"], devin["k"], devin["v"], devin["i"], devin["f"], chunk_size=L)
 
-    for name, fn, fl in (("fwbw_mLSTMexp", make(mlstm_chunkwise__xl_chunk), flops_fwbw),
+    for name, fn, fl in (("fwbw_mLSTMexp_recompute_states (its default)", make(mlstm_chunkwise__xl_chunk), flops_fwbw),
+                         ("fwbw_mLSTMexp_keep_states", make(mlstm_chunkwise__xl_chunk, recompute_states_in_bw=False), flops_fwbw),
                          ("fw_mLSTMexp", fw_only, flops_fw),
-                         ("fwbw_mLSTMsig", make(mlstm_siging_chunkwise__xl_chunk, normalize=True), flops_fwbw)):
+                         ("fwbw_mLSTMsig_recompute_states (its default)", make(mlstm_siging_chunkwise__xl_chunk, normalize=True), flops_fwbw)):
         try:
             ms = timed_local(torch, fn, 5, 3)
-            out[name] = dict(ms=ms, tflops=fl / (ms * 1e-3) / 1e12)
+            torch.cuda.synchronize()
+            torch.cuda.reset_peak_memory_stats()
+            base = torch.cuda.memory_allocated()
+            fn()
+            torch.cuda.synchronize()
+            out[name] = dict(ms=ms, tflops=fl / (ms * 1e-3) / 1e12,
+                             peak_extra_memory_gb=(torch.cuda.max_memory_allocated() - base) / 1e9)
         except Exception as e:  # noqa: BLE001
             out[name] = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
     try:
@@ -458,7 +760,7 @@ def bench_triton_reference(torch, devin, leaf, L, flops_fw, flops_fwbw):
             i = torch.randn(B, NH, 1, device=dev).bfloat16(); f = (3 + torch.randn(B, NH, 1, device=dev)).bfloat16()
             fn = lambda: mlstm_recurrent_step__triton(q, k, v, i, f, c, n, m)  # noqa: E731
             ms = timed_local(torch, fn, 200 if B <= 64 else 50, 10)
-            out[f"step_B{B}"] = dict(us_per_step=ms * 1e3)
+            out[f"step_B{B}"] = dict(us_per_step=ms * 1e3, tokens_per_s=B / (ms * 1e-3))
     except Exception as e:  # noqa: BLE001
         out["step"] = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
     return out
@@ -484,7 +786,7 @@ def bench_sweep(torch, mk, dev, peaks):
         def fwbw():
             for t in leaf:
                 t.grad = None
-            mk.mlstm_chunkwise__b200_xl_chunk(*leaf, chunk_size=L).backward(dH)
+            mk.mlstm_chunkwise__b200_xl_chunk(*leaf, chunk_size=L, recompute_states_in_bw=False).backward(dH)
         ms_fw, ms_fwbw = timed_local(torch, fw, 5, 3), timed_local(torch, fwbw, 5, 3)
         ffw = fw_flops(B, NH, S, DHQK, DHHV, L)
         ffb = ffw + bw_flops(B, NH, S, DHQK, DHHV, L)
@@ -493,36 +795,6 @@ def bench_sweep(torch, mk, dev, peaks):
                                  fwbw_frac_of_peak=ffb / ms_fwbw / 1e9 / peaks["tflops"])
         del q, k, v, i, f, dH, leaf
     return out
-
-
-def bench_long_prefill(torch, mk, dev, peaks):
-    """Single-GPU forward of the long-sequence configuration (the sequence-parallel runs compare with this)."""
-    B, NH, S, DHQK, DHHV, L = 1, 8, 131072, 256, 512, 256
-    torch.cuda.empty_cache()   # the sweep before this leaves the caching allocator fragmented
-    g = torch.Generator(device=dev).manual_seed(7)
-    mk_t = lambda *sh: torch.randn(*sh, device=dev, generator=g).bfloat16()  # noqa: E731
-    q, k, v = mk_t(B, NH, S, DHQK), mk_t(B, NH, S, DHQK), mk_t(B, NH, S, DHHV)
-    i, f = mk_t(B, NH, S), (3 + torch.randn(B, NH, S, device=dev, generator=g)).bfloat16()
-
-    def fw():
-        with torch.no_grad():
-            mk.mlstm_chunkwise__b200_xl_chunk(q, k, v, i, f, return_last_states=True, chunk_size=L)
-    ms = timed_local(torch, fw, 5, 3)
-    fl = fw_flops(B, NH, S, DHQK, DHHV, L)
-    return dict(ms=ms, tflops=fl / ms / 1e9, frac_of_peak=fl / ms / 1e9 / peaks["tflops"], tokens_per_s=S / (ms * 1e-3))
-
-
-def timed_local(torch, fn, steps, warmup):
-    for _ in range(warmup):
-        fn()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(steps):
-        fn()
-    e1.record()
-    torch.cuda.synchronize()
-    return e0.elapsed_time(e1) / steps
 
 
 def bench_step(torch, mk, dev, peaks):
@@ -541,13 +813,18 @@ def bench_step(torch, mk, dev, peaks):
         v = torch.randn(T, B, NH, DHHV, device=dev, generator=g).bfloat16()
         i = torch.randn(T, B, NH, 1, device=dev, generator=g).bfloat16()
         f = (3 + torch.randn(T, B, NH, 1, device=dev, generator=g)).bfloat16()
+        h = torch.empty(B, NH, DHHV, device=dev, dtype=torch.bfloat16)
         state = [(c, n, m), (c2, n2, m2)]
+
+        # per-step token tensors are sliced ahead of the loop (a decoder gets them from its projection layers)
+        toks = [(q[t], k[t], v[t], i[t], f[t]) for t in range(T)]
 
         def run(nsteps):
             for t in range(nsteps):
                 (ci, ni, mi), (co, no, mo) = state[t % 2], state[(t + 1) % 2]
-                mk.mlstm_recurrent_step__b200_fw(ci, ni, mi, q[t % T], k[t % T], v[t % T], i[t % T], f[t % T],
-                                                 matC_new=co, vecN_new=no, scaM_new=mo)
+                qt, kt, vt, it, ft = toks[t % T]
+                mk.mlstm_recurrent_step__b200_fw(ci, ni, mi, qt, kt, vt, it, ft,
+                                                 matC_new=co, vecN_new=no, scaM_new=mo, vecH_out=h)
         nsteps = 1024 if B <= 64 else 256
         run(16)
         torch.cuda.synchronize()
@@ -557,7 +834,7 @@ def bench_step(torch, mk, dev, peaks):
         e1.record()
         torch.cuda.synchronize()
         us = e0.elapsed_time(e1) / nsteps * 1e3
-        nbytes = B * NH * (2 * DHQK * DHHV * 4 + 2 * DHQK * 4 + 8 + (2 * DHQK + 2 * DHHV) * 2 + 4)
+        nbytes = step_bytes(B, NH, DHQK, DHHV)
         gbs = nbytes / (us * 1e-6) / 1e9
         out[f"B{B}"] = dict(us_per_step=us, tokens_per_s=B / (us * 1e-6), gbs=gbs, frac_of_hbm=gbs / peaks["hbm"],
                             note="includes Python launch overhead per step" if B <= 8 else "")
@@ -593,11 +870,14 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary measurements")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--triton-ref", action="store_true",
-                    help="also time the reference's Triton kernels on this GPU (needs the reference importable)")
+    ap.add_argument("--no-triton-ref", action="store_true",
+                    help="do not time the reference's Triton kernels on this GPU (they run by default at N=1 when the "
+                         "reference package is importable)")
     ap.add_argument("--batch", type=int, default=None, help="override the batch size B of the workload (profiling)")
     ap.add_argument("--quick", action="store_true",
                     help="profiling mode: timed region only (no end-to-end leg, no per-kernel pass, no extras, no CPU leg)")
+    ap.add_argument("--step-only", type=int, default=None, metavar="B",
+                    help="profiling mode: a short chain of decode steps at batch B (NH=8, 256/512) and nothing else")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "b200" and not args.quick:
         args.warmup = 3
@@ -606,10 +886,39 @@ def main():
         WORKLOAD["name"] = WORKLOAD["name"].replace("_B8_", f"_B{args.batch}_")
     if args.quick:
         args.no_extra = args.no_cpu = True
-    if args.impl == "reference":
+    if args.step_only is not None:
+        run_step_only(args.step_only)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_b200(args)
+
+
+def run_step_only(B):
+    """A chain of 24 decode steps at batch B, for a profiler capture of the decode kernel alone."""
+    import torch
+
+    import mlstm_kernels_b200 as mk
+    dev = torch.device("cuda", 0)
+    NH, DHQK, DHHV = 8, 256, 512
+    c = torch.randn(B, NH, DHQK, DHHV, device=dev) * 0.1
+    n = torch.randn(B, NH, DHQK, device=dev).abs()
+    m = torch.randn(B, NH, 1, device=dev)
+    state = [(c, n, m), (torch.empty_like(c), torch.empty_like(n), torch.empty_like(m))]
+    q, k = torch.randn(B, NH, DHQK, device=dev).bfloat16(), torch.randn(B, NH, DHQK, device=dev).bfloat16()
+    v = torch.randn(B, NH, DHHV, device=dev).bfloat16()
+    i, f = torch.randn(B, NH, 1, device=dev).bfloat16(), (3 + torch.randn(B, NH, 1, device=dev)).bfloat16()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for t in range(24):
+        if t == 8:
+            e0.record()
+        (ci, ni, mi), (co, no, mo) = state[t % 2], state[(t + 1) % 2]
+        mk.mlstm_recurrent_step__b200_fw(ci, ni, mi, q, k, v, i, f, matC_new=co, vecN_new=no, scaM_new=mo)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) / 16 * 1e3
+    print(json.dumps({"step_only_B": B, "us_per_step": us, "gbs": step_bytes(B, NH, DHQK, DHHV) / (us * 1e-6) / 1e9}))
 
 
 if __name__ == "__main__":

@@ -35,9 +35,9 @@ enum { MLSTM_F32 = 0, MLSTM_BF16 = 1, MLSTM_F16 = 2 };
 enum { MLSTM_EXP = 0, MLSTM_SIG = 1, MLSTM_SIG_NONORM = 2 };
 
 /* which implementation to run: AUTO picks the tcgen05/TMA kernels whenever the
- * shape allows and the portable CUDA-core kernels otherwise; TCGEN05_FUSED forces the forward kernel that keeps
- * the inter-chunk state on chip (backward is the same as TCGEN05) */
-enum { MLSTM_IMPL_AUTO = 0, MLSTM_IMPL_SIMT = 1, MLSTM_IMPL_TCGEN05 = 2, MLSTM_IMPL_TCGEN05_FUSED = 3 };
+ * shape allows and the portable CUDA-core kernels otherwise; SIMT / TCGEN05 force one of them
+ * (TCGEN05 returns MLSTM_ERR_UNSUPPORTED for a case it does not cover) */
+enum { MLSTM_IMPL_AUTO = 0, MLSTM_IMPL_SIMT = 1, MLSTM_IMPL_TCGEN05 = 2 };
 
 enum {
   MLSTM_OK = 0,
@@ -64,6 +64,15 @@ long long mlstm_b200_launch_count(void);
  * invalid); a negative MLSTM_ERR_* value if the query itself failed.  reset != 0 clears the word.
  */
 int mlstm_b200_device_status(int reset);
+
+/*
+ * Self-test of the bounded waits: launches one tiny kernel in which a single thread waits, for at most
+ * limit_polls polls (1 .. 1,000,000: a few milliseconds), on a barrier that nothing ever signals, gives up and
+ * records `code` (> 0) in the status word that mlstm_b200_device_status() returns.  Nothing else happens on the
+ * device: no copy is in flight and no tensor memory is held.  Lets a host check that an expired wait is reported
+ * and leaves the context usable.  No counterpart in the reference (Triton kernels have no device-side waits).
+ */
+int mlstm_b200_selftest_wait_expiry(unsigned int limit_polls, int code, void* stream);
 
 /*
  * Per-phase device timing.  After mlstm_b200_profile_enable(1) every phase of the entry points
@@ -129,12 +138,19 @@ int mlstm_b200_chunkwise_fw(const void* q, const void* k, const void* v, const v
  *   - Limit: the case must need no more scratch than that (roughly B*NH*S <= 500,000); larger cases
  *     are rejected with MLSTM_ERR_WORKSPACE before anything is launched.
  *   - The first call on each device looks up the array's device address (a short host-side set-up,
- *     done with that device current); make that first call before any stream capture begins.
+ *     done with that device current); make that first call before any stream capture begins.  The stream
+ *     must belong to the current device (checked; MLSTM_ERR_UNSUPPORTED otherwise).
+ *   - The CUDA runtime loads device code and the array itself lazily, on first use, and that loading takes
+ *     device memory from the driver.  A host that is about to hand all free memory to its own pool should
+ *     therefore call mlstm_b200_static_warmup() (array + gate and tcgen05 forward kernels) or run one small
+ *     forward per device and implementation BEFORE it does so; only calls after that are free of driver
+ *     allocations.  A cudaDeviceReset() invalidates the looked-up address: do not reset a device in use.
  *   - All calls on a device share the one array, which keeps whatever the previous call left in it.
  *     The forward overwrites every word it later reads, so nothing needs clearing; but two calls
  *     whose kernels overlap on the GPU (different streams, or threads) race on it - serialise them.
  */
 size_t mlstm_b200_static_scratch_bytes(void);
+int mlstm_b200_static_warmup(void);
 int mlstm_b200_chunkwise_fw_static(const void* q, const void* k, const void* v, const void* i, const void* f,
                                    const float* c_initial, const float* n_initial, const float* m_initial,
                                    void* h, float* n_out, float* m_out,
@@ -179,6 +195,22 @@ int mlstm_b200_chunkwise_bw_cached(const void* q, const void* k, const void* v, 
                                    int dtype, int gate_dtype, int variant, int impl, float eps, void* stream);
 
 /*
+ * Per-chunk C states only (no H, no n): what the backward needs when the forward did not keep them.
+ * Replaces the state recomputation at the top of the reference's backward when recompute_states_in_bw is set
+ * (mlstm_kernels/torch/chunkwise/triton_xl_chunk/bw.py:76-112; switch in fwbw.py:45,62,88-115).
+ *   c_states (B,NH,NC+1,DHQK,DHHV) out, element type mlstm_b200_chunkwise_state_dtype().
+ *   fw_workspace: the scratch buffer the forward call of the same problem left behind (its gate vectors are read
+ *   instead of being recomputed), or NULL - then `workspace` of
+ *   mlstm_b200_chunkwise_workspace_bytes(..., backward = 2) bytes is used for a fresh gate pre-pass.
+ */
+int mlstm_b200_chunkwise_states(const void* k, const void* v, const void* i, const void* f,
+                                const float* c_initial, const float* m_initial, void* c_states,
+                                const void* fw_workspace, size_t fw_workspace_bytes,
+                                void* workspace, size_t workspace_bytes,
+                                int B, int NH, int S, int DHQK, int DHHV, int L,
+                                int dtype, int gate_dtype, int variant, int impl, void* stream);
+
+/*
  * Sequence-parallel prefill: a long sequence is split into contiguous segments, one per GPU.
  * The reference has no multi-device code; these two entry points implement its state-passing
  * contract (chaining segments through c_initial / n_initial / m_initial and the returned last
@@ -210,7 +242,8 @@ int mlstm_b200_state_combine(const float* c_in, const float* n_in, const float* 
  * (mlstm_kernels/torch/recurrent/triton_step.py:15-127) and its kernel
  * recurrent_step_fw_kernel (mlstm_kernels/triton/recurrent/fw_step_fused.py:19-195).
  *
- *   q,k (B,NH,DHQK) dtype; v (B,NH,DHHV) dtype; i,f (B,NH) dtype
+ *   q,k (B,NH,DHQK) dtype; v (B,NH,DHHV) dtype; i,f (B,NH) gate_dtype (widened to f32 before any
+ *   arithmetic, as fw_step_fused.py:88-94 does)
  *   c (B,NH,DHQK,DHHV), n (B,NH,DHQK), m (B,NH) in state_dtype (MLSTM_F32 or MLSTM_BF16)
  *   h (B,NH,DHHV) dtype out; c_new, n_new, m_new out, state_dtype.
  *   c_new may alias c (each element is read and written by the same thread); n_new and
@@ -219,18 +252,20 @@ int mlstm_b200_state_combine(const float* c_in, const float* n_in, const float* 
 int mlstm_b200_step(const void* q, const void* k, const void* v, const void* i, const void* f,
                     const void* c, const void* n, const void* m,
                     void* h, void* c_new, void* n_new, void* m_new,
-                    int B, int NH, int DHQK, int DHHV, int dtype, int state_dtype, float eps, void* stream);
+                    int B, int NH, int DHQK, int DHHV, int dtype, int gate_dtype, int state_dtype, float eps,
+                    void* stream);
 
 /*
  * T decode steps in one launch with the state kept on chip between tokens.
  * Replaces the per-token Python loop _mlstm_recurrent_sequence_loop_fw
  * (mlstm_kernels/torch/recurrent/native_sequence.py:13-122) over the step kernel.
- *   q,k (B,NH,T,DHQK); v (B,NH,T,DHHV); i,f (B,NH,T); h (B,NH,T,DHHV); states f32 as in mlstm_b200_step.
+ *   q,k (B,NH,T,DHQK); v (B,NH,T,DHHV); i,f (B,NH,T) gate_dtype; h (B,NH,T,DHHV); states f32 as in mlstm_b200_step.
  */
 int mlstm_b200_step_sequence(const void* q, const void* k, const void* v, const void* i, const void* f,
                              const float* c, const float* n, const float* m,
                              void* h, float* c_new, float* n_new, float* m_new,
-                             int B, int NH, int T, int DHQK, int DHHV, int dtype, float eps, void* stream);
+                             int B, int NH, int T, int DHQK, int DHHV, int dtype, int gate_dtype, float eps,
+                             void* stream);
 
 #if defined(__GNUC__)
 #pragma GCC visibility pop

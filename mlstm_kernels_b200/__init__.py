@@ -6,6 +6,7 @@ libmlstm_b200.so through its C ABI (include/mlstm_b200.h); there is no CPU or Py
 from .chunkwise import (
     chunkwise_bw_raw,
     chunkwise_fw_raw,
+    chunkwise_states_raw,
     kernel_chunk_size,
     mlstm_chunkwise__b200_xl_chunk,
     mlstm_siging_chunkwise__b200_xl_chunk,
@@ -26,6 +27,7 @@ __all__ = [
     "mlstm_recurrent_sequence__b200",
     "chunkwise_fw_raw",
     "chunkwise_bw_raw",
+    "chunkwise_states_raw",
     "select_chunk_size",
     "kernel_chunk_size",
     "get_kernel",

@@ -15,7 +15,7 @@ LIB_PATH = os.path.join(_PKG, "libmlstm_b200.so")
 
 F32, BF16, F16 = 0, 1, 2
 EXP, SIG, SIG_NONORM = 0, 1, 2
-IMPL = {"auto": 0, "simt": 1, "tcgen05": 2, "tcgen05_fused": 3}
+IMPL = {"auto": 0, "simt": 1, "tcgen05": 2}
 
 _DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
 _CODE_DTYPE = {v: k for k, v in _DTYPE_CODE.items()}
@@ -29,6 +29,7 @@ SIGNATURES = {
     "mlstm_b200_last_cuda_error": (C.c_char_p, []),
     "mlstm_b200_launch_count": (C.c_longlong, []),
     "mlstm_b200_device_status": (_i, [_i]),
+    "mlstm_b200_selftest_wait_expiry": (_i, [C.c_uint, _i, _vp]),
     "mlstm_b200_profile_enable": (_i, [_i]),
     "mlstm_b200_profile_phases": (_i, []),
     "mlstm_b200_profile_phase_name": (C.c_char_p, [_i]),
@@ -39,16 +40,18 @@ SIGNATURES = {
     "mlstm_b200_chunkwise_fw": (_i, [_vp] * 5 + [_fp] * 3 + [_vp, _fp, _fp] + [_vp, _fp, _fp] + [_fp] * 3
                                 + [_vp, _sz] + [_i] * 6 + [_i, _i, _i, _i, _f, _vp]),
     "mlstm_b200_static_scratch_bytes": (_sz, []),
+    "mlstm_b200_static_warmup": (_i, []),
     "mlstm_b200_chunkwise_fw_static": (_i, [_vp] * 5 + [_fp] * 3 + [_vp, _fp, _fp] + [_vp, _fp, _fp] + [_fp] * 3
                                        + [_i] * 6 + [_i, _i, _i, _i, _f, _vp]),
     "mlstm_b200_chunkwise_bw": (_i, [_vp] * 5 + [_fp, _vp, _fp, _vp, _fp] + [_vp] * 3 + [_fp] * 3
                                 + [_vp, _sz] + [_i] * 6 + [_i, _i, _i, _i, _f, _vp]),
     "mlstm_b200_chunkwise_bw_cached": (_i, [_vp] * 5 + [_fp, _vp, _fp, _fp, _vp, _sz, _vp, _fp] + [_vp] * 3 + [_fp] * 3
                                        + [_vp, _sz] + [_i] * 6 + [_i, _i, _i, _i, _f, _vp]),
+    "mlstm_b200_chunkwise_states": (_i, [_vp] * 4 + [_fp, _fp, _vp, _vp, _sz, _vp, _sz] + [_i] * 6 + [_i, _i, _i, _i, _vp]),
     "mlstm_b200_chunkwise_summary": (_i, [_vp] * 4 + [_fp] * 4 + [_vp, _sz] + [_i] * 6 + [_i, _i, _i, _i, _vp]),
     "mlstm_b200_state_combine": (_i, [_fp] * 10 + [_i] * 5 + [_vp]),
-    "mlstm_b200_step": (_i, [_vp] * 12 + [_i] * 6 + [_f, _vp]),
-    "mlstm_b200_step_sequence": (_i, [_vp] * 12 + [_i] * 6 + [_f, _vp]),
+    "mlstm_b200_step": (_i, [_vp] * 12 + [_i] * 7 + [_f, _vp]),
+    "mlstm_b200_step_sequence": (_i, [_vp] * 12 + [_i] * 7 + [_f, _vp]),
 }
 
 _lib = None

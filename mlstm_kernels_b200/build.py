@@ -18,7 +18,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 OBJ = os.path.join(PKG, "build")
 LIB = os.path.join(PKG, "libmlstm_b200.so")
-SOURCES = ["api.cu", "gates.cu", "step.cu", "chunkwise_simt.cu", "chunkwise_sm100.cu", "chunkwise_fused_sm100.cu", "noalloc.cu"]
+SOURCES = ["api.cu", "gates.cu", "step.cu", "chunkwise_simt.cu", "chunkwise_sm100.cu", "noalloc.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "--use_fast_math=false", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",

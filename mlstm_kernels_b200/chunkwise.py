@@ -10,10 +10,16 @@ The Triton tuning keyword arguments are accepted and ignored.
 
 from __future__ import annotations
 
+import os
+
 import torch
 from torch.amp import custom_bwd, custom_fwd
 
 from . import _lib
+
+# MLSTM_B200_CHECK_STATUS=1: after every backward, synchronise and raise if a bounded wait of the tcgen05 kernels
+# ran out (their results are then invalid).  Off by default because the check waits for the device.
+_CHECK_STATUS = os.environ.get("MLSTM_B200_CHECK_STATUS", "0") == "1"
 
 
 def _is_pow2(x: int) -> bool:
@@ -84,12 +90,14 @@ def chunkwise_fw_raw(q, k, v, i, f, c_initial=None, n_initial=None, m_initial=No
     n_out = torch.empty((B, NH, S), dtype=torch.float32, device=dev)
     m_out = torch.empty((B, NH, S), dtype=torch.float32, device=dev)
     c_states = torch.empty((B, NH, NC + 1, DHQK, DHHV), dtype=sdt, device=dev)
-    n_states = torch.zeros((B, NH, NC + 1, DHQK), dtype=torch.float32, device=dev)
+    # mLSTMsig without normaliser never writes n: the buffers are then zero-filled, otherwise fully overwritten
+    n_alloc = torch.zeros if variant == _lib.SIG_NONORM else torch.empty
+    n_states = n_alloc((B, NH, NC + 1, DHQK), dtype=torch.float32, device=dev)
     m_states = torch.empty((B, NH, NC + 1), dtype=torch.float32, device=dev)
     c_last = n_last = m_last = None
     if want_last:
         c_last = torch.empty((B, NH, DHQK, DHHV), dtype=torch.float32, device=dev)
-        n_last = torch.zeros((B, NH, DHQK), dtype=torch.float32, device=dev)
+        n_last = n_alloc((B, NH, DHQK), dtype=torch.float32, device=dev)
         m_last = torch.empty((B, NH, 1), dtype=torch.float32, device=dev)
     ws_bytes = lib.mlstm_b200_chunkwise_workspace_bytes(B, NH, S, DHQK, DHHV, L, dt, variant, im, 0)
     ws = torch.empty((max(ws_bytes, 256),), dtype=torch.uint8, device=dev)
@@ -105,6 +113,38 @@ def chunkwise_fw_raw(q, k, v, i, f, c_initial=None, n_initial=None, m_initial=No
     _lib.check(rc, "mlstm_b200_chunkwise_fw")
     return dict(H=h, n_out=n_out, m_out=m_out, C_states=c_states, n_states=n_states, m_states=m_states,
                 C_last=c_last, n_last=n_last, m_last=m_last, workspace=ws)
+
+
+def chunkwise_states_raw(k, v, i, f, c_initial=None, m_initial=None, *, chunk_size: int, variant: int,
+                         impl: str = "auto", fw_workspace=None):
+    """Per-chunk C states (B, NH, NC+1, DHQK, DHHV) alone: the forward's recurrence re-run for a backward whose
+    forward did not keep them.  With `fw_workspace` (as returned by chunkwise_fw_raw for the same inputs) the gate
+    pre-pass is not repeated."""
+    _lib.require_cuda(k, v, i, f)
+    lib = _lib.load()
+    B, NH, S, DHQK = k.shape
+    DHHV = v.shape[-1]
+    L = chunk_size
+    dt, gdt, im = _lib.dtype_code(k.dtype), _lib.dtype_code(i.dtype), _lib.IMPL[impl]
+    if i.dtype != f.dtype:
+        f = f.to(i.dtype)
+    k, v, i, f = (t.contiguous() for t in (k, v, i, f))
+    c0 = _f32c(c_initial)
+    m0 = None if m_initial is None else _f32c(m_initial).reshape(B, NH)
+    dev = k.device
+    sdt = _lib.code_dtype(lib.mlstm_b200_chunkwise_state_dtype(S, DHQK, DHHV, L, dt, im))
+    c_states = torch.empty((B, NH, S // L + 1, DHQK, DHHV), dtype=sdt, device=dev)
+    ws, ws_bytes = None, 0
+    if fw_workspace is None:
+        ws_bytes = lib.mlstm_b200_chunkwise_workspace_bytes(B, NH, S, DHQK, DHHV, L, dt, variant, im, 2)
+        ws = torch.empty((max(ws_bytes, 256),), dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        rc = lib.mlstm_b200_chunkwise_states(
+            _lib.ptr(k), _lib.ptr(v), _lib.ptr(i), _lib.ptr(f), _lib.ptr(c0), _lib.ptr(m0), _lib.ptr(c_states),
+            _lib.ptr(fw_workspace), 0 if fw_workspace is None else fw_workspace.numel(), _lib.ptr(ws), ws_bytes,
+            B, NH, S, DHQK, DHHV, L, dt, gdt, variant, im, _lib.stream_handle(dev))
+    _lib.check(rc, "mlstm_b200_chunkwise_states")
+    return c_states
 
 
 def chunkwise_bw_raw(q, k, v, i, f, m_initial, c_states, n_out, dh, dc_last=None, *, chunk_size: int, eps: float,
@@ -156,14 +196,19 @@ def _make_fwbw(autocast_kernel_dtype: torch.dtype, variant: int):
     class _mlstm_chunkwise_fwbw(torch.autograd.Function):
         @staticmethod
         @custom_fwd(device_type="cuda", cast_inputs=autocast_kernel_dtype)
-        def forward(ctx, q, k, v, i, f, c_initial, n_initial, m_initial, return_last_states, eps, chunk_size, impl):
+        def forward(ctx, q, k, v, i, f, c_initial, n_initial, m_initial, return_last_states, eps, chunk_size, impl,
+                    recompute_states_in_bw):
             B, NH, S, DHQK = q.shape
             L = kernel_chunk_size(q, v, select_chunk_size(S, chunk_size), impl)
             out = chunkwise_fw_raw(q, k, v, i, f, c_initial, n_initial, m_initial, chunk_size=L, eps=eps,
                                    variant=variant, impl=impl, want_last=return_last_states)
-            # the forward's gate vectors (its scratch buffer and m_out) are kept for the backward: 24 B per token
-            ctx.save_for_backward(q, k, v, i, f, m_initial, out["C_states"], out["n_out"], out["m_out"],
-                                  out["workspace"])
+            # The forward's gate vectors (its scratch buffer and m_out) are kept for the backward: 24 B per token.
+            # The per-chunk C states (2 * DHQK * DHHV / L bytes per token on the tcgen05 path) are kept only when
+            # the caller asks for it; otherwise the backward runs the recurrence again, as the reference does
+            # (mlstm_kernels/torch/chunkwise/triton_xl_chunk/fwbw.py:88-115).
+            kept = None if recompute_states_in_bw else out["C_states"]
+            ctx.save_for_backward(q, k, v, i, f, c_initial if recompute_states_in_bw else None, m_initial, kept,
+                                  out["n_out"], out["m_out"], out["workspace"])
             ctx.cfg = (L, eps, impl, c_initial is not None, n_initial is not None, m_initial is not None,
                        None if c_initial is None else c_initial.dtype,
                        None if n_initial is None else n_initial.dtype)
@@ -175,8 +220,11 @@ def _make_fwbw(autocast_kernel_dtype: torch.dtype, variant: int):
         @staticmethod
         @custom_bwd(device_type="cuda")
         def backward(ctx, dH, dC_last, dN_last, dM_last):
-            q, k, v, i, f, m_initial, c_states, n_out, m_out, fw_ws = ctx.saved_tensors
+            q, k, v, i, f, c_initial, m_initial, c_states, n_out, m_out, fw_ws = ctx.saved_tensors
             L, eps, impl, has_c0, has_n0, has_m0, c0_dtype, n0_dtype = ctx.cfg
+            if c_states is None:
+                c_states = chunkwise_states_raw(k, v, i, f, c_initial, m_initial, chunk_size=L, variant=variant,
+                                                impl=impl, fw_workspace=fw_ws)
             dq, dk, dv, di, df, dc0 = chunkwise_bw_raw(
                 q, k, v, i, f, m_initial, c_states, n_out, dH, dC_last, chunk_size=L, eps=eps, variant=variant,
                 impl=impl, want_dc_initial=has_c0, m_out=m_out, fw_workspace=fw_ws)
@@ -185,7 +233,9 @@ def _make_fwbw(autocast_kernel_dtype: torch.dtype, variant: int):
             dm0 = torch.zeros_like(m_initial) if has_m0 else None
             if dc0 is not None:
                 dc0 = dc0.to(c0_dtype)
-            return (dq, dk, dv, di.to(i.dtype), df.to(f.dtype), dc0, dn0, dm0, None, None, None, None)
+            if _CHECK_STATUS and _lib.device_status() != 0:
+                raise RuntimeError("mlstm_kernels_b200: a bounded wait of the tcgen05 kernels ran out; results invalid")
+            return (dq, dk, dv, di.to(i.dtype), df.to(f.dtype), dc0, dn0, dm0, None, None, None, None, None)
 
     return _mlstm_chunkwise_fwbw
 
@@ -229,11 +279,14 @@ def mlstm_chunkwise__b200_xl_chunk(
     impl: str = "auto",
 ) -> torch.Tensor | tuple[torch.Tensor, tuple[torch.Tensor, torch.Tensor, torch.Tensor]]:
     """mLSTMexp chunkwise forward with autograd.  Returns H, or (H, (C_last, n_last, m_last)) with f32
-    states when return_last_states is set.  Tile / warp / stage arguments are Triton tuning knobs of the
-    reference and have no meaning here."""
+    states when return_last_states is set.  `recompute_states_in_bw` has the reference's meaning (and default):
+    True keeps only q, k, v, i, f and the per-token gate vectors between forward and backward and runs the
+    inter-chunk recurrence again in the backward; False keeps the per-chunk C states (faster backward, more
+    memory).  Tile / warp / stage arguments and chunk_size_inter / chunk_size_intra are Triton tuning knobs of
+    the reference and have no meaning here."""
     fn = _get_fwbw(autocast_kernel_dtype, _lib.EXP)
     h, c_last, n_last, m_last = fn.apply(q, k, v, i, f, c_initial, n_initial, m_initial, return_last_states,
-                                         eps, chunk_size, impl)
+                                         eps, chunk_size, impl, bool(recompute_states_in_bw))
     if return_last_states:
         return h, (c_last, n_last, m_last)
     return h
@@ -270,7 +323,7 @@ def mlstm_siging_chunkwise__b200_xl_chunk(
     (H, (C_last, n_last)) when return_last_states is set."""
     fn = _get_fwbw(autocast_kernel_dtype, _lib.SIG if normalize else _lib.SIG_NONORM)
     h, c_last, n_last, _ = fn.apply(q, k, v, i, f, c_initial, n_initial, None, return_last_states, eps, chunk_size,
-                                    impl)
+                                    impl, bool(recompute_states_in_bw))
     if return_last_states:
         return h, (c_last, n_last)
     return h

@@ -1,4 +1,5 @@
 // extern "C" entry points of libmlstm_b200.so: argument validation, workspace carving, dispatch.
+#include <algorithm>
 #include <atomic>
 #include <cstdio>
 #include <cstdlib>
@@ -44,25 +45,29 @@ PhaseScope::~PhaseScope() {
   if (slot < (int)g_prof_recs.size()) cudaEventRecord(g_prof_recs[slot].b, st);
 }
 
-// AUTO uses the two-kernel forward (faster at present); MLSTM_B200_FUSED_FW=1 in the environment makes AUTO
-// pick the fused forward where it applies
-static const bool g_fused_auto = []() { const char* e = getenv("MLSTM_B200_FUSED_FW"); return e && e[0] == '1'; }();
-
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 static int check_dims(int B, int NH, int S, int DHQK, int DHHV, int L) {
   if (B <= 0 || NH <= 0 || S <= 0 || DHQK <= 0 || DHHV <= 0 || L <= 0) return MLSTM_ERR_SHAPE;
   if (S % L != 0) return MLSTM_ERR_SHAPE;
   if (!is_pow2(L) || L < 16 || L > 1024) return MLSTM_ERR_SHAPE;
+  // Sizes the launches cannot express are refused here instead of failing at launch or overflowing an index:
+  // the grids carry (tiles x chunks x batch x heads) in one dimension, and the tcgen05 kernels address token and
+  // state rows with 32-bit coordinates.
+  const uint64_t lim = 0x7fffffffull;
+  const uint64_t bnh = (uint64_t)B * NH, nc = (uint64_t)S / L;
+  const uint64_t tiles = (uint64_t)std::max(ceil_div(DHQK, 64), ceil_div(DHHV, 64));
+  if (bnh * nc * tiles >= lim || bnh * S >= lim) return MLSTM_ERR_SHAPE;
   return MLSTM_OK;
 }
 
-static int resolve_impl(int impl, int S, int DHQK, int DHHV, int L, int dtype, bool* use_sm100) {
+static int resolve_impl(int impl, int B, int NH, int S, int DHQK, int DHHV, int L, int dtype, bool* use_sm100) {
   const bool ok = sm100_supported(S, DHQK, DHHV, L, dtype);
-  if (impl == MLSTM_IMPL_AUTO) { *use_sm100 = ok; return MLSTM_OK; }
-  if (impl == MLSTM_IMPL_SIMT) { *use_sm100 = false; return MLSTM_OK; }
-  if (impl == MLSTM_IMPL_TCGEN05 || impl == MLSTM_IMPL_TCGEN05_FUSED) { *use_sm100 = true; return ok ? MLSTM_OK : MLSTM_ERR_UNSUPPORTED; }
-  return MLSTM_ERR_UNSUPPORTED;
+  if (impl != MLSTM_IMPL_AUTO && impl != MLSTM_IMPL_SIMT && impl != MLSTM_IMPL_TCGEN05) return MLSTM_ERR_UNSUPPORTED;
+  *use_sm100 = ok && impl != MLSTM_IMPL_SIMT;
+  if (impl == MLSTM_IMPL_TCGEN05 && !ok) return MLSTM_ERR_UNSUPPORTED;
+  if (*use_sm100 && !sm100_sizes_ok(B, NH, S, DHQK, DHHV)) return MLSTM_ERR_SHAPE;
+  return MLSTM_OK;
 }
 
 // carve f32 arrays out of the workspace, each start 256-byte aligned
@@ -166,6 +171,10 @@ int mlstm_b200_device_status(int reset) {
   return rc != MLSTM_OK ? rc : status;
 }
 
+int mlstm_b200_selftest_wait_expiry(unsigned int limit_polls, int code, void* stream) {
+  return sm100_wait_expiry_selftest(limit_polls, code, static_cast<cudaStream_t>(stream));
+}
+
 int mlstm_b200_profile_enable(int on) {
   std::lock_guard<std::mutex> lk(g_prof_mu);
   for (auto& r : g_prof_recs) { cudaEventDestroy(r.a); cudaEventDestroy(r.b); }
@@ -203,7 +212,7 @@ int mlstm_b200_chunkwise_has_tcgen05(int S, int DHQK, int DHHV, int L, int dtype
 
 int mlstm_b200_chunkwise_state_dtype(int S, int DHQK, int DHHV, int L, int dtype, int impl) {
   bool use_sm100 = false;
-  if (resolve_impl(impl, S, DHQK, DHHV, L, dtype, &use_sm100) != MLSTM_OK) return MLSTM_F32;
+  if (resolve_impl(impl, 1, 1, S, DHQK, DHHV, L, dtype, &use_sm100) != MLSTM_OK) return MLSTM_F32;
   return use_sm100 ? MLSTM_BF16 : MLSTM_F32;
 }
 
@@ -235,7 +244,7 @@ int mlstm_b200_chunkwise_fw(const void* q, const void* k, const void* v, const v
                         c_last, n_last, m_last, workspace};
   for (const void* p : ptrs) if (p && !aligned16(p)) return MLSTM_ERR_ALIGN;
   bool use_sm100 = false;
-  if ((rc = resolve_impl(impl, S, DHQK, DHHV, L, dtype, &use_sm100)) != MLSTM_OK) return rc;
+  if ((rc = resolve_impl(impl, B, NH, S, DHQK, DHHV, L, dtype, &use_sm100)) != MLSTM_OK) return rc;
 
   ChunkwiseDims d{B, NH, S, DHQK, DHHV, L, S / L, variant, eps, 1.0f / sqrtf((float)DHQK)};
   FwLayout lay = carve_fw(workspace, B * NH, S, d.NC, m_out);
@@ -243,13 +252,7 @@ int mlstm_b200_chunkwise_fw(const void* q, const void* k, const void* v, const v
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 
   if ((rc = launch_gates(gate_dtype, i, f, variant == MLSTM_EXP ? m_initial : nullptr, nullptr, lay.gb, m_states, d, st)) != MLSTM_OK) return rc;
-  const bool fused_ok = use_sm100 && sm100_fused_fw_supported(B, NH, S, DHQK, DHHV, L, dtype);
-  if (impl == MLSTM_IMPL_TCGEN05_FUSED && !(use_sm100 && dtype == MLSTM_BF16 && DHQK == 256)) return MLSTM_ERR_UNSUPPORTED;
-  if (use_sm100 && (impl == MLSTM_IMPL_TCGEN05_FUSED || (impl == MLSTM_IMPL_AUTO && fused_ok && g_fused_auto))) {
-    if ((rc = sm100_fused_fw(q, k, v, lay.gb, c_initial, n_initial, h, n_out, c_states,
-                             variant == MLSTM_SIG_NONORM ? nullptr : n_states, c_last,
-                             variant == MLSTM_SIG_NONORM ? nullptr : n_last, d, st)) != MLSTM_OK) return rc;
-  } else if (use_sm100) {
+  if (use_sm100) {
     if ((rc = sm100_recurrent_fw(k, v, lay.gb, c_initial, n_initial, c_states, n_states, c_last, n_last, d, st)) != MLSTM_OK) return rc;
     if ((rc = sm100_parallel_fw(q, k, v, lay.gb, c_states, n_states, h, n_out, d, st)) != MLSTM_OK) return rc;
   } else {
@@ -284,7 +287,7 @@ static int bw_impl(const void* q, const void* k, const void* v, const void* i, c
   const void* ptrs[] = {q, k, v, i, f, m_initial, c_states, n_out, dh, dc_last, dq, dk, dv, di, df, dc_initial, workspace};
   for (const void* p : ptrs) if (p && !aligned16(p)) return MLSTM_ERR_ALIGN;
   bool use_sm100 = false;
-  if ((rc = resolve_impl(impl, S, DHQK, DHHV, L, dtype, &use_sm100)) != MLSTM_OK) return rc;
+  if ((rc = resolve_impl(impl, B, NH, S, DHQK, DHHV, L, dtype, &use_sm100)) != MLSTM_OK) return rc;
 
   ChunkwiseDims d{B, NH, S, DHQK, DHHV, L, S / L, variant, eps, 1.0f / sqrtf((float)DHQK)};
   const int sdt = use_sm100 ? MLSTM_BF16 : MLSTM_F32;
@@ -343,6 +346,39 @@ int mlstm_b200_chunkwise_bw_cached(const void* q, const void* k, const void* v, 
                  fw_workspace_bytes, m_out);
 }
 
+int mlstm_b200_chunkwise_states(const void* k, const void* v, const void* i, const void* f, const float* c_initial,
+                                const float* m_initial, void* c_states, const void* fw_workspace,
+                                size_t fw_workspace_bytes, void* workspace, size_t workspace_bytes, int B, int NH,
+                                int S, int DHQK, int DHHV, int L, int dtype, int gate_dtype, int variant, int impl,
+                                void* stream) {
+  int rc = check_dims(B, NH, S, DHQK, DHHV, L);
+  if (rc != MLSTM_OK) return rc;
+  if (dtype != MLSTM_F32 && dtype != MLSTM_BF16 && dtype != MLSTM_F16) return MLSTM_ERR_DTYPE;
+  if (gate_dtype != MLSTM_F32 && gate_dtype != MLSTM_BF16 && gate_dtype != MLSTM_F16) return MLSTM_ERR_DTYPE;
+  if (variant < MLSTM_EXP || variant > MLSTM_SIG_NONORM) return MLSTM_ERR_UNSUPPORTED;
+  if (!k || !v || !i || !f || !c_states) return MLSTM_ERR_NULL;
+  if (!fw_workspace && !workspace) return MLSTM_ERR_NULL;
+  const void* ptrs[] = {k, v, i, f, c_initial, m_initial, c_states, fw_workspace, workspace};
+  for (const void* p : ptrs) if (p && !aligned16(p)) return MLSTM_ERR_ALIGN;
+  bool use_sm100 = false;
+  if ((rc = resolve_impl(impl, B, NH, S, DHQK, DHHV, L, dtype, &use_sm100)) != MLSTM_OK) return rc;
+  ChunkwiseDims d{B, NH, S, DHQK, DHHV, L, S / L, variant, 1e-6f, 1.0f / sqrtf((float)DHQK)};
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  GateBuffers gb;
+  if (fw_workspace != nullptr) {   // the forward's gate vectors are still there: only abar and gbar are read
+    FwLayout fl = carve_fw(const_cast<void*>(fw_workspace), B * NH, S, d.NC, nullptr);
+    if (fw_workspace_bytes < fl.bytes) return MLSTM_ERR_WORKSPACE;
+    gb = fl.gb;
+  } else {
+    SumLayout lay = carve_summary(workspace, B * NH, S, d.NC);
+    if (workspace_bytes < lay.bytes) return MLSTM_ERR_WORKSPACE;
+    gb = lay.gb;
+    if ((rc = launch_gates(gate_dtype, i, f, variant == MLSTM_EXP ? m_initial : nullptr, nullptr, gb, lay.m_states, d, st)) != MLSTM_OK) return rc;
+  }
+  if (use_sm100) return sm100_recurrent_fw(k, v, gb, c_initial, nullptr, c_states, nullptr, nullptr, nullptr, d, st);
+  return simt_recurrent_fw(dtype, MLSTM_F32, k, v, gb, c_initial, nullptr, c_states, nullptr, nullptr, nullptr, d, st);
+}
+
 int mlstm_b200_chunkwise_summary(const void* k, const void* v, const void* i, const void* f, float* c_last,
                                  float* n_last, float* m_last, float* g_total, void* workspace,
                                  size_t workspace_bytes, int B, int NH, int S, int DHQK, int DHHV, int L, int dtype,
@@ -357,7 +393,7 @@ int mlstm_b200_chunkwise_summary(const void* k, const void* v, const void* i, co
   const void* ptrs[] = {k, v, i, f, c_last, n_last, m_last, g_total, workspace};
   for (const void* p : ptrs) if (p && !aligned16(p)) return MLSTM_ERR_ALIGN;
   bool use_sm100 = false;
-  if ((rc = resolve_impl(impl, S, DHQK, DHHV, L, dtype, &use_sm100)) != MLSTM_OK) return rc;
+  if ((rc = resolve_impl(impl, B, NH, S, DHQK, DHHV, L, dtype, &use_sm100)) != MLSTM_OK) return rc;
   ChunkwiseDims d{B, NH, S, DHQK, DHHV, L, S / L, variant, 1e-6f, 1.0f / sqrtf((float)DHQK)};
   SumLayout lay = carve_summary(workspace, B * NH, S, d.NC);
   if (workspace_bytes < lay.bytes) return MLSTM_ERR_WORKSPACE;
@@ -389,26 +425,28 @@ int mlstm_b200_state_combine(const float* c_in, const float* n_in, const float* 
 
 int mlstm_b200_step(const void* q, const void* k, const void* v, const void* i, const void* f, const void* c,
                     const void* n, const void* m, void* h, void* c_new, void* n_new, void* m_new, int B, int NH,
-                    int DHQK, int DHHV, int dtype, int state_dtype, float eps, void* stream) {
+                    int DHQK, int DHHV, int dtype, int gate_dtype, int state_dtype, float eps, void* stream) {
   if (B <= 0 || NH <= 0 || DHQK <= 0 || DHHV <= 0 || DHHV % 4 != 0) return MLSTM_ERR_SHAPE;
   if (!q || !k || !v || !i || !f || !c || !n || !m || !h || !c_new || !n_new || !m_new) return MLSTM_ERR_NULL;
   if (n_new == n || m_new == m) return MLSTM_ERR_UNSUPPORTED;
   const void* ptrs[] = {q, k, v, c, n, h, c_new, n_new};
   for (const void* p : ptrs) if (!aligned16(p)) return MLSTM_ERR_ALIGN;
   if (state_dtype != MLSTM_F32 && state_dtype != MLSTM_BF16) return MLSTM_ERR_DTYPE;
-  return launch_step(q, k, v, i, f, c, n, m, h, c_new, n_new, m_new, B, NH, DHQK, DHHV, dtype, state_dtype, eps,
+  if (gate_dtype != MLSTM_F32 && gate_dtype != MLSTM_BF16 && gate_dtype != MLSTM_F16) return MLSTM_ERR_DTYPE;
+  return launch_step(q, k, v, i, f, c, n, m, h, c_new, n_new, m_new, B, NH, DHQK, DHHV, dtype, gate_dtype, state_dtype, eps,
                      static_cast<cudaStream_t>(stream));
 }
 
 int mlstm_b200_step_sequence(const void* q, const void* k, const void* v, const void* i, const void* f,
                              const float* c, const float* n, const float* m, void* h, float* c_new, float* n_new,
-                             float* m_new, int B, int NH, int T, int DHQK, int DHHV, int dtype, float eps,
-                             void* stream) {
+                             float* m_new, int B, int NH, int T, int DHQK, int DHHV, int dtype, int gate_dtype,
+                             float eps, void* stream) {
   if (B <= 0 || NH <= 0 || T <= 0 || DHQK <= 0 || DHHV <= 0 || DHHV % 4 != 0 || DHQK > 512) return MLSTM_ERR_SHAPE;
   if (!q || !k || !v || !i || !f || !h || !c_new || !n_new || !m_new) return MLSTM_ERR_NULL;
   const void* ptrs[] = {q, k, v, c, h, c_new};
   for (const void* p : ptrs) if (p && !aligned16(p)) return MLSTM_ERR_ALIGN;
-  return launch_step_sequence(q, k, v, i, f, c, n, m, h, c_new, n_new, m_new, B, NH, T, DHQK, DHHV, dtype, eps,
+  if (gate_dtype != MLSTM_F32 && gate_dtype != MLSTM_BF16 && gate_dtype != MLSTM_F16) return MLSTM_ERR_DTYPE;
+  return launch_step_sequence(q, k, v, i, f, c, n, m, h, c_new, n_new, m_new, B, NH, T, DHQK, DHHV, dtype, gate_dtype, eps,
                               static_cast<cudaStream_t>(stream));
 }
 

@@ -20,7 +20,7 @@ constexpr int NTHR = 256;  // 16 x 16 threads, 4 x 4 outputs each
 // Inter-chunk recurrence.  state <- gbar * state + (left * lscale * lmul)^T (right * rscale)
 //   forward : left = K, lscale = abar, right = V;  also n <- gbar n + sum_j abar_j k_j
 //   backward: left = Q, lscale = bbar, lmul = qk_scale, right = deltaH, rscale = 1/(den+eps); chunks reversed
-// grid (ceil(DHHV/64), ceil(DHQK/64), B*NH)
+// grid (ceil(DHHV/64) * B*NH, ceil(DHQK/64))
 // =====================================================================================================
 template <typename T, typename TS, bool BWD>
 __global__ void __launch_bounds__(NTHR)
@@ -31,8 +31,10 @@ rec_kernel(const T* __restrict__ left, const T* __restrict__ right, const float*
   __shared__ float Ls[KSL][TILE + 1];
   __shared__ float Rs[KSL][TILE + 1];
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
-  const int e0 = blockIdx.x * TILE, d0 = blockIdx.y * TILE, bh = blockIdx.z;
-  const bool do_n = (!BWD) && (blockIdx.x == 0) && (n_states != nullptr || n_final != nullptr);
+  // grid (column tiles x batch x heads, row tiles): batch x heads sits in x, which has no 65535 limit
+  const int n_et = (DHHV + TILE - 1) / TILE, et = blockIdx.x % n_et;
+  const int e0 = et * TILE, d0 = blockIdx.y * TILE, bh = blockIdx.x / n_et;
+  const bool do_n = (!BWD) && (et == 0) && (n_states != nullptr || n_final != nullptr);
 
   float C[4][4];
 #pragma unroll
@@ -160,8 +162,11 @@ __global__ void __launch_bounds__(NTHR) par_kernel(ParArgs<T, TS> p) {
   float* s_n = s_qn + TILE;               // [32]
 
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
-  const int o0 = blockIdx.x * TILE, rb = blockIdx.y, r0 = rb * TILE;
-  const int bh = blockIdx.z / p.NC, ck = blockIdx.z % p.NC;
+  // grid (output tiles x chunks x batch x heads, row blocks): the large factor sits in x, which has no 65535 limit
+  const int n_ot = (((MODE == PAR_H || MODE == PAR_DV) ? p.DHHV : p.DHQK) + TILE - 1) / TILE;
+  const int ot = blockIdx.x % n_ot, bc = blockIdx.x / n_ot;
+  const int o0 = ot * TILE, rb = blockIdx.y, r0 = rb * TILE;
+  const int bh = bc / p.NC, ck = bc % p.NC;
   const size_t tok0 = (size_t)bh * p.S + (size_t)ck * L;
   constexpr bool LOWER = (MODE == PAR_H || MODE == PAR_DQ);
   const int DI = (MODE == PAR_H || MODE == PAR_DV) ? p.DHQK : p.DHHV;   // contraction dim of P
@@ -323,7 +328,7 @@ __global__ void __launch_bounds__(NTHR) par_kernel(ParArgs<T, TS> p) {
       const float nn = rowsum + p.qk_scale * p.bbar[tok0 + r] * qn;
       if (p.variant == MLSTM_EXP) den = fmaxf(fabsf(nn), expf(-s_m[r]));
       else if (p.variant == MLSTM_SIG) den = fmaxf(fabsf(nn), 1.f);
-      if (blockIdx.x == 0) p.n_out[tok0 + r] = den;
+      if (ot == 0) p.n_out[tok0 + r] = den;
     }
     s_row[tid] = den;
   }
@@ -357,7 +362,7 @@ template <typename T, typename TS>
 int rec_fw_t(const void* k, const void* v, const GateBuffers& gb, const float* c_initial, const float* n_initial,
              void* c_states, float* n_states, float* c_last, float* n_last, const ChunkwiseDims& d, cudaStream_t st) {
   PhaseScope ps(PH_REC_FW, st);
-  dim3 grid(ceil_div(d.DHHV, TILE), ceil_div(d.DHQK, TILE), d.B * d.NH);
+  dim3 grid(ceil_div(d.DHHV, TILE) * d.B * d.NH, ceil_div(d.DHQK, TILE));
   rec_kernel<T, TS, false><<<grid, NTHR, 0, st>>>((const T*)k, (const T*)v, gb.abar, 1.f, nullptr, gb.gbar, c_initial,
                                                   n_initial, (TS*)c_states, n_states, c_last, n_last, d.S, d.L, d.NC,
                                                   d.DHQK, d.DHHV);
@@ -368,7 +373,7 @@ template <typename T, typename TS>
 int rec_bw_t(const void* q, const void* dh, const GateBuffers& gb, const float* dc_last, void* dc_states,
              float* dc_initial, const ChunkwiseDims& d, cudaStream_t st) {
   PhaseScope ps(PH_REC_BW, st);
-  dim3 grid(ceil_div(d.DHHV, TILE), ceil_div(d.DHQK, TILE), d.B * d.NH);
+  dim3 grid(ceil_div(d.DHHV, TILE) * d.B * d.NH, ceil_div(d.DHQK, TILE));
   rec_kernel<T, TS, true><<<grid, NTHR, 0, st>>>((const T*)q, (const T*)dh, gb.bbar, d.qk_scale, gb.inv_den, gb.gbar,
                                                  dc_last, nullptr, (TS*)dc_states, nullptr, dc_initial, nullptr, d.S,
                                                  d.L, d.NC, d.DHQK, d.DHHV);
@@ -382,7 +387,7 @@ int par_launch(ParArgs<T, TS>& a, const ChunkwiseDims& d, cudaStream_t st) {
   const size_t smem = par_smem_bytes(d.L);
   auto kern = par_kernel<T, TS, MODE>;
   MLSTM_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  dim3 grid(ceil_div(DO, TILE), ceil_div(d.L, TILE), d.B * d.NH * d.NC);
+  dim3 grid(ceil_div(DO, TILE) * d.B * d.NH * d.NC, ceil_div(d.L, TILE));
   kern<<<grid, NTHR, smem, st>>>(a);
   MLSTM_LAUNCH_CHECK();
   return MLSTM_OK;

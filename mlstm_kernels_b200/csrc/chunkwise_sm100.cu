@@ -12,7 +12,7 @@
 //                    into the same TMEM tile first and row-scaled in place.  The L x L gate matrix never
 //                    leaves the SM.
 //                    fw_kernel_parallel.py:14-289, bw_kernel_parallel_dV.py, bw_kernel_parallel_dK.py, bw_kernel_parallel_dQ.py
-// Operands arrive by TMA (128-byte swizzle, no multicast) through a two-stage mbarrier ring; one warp produces,
+// Operands arrive by TMA (128-byte swizzle, no multicast) through mbarrier rings (four half-chunk stages in the recurrence, three stages in the intra-chunk kernels); one warp produces,
 // one thread issues the MMAs, the remaining warps do the element-wise work.  Every wait is bounded.
 #include "common.cuh"
 #include "launch.cuh"
@@ -67,16 +67,21 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
   constexpr int REC_STAGES = rec_stages(BWD);
   __shared__ uint64_t bar_full[REC_STAGES], bar_empty[REC_STAGES], bar_scaled[REC_STAGES], bar_acc_full[2], bar_acc_free[2], bar_nsum[2], bar_nread[2], bar_out_full[2], bar_out_free[2];
   __shared__ uint32_t s_tmem;
+  __shared__ int s_abort;   // set by the first wait of this CTA that runs out; every other wait polls it
   // per-row scale factors of the left tile, copied with the stage (backward: two factors per row)
   __shared__ __align__(16) float s_scale[REC_STAGES][REC_HALF], s_scale2[BWD ? REC_STAGES : 1][REC_HALF];
   __shared__ float s_g[8];          // decay of the chunk, ring of eight (outlives the operand ring)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int e0 = blockIdx.x * 128, d0 = blockIdx.y * 128, bh = blockIdx.z;
+  // 1-D grid (no 65535 limit on batch x heads), state tiles of one (batch, head) next to each other
+  const int n_et = p.DHHV / 128, n_dt = p.DHQK / 128;
+  const int et = blockIdx.x % n_et, dt = (blockIdx.x / n_et) % n_dt, bh = blockIdx.x / (n_et * n_dt);
+  const int e0 = et * 128, d0 = dt * 128;
   const int NC = p.NC, NH2 = 2 * p.NC;   // ring steps: two per chunk
-  const bool do_n = (!BWD) && blockIdx.x == 0 && (p.n_states != nullptr || p.n_final != nullptr);
+  const bool do_n = (!BWD) && et == 0 && (p.n_states != nullptr || p.n_final != nullptr);
 
   if (tid == 0) {
+    s_abort = 0;
     for (int s = 0; s < REC_STAGES; ++s) {
       mbar_init(&bar_full[s], 1); mbar_init(&bar_empty[s], 1); mbar_init(&bar_scaled[s], 256);
     }
@@ -112,7 +117,7 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
         if (lane == 0) s_g[s & 7] = g;   // read two or more barrier hand-overs later (MMA commit -> state warps)
       }
       int ok = 1;
-      if (lane == 0) ok = mbar_wait(&bar_empty[st], ((h / REC_STAGES) & 1) ^ 1, &g_sm100_status, 101) ? 1 : 0;
+      if (lane == 0) ok = mbar_wait(&bar_empty[st], ((h / REC_STAGES) & 1) ^ 1, &s_abort, &g_sm100_status, 101) ? 1 : 0;
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
       if (lane == 0) {
@@ -130,9 +135,8 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
       issued = h + 1;
     }
     if (lane == 0 && issued < NH2 && issued > 0) {  // error path: let the copies in flight land before the CTA retires
-      int dummy = 1;
       for (int h = max(0, issued - REC_STAGES); h < issued; ++h)
-        mbar_wait(&bar_full[h % REC_STAGES], (h / REC_STAGES) & 1, &dummy, 1);
+        mbar_wait(&bar_full[h % REC_STAGES], (h / REC_STAGES) & 1, nullptr, nullptr, 0);
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
@@ -140,8 +144,8 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
       constexpr uint32_t idesc = umma_idesc_bf16(128, 128, 1, 1);
       for (int h = 0; h < NH2; ++h) {
         const int st = h % REC_STAGES, s = h >> 1, buf = s & 1;
-        if (!mbar_wait(&bar_scaled[st], (h / REC_STAGES) & 1, &g_sm100_status, 102)) break;
-        if ((h & 1) == 0 && !mbar_wait(&bar_acc_free[buf], ((s >> 1) & 1) ^ 1, &g_sm100_status, 103)) break;
+        if (!mbar_wait(&bar_scaled[st], (h / REC_STAGES) & 1, &s_abort, &g_sm100_status, 102)) break;
+        if ((h & 1) == 0 && !mbar_wait(&bar_acc_free[buf], ((s >> 1) & 1) ^ 1, &s_abort, &g_sm100_status, 103)) break;
         tc_fence_after_sync();
         const uint32_t sl = smem_u32(smem + st * REC_STAGE_BYTES), sr = sl + 16384;
 #pragma unroll
@@ -159,7 +163,7 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
     float ns[2][8];
     for (int h = 0; h < NH2; ++h) {
       const int st = h % REC_STAGES, s = h >> 1, nb = s & 1;
-      if (!mbar_wait(&bar_full[st], (h / REC_STAGES) & 1, &g_sm100_status, 105)) { ok = false; break; }
+      if (!mbar_wait(&bar_full[st], (h / REC_STAGES) & 1, &s_abort, &g_sm100_status, 105)) { ok = false; break; }
       // two 64-column boxes of 64 rows x 128 B, 128-byte swizzle: the scale depends on the row only
       uint8_t* sl = smem + st * REC_STAGE_BYTES;
       if ((h & 1) == 0) {
@@ -188,7 +192,7 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
       float* npart = reinterpret_cast<float*>(smem + REC_STAGES * REC_STAGE_BYTES) + nb * (32 * 128);
       if (do_n && (h & 1)) {
         // the n warp has read the partial sums of chunk s - 2 out of this buffer
-        if (s >= 2 && !mbar_wait(&bar_nread[nb], ((s >> 1) - 1) & 1, &g_sm100_status, 109)) { ok = false; break; }
+        if (s >= 2 && !mbar_wait(&bar_nread[nb], ((s >> 1) - 1) & 1, &s_abort, &g_sm100_status, 109)) { ok = false; break; }
         const int lc = (ct & 7) ^ ((ct >> 3) & 7);   // logical 16-byte column chunk behind the swizzle
 #pragma unroll
         for (int b = 0; b < 2; ++b) {
@@ -207,7 +211,7 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
       uint8_t* stage_base = smem + REC_STAGES * REC_STAGE_BYTES + (BWD ? 0 : REC_NPART_BYTES);
       for (int n = 0; n <= NC; ++n) {
         const int ob = n & 1;
-        if (!mbar_wait(&bar_out_full[ob], (n >> 1) & 1, &g_sm100_status, 108)) break;
+        if (!mbar_wait(&bar_out_full[ob], (n >> 1) & 1, &s_abort, &g_sm100_status, 108)) break;
         const int slot = BWD ? NC - n : n;
         const int y = (bh * (NC + 1) + slot) * p.DHQK + d0;
         tma_store_2d(&mapS, stage_base + ob * 32768, e0, y);
@@ -230,7 +234,7 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
       bool ok = true;
       for (int s = 0; s < NC; ++s) {
         const int nb = s & 1;
-        if (!mbar_wait(&bar_nsum[nb], (s >> 1) & 1, &g_sm100_status, 106)) { ok = false; break; }
+        if (!mbar_wait(&bar_nsum[nb], (s >> 1) & 1, &s_abort, &g_sm100_status, 106)) { ok = false; break; }
         const float4* np4 = reinterpret_cast<const float4*>(smem + REC_STAGES * REC_STAGE_BYTES) + nb * (32 * 32) + lane;
         float4 cs = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 8
@@ -265,7 +269,7 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
     auto store_c = [&]() -> bool {
       if (p.c_states == nullptr) return true;
       const int ob = n_out & 1;
-      if (n_out >= 2 && !mbar_wait(&bar_out_free[ob], ((n_out >> 1) - 1) & 1, &g_sm100_status, 107)) return false;
+      if (n_out >= 2 && !mbar_wait(&bar_out_free[ob], ((n_out >> 1) - 1) & 1, &s_abort, &g_sm100_status, 107)) return false;
       uint8_t* rowp = stage_base + ob * 32768 + half * 16384 + row * 128;
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
@@ -282,7 +286,7 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
     bool ok = store_c();   // the state before the first step (slot 0 forward, slot NC backward)
     for (int s = 0; s < NC && ok; ++s) {
       const int buf = s & 1;
-      if (!mbar_wait(&bar_acc_full[buf], (s >> 1) & 1, &g_sm100_status, 104)) { ok = false; break; }
+      if (!mbar_wait(&bar_acc_full[buf], (s >> 1) & 1, &s_abort, &g_sm100_status, 104)) { ok = false; break; }
       tc_fence_after_sync();
       const float g = s_g[s & 7];
       const uint32_t ta = tmem + ((uint32_t)(quarter * 32) << 16) + buf * 128 + half * 64;
@@ -353,6 +357,7 @@ struct ParShared {
   uint64_t bar_full[PAR_NST], bar_empty[PAR_NST], bar_qdone[PAR_NST], bar_sfull, bar_afull, bar_gated, bar_hfull, bar_accfree, bar_done, bar_dot,
       bar_pair[4], bar_out;
   uint32_t tmem;
+  int abort;                       // set by the first wait of this CTA that runs out; every other wait polls it
   __align__(16) float s_colE[CL];  // per-column term of the gate exponent, base 2 (see par_body)
   __align__(16) float s_colF[CL];  // 2^(colE_c - colP of the column's 32-column block)
   float s_colP[4];                 // largest colE of each 32-column block
@@ -392,6 +397,7 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
   const bool use_n = (mode == PM_H) && p.variant != MLSTM_SIG_NONORM && p.n_states != nullptr;
 
   if (tid == 0) {
+    sh.abort = 0;
     for (int s = 0; s < PAR_NST; ++s) {
       mbar_init(&sh.bar_full[s], 1); mbar_init(&sh.bar_empty[s], 1); mbar_init(&sh.bar_qdone[s], 8);
     }
@@ -449,14 +455,14 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
           bool okw;
           if (pkind == LK_SCORE || pkind == LK_STATE || (pkind == LK_X && HAS_E)) {
             const int rm = st == 0 ? rm0 : (st == 1 ? rm1 : rm2);
-            okw = mbar_wait(&sh.bar_empty[st], (rm - 1) & 1, &g_sm100_status, 201);
+            okw = mbar_wait(&sh.bar_empty[st], (rm - 1) & 1, &sh.abort, &g_sm100_status, 201);
             // the element-wise warps read the A box of a score pair (q . n)
             if (okw && use_n && pkind == LK_SCORE) {
               const int rq = st == 0 ? rq0 : (st == 1 ? rq1 : rq2);
-              okw = mbar_wait(&sh.bar_qdone[st], (rq - 1) & 1, &g_sm100_status, 212);
+              okw = mbar_wait(&sh.bar_qdone[st], (rq - 1) & 1, &sh.abort, &g_sm100_status, 212);
             }
           } else {   // the staging buffer of a tile (its E stage, or its X stage in the modes without E) is handed
-            okw = mbar_wait(&sh.bar_done, psub & 1, &g_sm100_status, 215);   // back when the tile has been stored
+            okw = mbar_wait(&sh.bar_done, psub & 1, &sh.abort, &g_sm100_status, 215);   // back when the tile has been stored
           }
           if (!okw) break;
         }
@@ -487,9 +493,8 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
         if (++l == (sub == 0 ? n0 : n1)) { l = 0; ++sub; }
       }
       if (issued < n_loads && issued > 0) {  // error path: let the copies in flight land before the CTA retires
-        int dummy = 1;
         for (int ld = max(0, issued - PAR_NST); ld < issued; ++ld)
-          mbar_wait(&sh.bar_full[ld % PAR_NST], (ld / PAR_NST) & 1, &dummy, 1);
+          mbar_wait(&sh.bar_full[ld % PAR_NST], (ld / PAR_NST) & 1, nullptr, nullptr, 0);
       }
     }
   } else if (warp == 1) {
@@ -501,7 +506,7 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
       bool ok = true;
       for (int ld = 0; ld < ND; ++ld) {            // score: S = A . B^T
         const int st = ld % PAR_NST;
-        if (!mbar_wait(&sh.bar_full[st], (ld / PAR_NST) & 1, &g_sm100_status, 202)) { ok = false; break; }
+        if (!mbar_wait(&sh.bar_full[st], (ld / PAR_NST) & 1, &sh.abort, &g_sm100_status, 202)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t sa = smem_u32(smem + st * PAR_STAGE), sb = sa + 16384;
 #pragma unroll
@@ -514,11 +519,11 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
       for (int sub = 0; sub < nsub && ok; ++sub) {
         const int lbase = sub == 0 ? ND : n0 + (sub - 1) * n1;   // first state pair of this tile
         // the accumulator tile is free once the previous tile's epilogue has read it
-        if (sub > 0 && !mbar_wait(&sh.bar_accfree, (sub - 1) & 1, &g_sm100_status, 216)) { ok = false; break; }
+        if (sub > 0 && !mbar_wait(&sh.bar_accfree, (sub - 1) & 1, &sh.abort, &g_sm100_status, 216)) { ok = false; break; }
         if (sub > 0) tc_fence_after_sync();
         for (int it = 0; it < ND; ++it) {           // inter-chunk term: Acc = A . State
           const int ld = lbase + it, st = ld % PAR_NST;
-          if (!mbar_wait(&sh.bar_full[st], (ld / PAR_NST) & 1, &g_sm100_status, 213)) { ok = false; break; }
+          if (!mbar_wait(&sh.bar_full[st], (ld / PAR_NST) & 1, &sh.abort, &g_sm100_status, 213)) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t sa = smem_u32(smem + st * PAR_STAGE), ss = sa + 16384;
 #pragma unroll
@@ -531,8 +536,8 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
         if (!ok) break;
         umma_commit(&sh.bar_afull);
         const int ldx = lbase + ND, stx = ldx % PAR_NST;
-        ok = mbar_wait(&sh.bar_full[stx], (ldx / PAR_NST) & 1, &g_sm100_status, 203) &&
-             mbar_wait(&sh.bar_gated, sub & 1, &g_sm100_status, 204);
+        ok = mbar_wait(&sh.bar_full[stx], (ldx / PAR_NST) & 1, &sh.abort, &g_sm100_status, 203) &&
+             mbar_wait(&sh.bar_gated, sub & 1, &sh.abort, &g_sm100_status, 204);
         if (!ok) break;
         tc_fence_after_sync();
         const uint32_t sx = smem_u32(smem + stx * PAR_STAGE);
@@ -580,7 +585,7 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
     if (use_n) {
       for (int it = 0; it < ND && ok; ++it) {
         const int st = it % PAR_NST;
-        if (!mbar_wait(&sh.bar_full[st], (it / PAR_NST) & 1, &g_sm100_status, 207)) { ok = false; break; }
+        if (!mbar_wait(&sh.bar_full[st], (it / PAR_NST) & 1, &sh.abort, &g_sm100_status, 207)) { ok = false; break; }
         const uint8_t* rowp = smem + st * PAR_STAGE + r * 128;
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc) {
@@ -604,7 +609,7 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
 
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     float rowsum = 0.f;
-    ok = ok && mbar_wait(&sh.bar_sfull, 0, &g_sm100_status, 205);
+    ok = ok && mbar_wait(&sh.bar_sfull, 0, &sh.abort, &g_sm100_status, 205);
     if (ok) {
       tc_fence_after_sync();
       // Tensor memory is read 16 columns at a time, the next load in flight while the current one is processed.
@@ -667,7 +672,7 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
       // pair sync (bounded): both warps of the quarter have finished reading the score tile
       tc_fence_before_sync();
       mbar_arrive(&sh.bar_pair[quarter]);
-      ok = mbar_wait(&sh.bar_pair[quarter], 0, &g_sm100_status, 210);
+      ok = mbar_wait(&sh.bar_pair[quarter], 0, &sh.abort, &g_sm100_status, 210);
       if (ok) {
         tc_fence_after_sync();
 #pragma unroll
@@ -681,7 +686,7 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
     for (int sub = 0; sub < nsub && ok; ++sub) {
       const int o0 = o00 + 128 * sub;
       // the inter-chunk product of this tile has usually landed by now: row-scale it in place
-      if (!mbar_wait(&sh.bar_afull, sub & 1, &g_sm100_status, 214)) { ok = false; break; }
+      if (!mbar_wait(&sh.bar_afull, sub & 1, &sh.abort, &g_sm100_status, 214)) { ok = false; break; }
       tc_fence_after_sync();
 #pragma unroll 1
       for (int cq = half; cq < 4; cq += 2) {
@@ -701,7 +706,7 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(&sh.bar_gated);   // (first tile: the gated score tile is in place as well)
-      if (!mbar_wait(&sh.bar_hfull, sub & 1, &g_sm100_status, 206)) { ok = false; break; }
+      if (!mbar_wait(&sh.bar_hfull, sub & 1, &sh.abort, &g_sm100_status, 206)) { ok = false; break; }
       tc_fence_after_sync();
       if (sub == 0 && mode == PM_H) {
         float den = 1.f;
@@ -715,7 +720,7 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
       const uint8_t* erow = smem;
       if (HAS_E) {
         const int lde = ldx + 1, ste = lde % PAR_NST;
-        if (!mbar_wait(&sh.bar_full[ste], (lde / PAR_NST) & 1, &g_sm100_status, 208)) { ok = false; break; }
+        if (!mbar_wait(&sh.bar_full[ste], (lde / PAR_NST) & 1, &sh.abort, &g_sm100_status, 208)) { ok = false; break; }
         erow = smem + ste * PAR_STAGE + r * 128;
       }
       float dot4[4] = {0.f, 0.f, 0.f, 0.f};   // four partial sums: no 64-long chain of dependent FMAs
@@ -764,7 +769,7 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
       }
       const float dot = (dot4[0] + dot4[1]) + (dot4[2] + dot4[3]);
       mbar_arrive(&sh.bar_out);
-      if (!mbar_wait(&sh.bar_out, sub & 1, &g_sm100_status, 211)) { ok = false; break; }
+      if (!mbar_wait(&sh.bar_out, sub & 1, &sh.abort, &g_sm100_status, 211)) { ok = false; break; }
       {
         __nv_bfloat16* outp = (mode == PM_H) ? p.out_h : (mode == PM_DV) ? p.out_dv : (mode == PM_DK) ? p.out_dk : p.out_dq;
         uint8_t* gbase = reinterpret_cast<uint8_t*>(outp + (size_t)row0 * DO + o0);
@@ -780,7 +785,7 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
         sh.s_qn[half][r] = dot;
         mbar_arrive(&sh.bar_dot);
         if (half == 0) {
-          if (!mbar_wait(&sh.bar_dot, sub & 1, &g_sm100_status, 209)) { ok = false; break; }
+          if (!mbar_wait(&sh.bar_dot, sub & 1, &sh.abort, &g_sm100_status, 209)) { ok = false; break; }
           ((mode == PM_DQ) ? p.rowdot_q : p.rowdot_k)[(size_t)(o_tile0 + sub) * p.ntok + tok] = sh.s_qn[0][r] + sh.s_qn[1][r];
         }
       }
@@ -804,8 +809,11 @@ par_fw_sm100(const __grid_constant__ CUtensorMap mQ, const __grid_constant__ CUt
              const __grid_constant__ ParParams p) {
   __shared__ ParShared sh;
   const int T = p.DHHV / 128;                         // output tiles per chunk; a CTA takes up to PAR_MAXSUB of them
-  const int t0 = PAR_MAXSUB * blockIdx.x;
-  par_body(PM_H, &mQ, &mK, &mV, &mC, &mV, p, sh, t0, min(PAR_MAXSUB, T - t0), blockIdx.y, blockIdx.z);
+  // 1-D grid in the order (tile group, chunk, batch x head): no 65535 limit on chunks or batch x heads
+  const int gx = (T + PAR_MAXSUB - 1) / PAR_MAXSUB;
+  const int x = blockIdx.x % gx, ck = (blockIdx.x / gx) % p.NC, bh = blockIdx.x / (gx * p.NC);
+  const int t0 = PAR_MAXSUB * x;
+  par_body(PM_H, &mQ, &mK, &mV, &mC, &mV, p, sh, t0, min(PAR_MAXSUB, T - t0), ck, bh);
 }
 
 // deltaV, deltaK and deltaQ of one chunk in ONE launch: blockIdx.x enumerates the 128-wide output tiles of the three
@@ -820,13 +828,14 @@ par_bw_sm100(const __grid_constant__ CUtensorMap mQ, const __grid_constant__ CUt
   __shared__ ParShared sh;
   const int T_dv = p.DHHV / 128, T_dk = p.DHQK / 128;         // output tiles per chunk of dV, and of dK / dQ
   const int c_dv = (T_dv + PAR_MAXSUB - 1) / PAR_MAXSUB, c_dk = (T_dk + PAR_MAXSUB - 1) / PAR_MAXSUB;   // CTAs per mode
-  const int x = blockIdx.x;
+  const int gx = c_dv + 2 * c_dk;   // 1-D grid in the order (mode and tile group, chunk, batch x head)
+  const int x = blockIdx.x % gx, ck = (blockIdx.x / gx) % p.NC, bh = blockIdx.x / (gx * p.NC);
   int mode, pair, T;
   const CUtensorMap *a, *b, *xm, *stm, *e;
   if (x < c_dv) { mode = PM_DV; pair = x; T = T_dv; a = &mK; b = &mQ; xm = &mDH; stm = &mdC_mn; e = &mDH; }
   else if (x < c_dv + c_dk) { mode = PM_DK; pair = x - c_dv; T = T_dk; a = &mV; b = &mDH; xm = &mQ; stm = &mdC_k; e = &mK; }
   else { mode = PM_DQ; pair = x - c_dv - c_dk; T = T_dk; a = &mDH; b = &mV; xm = &mK; stm = &mC_k; e = &mQ; }
-  par_body(mode, a, b, xm, stm, e, p, sh, PAR_MAXSUB * pair, min(PAR_MAXSUB, T - PAR_MAXSUB * pair), blockIdx.y, blockIdx.z);
+  par_body(mode, a, b, xm, stm, e, p, sh, PAR_MAXSUB * pair, min(PAR_MAXSUB, T - PAR_MAXSUB * pair), ck, bh);
 }
 
 // =====================================================================================================
@@ -837,11 +846,57 @@ bool sm100_supported(int S, int DHQK, int DHHV, int L, int dtype) {
          DHHV <= 1024;
 }
 
+// The kernels address token rows and state rows with 32-bit TMA coordinates and use 1-D grids: both row counts and
+// every grid must stay below 2^31.
+bool sm100_sizes_ok(int B, int NH, int S, int DHQK, int DHHV) {
+  const uint64_t lim = 0x7fffffffull;
+  const uint64_t bnh = (uint64_t)B * NH, nc = (uint64_t)S / CL;
+  const uint64_t tiles = (uint64_t)(DHHV / 128 + 2 * (DHQK / 128));
+  return bnh * S < lim && bnh * (nc + 1) * DHQK < lim && bnh * nc * tiles < lim &&
+         bnh * (uint64_t)(DHHV / 128) * (DHQK / 128) < lim;
+}
+
+// cudaFuncSetAttribute once per kernel and device instead of on every call
+template <typename K>
+static int set_smem_once(K kern, int bytes, bool (&done)[64]) {
+  int dev = 0;
+  MLSTM_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64 || !done[dev]) {
+    MLSTM_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    if (dev >= 0 && dev < 64) done[dev] = true;
+  }
+  return MLSTM_OK;
+}
+
+// Tensor maps depend only on (base pointer, rows, columns, box): a training loop calls with the same buffers over
+// and over, so the last few encodings are kept per thread instead of calling the driver 3-7 times per launch.
+struct MapKey { const void* base; uint64_t rows, cols; uint32_t box_rows, box_cols; };
+static bool cached_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
+                       uint32_t box_cols) {
+  constexpr int N = 32;
+  static thread_local MapKey keys[N];
+  static thread_local CUtensorMap maps[N];
+  static thread_local int used = 0, next = 0;
+  for (int i = 0; i < used; ++i) {
+    const MapKey& k = keys[i];
+    if (k.base == base && k.rows == rows && k.cols == cols && k.box_rows == box_rows && k.box_cols == box_cols) {
+      *m = maps[i];
+      return true;
+    }
+  }
+  if (!sm100_host::make_map_bf16(m, base, rows, cols, box_rows, box_cols)) return false;
+  keys[next] = MapKey{base, rows, cols, box_rows, box_cols};
+  maps[next] = *m;
+  next = (next + 1) % N;
+  if (used < N) ++used;
+  return true;
+}
+
 static bool tok_map(CUtensorMap* m, const void* base, const ChunkwiseDims& d, int cols) {
-  return sm100_host::make_map_bf16(m, base, (uint64_t)d.B * d.NH * d.S, (uint64_t)cols, 128, 64);
+  return cached_map(m, base, (uint64_t)d.B * d.NH * d.S, (uint64_t)cols, 128, 64);
 }
 static bool state_map(CUtensorMap* m, const void* base, const ChunkwiseDims& d, int box_rows) {
-  return sm100_host::make_map_bf16(m, base, (uint64_t)d.B * d.NH * (d.NC + 1) * d.DHQK, (uint64_t)d.DHHV, box_rows, 64);
+  return cached_map(m, base, (uint64_t)d.B * d.NH * (d.NC + 1) * d.DHQK, (uint64_t)d.DHHV, box_rows, 64);
 }
 
 template <bool BWD>
@@ -849,14 +904,15 @@ static int launch_rec(const void* left, const void* right, const RecParams& rp, 
   CUtensorMap mL, mR, mS;
   // recurrence operands arrive in half-chunk boxes (64 tokens x 64 columns)
   const uint64_t ntok = (uint64_t)d.B * d.NH * d.S;
-  if (!sm100_host::make_map_bf16(&mL, left, ntok, (uint64_t)d.DHQK, REC_HALF, 64) ||
-      !sm100_host::make_map_bf16(&mR, right, ntok, (uint64_t)d.DHHV, REC_HALF, 64))
+  if (!cached_map(&mL, left, ntok, (uint64_t)d.DHQK, REC_HALF, 64) ||
+      !cached_map(&mR, right, ntok, (uint64_t)d.DHHV, REC_HALF, 64))
     return MLSTM_ERR_CUDA;
   // store map over the per-chunk states; when no states are wanted (segment summary) the map is never used
   if (!state_map(&mS, rp.c_states ? (const void*)rp.c_states : left, d, 128)) return MLSTM_ERR_CUDA;
   auto kern = rec_sm100<BWD>;
-  MLSTM_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, rec_smem_bytes(BWD)));
-  dim3 grid(d.DHHV / 128, d.DHQK / 128, d.B * d.NH);
+  static bool attr_done[64] = {};
+  if (int rc = set_smem_once(kern, rec_smem_bytes(BWD), attr_done)) return rc;
+  const unsigned grid = (unsigned)(d.DHHV / 128) * (unsigned)(d.DHQK / 128) * (unsigned)(d.B * d.NH);
   kern<<<grid, REC_THREADS, rec_smem_bytes(BWD), st>>>(mL, mR, mS, rp);
   MLSTM_LAUNCH_CHECK();
   return MLSTM_OK;
@@ -898,8 +954,10 @@ int sm100_parallel_fw(const void* q, const void* k, const void* v, const GateBuf
     return MLSTM_ERR_CUDA;
   ParParams pp = base_params(gb, d);
   pp.n_states = n_states; pp.out_h = (__nv_bfloat16*)h; pp.n_out = n_out;
-  MLSTM_CUDA_CHECK(cudaFuncSetAttribute(par_fw_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, PAR_SMEM));
-  dim3 grid((d.DHHV / 128 + PAR_MAXSUB - 1) / PAR_MAXSUB, d.NC, d.B * d.NH);   // up to PAR_MAXSUB output tiles per CTA
+  static bool attr_done[64] = {};
+  if (int rc = set_smem_once(par_fw_sm100, PAR_SMEM, attr_done)) return rc;
+  // up to PAR_MAXSUB output tiles per CTA
+  const unsigned grid = (unsigned)((d.DHHV / 128 + PAR_MAXSUB - 1) / PAR_MAXSUB) * (unsigned)d.NC * (unsigned)(d.B * d.NH);
   par_fw_sm100<<<grid, PAR_THREADS, PAR_SMEM, st>>>(mQ, mK, mV, mC, pp);
   MLSTM_LAUNCH_CHECK();
   return MLSTM_OK;
@@ -917,11 +975,41 @@ int sm100_parallel_bw(const void* q, const void* k, const void* v, const void* d
   ParParams pp = base_params(gb, d);
   pp.out_dv = (__nv_bfloat16*)dv; pp.out_dk = (__nv_bfloat16*)dk; pp.out_dq = (__nv_bfloat16*)dq;
   pp.rowdot_q = qdq_parts; pp.rowdot_k = kdk_parts;
-  MLSTM_CUDA_CHECK(cudaFuncSetAttribute(par_bw_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, PAR_SMEM));
-  dim3 grid((d.DHHV / 128 + PAR_MAXSUB - 1) / PAR_MAXSUB + 2 * ((d.DHQK / 128 + PAR_MAXSUB - 1) / PAR_MAXSUB), d.NC,
-            d.B * d.NH);   // up to PAR_MAXSUB output tiles per CTA
+  static bool attr_done[64] = {};
+  if (int rc = set_smem_once(par_bw_sm100, PAR_SMEM, attr_done)) return rc;
+  // up to PAR_MAXSUB output tiles per CTA
+  const unsigned grid = (unsigned)((d.DHHV / 128 + PAR_MAXSUB - 1) / PAR_MAXSUB + 2 * ((d.DHQK / 128 + PAR_MAXSUB - 1) / PAR_MAXSUB)) *
+                        (unsigned)d.NC * (unsigned)(d.B * d.NH);
   par_bw_sm100<<<grid, PAR_THREADS, PAR_SMEM, st>>>(mQ, mK, mV, mDH, mC_k, mdC_mn, mdC_k, pp);
   MLSTM_LAUNCH_CHECK();
+  return MLSTM_OK;
+}
+
+// Self-test of the bounded wait: one thread waits, for at most `limit` polls, on an mbarrier that nothing arrives
+// at.  No copy is in flight and no tensor memory is held, so giving up is all that happens: the wait records
+// `code` in the status word and the kernel returns.
+__global__ void wait_expiry_selftest_kernel(uint32_t limit, int code) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(&bar, 1);
+    fence_barrier_init();
+    mbar_wait(&bar, 0, &abort_flag, &g_sm100_status, code, limit);
+  }
+}
+
+int sm100_wait_expiry_selftest(unsigned limit, int code, cudaStream_t st) {
+  if (limit == 0 || limit > 1000000u || code <= 0) return MLSTM_ERR_UNSUPPORTED;   // a few milliseconds at most
+  wait_expiry_selftest_kernel<<<1, 32, 0, st>>>(limit, code);
+  MLSTM_LAUNCH_CHECK();
+  return MLSTM_OK;
+}
+
+int sm100_force_load() {
+  cudaFuncAttributes a;
+  MLSTM_CUDA_CHECK(cudaFuncGetAttributes(&a, rec_sm100<false>));
+  MLSTM_CUDA_CHECK(cudaFuncGetAttributes(&a, par_fw_sm100));
   return MLSTM_OK;
 }
 

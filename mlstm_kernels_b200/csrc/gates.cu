@@ -245,6 +245,16 @@ int launch_gates(int dtype, const void* i, const void* f, const float* m_initial
   return MLSTM_ERR_DTYPE;
 }
 
+int gates_force_load() {
+  cudaFuncAttributes a;
+  MLSTM_CUDA_CHECK(cudaFuncGetAttributes(&a, gates_chunk_kernel<float>));
+  MLSTM_CUDA_CHECK(cudaFuncGetAttributes(&a, gates_chunk_kernel<__nv_bfloat16>));
+  MLSTM_CUDA_CHECK(cudaFuncGetAttributes(&a, gates_chunk_kernel<__half>));
+  MLSTM_CUDA_CHECK(cudaFuncGetAttributes(&a, gates_scan_kernel));
+  MLSTM_CUDA_CHECK(cudaFuncGetAttributes(&a, gates_token_kernel));
+  return MLSTM_OK;
+}
+
 template <typename T>
 int launch_gate_grad_rows_t(const void* q, const void* k, const void* dq, const void* dk, float* acc, float* kdk,
                             const ChunkwiseDims& d, cudaStream_t st) {

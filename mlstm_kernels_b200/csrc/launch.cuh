@@ -32,8 +32,9 @@ int simt_parallel_bw(int dtype, int state_dtype, const void* q, const void* k, c
                      const GateBuffers& gb, const void* c_states, const void* dc_states, void* dq, void* dk, void* dv,
                      const ChunkwiseDims& d, cudaStream_t st);
 
-// chunkwise_sm100.cu : tcgen05 + TMA kernels (bf16, L = 128, head dims multiples of 64)
+// chunkwise_sm100.cu : tcgen05 + TMA kernels (bf16, L = 128, head dims multiples of 128)
 bool sm100_supported(int S, int DHQK, int DHHV, int L, int dtype);
+bool sm100_sizes_ok(int B, int NH, int S, int DHQK, int DHHV);
 int sm100_recurrent_fw(const void* k, const void* v, const GateBuffers& gb, const float* c_initial,
                        const float* n_initial, void* c_states, float* n_states, float* c_last, float* n_last,
                        const ChunkwiseDims& d, cudaStream_t st);
@@ -46,19 +47,17 @@ int sm100_parallel_bw(const void* q, const void* k, const void* v, const void* d
                       float* kdk_parts, const ChunkwiseDims& d, cudaStream_t st);
 
 int sm100_device_status(int reset, int* status);
-
-// chunkwise_fused_sm100.cu : forward with the inter-chunk state kept on chip
-bool sm100_fused_fw_supported(int B, int NH, int S, int DHQK, int DHHV, int L, int dtype);
-int sm100_fused_fw(const void* q, const void* k, const void* v, const GateBuffers& gb, const float* c_initial,
-                   const float* n_initial, void* h, float* n_out, void* c_states, float* n_states, float* c_last,
-                   float* n_last, const ChunkwiseDims& d, cudaStream_t st);
+int sm100_wait_expiry_selftest(unsigned limit, int code, cudaStream_t st);
+// make the runtime load the forward kernels' code on the current device now (CUDA loads modules lazily, on first use)
+int sm100_force_load();
+int gates_force_load();
 
 // step.cu
 int launch_step(const void* q, const void* k, const void* v, const void* i, const void* f, const void* c,
                 const void* n, const void* m, void* h, void* c_new, void* n_new, void* m_new, int B, int NH, int DHQK,
-                int DHHV, int dtype, int state_dtype, float eps, cudaStream_t st);
+                int DHHV, int dtype, int gate_dtype, int state_dtype, float eps, cudaStream_t st);
 int launch_step_sequence(const void* q, const void* k, const void* v, const void* i, const void* f, const float* c,
                          const float* n, const float* m, void* h, float* c_new, float* n_new, float* m_new, int B,
-                         int NH, int T, int DHQK, int DHHV, int dtype, float eps, cudaStream_t st);
+                         int NH, int T, int DHQK, int DHHV, int dtype, int gate_dtype, float eps, cudaStream_t st);
 
 }  // namespace mlstm

@@ -9,6 +9,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "launch.cuh"
 
 namespace {
 
@@ -35,11 +36,31 @@ int scratch_for_current_device(void** out) {
   return MLSTM_OK;
 }
 
+// The scratch address belongs to the CURRENT device; a stream of another device would make the kernels of that
+// device write through a pointer that means something else there.  Refuse the mismatch where the runtime can tell.
+int check_stream_on_current_device(void* stream) {
+  int cur = -1, sdev = -1;
+  MLSTM_CUDA_CHECK(cudaGetDevice(&cur));
+  if (cudaStreamGetDevice(static_cast<cudaStream_t>(stream), &sdev) != cudaSuccess) {
+    (void)cudaGetLastError();   // the query is unavailable for this stream: nothing to compare
+    return MLSTM_OK;
+  }
+  return sdev == cur ? MLSTM_OK : MLSTM_ERR_UNSUPPORTED;
+}
+
 }  // namespace
 
 extern "C" {
 
 size_t mlstm_b200_static_scratch_bytes(void) { return kStaticScratchBytes; }
+
+int mlstm_b200_static_warmup(void) {
+  void* scratch = nullptr;
+  int rc = scratch_for_current_device(&scratch);   // materialises the array on this device
+  if (rc != MLSTM_OK) return rc;
+  if ((rc = mlstm::gates_force_load()) != MLSTM_OK) return rc;
+  return mlstm::sm100_force_load();
+}
 
 int mlstm_b200_chunkwise_fw_static(const void* q, const void* k, const void* v, const void* i, const void* f,
                                    const float* c_initial, const float* n_initial, const float* m_initial, void* h,
@@ -51,8 +72,9 @@ int mlstm_b200_chunkwise_fw_static(const void* q, const void* k, const void* v, 
   if (need == 0) return MLSTM_ERR_SHAPE;
   if (need > kStaticScratchBytes) return MLSTM_ERR_WORKSPACE;  // problem too large for the built-in scratch
   void* scratch = nullptr;
-  const int rc = scratch_for_current_device(&scratch);
+  int rc = check_stream_on_current_device(stream);
   if (rc != MLSTM_OK) return rc;
+  if ((rc = scratch_for_current_device(&scratch)) != MLSTM_OK) return rc;
   // The forward writes every scratch word before it reads it, so nothing has to be cleared between calls.
   return mlstm_b200_chunkwise_fw(q, k, v, i, f, c_initial, n_initial, m_initial, h, n_out, m_out, c_states, n_states,
                                  m_states, c_last, n_last, m_last, scratch, kStaticScratchBytes, B, NH, S, DHQK, DHHV,

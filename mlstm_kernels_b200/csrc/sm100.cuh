@@ -32,16 +32,26 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait.  Returns false (and sets *err to `code` once) if the phase did not complete within the limit;
-// callers then stop issuing work and fall through to the common exit path.
+// Bounded wait.  Returns false if the phase did not complete within `limit` polls, or if another role of the same
+// CTA has already given up.  Two words are involved: `abort` is the CTA's own flag in shared memory (set on expiry,
+// polled by every other wait of the CTA so that all roles fall through to the common exit; nullptr = never abort
+// early, used where the CTA must wait for copies still in flight), `status` is the device-wide word the host reads:
+// it keeps the code of the FIRST wait that ran out and is never consulted by a kernel, so one expired wait does not
+// make later launches give up.
 constexpr uint32_t kWaitLimit = 20u * 1000u * 1000u;
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err, int code) {
-  for (uint32_t it = 0; it < kWaitLimit; ++it) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* abort, int* status, int code,
+                                          uint32_t limit = kWaitLimit) {
+  for (uint32_t it = 0; it < limit; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if (it > 64) __nanosleep(32);
-    if ((it & 1023) == 1023 && *(volatile int*)err != 0) return false;
+    if (abort != nullptr && (it & 1023) == 1023) {
+      uint32_t a;
+      asm volatile("ld.volatile.shared::cta.u32 %0, [%1];" : "=r"(a) : "r"(smem_u32(abort)) : "memory");
+      if (a != 0) return false;
+    }
   }
-  atomicCAS(err, 0, code);
+  if (abort != nullptr) asm volatile("st.volatile.shared::cta.u32 [%0], %1;" :: "r"(smem_u32(abort)), "r"(1u) : "memory");
+  if (status != nullptr) atomicCAS(status, 0, code);
   return false;
 }
 

@@ -37,12 +37,20 @@ template <> struct Vec4<__nv_bfloat16> {
   }
 };
 
+// The gate pre-activations keep their own element type (f32 gates next to bf16 q, k, v is the usual set-up) and are
+// widened to f32 before any arithmetic, as the reference does (fw_step_fused.py:88-94).
+__device__ __forceinline__ float load_gate(const void* p, size_t idx, int gate_dtype) {
+  if (gate_dtype == MLSTM_F32) return static_cast<const float*>(p)[idx];
+  if (gate_dtype == MLSTM_BF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[idx]);
+  return __half2float(static_cast<const __half*>(p)[idx]);
+}
+
 template <typename T, typename TS>
 __global__ void __launch_bounds__(STEP_THREADS)
-step_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, const T* __restrict__ gi,
-            const T* __restrict__ gf, const TS* __restrict__ c, const TS* __restrict__ n, const TS* __restrict__ m,
-            T* __restrict__ h, TS* __restrict__ c_new, TS* __restrict__ n_new, TS* __restrict__ m_new, int DHQK,
-            int DHHV, float eps) {
+step_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, const void* __restrict__ gi,
+            const void* __restrict__ gf, int gate_dtype, const TS* __restrict__ c, const TS* __restrict__ n,
+            const TS* __restrict__ m, T* __restrict__ h, TS* __restrict__ c_new, TS* __restrict__ n_new,
+            TS* __restrict__ m_new, int DHQK, int DHHV, float eps) {
   extern __shared__ float sm[];
   float* s_q = sm;             // [DHQK] scaled q
   float* s_k = s_q + DHQK;     // [DHQK] ibar * k
@@ -55,8 +63,8 @@ step_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restric
   const int cgi = tid % STEP_CG, rg = tid / STEP_CG;
   const int e = e0 + cgi * 4;
 
-  const float lf = logsigmoid_f(to_f32(gf[bh]));
-  const float iv = to_f32(gi[bh]);
+  const float lf = logsigmoid_f(load_gate(gf, bh, gate_dtype));
+  const float iv = load_gate(gi, bh, gate_dtype);
   const float m_old = to_f32(m[bh]);
   const float m_n = fmaxf(lf + m_old, iv);
   const float fbar = expf(lf + m_old - m_n);
@@ -144,7 +152,7 @@ step_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restric
 template <typename T, int ROWS>
 __global__ void __launch_bounds__(STEP_THREADS)
 step_sequence_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
-                     const T* __restrict__ gi, const T* __restrict__ gf, const float* __restrict__ c,
+                     const void* __restrict__ gi, const void* __restrict__ gf, int gate_dtype, const float* __restrict__ c,
                      const float* __restrict__ n, const float* __restrict__ m, T* __restrict__ h,
                      float* __restrict__ c_new, float* __restrict__ n_new, float* __restrict__ m_new, int Tn, int DHQK,
                      int DHHV, float eps) {
@@ -175,8 +183,8 @@ step_sequence_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* 
 
   for (int t = 0; t < Tn; ++t) {
     const size_t tok = (size_t)bh * Tn + t;
-    const float lf = logsigmoid_f(to_f32(gf[tok]));
-    const float iv = to_f32(gi[tok]);
+    const float lf = logsigmoid_f(load_gate(gf, tok, gate_dtype));
+    const float iv = load_gate(gi, tok, gate_dtype);
     const float m_n = fmaxf(lf + m_run, iv);
     const float fbar = expf(lf + m_run - m_n);
     const float ibar = expf(iv - m_n);
@@ -245,15 +253,15 @@ step_sequence_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* 
 
 // ---- launchers ----------------------------------------------------------------------------------------
 template <typename T, typename TS>
-int step_t(const void* q, const void* k, const void* v, const void* i, const void* f, const void* c, const void* n,
-           const void* m, void* h, void* c_new, void* n_new, void* m_new, int B, int NH, int DHQK, int DHHV, float eps,
-           cudaStream_t st) {
+int step_t(const void* q, const void* k, const void* v, const void* i, const void* f, int gate_dtype, const void* c,
+           const void* n, const void* m, void* h, void* c_new, void* n_new, void* m_new, int B, int NH, int DHQK,
+           int DHHV, float eps, cudaStream_t st) {
   PhaseScope ps(PH_STEP, st);
   dim3 grid(ceil_div(DHHV, STEP_TV), B * NH);
   const size_t smem = sizeof(float) * (2 * (size_t)DHQK + (STEP_THREADS / 32) * STEP_TV);
   auto kern = step_kernel<T, TS>;
   if (smem > 48 * 1024) MLSTM_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<grid, STEP_THREADS, smem, st>>>((const T*)q, (const T*)k, (const T*)v, (const T*)i, (const T*)f,
+  kern<<<grid, STEP_THREADS, smem, st>>>((const T*)q, (const T*)k, (const T*)v, i, f, gate_dtype,
                                          (const TS*)c, (const TS*)n, (const TS*)m, (T*)h, (TS*)c_new, (TS*)n_new,
                                          (TS*)m_new, DHQK, DHHV, eps);
   MLSTM_LAUNCH_CHECK();
@@ -262,9 +270,9 @@ int step_t(const void* q, const void* k, const void* v, const void* i, const voi
 
 int launch_step(const void* q, const void* k, const void* v, const void* i, const void* f, const void* c,
                 const void* n, const void* m, void* h, void* c_new, void* n_new, void* m_new, int B, int NH, int DHQK,
-                int DHHV, int dtype, int state_dtype, float eps, cudaStream_t st) {
+                int DHHV, int dtype, int gate_dtype, int state_dtype, float eps, cudaStream_t st) {
 #define STEP_CASE(DT, T, SDT, TS) \
-  if (dtype == DT && state_dtype == SDT) return step_t<T, TS>(q, k, v, i, f, c, n, m, h, c_new, n_new, m_new, B, NH, DHQK, DHHV, eps, st);
+  if (dtype == DT && state_dtype == SDT) return step_t<T, TS>(q, k, v, i, f, gate_dtype, c, n, m, h, c_new, n_new, m_new, B, NH, DHQK, DHHV, eps, st);
   STEP_CASE(MLSTM_F32, float, MLSTM_F32, float)
   STEP_CASE(MLSTM_BF16, __nv_bfloat16, MLSTM_F32, float)
   STEP_CASE(MLSTM_F16, __half, MLSTM_F32, float)
@@ -276,26 +284,26 @@ int launch_step(const void* q, const void* k, const void* v, const void* i, cons
 }
 
 template <typename T, int ROWS>
-int step_seq_t(const void* q, const void* k, const void* v, const void* i, const void* f, const float* c,
+int step_seq_t(const void* q, const void* k, const void* v, const void* i, const void* f, int gate_dtype, const float* c,
                const float* n, const float* m, void* h, float* c_new, float* n_new, float* m_new, int B, int NH, int Tn,
                int DHQK, int DHHV, float eps, cudaStream_t st) {
   dim3 grid(ceil_div(DHHV, STEP_TV), B * NH);
   const size_t smem = sizeof(float) * (3 * (size_t)DHQK + (STEP_THREADS / 32) * STEP_TV);
   auto kern = step_sequence_kernel<T, ROWS>;
   if (smem > 48 * 1024) MLSTM_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<grid, STEP_THREADS, smem, st>>>((const T*)q, (const T*)k, (const T*)v, (const T*)i, (const T*)f, c, n, m,
+  kern<<<grid, STEP_THREADS, smem, st>>>((const T*)q, (const T*)k, (const T*)v, i, f, gate_dtype, c, n, m,
                                          (T*)h, c_new, n_new, m_new, Tn, DHQK, DHHV, eps);
   MLSTM_LAUNCH_CHECK();
   return MLSTM_OK;
 }
 
 template <typename T>
-int step_seq_rows(const void* q, const void* k, const void* v, const void* i, const void* f, const float* c,
-                  const float* n, const float* m, void* h, float* c_new, float* n_new, float* m_new, int B, int NH,
-                  int Tn, int DHQK, int DHHV, float eps, cudaStream_t st) {
+int step_seq_rows(const void* q, const void* k, const void* v, const void* i, const void* f, int gate_dtype,
+                  const float* c, const float* n, const float* m, void* h, float* c_new, float* n_new, float* m_new,
+                  int B, int NH, int Tn, int DHQK, int DHHV, float eps, cudaStream_t st) {
   const int rows = ceil_div(DHQK, STEP_RG);
 #define SEQ_CASE(R) \
-  if (rows <= R) return step_seq_t<T, R>(q, k, v, i, f, c, n, m, h, c_new, n_new, m_new, B, NH, Tn, DHQK, DHHV, eps, st);
+  if (rows <= R) return step_seq_t<T, R>(q, k, v, i, f, gate_dtype, c, n, m, h, c_new, n_new, m_new, B, NH, Tn, DHQK, DHHV, eps, st);
   SEQ_CASE(4) SEQ_CASE(8) SEQ_CASE(16) SEQ_CASE(32)
 #undef SEQ_CASE
   return MLSTM_ERR_SHAPE;
@@ -303,11 +311,11 @@ int step_seq_rows(const void* q, const void* k, const void* v, const void* i, co
 
 int launch_step_sequence(const void* q, const void* k, const void* v, const void* i, const void* f, const float* c,
                          const float* n, const float* m, void* h, float* c_new, float* n_new, float* m_new, int B,
-                         int NH, int T, int DHQK, int DHHV, int dtype, float eps, cudaStream_t st) {
+                         int NH, int T, int DHQK, int DHHV, int dtype, int gate_dtype, float eps, cudaStream_t st) {
   switch (dtype) {
-    case MLSTM_F32: return step_seq_rows<float>(q, k, v, i, f, c, n, m, h, c_new, n_new, m_new, B, NH, T, DHQK, DHHV, eps, st);
-    case MLSTM_BF16: return step_seq_rows<__nv_bfloat16>(q, k, v, i, f, c, n, m, h, c_new, n_new, m_new, B, NH, T, DHQK, DHHV, eps, st);
-    case MLSTM_F16: return step_seq_rows<__half>(q, k, v, i, f, c, n, m, h, c_new, n_new, m_new, B, NH, T, DHQK, DHHV, eps, st);
+    case MLSTM_F32: return step_seq_rows<float>(q, k, v, i, f, gate_dtype, c, n, m, h, c_new, n_new, m_new, B, NH, T, DHQK, DHHV, eps, st);
+    case MLSTM_BF16: return step_seq_rows<__nv_bfloat16>(q, k, v, i, f, gate_dtype, c, n, m, h, c_new, n_new, m_new, B, NH, T, DHQK, DHHV, eps, st);
+    case MLSTM_F16: return step_seq_rows<__half>(q, k, v, i, f, gate_dtype, c, n, m, h, c_new, n_new, m_new, B, NH, T, DHQK, DHHV, eps, st);
   }
   return MLSTM_ERR_DTYPE;
 }

@@ -2,13 +2,37 @@
 
 `mlstm_recurrent_step__b200` keeps the signature of mlstm_recurrent_step__triton
 (mlstm_kernels/torch/recurrent/triton_step.py:130-158); `mlstm_recurrent_sequence__b200` that of the
-sequence kernels (mlstm_kernels/torch/recurrent/native_sequence.py:125-170)."""
+sequence kernels (mlstm_kernels/torch/recurrent/native_sequence.py:125-170).
+
+A decode step at small batch is a few microseconds of device time, so the host side of the step is written
+to do as little as possible: tensors that already have the expected element type and layout are passed
+through untouched (no `.to()`, no `.contiguous()`), the gate pre-activations keep their own element type
+(the kernel widens them to f32, as mlstm_kernels/triton/recurrent/fw_step_fused.py:88-94 does), and the
+device guard is skipped when the tensors' device is already current.
+"""
 
 from __future__ import annotations
+
+import ctypes as C
 
 import torch
 
 from . import _lib
+
+_STATE_DTYPES = (torch.float32, torch.bfloat16)
+
+
+def _conform(t: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    if t.dtype is not dtype:
+        t = t.to(dtype)
+    return t if t.is_contiguous() else t.contiguous()
+
+
+def _gate(t: torch.Tensor) -> torch.Tensor:
+    """Gate pre-activations in one of the kernel's gate element types, contiguous."""
+    if t.dtype not in _lib._DTYPE_CODE:
+        t = t.to(torch.float32)
+    return t if t.is_contiguous() else t.contiguous()
 
 
 def mlstm_recurrent_step__b200_fw(
@@ -25,9 +49,11 @@ def mlstm_recurrent_step__b200_fw(
     scaM_new: torch.Tensor = None,
     eps: float = 1e-6,
     dtype_state: torch.dtype = torch.float32,
+    vecH_out: torch.Tensor = None,  # optional caller-owned output (B, NH, DHHV) in q's dtype
     **kwargs,
 ):
-    _lib.require_cuda(matC_old, vecN_old, scaM_old, vecQ, vecK, vecV, scaI, scaF)
+    if not (vecQ.is_cuda and matC_old.is_cuda):
+        raise RuntimeError("mlstm_kernels_b200 kernels run on CUDA tensors only (there is no CPU fallback)")
     lib = _lib.load()
     B, NH, DHQK = vecQ.shape
     DHHV = vecV.shape[-1]
@@ -37,29 +63,42 @@ def mlstm_recurrent_step__b200_fw(
     assert scaM_old.shape == (B, NH, 1), f"scaM_old has wrong shape, got {scaM_old.shape}"
     assert scaI.shape == (B, NH, 1), f"scaI has wrong shape, got {scaI.shape}"
     assert scaF.shape == (B, NH, 1), f"scaF has wrong shape, got {scaF.shape}"
-    if dtype_state not in (torch.float32, torch.bfloat16):
+    if dtype_state not in _STATE_DTYPES:
         raise ValueError(f"Unsupported state dtype {dtype_state}.")
-    dt = _lib.dtype_code(vecQ.dtype)
-    q, k, v = vecQ.contiguous(), vecK.to(vecQ.dtype).contiguous(), vecV.to(vecQ.dtype).contiguous()
-    gi, gf = scaI.to(vecQ.dtype).contiguous(), scaF.to(vecQ.dtype).contiguous()
-    c, n, m = (t.to(dtype_state).contiguous() for t in (matC_old, vecN_old, scaM_old))
+    qdt = vecQ.dtype
+    dt = _lib.dtype_code(qdt)
+    q = vecQ if vecQ.is_contiguous() else vecQ.contiguous()
+    k, v = _conform(vecK, qdt), _conform(vecV, qdt)
+    gi = _gate(scaI)
+    gf = _gate(scaF) if scaF.dtype is gi.dtype else _conform(scaF, gi.dtype)
+    c, n, m = _conform(matC_old, dtype_state), _conform(vecN_old, dtype_state), _conform(scaM_old, dtype_state)
     if matC_new is None:
         assert vecN_new is None and scaM_new is None, "Initial states must be provided together."
         matC_new, vecN_new, scaM_new = torch.empty_like(c), torch.empty_like(n), torch.empty_like(m)
     else:
         assert vecN_new is not None and scaM_new is not None, "Initial states must be provided together."
         for t in (matC_new, vecN_new, scaM_new):
-            if t.dtype != dtype_state or not t.is_contiguous():
+            if t.dtype is not dtype_state or not t.is_contiguous():
                 raise ValueError("output state tensors must be contiguous and of dtype_state")
-    h = torch.empty_like(v)
+    if vecH_out is None:
+        h = torch.empty_like(v)
+    else:
+        h = vecH_out
+        if h.dtype is not qdt or h.shape != v.shape or not h.is_contiguous():
+            raise ValueError("vecH_out must be a contiguous (B, NH, DHHV) tensor of q's dtype")
     dev = q.device
-    with torch.cuda.device(dev):
-        rc = lib.mlstm_b200_step(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(gi), _lib.ptr(gf),
-                                 _lib.ptr(c), _lib.ptr(n), _lib.ptr(m), _lib.ptr(h),
-                                 _lib.ptr(matC_new), _lib.ptr(vecN_new), _lib.ptr(scaM_new),
-                                 B, NH, DHQK, DHHV, dt, _lib.dtype_code(dtype_state), float(eps),
-                                 _lib.stream_handle(dev))
-    _lib.check(rc, "mlstm_b200_step")
+    VP = C.c_void_p
+    args = (VP(q.data_ptr()), VP(k.data_ptr()), VP(v.data_ptr()), VP(gi.data_ptr()), VP(gf.data_ptr()),
+            VP(c.data_ptr()), VP(n.data_ptr()), VP(m.data_ptr()), VP(h.data_ptr()),
+            VP(matC_new.data_ptr()), VP(vecN_new.data_ptr()), VP(scaM_new.data_ptr()),
+            B, NH, DHQK, DHHV, dt, _lib._DTYPE_CODE[gi.dtype], _lib._DTYPE_CODE[dtype_state], eps)
+    if torch.cuda.current_device() == dev.index:
+        rc = lib.mlstm_b200_step(*args, VP(torch.cuda.current_stream().cuda_stream))
+    else:
+        with torch.cuda.device(dev):
+            rc = lib.mlstm_b200_step(*args, VP(torch.cuda.current_stream(dev).cuda_stream))
+    if rc != 0:
+        _lib.check(rc, "mlstm_b200_step")
     return h, (matC_new, vecN_new, scaM_new)
 
 
@@ -101,8 +140,9 @@ def mlstm_recurrent_sequence__b200(
     B, NH, S, DHQK = q.shape
     DHHV = v.shape[-1]
     dt = _lib.dtype_code(q.dtype)
-    q, k, v = q.contiguous(), k.to(q.dtype).contiguous(), v.to(q.dtype).contiguous()
-    gi, gf = i.to(q.dtype).contiguous(), f.to(q.dtype).contiguous()
+    q, k, v = q.contiguous(), _conform(k, q.dtype), _conform(v, q.dtype)
+    gi = _gate(i)
+    gf = _conform(f, gi.dtype)
     f32 = lambda t: None if t is None else t.to(torch.float32).contiguous()  # noqa: E731
     c0, n0, m0 = f32(c_initial), f32(n_initial), f32(m_initial)
     dev = q.device
@@ -114,7 +154,8 @@ def mlstm_recurrent_sequence__b200(
         rc = lib.mlstm_b200_step_sequence(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(gi), _lib.ptr(gf),
                                           _lib.ptr(c0), _lib.ptr(n0), _lib.ptr(m0), _lib.ptr(h),
                                           _lib.ptr(c_new), _lib.ptr(n_new), _lib.ptr(m_new),
-                                          B, NH, S, DHQK, DHHV, dt, float(eps), _lib.stream_handle(dev))
+                                          B, NH, S, DHQK, DHHV, dt, _lib.dtype_code(gi.dtype), float(eps),
+                                          _lib.stream_handle(dev))
     _lib.check(rc, "mlstm_b200_step_sequence")
     if return_last_states:
         return h, (c_new.to(dtype_state), n_new.to(dtype_state), m_new.to(dtype_state))

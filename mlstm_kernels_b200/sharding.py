@@ -9,8 +9,8 @@ c_initial / n_initial / m_initial in, last states out: mlstm_kernels/torch/kerne
 * sequence-parallel prefill of one long sequence (`mlstm_chunkwise_sequence_parallel`): rank r holds the
   r-th contiguous segment of the sequence.  "scan" mode: (1) all ranks compute, concurrently, the state
   their segment produces from the empty state; (2) the boundary state travels along the chain
-  rank 0 -> 1 -> ... with one point-to-point message per boundary (NCCL send/recv, i.e. NVLink between
-  GPUs of a node), each rank folding its summary onto the incoming state; (3) all ranks run the full
+  rank 0 -> 1 -> ... with one point-to-point message per boundary ((C, n, m) packed into one buffer; NCCL
+  send/recv, i.e. NVLink between GPUs of a node), each rank folding its summary onto the incoming state; (3) all ranks run the full
   forward of their segment, concurrently, from the true incoming state.  "chain" mode is the plain
   serial hand-off (segment r starts when r-1 has finished its recurrence).  Both reproduce the
   single-GPU (C, n, m) path.
@@ -163,10 +163,9 @@ class _SequenceParallelFn(torch.autograd.Function):
         DHHV = v.shape[-1]
         dc_last, tail = None, None
         if next_rank is not None:   # gradient of the state handed to rank r+1, and the sum over all later tokens
-            dc_last = torch.empty((B, NH, DHQK, DHHV), dtype=torch.float32, device=q.device)
-            tail = torch.empty((B, NH), dtype=torch.float32, device=q.device)
-            dist.recv(dc_last, src=next_rank, group=group)
-            dist.recv(tail, src=next_rank, group=group)
+            like = (torch.empty((B, NH, DHQK, DHHV), dtype=torch.float32, device=q.device),
+                    torch.empty((B, NH), dtype=torch.float32, device=q.device))
+            dc_last, tail = _recv_state(like, next_rank, group)
         dq, dk, dv, di, df, dc0 = _segment_backward(q, k, v, i, f, ctx.saved, dh.contiguous(), dc_last,
                                                     chunk_size=opts["L"], eps=opts["eps"], variant=opts["variant"],
                                                     impl=opts["impl"])
@@ -177,21 +176,32 @@ class _SequenceParallelFn(torch.autograd.Function):
         if tail is not None:
             df = df + torch.sigmoid(-f.float()) * tail[..., None]
         if prev_rank is not None:
-            dist.send(dc0.contiguous(), dst=prev_rank, group=group)
-            dist.send(total.contiguous(), dst=prev_rank, group=group)
+            _send_state((dc0, total), prev_rank, group)
         return dq, dk, dv, di.to(i.dtype), df.to(f.dtype), None, None
 
 
+def _pack(tensors):
+    """One flat f32 buffer holding the given tensors back to back (one message per hop instead of one per tensor)."""
+    return torch.cat([t.reshape(-1).to(torch.float32) for t in tensors])
+
+
+def _unpack(flat, like):
+    out, off = [], 0
+    for t in like:
+        n = t.numel()
+        out.append(flat[off:off + n].view(t.shape))
+        off += n
+    return tuple(out)
+
+
 def _send_state(state, dst, group):
-    for t in state:
-        dist.send(t.contiguous(), dst=dst, group=group)
+    dist.send(_pack(state), dst=dst, group=group)
 
 
 def _recv_state(like, src, group):
-    out = tuple(torch.empty_like(t) for t in like)
-    for t in out:
-        dist.recv(t, src=src, group=group)
-    return out
+    flat = torch.empty(sum(t.numel() for t in like), dtype=torch.float32, device=like[0].device)
+    dist.recv(flat, src=src, group=group)
+    return _unpack(flat, like)
 
 
 def mlstm_chunkwise_sequence_parallel(

@@ -82,6 +82,32 @@ def run_sig_parallel(case):
     return {n: x.detach().numpy().astype(np.float32) for n, x in out.items()}
 
 
+def run_sig_states(case):
+    """Final mLSTMsig state (C_last, n_last) out of the reference's quadratic implementation, which returns H only.
+    DHQK probe tokens are appended to the sequence: probe d has q = e_d / qk_scale, k = 0, v = 0 and a forget logit of
+    +40 (logsigmoid = 0 in f32), so it adds nothing to the state, nothing decays, and its un-normalised output row is
+    H_probe[d, :] = sum_j exp(sum_{t>j} logsigmoid f_t + logsigmoid i_j) k_j[d] v_j = C_last[d, :].  A second run with
+    every v set to ones gives n_last[d] in every output column."""
+    from mlstm_kernels.torch.parallel.native_siging.fwbw import mlstm_siging_parallel__native_custbw
+
+    inp = make_chunkwise_inputs(case)
+    B, NH, S, DHQK = inp["q"].shape
+    DHHV = inp["v"].shape[-1]
+    probe_q = np.broadcast_to((np.eye(DHQK) * np.sqrt(DHQK)).astype(np.float32), (B, NH, DHQK, DHQK))
+    q = np.concatenate([inp["q"], probe_q], 2)
+    k = np.concatenate([inp["k"], np.zeros((B, NH, DHQK, DHQK), np.float32)], 2)
+    v = np.concatenate([inp["v"], np.zeros((B, NH, DHQK, DHHV), np.float32)], 2)
+    i = np.concatenate([inp["i"], np.zeros((B, NH, DHQK), np.float32)], 2)
+    f = np.concatenate([inp["f"], np.full((B, NH, DHQK), 40.0, np.float32)], 2)
+    with torch.no_grad():
+        H = mlstm_siging_parallel__native_custbw(t(q), t(k), t(v), t(i), t(f), eps=1e-6, stable_fgate=True,
+                                                 normalize=False)
+        Hn = mlstm_siging_parallel__native_custbw(t(q), t(k), t(np.ones_like(v)), t(i), t(f), eps=1e-6,
+                                                  stable_fgate=True, normalize=False)
+    out = dict(C_last=H[:, :, S:], n_last=Hn[:, :, S:, 0])
+    return {n_: x.detach().numpy().astype(np.float32) for n_, x in out.items()}
+
+
 def run_step(case):
     from mlstm_kernels.torch.recurrent.native_step import mlstm_recurrent_step__native
 
@@ -97,7 +123,7 @@ def run_step(case):
 
 
 RUNNERS = dict(exp_chunkwise=run_exp_chunkwise, exp_parallel=run_exp_parallel, sig_parallel=run_sig_parallel,
-               step=run_step)
+               sig_states=run_sig_states, step=run_step)
 
 
 def main():

@@ -29,6 +29,8 @@ CASES = {
                      normalize=True),
     "sig_nonorm": dict(kind="sig_parallel", seed=4, B=1, NH=2, S=256, DHQK=64, DHHV=128, L=64, f_offset=3.0,
                        normalize=False),
+    # mLSTMsig final states (C, n) read out of the reference's quadratic implementation with probe tokens
+    "sig_states": dict(kind="sig_states", seed=6, B=1, NH=2, S=256, DHQK=64, DHHV=128, L=64, f_offset=3.0),
     # decode: 4 chained steps
     "step_small": dict(kind="step", seed=5, B=2, NH=4, DHQK=64, DHHV=128, steps=4, f_offset=3.0),
 }
@@ -79,3 +81,14 @@ def max_rel_err(a: np.ndarray, b: np.ndarray) -> float:
     """max |a-b| / max |b|: the normalised maximum error used for the stated tolerances."""
     a = np.asarray(a, np.float64); b = np.asarray(b, np.float64)
     return float(np.abs(a - b).max() / max(np.abs(b).max(), 1e-30))
+
+
+def elementwise_ok_fraction(a: np.ndarray, b: np.ndarray, rtol: float, atol: float) -> float:
+    """Fraction of elements with |a - b| <= rtol * |b| + atol."""
+    a = np.asarray(a, np.float64); b = np.asarray(b, np.float64)
+    return float(np.mean(np.abs(a - b) <= rtol * np.abs(b) + atol))
+
+
+def rms(x: np.ndarray) -> float:
+    x = np.asarray(x, np.float64)
+    return float(np.sqrt(np.mean(x * x)))

@@ -36,10 +36,14 @@ def test_error_strings_and_argument_validation():
     assert lib.mlstm_b200_chunkwise_workspace_bytes(1, 1, 100, 64, 64, 64, 0, 0, 0, 0) == 0
     assert lib.mlstm_b200_chunkwise_workspace_bytes(1, 1, 96, 64, 64, 48, 0, 0, 0, 0) == 0
     assert lib.mlstm_b200_chunkwise_workspace_bytes(2, 4, 512, 128, 256, 64, 0, 0, 0, 0) > 0
+    # sizes whose grids or 32-bit row coordinates would overflow are refused, not launched
+    assert lib.mlstm_b200_chunkwise_workspace_bytes(65536, 64, 1 << 20, 128, 128, 128, 1, 0, 0, 0) == 0
+    # the removed implementation code is rejected
+    assert lib.mlstm_b200_chunkwise_state_dtype(256, 256, 256, 128, 1, 3) == 0
     null = ctypes.c_void_p(None)
-    rc = lib.mlstm_b200_step(*([null] * 12), 1, 1, 64, 64, 0, 0, 1e-6, null)
+    rc = lib.mlstm_b200_step(*([null] * 12), 1, 1, 64, 64, 0, 0, 0, 1e-6, null)
     assert rc == -3  # MLSTM_ERR_NULL
-    rc = lib.mlstm_b200_step(*([null] * 12), 1, 1, 64, 66, 0, 0, 1e-6, null)
+    rc = lib.mlstm_b200_step(*([null] * 12), 1, 1, 64, 66, 0, 0, 0, 1e-6, null)
     assert rc == -1  # MLSTM_ERR_SHAPE
 
 

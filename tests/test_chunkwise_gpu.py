@@ -51,6 +51,17 @@ def test_sig_f32_vs_reference_golden(name, L):
     compare(got, gold, TOL_F32_FW, TOL_F32_BW, keys_fw=("H",))
 
 
+@pytest.mark.parametrize("normalize", [True, False])
+def test_sig_states_vs_reference_golden(normalize):
+    """mLSTMsig final states against the values read out of the reference's quadratic implementation."""
+    case = CASES["sig_states"]
+    gold = dict(np.load(os.path.join(GOLD, "sig_states.npz")))
+    got = run_cuda_fwbw(make_chunkwise_inputs(case), case["L"], siging=True, normalize=normalize)
+    assert max_rel_err(got["C_last"], gold["C_last"]) < TOL_F32_FW
+    if normalize:
+        assert max_rel_err(got["n_last"], gold["n_last"]) < TOL_F32_FW
+
+
 def test_exp_f32_vs_reference_parallel_golden():
     case = CASES["exp_parallel"]
     gold = dict(np.load(os.path.join(GOLD, "exp_parallel.npz")))
@@ -216,23 +227,6 @@ def test_long_prefill_geometry_chunk256(variant):
     assert max_rel_err(got["H"], ref256["H"]) < TOL_BF16
 
 
-@pytest.mark.parametrize("variant", ["exp", "sig", "sig_nonorm"])
-@pytest.mark.parametrize("shape,init", [((1, 2, 256, 256, 256, 128), False), ((2, 2, 1024, 256, 256, 128), True),
-                                        ((1, 1, 512, 256, 512, 128), True)])
-def test_fused_forward_keeps_state_on_chip(variant, shape, init):
-    """The forward kernel that keeps the inter-chunk state in tensor memory: same results as the oracle (bf16
-    tolerance) and as the two-kernel tcgen05 path, including the per-chunk states the backward consumes."""
-    B, NH, S, DHQK, DHHV, L = shape
-    inp = case_inputs(14, B, NH, S, DHQK, DHHV, init=init, dC_last=init)
-    siging, normalize = variant != "exp", variant != "sig_nonorm"
-    got = run_cuda_fwbw(inp, L, dtype=torch.bfloat16, siging=siging, normalize=normalize, impl="tcgen05_fused")
-    two = run_cuda_fwbw(inp, L, dtype=torch.bfloat16, siging=siging, normalize=normalize, impl="tcgen05")
-    ref = run_oracle_fwbw(inp, L, dtype=torch.bfloat16, siging=siging, normalize=normalize)
-    keys = FW_KEYS if not siging else (("H", "C_last", "n_last") if normalize else ("H", "C_last"))
-    compare(got, ref, TOL_BF16, TOL_BF16, keys_fw=keys)
-    compare(got, two, 1e-2, 1e-2, keys_fw=keys)
-
-
 def test_forward_backward_capture_in_cuda_graph():
     """The kernels enqueue on the current stream without host synchronisation, so a forward + backward can be captured
     in a CUDA graph and replayed (the reference's callers compile and capture their models)."""
@@ -310,3 +304,61 @@ def test_benchmark_size_properties():
     assert max_rel_err(npy(c[0]), ref_fw["H"]) < TOL_BF16
     for j, key in enumerate(("dQ", "dK", "dV", "dI", "dF"), start=1):
         assert max_rel_err(npy(c[j]), ref_bw[key]) < TOL_BF16, key
+
+
+@pytest.mark.parametrize("variant", ["exp", "sig"])
+@pytest.mark.parametrize("impl,dtype,shape", [("auto", torch.bfloat16, (2, 2, 512, 256, 256, 128)),
+                                              ("simt", torch.float32, (1, 2, 256, 64, 128, 64))])
+def test_recompute_states_in_bw(variant, impl, dtype, shape):
+    """recompute_states_in_bw=True (the reference's default: the per-chunk states are not kept, the backward runs the
+    recurrence again) and False (states kept) give bit-identical outputs and gradients, both match the oracle, and the
+    recompute setting holds less memory between forward and backward (by the size of the state buffer)."""
+    B, NH, S, DHQK, DHHV, L = shape
+    inp = case_inputs(41, B, NH, S, DHQK, DHHV, init=True, dC_last=True)
+    siging = variant != "exp"
+    fn = mk.mlstm_siging_chunkwise__b200_xl_chunk if siging else mk.mlstm_chunkwise__b200_xl_chunk
+    res, held = {}, {}
+    for rc in (True, False):
+        leaves = [to_dev(inp[n], dtype, True) for n in "qkvif"]
+        c0 = to_dev(inp["c0"], torch.float32, True)
+        n0, m0 = to_dev(inp["n0"], torch.float32), to_dev(inp["m0"], torch.float32)
+        torch.cuda.synchronize()
+        base = torch.cuda.memory_allocated()
+        h, last = fn(*leaves, c0, n0, None if siging else m0, True, chunk_size=L, impl=impl,
+                     recompute_states_in_bw=rc)
+        loss = (h.float() * to_dev(inp["dH"], torch.float32)).sum() + (last[0] * to_dev(inp["dC_last"], torch.float32)).sum()
+        torch.cuda.synchronize()
+        held[rc] = torch.cuda.memory_allocated() - base
+        loss.backward()
+        res[rc] = [npy(h)] + [npy(t.grad) for t in leaves] + [npy(c0.grad)]
+    for a, b in zip(res[True], res[False]):
+        assert np.array_equal(a, b)
+    state_bytes = B * NH * (S // L + 1) * DHQK * DHHV * (2 if impl == "auto" else 4)
+    assert held[False] - held[True] >= 0.9 * state_bytes
+    ref = run_oracle_fwbw(inp, L, dtype=dtype, siging=siging)
+    tol_fw, tol_bw = (TOL_BF16, TOL_BF16) if dtype == torch.bfloat16 else (TOL_F32_FW, TOL_F32_BW)
+    got = dict(zip(("H", "dQ", "dK", "dV", "dI", "dF", "dC_initial"), res[True]))
+    compare(got, ref, tol_fw, tol_bw, keys_fw=("H",))
+
+
+def test_bounded_wait_expiry_is_reported():
+    """A wait that runs out records its code in the device status word and the context stays usable.  The self-test
+    kernel waits a few thousand polls on a barrier that nothing signals (no copy in flight, no tensor memory held),
+    gives up and returns; afterwards the word is cleared and a normal forward runs and leaves it at 0."""
+    from mlstm_kernels_b200 import _lib
+    lib = _lib.load()
+    assert _lib.device_status() == 0
+    assert lib.mlstm_b200_selftest_wait_expiry(2000, 901, None) == 0
+    assert _lib.device_status(reset=False) == 901
+    assert lib.mlstm_b200_selftest_wait_expiry(2000, 902, None) == 0
+    assert _lib.device_status(reset=True) == 901        # the FIRST code is kept until the word is cleared
+    assert _lib.device_status() == 0
+    assert lib.mlstm_b200_selftest_wait_expiry(0, 901, None) == -7          # limits outside 1 .. 1e6 are refused
+    assert lib.mlstm_b200_selftest_wait_expiry(5_000_000, 901, None) == -7
+    # an expired wait does not poison later launches: the status word is never read by a kernel
+    assert lib.mlstm_b200_selftest_wait_expiry(2000, 903, None) == 0
+    inp = case_inputs(43, 1, 2, 256, 256, 256)
+    got = run_cuda_fwbw(inp, 128, dtype=torch.bfloat16, impl="tcgen05")
+    ref = run_oracle_fwbw(inp, 128, dtype=torch.bfloat16)
+    compare(got, ref, TOL_BF16, TOL_BF16)
+    assert _lib.device_status(reset=True) == 903

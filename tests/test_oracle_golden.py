@@ -61,6 +61,17 @@ def test_sig_chunkwise_matches_reference_parallel(name, L):
     assert max_rel_err(H2, gold["H"]) < TOL_FW
 
 
+@pytest.mark.parametrize("L", [32, 64, 256])
+def test_siging_states_match_reference(L):
+    """The oracle's mLSTMsig final state (C, n) against values read out of the reference's quadratic implementation
+    through probe tokens (tests/golden/make_golden.py:run_sig_states); independent of the chunk size."""
+    case, gold = CASES["sig_states"], load("sig_states")
+    inp = make_chunkwise_inputs(case)
+    fw = O.chunkwise_fw(inp["q"], inp["k"], inp["v"], inp["i"], inp["f"], chunk_size=L, siging=True)
+    assert max_rel_err(fw["C_last"], gold["C_last"]) < TOL_FW
+    assert max_rel_err(fw["n_last"], gold["n_last"]) < TOL_FW
+
+
 def test_step_matches_reference():
     case, gold = CASES["step_small"], load("step_small")
     inp = make_step_inputs(case)

@@ -49,6 +49,40 @@ def test_step_vs_oracle(B, NH, DHQK, DHHV, dtype):
     assert max_rel_err(npy(m), mo) < 1e-4
 
 
+def test_step_bf16_tokens_with_f32_gates():
+    """bf16 q, k, v next to f32 gate pre-activations (the usual xLSTM set-up): the gates reach the kernel unrounded
+    and are widened to f32 as the reference does (mlstm_kernels/triton/recurrent/fw_step_fused.py:88-94).  Large gate
+    values make the difference visible: rounding i ~ 8 to bf16 moves exp(i - m) by up to 3 %."""
+    inp = make_step_inputs(dict(seed=12, B=2, NH=4, DHQK=64, DHHV=128, steps=2))
+    inp["i"] = (inp["i"] * 4 + 6).astype(np.float32)
+    c, n, m = (to_dev(inp[x], torch.float32) for x in "cnm")
+    co, no, mo = inp["c"], inp["n"], inp["m"]
+    for s in range(2):
+        q, k, v = (to_dev(inp[x][s], torch.bfloat16) for x in "qkv")
+        i, f = (to_dev(inp[x][s], torch.float32) for x in "if")
+        h, (c, n, m) = mk.mlstm_recurrent_step__b200(q, k, v, i, f, c, n, m)
+        ho, (co, no, mo) = O.recurrent_step(*(rounded(inp[x][s], torch.bfloat16) for x in "qkv"), inp["i"][s], inp["f"][s],
+                                            co, no, mo)
+        assert max_rel_err(npy(h), ho) < 2e-2
+    # states carry no bf16 rounding of the gates: f32 accuracy
+    assert max_rel_err(npy(c), co) < 1e-4
+    assert max_rel_err(npy(n), no) < 1e-4
+    assert max_rel_err(npy(m), mo) < 1e-5
+    # the sequence kernel takes the gates the same way
+    T = 8
+    cw = case_inputs(13, 1, 2, T, 64, 128)
+    q, k, v = (to_dev(cw[x], torch.bfloat16) for x in "qkv")
+    gi, gf = to_dev(cw["i"] * 4 + 6, torch.float32), to_dev(cw["f"], torch.float32)
+    h_seq, (c_s, _, m_s) = mk.mlstm_recurrent_sequence__b200(q, k, v, gi, gf, return_last_states=True)
+    c = torch.zeros(1, 2, 64, 128, device="cuda"); n = torch.zeros(1, 2, 64, device="cuda"); m = torch.zeros(1, 2, 1, device="cuda")
+    for t in range(T):
+        h, (c, n, m) = mk.mlstm_recurrent_step__b200(q[:, :, t], k[:, :, t], v[:, :, t], gi[:, :, t, None],
+                                                     gf[:, :, t, None], c, n, m)
+    assert max_rel_err(npy(c_s), npy(c)) < 1e-5
+    assert max_rel_err(npy(m_s), npy(m)) < 1e-6
+    assert max_rel_err(npy(h_seq[:, :, -1]), npy(h)) < 1e-2
+
+
 def test_step_bf16_state_and_out_buffers():
     inp = make_step_inputs(dict(seed=10, B=2, NH=2, DHQK=64, DHHV=128, steps=1))
     q, k, v, i, f = (to_dev(inp[x][0], torch.bfloat16) for x in "qkvif")
@@ -66,6 +100,11 @@ def test_step_bf16_state_and_out_buffers():
                                                         vecN_new=nb, scaM_new=mb)
     assert c3.data_ptr() == cf.data_ptr()
     assert max_rel_err(npy(h3), ho) < 2e-2
+    # caller-owned h
+    hb = torch.empty_like(v)
+    h4, _ = mk.mlstm_recurrent_step__b200_fw(c.float(), n.float(), m.float(), q, k, v, i, f, vecH_out=hb)
+    assert h4.data_ptr() == hb.data_ptr()
+    assert max_rel_err(npy(h4), ho) < 2e-2
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])

@@ -63,6 +63,27 @@ def test_static_scratch_forward_matches_regular_entry_point_twice():
     assert _lib.device_status() == 0
 
 
+def test_static_warmup_then_calls_take_no_driver_memory():
+    """After mlstm_b200_static_warmup() and one call, a further call leaves the driver's free-memory figure where it
+    was: the array and the kernels' code were materialised up front, the call itself allocates nothing."""
+    lib = _lib.load()
+    assert lib.mlstm_b200_static_warmup() == 0
+    B, NH, S, DHQK, DHHV, L = 1, 2, 256, 128, 128, 128
+    dims = (B, NH, S, DHQK, DHHV, L)
+    sdt = _lib.code_dtype(lib.mlstm_b200_chunkwise_state_dtype(S, DHQK, DHHV, L, _lib.BF16, 0))
+    inp = case_inputs(103, B, NH, S, DHQK, DHHV)
+    tensors = [to_dev(inp[n], torch.bfloat16) for n in "qkvif"]
+    out = _buffers(*dims, sdt)
+    assert _call(lib, True, tensors, out, dims) == 0
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    assert _call(lib, True, tensors, out, dims) == 0
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
+    assert _lib.device_status() == 0
+
+
 def test_static_scratch_rejects_cases_beyond_its_limit():
     lib = _lib.load()
     B, NH, S, DHQK, DHHV, L = 16, 16, 8192, 128, 128, 128   # 2M token-heads: needs ~34 MB of scratch
