@@ -114,7 +114,11 @@ size_t mlstm_b200_chunkwise_workspace_bytes(int B, int NH, int S, int DHQK, int 
  *                                        before chunk k, slot NC = final state
  *   n_states    (B,NH,NC+1,DHQK) f32 out,  m_states (B,NH,NC+1) f32 out
  *   c_last,n_last,m_last  f32 copies of the final state (B,NH,DHQK,DHHV),(B,NH,DHQK),(B,NH); each may be NULL
- *   S % L == 0, L a power of two >= 16.
+ *   L a power of two >= 16.  S % L == 0 for the portable kernels.  Where the tcgen05 kernels run (bf16, L = 128,
+ *   head dims multiples of 128) S may be ANY length >= 1: NC = ceil(S / L) and the last chunk is ragged - its
+ *   missing tokens are read as zeros and switched off in the gates, no output row past S is written.  This
+ *   replaces the host-side zero padding of wrap_chunkwise__pad_zeros and the chunk-size ladder 64/32/16 of
+ *   wrap_chunkwise__arbitrary_sequence_length (mlstm_kernels/torch/kernel_wrappers.py:76-171,206-267).
  */
 int mlstm_b200_chunkwise_fw(const void* q, const void* k, const void* v, const void* i, const void* f,
                             const float* c_initial, const float* n_initial, const float* m_initial,
@@ -135,7 +139,7 @@ int mlstm_b200_chunkwise_fw(const void* q, const void* k, const void* v, const v
  * without `workspace`: the scratch lives in a fixed array of mlstm_b200_static_scratch_bytes() bytes
  * (8 MiB) in device global memory that belongs to the library; every GPU that loads the library holds
  * it until the process exits.  The call itself allocates nothing.
- *   - Limit: the case must need no more scratch than that (roughly B*NH*S <= 500,000); larger cases
+ *   - Limit: the case must need no more scratch than that (roughly B*NH*S <= 400,000); larger cases
  *     are rejected with MLSTM_ERR_WORKSPACE before anything is launched.
  *   - The first call on each device looks up the array's device address (a short host-side set-up,
  *     done with that device current); make that first call before any stream capture begins.  The stream
@@ -184,6 +188,7 @@ int mlstm_b200_chunkwise_bw(const void* q, const void* k, const void* v, const v
  * `fw_workspace` (and its m_out output) are still intact: the gate pre-pass (logsigmoid, cumulative sums, max-state
  * recursion) is not repeated, its per-token vectors are read back from that buffer.  The reference keeps no such
  * cache (it recomputes vecB / vecA in mlstm_kernels/torch/chunkwise/triton_xl_chunk/bw.py:116-118).
+ * m_out is not read (the buffer holds its own copy of the per-token max state); it may be NULL.
  */
 int mlstm_b200_chunkwise_bw_cached(const void* q, const void* k, const void* v, const void* i, const void* f,
                                    const float* m_initial, const void* c_states, const float* n_out,

@@ -9,6 +9,7 @@ from .chunkwise import (
     chunkwise_states_raw,
     kernel_chunk_size,
     mlstm_chunkwise__b200_xl_chunk,
+    resolve_chunk_size,
     mlstm_siging_chunkwise__b200_xl_chunk,
     select_chunk_size,
 )
@@ -30,6 +31,7 @@ __all__ = [
     "chunkwise_states_raw",
     "select_chunk_size",
     "kernel_chunk_size",
+    "resolve_chunk_size",
     "get_kernel",
     "register_with_mlstm_kernels",
 ]

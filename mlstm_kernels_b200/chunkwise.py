@@ -48,16 +48,28 @@ def select_chunk_size(sequence_length: int, target_chunk_size: int) -> int:
     return target_chunk_size
 
 
+def tcgen05_applies(q: torch.Tensor, v: torch.Tensor, impl: str = "auto") -> bool:
+    """True where the tcgen05 kernels run: bf16, head dims multiples of 128 (any sequence length)."""
+    if impl == "simt" or not q.is_cuda or q.dtype not in _lib._DTYPE_CODE:
+        return False
+    lib = _lib.load()
+    return bool(lib.mlstm_b200_chunkwise_has_tcgen05(q.shape[2], q.shape[3], v.shape[3], 128, _lib.dtype_code(q.dtype)))
+
+
 def kernel_chunk_size(q: torch.Tensor, v: torch.Tensor, chunk_size: int, impl: str = "auto") -> int:
-    """Chunk size the kernels run with.  Where the tcgen05 path applies (bf16, head dims multiples of 128, sequence a
-    multiple of 128) every requested chunk size runs as chunks of 128
+    """Chunk size the kernels run with.  Where the tcgen05 path applies (bf16, head dims multiples of 128) every
+    requested chunk size runs as chunks of 128, the last one ragged if the sequence length is no multiple of 128
     (H does not depend on the chunk size; the reference does the same for its inter-chunk kernel:
     chunk_size_inter = min(128, chunk_size), mlstm_kernels/triton/chunkwise/kernel_param_heuristics.py:96-121)."""
-    if chunk_size != 128 and q.shape[2] % 128 == 0 and impl != "simt" and q.is_cuda:
-        lib = _lib.load()
-        if lib.mlstm_b200_chunkwise_has_tcgen05(q.shape[2], q.shape[3], v.shape[3], 128, _lib.dtype_code(q.dtype)):
-            return 128
-    return chunk_size
+    return 128 if tcgen05_applies(q, v, impl) else chunk_size
+
+
+def resolve_chunk_size(q: torch.Tensor, v: torch.Tensor, chunk_size: int, impl: str = "auto") -> int:
+    """The chunk size a call runs with.  On the tcgen05 path any sequence length is accepted (no padding, no
+    divisibility rule); elsewhere the reference's rules apply (select_chunk_size)."""
+    if tcgen05_applies(q, v, impl):
+        return 128
+    return select_chunk_size(q.shape[2], chunk_size)
 
 
 def _f32c(t):
@@ -79,7 +91,7 @@ def chunkwise_fw_raw(q, k, v, i, f, c_initial=None, n_initial=None, m_initial=No
     if i.dtype != f.dtype:
         f = f.to(i.dtype)
     L = chunk_size
-    NC = S // L
+    NC = -(-S // L)   # the last chunk may be ragged on the tcgen05 path (the library refuses it elsewhere)
     dt, gdt, im = _lib.dtype_code(q.dtype), _lib.dtype_code(i.dtype), _lib.IMPL[impl]
     q, k, v, i, f = (t.contiguous() for t in (q, k, v, i, f))
     c0, n0 = _f32c(c_initial), _f32c(n_initial)
@@ -133,7 +145,7 @@ def chunkwise_states_raw(k, v, i, f, c_initial=None, m_initial=None, *, chunk_si
     m0 = None if m_initial is None else _f32c(m_initial).reshape(B, NH)
     dev = k.device
     sdt = _lib.code_dtype(lib.mlstm_b200_chunkwise_state_dtype(S, DHQK, DHHV, L, dt, im))
-    c_states = torch.empty((B, NH, S // L + 1, DHQK, DHHV), dtype=sdt, device=dev)
+    c_states = torch.empty((B, NH, -(-S // L) + 1, DHQK, DHHV), dtype=sdt, device=dev)
     ws, ws_bytes = None, 0
     if fw_workspace is None:
         ws_bytes = lib.mlstm_b200_chunkwise_workspace_bytes(B, NH, S, DHQK, DHHV, L, dt, variant, im, 2)
@@ -199,7 +211,7 @@ def _make_fwbw(autocast_kernel_dtype: torch.dtype, variant: int):
         def forward(ctx, q, k, v, i, f, c_initial, n_initial, m_initial, return_last_states, eps, chunk_size, impl,
                     recompute_states_in_bw):
             B, NH, S, DHQK = q.shape
-            L = kernel_chunk_size(q, v, select_chunk_size(S, chunk_size), impl)
+            L = resolve_chunk_size(q, v, chunk_size, impl)
             out = chunkwise_fw_raw(q, k, v, i, f, c_initial, n_initial, m_initial, chunk_size=L, eps=eps,
                                    variant=variant, impl=impl, want_last=return_last_states)
             # The forward's gate vectors (its scratch buffer and m_out) are kept for the backward: 24 B per token.

@@ -47,15 +47,16 @@ PhaseScope::~PhaseScope() {
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// S need not be a multiple of L where the tcgen05 kernels run (they mask a ragged last chunk); resolve_impl refuses
+// that case for the portable kernels.
 static int check_dims(int B, int NH, int S, int DHQK, int DHHV, int L) {
   if (B <= 0 || NH <= 0 || S <= 0 || DHQK <= 0 || DHHV <= 0 || L <= 0) return MLSTM_ERR_SHAPE;
-  if (S % L != 0) return MLSTM_ERR_SHAPE;
   if (!is_pow2(L) || L < 16 || L > 1024) return MLSTM_ERR_SHAPE;
   // Sizes the launches cannot express are refused here instead of failing at launch or overflowing an index:
   // the grids carry (tiles x chunks x batch x heads) in one dimension, and the tcgen05 kernels address token and
   // state rows with 32-bit coordinates.
   const uint64_t lim = 0x7fffffffull;
-  const uint64_t bnh = (uint64_t)B * NH, nc = (uint64_t)S / L;
+  const uint64_t bnh = (uint64_t)B * NH, nc = ((uint64_t)S + L - 1) / L;
   const uint64_t tiles = (uint64_t)std::max(ceil_div(DHQK, 64), ceil_div(DHHV, 64));
   if (bnh * nc * tiles >= lim || bnh * S >= lim) return MLSTM_ERR_SHAPE;
   return MLSTM_OK;
@@ -67,6 +68,7 @@ static int resolve_impl(int impl, int B, int NH, int S, int DHQK, int DHHV, int 
   *use_sm100 = ok && impl != MLSTM_IMPL_SIMT;
   if (impl == MLSTM_IMPL_TCGEN05 && !ok) return MLSTM_ERR_UNSUPPORTED;
   if (*use_sm100 && !sm100_sizes_ok(B, NH, S, DHQK, DHHV)) return MLSTM_ERR_SHAPE;
+  if (!*use_sm100 && S % L != 0) return MLSTM_ERR_SHAPE;   // the portable kernels need whole chunks
   return MLSTM_OK;
 }
 
@@ -83,27 +85,28 @@ struct Carver {
 };
 
 struct FwLayout { GateBuffers gb; size_t bytes; };
-static FwLayout carve_fw(void* ws, int BNH, int S, int NC, float* m_out) {
+// per-token arrays have SP = NC * L slots per (batch, head)
+static FwLayout carve_fw(void* ws, int BNH, int SP, int NC) {
   Carver c(ws);
   FwLayout l{};
-  const size_t tok = (size_t)BNH * S;
+  const size_t tok = (size_t)BNH * SP;
   l.gb.vecB = c.take<float>(tok);
   l.gb.iota = c.take<float>(tok);
   l.gb.abar = c.take<float>(tok);
   l.gb.bbar = c.take<float>(tok);
+  l.gb.m_tok = c.take<float>(tok);
   l.gb.gbar = c.take<float>((size_t)BNH * NC);
   l.gb.scratch = c.take<float>((size_t)BNH * NC * 2);
-  l.gb.m_tok = m_out;
   l.gb.inv_den = nullptr;
   l.bytes = align_up(c.off, 256);
   return l;
 }
 
 struct SumLayout { GateBuffers gb; float* m_states; size_t bytes; };
-static SumLayout carve_summary(void* ws, int BNH, int S, int NC) {
+static SumLayout carve_summary(void* ws, int BNH, int SP, int NC) {
   Carver c(ws);
   SumLayout l{};
-  const size_t tok = (size_t)BNH * S;
+  const size_t tok = (size_t)BNH * SP;
   l.gb.vecB = c.take<float>(tok);
   l.gb.iota = c.take<float>(tok);
   l.gb.m_tok = c.take<float>(tok);
@@ -117,11 +120,15 @@ static SumLayout carve_summary(void* ws, int BNH, int S, int NC) {
   return l;
 }
 
-struct BwLayout { GateBuffers gb; float* m_states; float* acc; float* kdk; void* dc_states; size_t bytes; };
-static BwLayout carve_bw(void* ws, int BNH, int S, int NC, int DHQK, int DHHV, size_t state_elem) {
+// every kAnchorEvery-th chunk boundary carries an exact value of the forget-gate gradient's running sum
+constexpr int kAnchorEvery = 4;
+static int anchor_count(int NC) { return (NC + kAnchorEvery - 1) / kAnchorEvery + 1; }
+
+struct BwLayout { GateBuffers gb; float* m_states; float* acc; float* kdk; float* anchors; void* dc_states; size_t bytes; };
+static BwLayout carve_bw(void* ws, int BNH, int SP, int NC, int DHQK, int DHHV, size_t state_elem) {
   Carver c(ws);
   BwLayout l{};
-  const size_t tok = (size_t)BNH * S;
+  const size_t tok = (size_t)BNH * SP;
   l.gb.vecB = c.take<float>(tok);
   l.gb.iota = c.take<float>(tok);
   l.gb.m_tok = c.take<float>(tok);
@@ -134,6 +141,7 @@ static BwLayout carve_bw(void* ws, int BNH, int S, int NC, int DHQK, int DHHV, s
   const size_t parts = (size_t)(DHQK + 127) / 128;  // one partial row sum per 128-wide tile of DHQK
   l.acc = c.take<float>(tok * parts);
   l.kdk = c.take<float>(tok * parts);
+  l.anchors = c.take<float>((size_t)BNH * anchor_count(NC));
   l.dc_states = c.take<char>((size_t)BNH * (NC + 1) * DHQK * DHHV * state_elem);
   l.bytes = align_up(c.off, 256);
   return l;
@@ -220,11 +228,12 @@ size_t mlstm_b200_chunkwise_workspace_bytes(int B, int NH, int S, int DHQK, int 
                                             int impl, int backward) {
   (void)variant;
   if (check_dims(B, NH, S, DHQK, DHHV, L) != MLSTM_OK) return 0;
-  const int NC = S / L;
-  if (backward == 2) return carve_summary(nullptr, B * NH, S, NC).bytes;
-  if (!backward) return carve_fw(nullptr, B * NH, S, NC, nullptr).bytes;
-  const size_t se = dtype_size(mlstm_b200_chunkwise_state_dtype(S, DHQK, DHHV, L, dtype, impl));
-  return carve_bw(nullptr, B * NH, S, NC, DHQK, DHHV, se).bytes;
+  bool use_sm100 = false;
+  if (resolve_impl(impl, B, NH, S, DHQK, DHHV, L, dtype, &use_sm100) != MLSTM_OK) return 0;
+  const int NC = (S + L - 1) / L, SP = NC * L;
+  if (backward == 2) return carve_summary(nullptr, B * NH, SP, NC).bytes;
+  if (!backward) return carve_fw(nullptr, B * NH, SP, NC).bytes;
+  return carve_bw(nullptr, B * NH, SP, NC, DHQK, DHHV, dtype_size(use_sm100 ? MLSTM_BF16 : MLSTM_F32)).bytes;
 }
 
 int mlstm_b200_chunkwise_fw(const void* q, const void* k, const void* v, const void* i, const void* f,
@@ -246,12 +255,12 @@ int mlstm_b200_chunkwise_fw(const void* q, const void* k, const void* v, const v
   bool use_sm100 = false;
   if ((rc = resolve_impl(impl, B, NH, S, DHQK, DHHV, L, dtype, &use_sm100)) != MLSTM_OK) return rc;
 
-  ChunkwiseDims d{B, NH, S, DHQK, DHHV, L, S / L, variant, eps, 1.0f / sqrtf((float)DHQK)};
-  FwLayout lay = carve_fw(workspace, B * NH, S, d.NC, m_out);
+  const ChunkwiseDims d = make_dims(B, NH, S, DHQK, DHHV, L, variant, eps);
+  FwLayout lay = carve_fw(workspace, B * NH, d.SP, d.NC);
   if (workspace_bytes < lay.bytes) return MLSTM_ERR_WORKSPACE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 
-  if ((rc = launch_gates(gate_dtype, i, f, variant == MLSTM_EXP ? m_initial : nullptr, nullptr, lay.gb, m_states, d, st)) != MLSTM_OK) return rc;
+  if ((rc = launch_gates(gate_dtype, i, f, variant == MLSTM_EXP ? m_initial : nullptr, nullptr, m_out, lay.gb, m_states, d, st)) != MLSTM_OK) return rc;
   if (use_sm100) {
     if ((rc = sm100_recurrent_fw(k, v, lay.gb, c_initial, n_initial, c_states, n_states, c_last, n_last, d, st)) != MLSTM_OK) return rc;
     if ((rc = sm100_parallel_fw(q, k, v, lay.gb, c_states, n_states, h, n_out, d, st)) != MLSTM_OK) return rc;
@@ -289,29 +298,32 @@ static int bw_impl(const void* q, const void* k, const void* v, const void* i, c
   bool use_sm100 = false;
   if ((rc = resolve_impl(impl, B, NH, S, DHQK, DHHV, L, dtype, &use_sm100)) != MLSTM_OK) return rc;
 
-  ChunkwiseDims d{B, NH, S, DHQK, DHHV, L, S / L, variant, eps, 1.0f / sqrtf((float)DHQK)};
+  const ChunkwiseDims d = make_dims(B, NH, S, DHQK, DHHV, L, variant, eps);
   const int sdt = use_sm100 ? MLSTM_BF16 : MLSTM_F32;
-  BwLayout lay = carve_bw(workspace, B * NH, S, d.NC, DHQK, DHHV, dtype_size(sdt));
+  BwLayout lay = carve_bw(workspace, B * NH, d.SP, d.NC, DHQK, DHHV, dtype_size(sdt));
   if (workspace_bytes < lay.bytes) return MLSTM_ERR_WORKSPACE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 
   if (fw_workspace != nullptr) {
-    if (!m_out || !aligned16(fw_workspace) || !aligned16(m_out)) return MLSTM_ERR_NULL;
-    FwLayout fl = carve_fw(const_cast<void*>(fw_workspace), B * NH, S, d.NC, const_cast<float*>(m_out));
+    if (!aligned16(fw_workspace)) return MLSTM_ERR_ALIGN;
+    FwLayout fl = carve_fw(const_cast<void*>(fw_workspace), B * NH, d.SP, d.NC);
     if (fw_workspace_bytes < fl.bytes) return MLSTM_ERR_WORKSPACE;
     float* inv_den = lay.gb.inv_den;
     lay.gb = fl.gb;
     lay.gb.inv_den = inv_den;
-    if ((rc = launch_inv_den(n_out, inv_den, (size_t)B * NH * S, variant, eps, st)) != MLSTM_OK) return rc;
+    if ((rc = launch_inv_den(n_out, inv_den, d, st)) != MLSTM_OK) return rc;
   } else {
-    if ((rc = launch_gates(gate_dtype, i, f, variant == MLSTM_EXP ? m_initial : nullptr, n_out, lay.gb, lay.m_states, d, st)) != MLSTM_OK) return rc;
+    if ((rc = launch_gates(gate_dtype, i, f, variant == MLSTM_EXP ? m_initial : nullptr, n_out, nullptr, lay.gb, lay.m_states, d, st)) != MLSTM_OK) return rc;
   }
   if (use_sm100) {
     if ((rc = sm100_recurrent_bw(q, dh, lay.gb, dc_last, lay.dc_states, dc_initial, d, st)) != MLSTM_OK) return rc;
     if ((rc = sm100_parallel_bw(q, k, v, dh, lay.gb, c_states, lay.dc_states, dq, dk, dv, lay.acc, lay.kdk, d, st)) != MLSTM_OK) return rc;
     {
       PhaseScope ps(PH_GATE_GRADS, st);
-      if ((rc = launch_gate_grad_scan(gate_dtype, i, f, lay.acc, lay.kdk, DHQK / 128, di, df, d, st)) != MLSTM_OK) return rc;
+      const int n_anchors = anchor_count(d.NC);
+      if ((rc = launch_state_dot(c_states, lay.dc_states, lay.anchors, kAnchorEvery, n_anchors, d, st)) != MLSTM_OK) return rc;
+      if ((rc = launch_gate_grad_scan(gate_dtype, i, f, lay.acc, lay.kdk, DHQK / 128, di, df, d, st, lay.anchors,
+                                      n_anchors, kAnchorEvery * L)) != MLSTM_OK) return rc;
     }
   } else {
     if ((rc = simt_recurrent_bw(dtype, sdt, q, dh, lay.gb, dc_last, lay.dc_states, dc_initial, d, st)) != MLSTM_OK) return rc;
@@ -340,7 +352,7 @@ int mlstm_b200_chunkwise_bw_cached(const void* q, const void* k, const void* v, 
                                    float* df, float* dc_initial, void* workspace, size_t workspace_bytes, int B,
                                    int NH, int S, int DHQK, int DHHV, int L, int dtype, int gate_dtype, int variant,
                                    int impl, float eps, void* stream) {
-  if (!fw_workspace || !m_out) return MLSTM_ERR_NULL;
+  if (!fw_workspace) return MLSTM_ERR_NULL;
   return bw_impl(q, k, v, i, f, m_initial, c_states, n_out, dh, dc_last, dq, dk, dv, di, df, dc_initial, workspace,
                  workspace_bytes, B, NH, S, DHQK, DHHV, L, dtype, gate_dtype, variant, impl, eps, stream, fw_workspace,
                  fw_workspace_bytes, m_out);
@@ -362,18 +374,18 @@ int mlstm_b200_chunkwise_states(const void* k, const void* v, const void* i, con
   for (const void* p : ptrs) if (p && !aligned16(p)) return MLSTM_ERR_ALIGN;
   bool use_sm100 = false;
   if ((rc = resolve_impl(impl, B, NH, S, DHQK, DHHV, L, dtype, &use_sm100)) != MLSTM_OK) return rc;
-  ChunkwiseDims d{B, NH, S, DHQK, DHHV, L, S / L, variant, 1e-6f, 1.0f / sqrtf((float)DHQK)};
+  const ChunkwiseDims d = make_dims(B, NH, S, DHQK, DHHV, L, variant, 1e-6f);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   GateBuffers gb;
   if (fw_workspace != nullptr) {   // the forward's gate vectors are still there: only abar and gbar are read
-    FwLayout fl = carve_fw(const_cast<void*>(fw_workspace), B * NH, S, d.NC, nullptr);
+    FwLayout fl = carve_fw(const_cast<void*>(fw_workspace), B * NH, d.SP, d.NC);
     if (fw_workspace_bytes < fl.bytes) return MLSTM_ERR_WORKSPACE;
     gb = fl.gb;
   } else {
-    SumLayout lay = carve_summary(workspace, B * NH, S, d.NC);
+    SumLayout lay = carve_summary(workspace, B * NH, d.SP, d.NC);
     if (workspace_bytes < lay.bytes) return MLSTM_ERR_WORKSPACE;
     gb = lay.gb;
-    if ((rc = launch_gates(gate_dtype, i, f, variant == MLSTM_EXP ? m_initial : nullptr, nullptr, gb, lay.m_states, d, st)) != MLSTM_OK) return rc;
+    if ((rc = launch_gates(gate_dtype, i, f, variant == MLSTM_EXP ? m_initial : nullptr, nullptr, nullptr, gb, lay.m_states, d, st)) != MLSTM_OK) return rc;
   }
   if (use_sm100) return sm100_recurrent_fw(k, v, gb, c_initial, nullptr, c_states, nullptr, nullptr, nullptr, d, st);
   return simt_recurrent_fw(dtype, MLSTM_F32, k, v, gb, c_initial, nullptr, c_states, nullptr, nullptr, nullptr, d, st);
@@ -394,12 +406,12 @@ int mlstm_b200_chunkwise_summary(const void* k, const void* v, const void* i, co
   for (const void* p : ptrs) if (p && !aligned16(p)) return MLSTM_ERR_ALIGN;
   bool use_sm100 = false;
   if ((rc = resolve_impl(impl, B, NH, S, DHQK, DHHV, L, dtype, &use_sm100)) != MLSTM_OK) return rc;
-  ChunkwiseDims d{B, NH, S, DHQK, DHHV, L, S / L, variant, 1e-6f, 1.0f / sqrtf((float)DHQK)};
-  SumLayout lay = carve_summary(workspace, B * NH, S, d.NC);
+  const ChunkwiseDims d = make_dims(B, NH, S, DHQK, DHHV, L, variant, 1e-6f);
+  SumLayout lay = carve_summary(workspace, B * NH, d.SP, d.NC);
   if (workspace_bytes < lay.bytes) return MLSTM_ERR_WORKSPACE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // the segment starts from the empty state: C = 0, n = 0, m = -inf
-  if ((rc = launch_gates(gate_dtype, i, f, nullptr, nullptr, lay.gb, lay.m_states, d, st, -INFINITY, g_total)) != MLSTM_OK) return rc;
+  if ((rc = launch_gates(gate_dtype, i, f, nullptr, nullptr, nullptr, lay.gb, lay.m_states, d, st, -INFINITY, g_total)) != MLSTM_OK) return rc;
   if (use_sm100) {
     if ((rc = sm100_recurrent_fw(k, v, lay.gb, nullptr, nullptr, nullptr, nullptr, c_last, n_last, d, st)) != MLSTM_OK) return rc;
   } else {

@@ -40,7 +40,7 @@ struct RecParams {
   float* n_states;          // (BNH, NC+1, DHQK) or nullptr
   float* c_final;           // (BNH, DHQK, DHHV) f32 or nullptr
   float* n_final;
-  int S, NC, DHQK, DHHV;
+  int S, SP, NC, DHQK, DHHV;   // SP = NC * 128: slots per (batch, head) of the per-token scale vectors
 };
 
 constexpr int REC_THREADS = 640;                 // warp 0 TMA, 1 MMA, 2..9 gate the left tile, 10..17 own the state, 18 stores it, 19 keeps n
@@ -122,15 +122,17 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
       if (!ok) break;
       if (lane == 0) {
         const int ck = BWD ? NC - 1 - s : s;
-        const int row0 = bh * p.S + ck * CL + (h & 1) * REC_HALF;
+        // token rows past the end of the sequence (ragged last chunk) arrive as zeros; their scale slots hold zeros
+        const int y = ck * CL + (h & 1) * REC_HALF;          // first token of this half chunk inside the sequence
+        const size_t slot0 = (size_t)bh * p.SP + y;
         uint8_t* sl = smem + st * REC_STAGE_BYTES;
         mbar_expect_tx(&bar_full[st], REC_STAGE_BYTES + (BWD ? 2 : 1) * REC_HALF * 4);
-        bulk_load(s_scale[st], p.lscale + row0, REC_HALF * 4, &bar_full[st]);
-        if (BWD) bulk_load(s_scale2[st], p.rscale + row0, REC_HALF * 4, &bar_full[st]);
-        tma_load_2d(sl, &mapL, &bar_full[st], d0, row0);
-        tma_load_2d(sl + 8192, &mapL, &bar_full[st], d0 + 64, row0);
-        tma_load_2d(sl + 16384, &mapR, &bar_full[st], e0, row0);
-        tma_load_2d(sl + 24576, &mapR, &bar_full[st], e0 + 64, row0);
+        bulk_load(s_scale[st], p.lscale + slot0, REC_HALF * 4, &bar_full[st]);
+        if (BWD) bulk_load(s_scale2[st], p.rscale + slot0, REC_HALF * 4, &bar_full[st]);
+        tma_load_3d(sl, &mapL, &bar_full[st], d0, y, bh);
+        tma_load_3d(sl + 8192, &mapL, &bar_full[st], d0 + 64, y, bh);
+        tma_load_3d(sl + 16384, &mapR, &bar_full[st], e0, y, bh);
+        tma_load_3d(sl + 24576, &mapR, &bar_full[st], e0 + 64, y, bh);
       }
       issued = h + 1;
     }
@@ -341,8 +343,8 @@ struct ParParams {
   __nv_bfloat16 *out_h, *out_dv, *out_dk, *out_dq;
   float* n_out;               // H only
   float *rowdot_q, *rowdot_k; // sum_d q dq (from DQ), sum_d k dk (from DK); one partial per output tile: [DHQK/128][tokens]
-  size_t ntok;                // B * NH * S
-  int S, NC, DHQK, DHHV, variant;
+  size_t nslots;              // B * NH * SP
+  int S, SP, NC, DHQK, DHHV, variant;   // SP = NC * 128: slots per (batch, head) of the per-token gate vectors
   float eps, qk_scale;
 };
 
@@ -393,7 +395,9 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
   const int DI = (mode == PM_H || mode == PM_DV) ? p.DHQK : p.DHHV;   // contraction dim of the score product
   const int DO = (mode == PM_H || mode == PM_DV) ? p.DHHV : p.DHQK;   // output width
   const int NC = p.NC, ND = DI / 64;
-  const int row0 = bh * p.S + ck * CL;
+  const int y0 = ck * CL;                         // first token of the chunk inside its sequence
+  const int valid = min(CL, p.S - y0);            // tokens of the chunk that exist (ragged last chunk: < 128)
+  const size_t out_row0 = (size_t)bh * p.S + y0;  // first row of the chunk in the (B*NH*S)-row token tensors
   const bool use_n = (mode == PM_H) && p.variant != MLSTM_SIG_NONORM && p.n_states != nullptr;
 
   if (tid == 0) {
@@ -470,10 +474,10 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
         uint8_t* sb = smem + st * PAR_STAGE;
         mbar_expect_tx(&sh.bar_full[st], PAR_STAGE);
         if (kind == LK_SCORE) {
-          tma_load_2d(sb, mapA, &sh.bar_full[st], 64 * it, row0);
-          tma_load_2d(sb + 16384, mapB, &sh.bar_full[st], 64 * it, row0);
+          tma_load_3d(sb, mapA, &sh.bar_full[st], 64 * it, y0, bh);
+          tma_load_3d(sb + 16384, mapB, &sh.bar_full[st], 64 * it, y0, bh);
         } else if (kind == LK_STATE) {
-          tma_load_2d(sb, mapA, &sh.bar_full[st], 64 * it, row0);
+          tma_load_3d(sb, mapA, &sh.bar_full[st], 64 * it, y0, bh);
           if (ST_MN) {
             tma_load_2d(sb + 16384, mapSt, &sh.bar_full[st], o0, srow + 64 * it);
             tma_load_2d(sb + 16384 + 8192, mapSt, &sh.bar_full[st], o0 + 64, srow + 64 * it);
@@ -482,8 +486,8 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
           }
         } else {
           const CUtensorMap* m = (kind == LK_X) ? mapX : mapE;
-          tma_load_2d(sb, m, &sh.bar_full[st], o0, row0);
-          tma_load_2d(sb + 16384, m, &sh.bar_full[st], o0 + 64, row0);
+          tma_load_3d(sb, m, &sh.bar_full[st], o0, y0, bh);
+          tma_load_3d(sb + 16384, m, &sh.bar_full[st], o0 + 64, y0, bh);
         }
         if (kind == LK_SCORE || kind == LK_STATE || (kind == LK_X && HAS_E)) { rm0 += (st == 0); rm1 += (st == 1); rm2 += (st == 2); }
         if (kind == LK_SCORE) { rq0 += (st == 0); rq1 += (st == 1); rq2 += (st == 2); }
@@ -552,7 +556,7 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
     // ---------------- element-wise warps: two warps per 32-row quarter, each owning two 32-column chunks ----
     const int quarter = warp & 3, half = (warp - 2) >> 2;
     const int r = quarter * 32 + lane;
-    const size_t tok = (size_t)row0 + r;
+    const size_t tok = (size_t)bh * p.SP + y0 + r;   // slot of this row in the per-token gate vectors
     const float b_r = p.vecB[tok], iota_r = p.iota[tok], m_r = p.m_tok[tok];
     const float inv_r = (mode == PM_H) ? 1.f : p.inv_den[tok];
     constexpr float kLog2e = 1.4426950408889634f;
@@ -714,7 +718,7 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
         if (p.variant == MLSTM_EXP) den = fmaxf(fabsf(nn), __expf(-m_r));
         else if (p.variant == MLSTM_SIG) den = fmaxf(fabsf(nn), 1.f);
         if (p.variant != MLSTM_SIG_NONORM) inv = 1.f / (den + p.eps);
-        if (o_tile0 == 0 && half == 0) p.n_out[tok] = den;
+        if (o_tile0 == 0 && half == 0 && r < valid) p.n_out[out_row0 + r] = den;
       }
       const int ldx = (sub == 0 ? 2 * ND : n0 + (sub - 1) * n1 + ND);    // ring index of this tile's X load; E follows it
       const uint8_t* erow = smem;
@@ -772,13 +776,13 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
       if (!mbar_wait(&sh.bar_out, sub & 1, &sh.abort, &g_sm100_status, 211)) { ok = false; break; }
       {
         __nv_bfloat16* outp = (mode == PM_H) ? p.out_h : (mode == PM_DV) ? p.out_dv : (mode == PM_DK) ? p.out_dk : p.out_dq;
-        uint8_t* gbase = reinterpret_cast<uint8_t*>(outp + (size_t)row0 * DO + o0);
+        uint8_t* gbase = reinterpret_cast<uint8_t*>(outp + out_row0 * DO + o0);
         const int ew = warp - 2, j = lane & 15;          // 16-byte piece j of the 256-byte tile row
 #pragma unroll
         for (int i2 = 0; i2 < 8; ++i2) {
           const int orow_i = 16 * i2 + 2 * ew + (lane >> 4);
           const uint4 o = *reinterpret_cast<const uint4*>(ostage + (j >> 3) * 16384 + orow_i * 128 + (((j & 7) ^ (orow_i & 7)) << 4));
-          *reinterpret_cast<uint4*>(gbase + (size_t)orow_i * DO * 2 + j * 16) = o;
+          if (orow_i < valid) *reinterpret_cast<uint4*>(gbase + (size_t)orow_i * DO * 2 + j * 16) = o;
         }
       }
       if (HAS_E) {
@@ -786,7 +790,7 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
         mbar_arrive(&sh.bar_dot);
         if (half == 0) {
           if (!mbar_wait(&sh.bar_dot, sub & 1, &sh.abort, &g_sm100_status, 209)) { ok = false; break; }
-          ((mode == PM_DQ) ? p.rowdot_q : p.rowdot_k)[(size_t)(o_tile0 + sub) * p.ntok + tok] = sh.s_qn[0][r] + sh.s_qn[1][r];
+          ((mode == PM_DQ) ? p.rowdot_q : p.rowdot_k)[(size_t)(o_tile0 + sub) * p.nslots + tok] = sh.s_qn[0][r] + sh.s_qn[1][r];
         }
       }
       if (sub + 1 < nsub) {
@@ -842,7 +846,8 @@ par_bw_sm100(const __grid_constant__ CUtensorMap mQ, const __grid_constant__ CUt
 // Host side
 // =====================================================================================================
 bool sm100_supported(int S, int DHQK, int DHHV, int L, int dtype) {
-  return dtype == MLSTM_BF16 && L == CL && S % CL == 0 && DHQK % 128 == 0 && DHHV % 128 == 0 && DHQK <= 512 &&
+  // any sequence length: a ragged last chunk is handled by zero-filled loads and masked stores
+  return dtype == MLSTM_BF16 && L == CL && S >= 1 && DHQK % 128 == 0 && DHHV % 128 == 0 && DHQK <= 512 &&
          DHHV <= 1024;
 }
 
@@ -850,7 +855,7 @@ bool sm100_supported(int S, int DHQK, int DHHV, int L, int dtype) {
 // every grid must stay below 2^31.
 bool sm100_sizes_ok(int B, int NH, int S, int DHQK, int DHHV) {
   const uint64_t lim = 0x7fffffffull;
-  const uint64_t bnh = (uint64_t)B * NH, nc = (uint64_t)S / CL;
+  const uint64_t bnh = (uint64_t)B * NH, nc = ((uint64_t)S + CL - 1) / CL;
   const uint64_t tiles = (uint64_t)(DHHV / 128 + 2 * (DHQK / 128));
   return bnh * S < lim && bnh * (nc + 1) * DHQK < lim && bnh * nc * tiles < lim &&
          bnh * (uint64_t)(DHHV / 128) * (DHQK / 128) < lim;
@@ -870,30 +875,36 @@ static int set_smem_once(K kern, int bytes, bool (&done)[64]) {
 
 // Tensor maps depend only on (base pointer, rows, columns, box): a training loop calls with the same buffers over
 // and over, so the last few encodings are kept per thread instead of calling the driver 3-7 times per launch.
-struct MapKey { const void* base; uint64_t rows, cols; uint32_t box_rows, box_cols; };
+struct MapKey { const void* base; uint64_t rows, cols, slabs; uint32_t box_rows, box_cols; };
+// slabs == 0: plain 2-D matrix [rows x cols]; otherwise a 3-D tensor [slabs x rows x cols]
 static bool cached_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
-                       uint32_t box_cols) {
+                       uint32_t box_cols, uint64_t slabs = 0) {
   constexpr int N = 32;
   static thread_local MapKey keys[N];
   static thread_local CUtensorMap maps[N];
   static thread_local int used = 0, next = 0;
   for (int i = 0; i < used; ++i) {
     const MapKey& k = keys[i];
-    if (k.base == base && k.rows == rows && k.cols == cols && k.box_rows == box_rows && k.box_cols == box_cols) {
+    if (k.base == base && k.rows == rows && k.cols == cols && k.slabs == slabs && k.box_rows == box_rows &&
+        k.box_cols == box_cols) {
       *m = maps[i];
       return true;
     }
   }
-  if (!sm100_host::make_map_bf16(m, base, rows, cols, box_rows, box_cols)) return false;
-  keys[next] = MapKey{base, rows, cols, box_rows, box_cols};
+  const bool ok = slabs == 0 ? sm100_host::make_map_bf16(m, base, rows, cols, box_rows, box_cols)
+                             : sm100_host::make_map_bf16_3d(m, base, slabs, rows, cols, box_rows, box_cols);
+  if (!ok) return false;
+  keys[next] = MapKey{base, rows, cols, slabs, box_rows, box_cols};
   maps[next] = *m;
   next = (next + 1) % N;
   if (used < N) ++used;
   return true;
 }
 
-static bool tok_map(CUtensorMap* m, const void* base, const ChunkwiseDims& d, int cols) {
-  return cached_map(m, base, (uint64_t)d.B * d.NH * d.S, (uint64_t)cols, 128, 64);
+// token tensors (q, k, v, deltaH): one slab of S rows per (batch, head), so that a box hanging over the end of a
+// sequence (ragged last chunk) reads zeros instead of the next head's tokens
+static bool tok_map(CUtensorMap* m, const void* base, const ChunkwiseDims& d, int cols, int box_rows = 128) {
+  return cached_map(m, base, (uint64_t)d.S, (uint64_t)cols, box_rows, 64, (uint64_t)d.B * d.NH);
 }
 static bool state_map(CUtensorMap* m, const void* base, const ChunkwiseDims& d, int box_rows) {
   return cached_map(m, base, (uint64_t)d.B * d.NH * (d.NC + 1) * d.DHQK, (uint64_t)d.DHHV, box_rows, 64);
@@ -903,10 +914,7 @@ template <bool BWD>
 static int launch_rec(const void* left, const void* right, const RecParams& rp, const ChunkwiseDims& d, cudaStream_t st) {
   CUtensorMap mL, mR, mS;
   // recurrence operands arrive in half-chunk boxes (64 tokens x 64 columns)
-  const uint64_t ntok = (uint64_t)d.B * d.NH * d.S;
-  if (!cached_map(&mL, left, ntok, (uint64_t)d.DHQK, REC_HALF, 64) ||
-      !cached_map(&mR, right, ntok, (uint64_t)d.DHHV, REC_HALF, 64))
-    return MLSTM_ERR_CUDA;
+  if (!tok_map(&mL, left, d, d.DHQK, REC_HALF) || !tok_map(&mR, right, d, d.DHHV, REC_HALF)) return MLSTM_ERR_CUDA;
   // store map over the per-chunk states; when no states are wanted (segment summary) the map is never used
   if (!state_map(&mS, rp.c_states ? (const void*)rp.c_states : left, d, 128)) return MLSTM_ERR_CUDA;
   auto kern = rec_sm100<BWD>;
@@ -923,7 +931,7 @@ int sm100_recurrent_fw(const void* k, const void* v, const GateBuffers& gb, cons
                        const ChunkwiseDims& d, cudaStream_t st) {
   PhaseScope ps(PH_REC_FW, st);
   RecParams rp{gb.abar, nullptr, 1.f, gb.gbar, c_initial, n_initial, (__nv_bfloat16*)c_states,
-               d.variant == MLSTM_SIG_NONORM ? nullptr : n_states, c_last, d.variant == MLSTM_SIG_NONORM ? nullptr : n_last, d.S, d.NC, d.DHQK, d.DHHV};
+               d.variant == MLSTM_SIG_NONORM ? nullptr : n_states, c_last, d.variant == MLSTM_SIG_NONORM ? nullptr : n_last, d.S, d.SP, d.NC, d.DHQK, d.DHHV};
   return launch_rec<false>(k, v, rp, d, st);
 }
 
@@ -931,7 +939,7 @@ int sm100_recurrent_bw(const void* q, const void* dh, const GateBuffers& gb, con
                        float* dc_initial, const ChunkwiseDims& d, cudaStream_t st) {
   PhaseScope ps(PH_REC_BW, st);
   RecParams rp{gb.bbar, gb.inv_den, d.qk_scale, gb.gbar, dc_last, nullptr, (__nv_bfloat16*)dc_states, nullptr,
-               dc_initial, nullptr, d.S, d.NC, d.DHQK, d.DHHV};
+               dc_initial, nullptr, d.S, d.SP, d.NC, d.DHQK, d.DHHV};
   return launch_rec<true>(q, dh, rp, d, st);
 }
 
@@ -939,8 +947,8 @@ static ParParams base_params(const GateBuffers& gb, const ChunkwiseDims& d) {
   ParParams pp{};
   pp.vecB = gb.vecB; pp.iota = gb.iota; pp.m_tok = gb.m_tok; pp.abar = gb.abar; pp.bbar = gb.bbar;
   pp.inv_den = gb.inv_den;
-  pp.ntok = (size_t)d.B * d.NH * d.S;
-  pp.S = d.S; pp.NC = d.NC; pp.DHQK = d.DHQK; pp.DHHV = d.DHHV; pp.variant = d.variant; pp.eps = d.eps;
+  pp.nslots = (size_t)d.B * d.NH * d.SP;
+  pp.S = d.S; pp.SP = d.SP; pp.NC = d.NC; pp.DHQK = d.DHQK; pp.DHHV = d.DHHV; pp.variant = d.variant; pp.eps = d.eps;
   pp.qk_scale = d.qk_scale;
   return pp;
 }

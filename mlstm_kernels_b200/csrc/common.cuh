@@ -4,6 +4,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
+#include <math.h>
 #include <stdint.h>
 
 #include "../../include/mlstm_b200.h"
@@ -72,14 +73,24 @@ inline bool is_pow2(int x) { return x > 0 && (x & (x - 1)) == 0; }
 inline size_t dtype_size(int dtype) { return dtype == MLSTM_F32 ? 4 : 2; }
 
 // Problem description passed to every launcher.
+// The last chunk may be ragged (S not a multiple of L; tcgen05 path only): NC = ceil(S / L) and the library's own
+// per-token vectors are laid out with SP = NC * L slots per (batch, head), the slots past S holding neutral values
+// (input gate switched off, nothing decays), so that the contraction kernels need no per-token bounds checks on
+// them.  User-visible per-token arrays (i, f, n_out, m_out, dI, dF) keep S entries per (batch, head).
 struct ChunkwiseDims {
   int B, NH, S, DHQK, DHHV, L, NC;
   int variant;  // MLSTM_EXP / MLSTM_SIG / MLSTM_SIG_NONORM
   float eps;
   float qk_scale;
+  int SP;       // NC * L
 };
+inline ChunkwiseDims make_dims(int B, int NH, int S, int DHQK, int DHHV, int L, int variant, float eps) {
+  const int NC = (S + L - 1) / L;
+  return ChunkwiseDims{B, NH, S, DHQK, DHHV, L, NC, variant, eps, 1.0f / sqrtf((float)DHQK), NC * L};
+}
 
 // Per-token / per-chunk gate vectors produced by the gate pre-pass (all f32, device memory).
+// Per-token arrays have SP slots per (batch, head) (see ChunkwiseDims).
 struct GateBuffers {
   float* vecB;     // (BNH, S)  in-chunk inclusive cumsum of logsigmoid(f)
   float* iota;     // (BNH, S)  i, or logsigmoid(i) for the sigmoid input gate

@@ -22,8 +22,8 @@ constexpr int kGateThreads = 256;
 //   gates_token_kernel  m_i, abar_j, bbar_i, 1/(den+eps)   one warp per chunk
 template <typename T>
 __global__ void __launch_bounds__(kGateThreads)
-gates_chunk_kernel(const T* __restrict__ vecI, const T* __restrict__ vecF, GateBuffers gb, int S, int L, int NC,
-                   int variant) {
+gates_chunk_kernel(const T* __restrict__ vecI, const T* __restrict__ vecF, GateBuffers gb, int S, int SP, int L,
+                   int NC, int variant) {
   const int bh = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int k = blockIdx.x * (kGateThreads / 32) + warp;
@@ -31,11 +31,15 @@ gates_chunk_kernel(const T* __restrict__ vecI, const T* __restrict__ vecF, GateB
   const bool siging = variant != MLSTM_EXP;
   float* g_arr = gb.scratch + (size_t)bh * 2 * NC;
   float* amax_arr = g_arr + NC;
-  const size_t base = (size_t)bh * S + (size_t)k * L;
+  // inputs have S tokens per (batch, head), the gate vectors SP = NC * L slots; slots past the sequence end are
+  // filled with neutral values: log forget gate 0 (nothing decays), input gate -inf (contributes nothing)
+  const size_t base_in = (size_t)bh * S + (size_t)k * L;
+  const size_t base = (size_t)bh * SP + (size_t)k * L;
+  const int valid = min(L, S - k * L);
   float carry = 0.f;
   for (int j0 = 0; j0 < L; j0 += 32) {
     const int j = j0 + lane;
-    float x = (j < L) ? logsigmoid_f(to_f32(vecF[base + j])) : 0.f;
+    float x = (j < valid) ? logsigmoid_f(to_f32(vecF[base_in + j])) : 0.f;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
       float y = __shfl_up_sync(0xffffffffu, x, o);
@@ -50,7 +54,7 @@ gates_chunk_kernel(const T* __restrict__ vecI, const T* __restrict__ vecF, GateB
   float suffix = 0.f, amax = -INFINITY;
   for (int j0 = ((L - 1) / 32) * 32; j0 >= 0; j0 -= 32) {
     const int j = j0 + lane;
-    float x = (j < L) ? logsigmoid_f(to_f32(vecF[base + j])) : 0.f;
+    float x = (j < valid) ? logsigmoid_f(to_f32(vecF[base_in + j])) : 0.f;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
       float y = __shfl_down_sync(0xffffffffu, x, o);
@@ -61,8 +65,11 @@ gates_chunk_kernel(const T* __restrict__ vecI, const T* __restrict__ vecF, GateB
     excl += suffix;
     suffix += __shfl_sync(0xffffffffu, x, 0);
     if (j < L) {
-      const float iv = to_f32(vecI[base + j]);
-      const float iota = siging ? logsigmoid_f(iv) : iv;
+      float iota = -INFINITY;
+      if (j < valid) {
+        const float iv = to_f32(vecI[base_in + j]);
+        iota = siging ? logsigmoid_f(iv) : iv;
+      }
       const float a = excl + iota;
       gb.iota[base + j] = iota;
       gb.abar[base + j] = a;  // finalised by gates_token_kernel
@@ -115,14 +122,16 @@ gates_scan_kernel(const float* __restrict__ m_initial, GateBuffers gb, float* __
 }
 
 __global__ void __launch_bounds__(kGateThreads)
-gates_token_kernel(const float* __restrict__ n_out, GateBuffers gb, const float* __restrict__ m_states, int S, int L,
-                   int NC, int variant, float eps) {
+gates_token_kernel(const float* __restrict__ n_out, float* __restrict__ m_out, GateBuffers gb,
+                   const float* __restrict__ m_states, int S, int SP, int L, int NC, int variant, float eps) {
   const int bh = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int k = blockIdx.x * (kGateThreads / 32) + warp;
   if (k >= NC) return;
   const bool siging = variant != MLSTM_EXP;
-  const size_t base = (size_t)bh * S + (size_t)k * L;
+  const size_t base_in = (size_t)bh * S + (size_t)k * L;
+  const size_t base = (size_t)bh * SP + (size_t)k * L;
+  const int valid = min(L, S - k * L);
   const float m_prev = m_states[(size_t)bh * (NC + 1) + k];
   const float m_next = m_states[(size_t)bh * (NC + 1) + k + 1];
   float carry = -INFINITY;
@@ -147,11 +156,14 @@ gates_token_kernel(const float* __restrict__ n_out, GateBuffers gb, const float*
         bbar = expf(b + m_prev - m_i);
         abar = expf(a - m_next);
       }
+      const bool pad = j >= valid;     // slot past the sequence end: finite max state, every factor zero
       gb.m_tok[base + j] = m_i;
-      gb.bbar[base + j] = bbar;
-      gb.abar[base + j] = abar;
+      gb.bbar[base + j] = pad ? 0.f : bbar;
+      gb.abar[base + j] = pad ? 0.f : abar;
+      if (m_out != nullptr && !pad) m_out[base_in + j] = m_i;
       if (gb.inv_den) {
-        gb.inv_den[base + j] = (variant == MLSTM_SIG_NONORM || n_out == nullptr) ? 1.f : 1.f / (n_out[base + j] + eps);
+        gb.inv_den[base + j] = pad ? 0.f
+                               : ((variant == MLSTM_SIG_NONORM || n_out == nullptr) ? 1.f : 1.f / (n_out[base_in + j] + eps));
       }
     }
   }
@@ -182,15 +194,28 @@ gate_grad_rows_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
 // qdq / kdk may arrive as `nparts` partial sums (one per 128-wide head-dim tile), `part_stride` floats apart;
 // they are added in a fixed order, so the result does not depend on scheduling.
 // One CTA per (batch, head); each thread owns a contiguous token range, block scan over the range sums.
+//
+// Anchors (tcgen05 path).  q.dq and k.dk nearly cancel, and what is left of their rounding errors (bf16 states and
+// operands) adds up along the reverse sum like a random walk: its error grows with the square root of the sequence
+// length.  At a chunk boundary the exact value of the sum is known in closed form: with C_k the state before chunk k
+// and dC_k its gradient,  sum over all tokens t' >= k L of (q.dq - k.dk) = <C_k, dC_k> - <C_NC, dC_NC>
+// (the per-chunk totals telescope: <C_k, dP_k> - <P_k, dC_{k+1}> = <C_k, dC_k> - <C_{k+1}, dC_{k+1}> for
+// C_{k+1} = g C_k + P_k, dC_k = g dC_{k+1} + dP_k).  `anchors` holds those inner products for every
+// `anchor_tokens`-th token position (state_dot_kernel); the running sum of a token is then taken from the next anchor
+// instead of from the end of the sequence, which bounds the walk to one anchor interval.
 constexpr int kScanThreads = 1024;
+constexpr int kMaxAnchors = 1024;
 template <typename T>
 __global__ void __launch_bounds__(kScanThreads)
 gate_grad_scan_kernel(const T* __restrict__ vecI, const T* __restrict__ vecF, const float* __restrict__ qdq,
                       const float* __restrict__ kdk, float* __restrict__ dI, float* __restrict__ dF,
-                      int S, int variant, int nparts, size_t part_stride) {
+                      int S, int SP, int variant, int nparts, size_t part_stride, const float* __restrict__ anchors,
+                      int n_anchors, int anchor_tokens) {
   __shared__ float s_part[kScanThreads];
+  __shared__ float s_run_at_anchor[kMaxAnchors];
   const int bh = blockIdx.x, t = threadIdx.x;
-  const size_t base = (size_t)bh * S;
+  const size_t base = (size_t)bh * S;      // gate logits and outputs: S tokens per (batch, head)
+  const size_t pbase = (size_t)bh * SP;    // row sums: SP slots per (batch, head)
   const int seg = (S + kScanThreads - 1) / kScanThreads;
   const int s0 = min(S, t * seg), s1 = min(S, (t + 1) * seg);
   auto parts = [&](const float* src, size_t idx) {
@@ -199,7 +224,7 @@ gate_grad_scan_kernel(const T* __restrict__ vecI, const T* __restrict__ vecF, co
     return t;
   };
   float sum = 0.f;
-  for (int s = s0; s < s1; ++s) sum += parts(qdq, base + s) - parts(kdk, base + s);
+  for (int s = s0; s < s1; ++s) sum += parts(qdq, pbase + s) - parts(kdk, pbase + s);
   s_part[t] = sum;
   __syncthreads();
   // suffix sums over threads (exclusive): sum of the ranges to the right
@@ -209,38 +234,88 @@ gate_grad_scan_kernel(const T* __restrict__ vecI, const T* __restrict__ vecF, co
     s_part[t] += y;
     __syncthreads();
   }
-  float run = (t + 1 < kScanThreads) ? s_part[t + 1] : 0.f;
+  const float run0 = (t + 1 < kScanThreads) ? s_part[t + 1] : 0.f;
+  const bool anchored = anchors != nullptr;
+  if (anchored) {   // value of the plain running sum at every interior anchor position
+    float run = run0;
+    for (int s = s1 - 1; s >= s0; --s) {
+      run += parts(qdq, pbase + s) - parts(kdk, pbase + s);
+      if (s > 0 && s % anchor_tokens == 0) s_run_at_anchor[s / anchor_tokens] = run;
+    }
+    __syncthreads();
+  }
+  const float* anc = anchored ? anchors + (size_t)bh * n_anchors : nullptr;
+  float run = run0;
   for (int s = s1 - 1; s >= s0; --s) {
-    float di = parts(kdk, base + s);
-    run += parts(qdq, base + s) - di;
-    dF[base + s] = run * sigmoid_f(-to_f32(vecF[base + s]));
+    float di = parts(kdk, pbase + s);
+    run += parts(qdq, pbase + s) - di;
+    float total = run;
+    if (anchored) {
+      const int a = s / anchor_tokens + 1;   // next anchor after this token; the last one is the end of the sequence
+      if (a < n_anchors - 1) total = (run - s_run_at_anchor[a]) + (anc[a] - anc[n_anchors - 1]);
+    }
+    dF[base + s] = total * sigmoid_f(-to_f32(vecF[base + s]));
     if (variant != MLSTM_EXP) di *= sigmoid_f(-to_f32(vecI[base + s]));
     dI[base + s] = di;
   }
 }
 
+// anchors[bh][a] = <C_k, dC_k> over the whole DHQK x DHHV state, k = min(a * every, NC), a = 1 .. n_anchors - 1
+// (a = 0 is never read).  One CTA per (anchor, batch x head); the partial sums are added in a fixed order.
+__global__ void __launch_bounds__(256)
+state_dot_kernel(const __nv_bfloat16* __restrict__ c_states, const __nv_bfloat16* __restrict__ dc_states,
+                 float* __restrict__ anchors, int NC, int every, int n_anchors, size_t state_elems) {
+  __shared__ float s_w[8];
+  const int bh = blockIdx.y, a = blockIdx.x + 1;
+  const int k = min(a * every, NC);
+  const size_t off = ((size_t)bh * (NC + 1) + k) * state_elems;
+  const uint4* pc = reinterpret_cast<const uint4*>(c_states + off);
+  const uint4* pd = reinterpret_cast<const uint4*>(dc_states + off);
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (size_t idx = threadIdx.x; idx < state_elems / 8; idx += 256) {
+    const uint4 x = __ldcs(pc + idx), y = __ldcs(pd + idx);
+    const uint32_t xw[4] = {x.x, x.y, x.z, x.w}, yw[4] = {y.x, y.y, y.z, y.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const __nv_bfloat162 xa = *reinterpret_cast<const __nv_bfloat162*>(&xw[e]);
+      const __nv_bfloat162 ya = *reinterpret_cast<const __nv_bfloat162*>(&yw[e]);
+      acc[e] = fmaf(__low2float(xa), __low2float(ya), acc[e]);
+      acc[e] = fmaf(__high2float(xa), __high2float(ya), acc[e]);
+    }
+  }
+  float v = warp_sum((acc[0] + acc[1]) + (acc[2] + acc[3]));
+  if ((threadIdx.x & 31) == 0) s_w[threadIdx.x >> 5] = v;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float tot = 0.f;
+    for (int w = 0; w < 8; ++w) tot += s_w[w];
+    anchors[(size_t)bh * n_anchors + a] = tot;
+  }
+}
+
 // ---- launchers ----------------------------------------------------------------------------------
 template <typename T>
-int launch_gates_t(const void* i, const void* f, const float* m_initial, const float* n_out, const GateBuffers& gb,
-                   float* m_states, const ChunkwiseDims& d, cudaStream_t st, float m_default, float* g_sum) {
+int launch_gates_t(const void* i, const void* f, const float* m_initial, const float* n_out, float* m_out,
+                   const GateBuffers& gb, float* m_states, const ChunkwiseDims& d, cudaStream_t st, float m_default,
+                   float* g_sum) {
   PhaseScope ps(PH_GATES, st);
   const dim3 grid(ceil_div(d.NC, kGateThreads / 32), d.B * d.NH);
-  gates_chunk_kernel<T><<<grid, kGateThreads, 0, st>>>((const T*)i, (const T*)f, gb, d.S, d.L, d.NC, d.variant);
+  gates_chunk_kernel<T><<<grid, kGateThreads, 0, st>>>((const T*)i, (const T*)f, gb, d.S, d.SP, d.L, d.NC, d.variant);
   MLSTM_LAUNCH_CHECK();
   gates_scan_kernel<<<d.B * d.NH, kGateThreads, 0, st>>>(m_initial, gb, m_states, d.NC, d.variant, m_default, g_sum);
   MLSTM_LAUNCH_CHECK();
-  gates_token_kernel<<<grid, kGateThreads, 0, st>>>(n_out, gb, m_states, d.S, d.L, d.NC, d.variant, d.eps);
+  gates_token_kernel<<<grid, kGateThreads, 0, st>>>(n_out, m_out, gb, m_states, d.S, d.SP, d.L, d.NC, d.variant, d.eps);
   MLSTM_LAUNCH_CHECK();
   return MLSTM_OK;
 }
 
-int launch_gates(int dtype, const void* i, const void* f, const float* m_initial, const float* n_out,
+int launch_gates(int dtype, const void* i, const void* f, const float* m_initial, const float* n_out, float* m_out,
                  const GateBuffers& gb, float* m_states, const ChunkwiseDims& d, cudaStream_t st, float m_default,
                  float* g_sum) {
   switch (dtype) {
-    case MLSTM_F32: return launch_gates_t<float>(i, f, m_initial, n_out, gb, m_states, d, st, m_default, g_sum);
-    case MLSTM_BF16: return launch_gates_t<__nv_bfloat16>(i, f, m_initial, n_out, gb, m_states, d, st, m_default, g_sum);
-    case MLSTM_F16: return launch_gates_t<__half>(i, f, m_initial, n_out, gb, m_states, d, st, m_default, g_sum);
+    case MLSTM_F32: return launch_gates_t<float>(i, f, m_initial, n_out, m_out, gb, m_states, d, st, m_default, g_sum);
+    case MLSTM_BF16: return launch_gates_t<__nv_bfloat16>(i, f, m_initial, n_out, m_out, gb, m_states, d, st, m_default, g_sum);
+    case MLSTM_F16: return launch_gates_t<__half>(i, f, m_initial, n_out, m_out, gb, m_states, d, st, m_default, g_sum);
   }
   return MLSTM_ERR_DTYPE;
 }
@@ -278,7 +353,7 @@ int launch_gate_grads(int dtype, int gate_dtype, const void* q, const void* k, c
     case MLSTM_F16: rc = launch_gate_grad_rows_t<__half>(q, k, dq, dk, acc, kdk, d, st); break;
   }
   if (rc != MLSTM_OK) return rc;
-  return launch_gate_grad_scan(gate_dtype, i, f, acc, kdk, 1, dI, dF, d, st);
+  return launch_gate_grad_scan(gate_dtype, i, f, acc, kdk, 1, dI, dF, d, st, nullptr, 0, 1);
 }
 
 // Joins the state a sequence segment produced from the EMPTY state (C = 0, n = 0, m = -inf) onto the state that
@@ -324,39 +399,64 @@ int launch_state_combine(const float* c_in, const float* n_in, const float* m_in
   return MLSTM_OK;
 }
 
-// inv_den_t = 1 / (n_out_t + eps), or 1 where the variant has no normaliser
+// inv_den_t = 1 / (n_out_t + eps), or 1 where the variant has no normaliser; 0 in the slots past the sequence end
+// (n_out has S entries per (batch, head), inv_den SP slots)
 __global__ void __launch_bounds__(256)
-inv_den_kernel(const float* __restrict__ n_out, float* __restrict__ inv_den, size_t ntok, int variant, float eps) {
+inv_den_kernel(const float* __restrict__ n_out, float* __restrict__ inv_den, size_t nslots, int S, int SP, int variant,
+               float eps) {
   const size_t t = (size_t)blockIdx.x * 256 + threadIdx.x;
-  if (t < ntok) inv_den[t] = (variant == MLSTM_SIG_NONORM || n_out == nullptr) ? 1.f : 1.f / (n_out[t] + eps);
+  if (t >= nslots) return;
+  const size_t bh = t / SP;
+  const int s = (int)(t - bh * SP);
+  float v = 0.f;
+  if (s < S) v = (variant == MLSTM_SIG_NONORM || n_out == nullptr) ? 1.f : 1.f / (n_out[bh * S + s] + eps);
+  inv_den[t] = v;
 }
 
-int launch_inv_den(const float* n_out, float* inv_den, size_t ntok, int variant, float eps, cudaStream_t st) {
+int launch_inv_den(const float* n_out, float* inv_den, const ChunkwiseDims& d, cudaStream_t st) {
   PhaseScope ps(PH_GATES, st);
-  inv_den_kernel<<<(unsigned)((ntok + 255) / 256), 256, 0, st>>>(n_out, inv_den, ntok, variant, eps);
+  const size_t nslots = (size_t)d.B * d.NH * d.SP;
+  inv_den_kernel<<<(unsigned)((nslots + 255) / 256), 256, 0, st>>>(n_out, inv_den, nslots, d.S, d.SP, d.variant, d.eps);
   MLSTM_LAUNCH_CHECK();
   return MLSTM_OK;
 }
 
 // Scan-only entry: the row sums were already produced (in f32, before rounding) by the backward kernels.
+// With `anchors` (see gate_grad_scan_kernel) the reverse sum restarts from an exact value every `anchor_tokens` tokens.
 int launch_gate_grad_scan(int dtype, const void* i, const void* f, const float* qdq, const float* kdk, int nparts,
-                          float* dI, float* dF, const ChunkwiseDims& d, cudaStream_t st) {
-  const size_t stride = (size_t)d.B * d.NH * d.S;
+                          float* dI, float* dF, const ChunkwiseDims& d, cudaStream_t st, const float* anchors,
+                          int n_anchors, int anchor_tokens) {
+  const size_t stride = (size_t)d.B * d.NH * d.SP;
+  if (n_anchors > kMaxAnchors) anchors = nullptr;   // sequences beyond kMaxAnchors intervals fall back to the plain sum
   switch (dtype) {
     case MLSTM_F32:
       gate_grad_scan_kernel<float><<<d.B * d.NH, kScanThreads, 0, st>>>((const float*)i, (const float*)f, qdq, kdk,
-                                                                        dI, dF, d.S, d.variant, nparts, stride);
+                                                                        dI, dF, d.S, d.SP, d.variant, nparts,
+                                                                        stride, anchors, n_anchors, anchor_tokens);
       break;
     case MLSTM_BF16:
       gate_grad_scan_kernel<__nv_bfloat16><<<d.B * d.NH, kScanThreads, 0, st>>>(
-          (const __nv_bfloat16*)i, (const __nv_bfloat16*)f, qdq, kdk, dI, dF, d.S, d.variant, nparts, stride);
+          (const __nv_bfloat16*)i, (const __nv_bfloat16*)f, qdq, kdk, dI, dF, d.S, d.SP, d.variant, nparts, stride,
+          anchors, n_anchors, anchor_tokens);
       break;
     case MLSTM_F16:
       gate_grad_scan_kernel<__half><<<d.B * d.NH, kScanThreads, 0, st>>>((const __half*)i, (const __half*)f, qdq, kdk,
-                                                                         dI, dF, d.S, d.variant, nparts, stride);
+                                                                         dI, dF, d.S, d.SP, d.variant, nparts,
+                                                                         stride, anchors, n_anchors, anchor_tokens);
       break;
     default: return MLSTM_ERR_DTYPE;
   }
+  MLSTM_LAUNCH_CHECK();
+  return MLSTM_OK;
+}
+
+// <C_k, dC_k> at every `every`-th chunk boundary and at the end (bf16 states of the tcgen05 path).
+int launch_state_dot(const void* c_states, const void* dc_states, float* anchors, int every, int n_anchors,
+                     const ChunkwiseDims& d, cudaStream_t st) {
+  if (n_anchors < 2) return MLSTM_OK;
+  dim3 grid(n_anchors - 1, d.B * d.NH);
+  state_dot_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)c_states, (const __nv_bfloat16*)dc_states, anchors, d.NC,
+                                         every, n_anchors, (size_t)d.DHQK * d.DHHV);
   MLSTM_LAUNCH_CHECK();
   return MLSTM_OK;
 }

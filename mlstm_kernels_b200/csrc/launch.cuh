@@ -5,10 +5,11 @@
 namespace mlstm {
 
 // gates.cu
-int launch_gates(int dtype, const void* i, const void* f, const float* m_initial, const float* n_out,
+// m_out (nullable): user-visible copy of the per-token max state, S entries per (batch, head)
+int launch_gates(int dtype, const void* i, const void* f, const float* m_initial, const float* n_out, float* m_out,
                  const GateBuffers& gb, float* m_states, const ChunkwiseDims& d, cudaStream_t st,
                  float m_default = 0.f, float* g_sum = nullptr);
-int launch_inv_den(const float* n_out, float* inv_den, size_t ntok, int variant, float eps, cudaStream_t st);
+int launch_inv_den(const float* n_out, float* inv_den, const ChunkwiseDims& d, cudaStream_t st);
 int launch_state_combine(const float* c_in, const float* n_in, const float* m_in, const float* c_loc,
                          const float* n_loc, const float* m_loc, const float* g_total, float* c_out, float* n_out,
                          float* m_out, int BNH, int DHQK, int DHHV, int variant, cudaStream_t st);
@@ -16,7 +17,10 @@ int launch_gate_grads(int dtype, int gate_dtype, const void* q, const void* k, c
                       const void* f, float* acc, float* kdk, float* dI, float* dF, const ChunkwiseDims& d,
                       cudaStream_t st);
 int launch_gate_grad_scan(int dtype, const void* i, const void* f, const float* qdq, const float* kdk, int nparts,
-                          float* dI, float* dF, const ChunkwiseDims& d, cudaStream_t st);
+                          float* dI, float* dF, const ChunkwiseDims& d, cudaStream_t st, const float* anchors,
+                          int n_anchors, int anchor_tokens);
+int launch_state_dot(const void* c_states, const void* dc_states, float* anchors, int every, int n_anchors,
+                     const ChunkwiseDims& d, cudaStream_t st);
 
 // chunkwise_simt.cu : portable CUDA-core kernels, any shape, any element type
 int simt_recurrent_fw(int dtype, int state_dtype, const void* k, const void* v, const GateBuffers& gb,

@@ -13,7 +13,7 @@
 
 namespace {
 
-constexpr size_t kStaticScratchBytes = 8u << 20;  // 8 MiB, enough for about 500k (batch x head x token) units
+constexpr size_t kStaticScratchBytes = 8u << 20;  // 8 MiB, enough for about 400k (batch x head x token) units
 __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 constexpr int kMaxDevices = 64;

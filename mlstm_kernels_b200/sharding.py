@@ -27,7 +27,7 @@ import torch
 import torch.distributed as dist
 
 from . import _lib
-from .chunkwise import chunkwise_bw_raw, chunkwise_fw_raw, kernel_chunk_size, select_chunk_size
+from .chunkwise import chunkwise_bw_raw, chunkwise_fw_raw, resolve_chunk_size
 
 
 def shard_range(total: int, world: int, rank: int) -> tuple[int, int]:
@@ -234,7 +234,7 @@ def mlstm_chunkwise_sequence_parallel(
     variant = _variant(siging, normalize)
     B, NH, S, DHQK = q.shape
     DHHV = v.shape[-1]
-    L = kernel_chunk_size(q, v, select_chunk_size(S, chunk_size), impl)
+    L = resolve_chunk_size(q, v, chunk_size, impl)
     dev = q.device
     ranks = dist.get_process_group_ranks(group) if group is not None else list(range(world))
     zeros = (torch.zeros((B, NH, DHQK, DHHV), dtype=torch.float32, device=dev),

@@ -317,20 +317,24 @@ def test_recompute_states_in_bw(variant, impl, dtype, shape):
     inp = case_inputs(41, B, NH, S, DHQK, DHHV, init=True, dC_last=True)
     siging = variant != "exp"
     fn = mk.mlstm_siging_chunkwise__b200_xl_chunk if siging else mk.mlstm_chunkwise__b200_xl_chunk
-    res, held = {}, {}
-    for rc in (True, False):
+    def run(rc):
         leaves = [to_dev(inp[n], dtype, True) for n in "qkvif"]
         c0 = to_dev(inp["c0"], torch.float32, True)
         n0, m0 = to_dev(inp["n0"], torch.float32), to_dev(inp["m0"], torch.float32)
+        dh, dcl = to_dev(inp["dH"], torch.float32), to_dev(inp["dC_last"], torch.float32)
         torch.cuda.synchronize()
         base = torch.cuda.memory_allocated()
         h, last = fn(*leaves, c0, n0, None if siging else m0, True, chunk_size=L, impl=impl,
                      recompute_states_in_bw=rc)
-        loss = (h.float() * to_dev(inp["dH"], torch.float32)).sum() + (last[0] * to_dev(inp["dC_last"], torch.float32)).sum()
         torch.cuda.synchronize()
-        held[rc] = torch.cuda.memory_allocated() - base
+        held_bytes = torch.cuda.memory_allocated() - base     # outputs + what autograd keeps for the backward
+        loss = (h.float() * dh).sum() + (last[0] * dcl).sum()
         loss.backward()
-        res[rc] = [npy(h)] + [npy(t.grad) for t in leaves] + [npy(c0.grad)]
+        return [npy(h)] + [npy(t.grad) for t in leaves] + [npy(c0.grad)], held_bytes
+
+    res, held = {}, {}
+    for rc in (True, False):
+        res[rc], held[rc] = run(rc)
     for a, b in zip(res[True], res[False]):
         assert np.array_equal(a, b)
     state_bytes = B * NH * (S // L + 1) * DHQK * DHHV * (2 if impl == "auto" else 4)
@@ -362,3 +366,49 @@ def test_bounded_wait_expiry_is_reported():
     ref = run_oracle_fwbw(inp, 128, dtype=torch.bfloat16)
     compare(got, ref, TOL_BF16, TOL_BF16)
     assert _lib.device_status(reset=True) == 903
+
+
+def _largest_divisor_up_to(n, cap):
+    return max(d for d in range(1, cap + 1) if n % d == 0)
+
+
+@pytest.mark.parametrize("shape", [(2, 2, 300, 128, 128), (1, 2, 64, 256, 256), (1, 2, 448, 128, 256),
+                                   (1, 1, 129, 256, 256), (1, 2, 1000, 128, 128), (2, 1, 17, 128, 128)])
+@pytest.mark.parametrize("variant", ["exp", "sig", "sig_nonorm"])
+def test_tcgen05_any_sequence_length(shape, variant):
+    """On the tcgen05 path the sequence length need not be a multiple of the chunk size (nor of 16): the last chunk
+    is ragged, its missing tokens are read as zeros and switched off in the gates, and no row past S is written.
+    Checked against the oracle run with a chunk size that divides S (H and the gradients do not depend on the chunk
+    size; the (C, n, m) triple is compared through C exp(m), n exp(m)), with initial states and an incoming state
+    gradient."""
+    B, NH, S, DHQK, DHHV = shape
+    inp = case_inputs(71, B, NH, S, DHQK, DHHV, init=True, dC_last=(variant != "exp"))
+    siging, normalize = variant != "exp", variant != "sig_nonorm"
+    q, v = to_dev(inp["q"], torch.bfloat16), to_dev(inp["v"], torch.bfloat16)
+    assert mk.resolve_chunk_size(q, v, 64) == 128
+    got = run_cuda_fwbw(inp, 64, dtype=torch.bfloat16, siging=siging, normalize=normalize)
+    assert got["H"].shape == (B, NH, S, DHHV) and got["dF"].shape == (B, NH, S)
+    ref = run_oracle_fwbw(inp, _largest_divisor_up_to(S, 128), dtype=torch.bfloat16, siging=siging, normalize=normalize)
+    compare(got, ref, TOL_BF16, TOL_BF16, keys_fw=("H",))
+    if siging:
+        assert max_rel_err(got["C_last"], ref["C_last"]) < TOL_BF16
+        if normalize:
+            assert max_rel_err(got["n_last"], ref["n_last"]) < TOL_BF16
+    else:
+        sg, sr = np.exp(got["m_last"]), np.exp(ref["m_last"])
+        assert max_rel_err(got["C_last"] * sg[..., None], ref["C_last"] * sr[..., None]) < TOL_BF16
+        assert max_rel_err(got["n_last"] * sg, ref["n_last"] * sr) < TOL_BF16
+
+
+def test_ragged_tail_writes_nothing_past_the_sequence():
+    """The (batch, head) blocks of an output are contiguous, so a row written past the last token of one head would
+    land in the first rows of the next head.  Each head computed alone must therefore reproduce its block of the
+    joint run bit for bit."""
+    B, NH, S, D = 1, 3, 200, 128
+    inp = case_inputs(72, B, NH, S, D, D)
+    full = run_cuda_fwbw(inp, 128, dtype=torch.bfloat16)
+    for h in range(NH):
+        one = {n: x[:, h:h + 1] for n, x in inp.items()}
+        alone = run_cuda_fwbw(one, 128, dtype=torch.bfloat16)
+        for key in ("H", "dQ", "dK", "dV", "dI", "dF"):
+            assert np.array_equal(full[key][:, h:h + 1], alone[key]), (h, key)

@@ -67,6 +67,43 @@ def test_backend_inference_arbitrary_length(S):
     assert max_rel_err(npy(sb), npy(sn)) < 1e-4
 
 
+@pytest.mark.parametrize("S", [93, 500, 777])
+def test_backend_inference_arbitrary_length_tensor_cores(S):
+    """Same wrapper, bf16 and head dims that the tcgen05 kernels take: every chunk size of the wrapper's ladder
+    (64, 32, 16) runs on the tensor cores as ragged 128-token chunks.  Compared with the reference's native kernels
+    in f32 on the same (bf16-rounded) inputs."""
+    mk.register_with_mlstm_kernels()
+    inp = case_inputs(55, 1, 2, 1024, 128, 256)
+    q, k, v, i, f = (to_dev(inp[n][:, :, :S], torch.bfloat16) for n in "qkvif")
+    kw = dict(chunk_size=64, return_last_states=True, inference_state_dtype="float32")
+    h_b, st_b = _backend("chunkwise--b200_xl_chunk", "inference", sequence_kernel="native_sequence__b200",
+                         step_kernel="b200", **kw)(q, k, v, i, f)
+    h_n, st_n = _backend("chunkwise--native_custbw", "inference", sequence_kernel="native_sequence__native",
+                         step_kernel="native", **kw)(q.float(), k.float(), v.float(), i.float(), f.float())
+    assert h_b.shape == (1, 2, S, 256) and h_b.dtype == torch.bfloat16
+    assert max_rel_err(npy(h_b), npy(h_n)) < 2e-2
+    sb = st_b[0] * torch.exp(st_b[2])[..., None]
+    sn = st_n[0] * torch.exp(st_n[2])[..., None]
+    assert max_rel_err(npy(sb), npy(sn)) < 2e-2
+
+
+def test_train_mode_any_length_without_padding():
+    """mode="train" with a sequence length that is no multiple of the chunk size: the B200 kernel masks the ragged
+    tail itself, so the host-side zero-padding copies of mode="train_with_padding" are not needed; both give the
+    reference's padded result."""
+    mk.register_with_mlstm_kernels()
+    inp = case_inputs(56, 2, 2, 512, 128, 128)
+    q, k, v, i, f = (to_dev(inp[n][:, :, :300], torch.bfloat16) for n in "qkvif")
+    kw = dict(chunk_size=128, return_last_states=False)
+    h_direct = _backend("chunkwise--b200_xl_chunk", "train", **kw)(q, k, v, i, f)
+    h_padded = _backend("chunkwise--b200_xl_chunk", "train_with_padding", **kw)(q, k, v, i, f)
+    h_n = _backend("chunkwise--native_custbw", "train_with_padding", **kw)(q.float(), k.float(), v.float(), i.float(), f.float())
+    assert h_direct.shape == (2, 2, 300, 128)
+    assert max_rel_err(npy(h_direct), npy(h_n)) < 2e-2
+    assert max_rel_err(npy(h_padded), npy(h_n)) < 2e-2
+    assert max_rel_err(npy(h_direct), npy(h_padded)) < 1e-2
+
+
 def test_backend_train_with_padding():
     mk.register_with_mlstm_kernels()
     inp = case_inputs(53, 1, 2, 512, 64, 128)
