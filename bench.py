@@ -334,33 +334,47 @@ def run_b200(args):
 
     s_in, s_cmp, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
 
+    # (batch, head) units are independent: the batch is fed in E2E_SLICES contiguous groups of units through two
+    # preallocated sets of device staging buffers (no allocator traffic for the inputs inside the timed region)
+    E2E_SLICES = args.e2e_slices
+    units = B * NH
+    per = units // E2E_SLICES
+    hv = {n: t.view(1, units, *t.shape[2:]) for n, t in host.items()}
+    hov = {n: t.view(1, units, *t.shape[2:]) for n, t in host_out.items()}
+    stage = [{n: torch.empty((1, per, *t.shape[2:]), dtype=t.dtype, device=dev) for n, t in hv.items()} for _ in range(2)]
+
     def step_e2e():
         """Whole step from pinned host buffers to pinned host buffers through the public API.  The batch is fed in
-        slices of one sequence per head group so that the H2D copy of slice b+1, the kernels of slice b and the D2H
-        copy of slice b-1 overlap (three streams); every byte still crosses PCIe inside the timed region."""
+        groups of (batch, head) units so that the H2D copy of group g+1, the kernels of group g and the D2H copy of
+        group g-1 overlap (three streams); every byte still crosses PCIe inside the timed region."""
         cur = torch.cuda.current_stream()
         for st in (s_in, s_cmp, s_out):
             st.wait_stream(cur)
-        for b in range(B):
+        consumed = [None, None]   # event: the kernels that read staging set j have finished
+        for g in range(E2E_SLICES):
+            sl = slice(g * per, (g + 1) * per)
+            buf = stage[g % 2]
             with torch.cuda.stream(s_in):
-                d = {n: host[n][b:b + 1].to(dev, non_blocking=True) for n in host}
+                if consumed[g % 2] is not None:
+                    s_in.wait_event(consumed[g % 2])
+                for n in hv:
+                    buf[n].copy_(hv[n][:, sl], non_blocking=True)
                 ev_in = torch.cuda.Event()
                 ev_in.record(s_in)
             with torch.cuda.stream(s_cmp):
                 s_cmp.wait_event(ev_in)
-                for t in d.values():
-                    t.record_stream(s_cmp)
-                lf = {n: d[n].requires_grad_(True) for n in "qkvif"}
+                lf = {n: buf[n].detach().requires_grad_(True) for n in "qkvif"}
                 H = mk.mlstm_chunkwise__b200_xl_chunk(lf["q"], lf["k"], lf["v"], lf["i"], lf["f"], chunk_size=L,
                                                       recompute_states_in_bw=RECOMPUTE)
-                H.backward(d["dH"])
+                H.backward(buf["dH"])
                 ev_c = torch.cuda.Event()
                 ev_c.record(s_cmp)
+                consumed[g % 2] = ev_c
             with torch.cuda.stream(s_out):
                 s_out.wait_event(ev_c)
                 outs = [("H", H.detach())] + [(n, lf[n].grad) for n in "qkvif"]
                 for n, t in outs:
-                    host_out[n][b:b + 1].copy_(t, non_blocking=True)
+                    hov[n][:, sl].copy_(t, non_blocking=True)
                     t.record_stream(s_out)
         cur.wait_stream(s_cmp)
         cur.wait_stream(s_out)
@@ -500,6 +514,8 @@ def run_b200(args):
         extra["reference_protocol_fw"] = {
             "no_flush": timed_reps(torch, fw_only, 30, 10, flush=False),
             "l2_flush": timed_reps(torch, fw_only, 30, 10, flush=True)}
+        extra["portable_kernels_f32_B4_NH4_S2048_64_128_L64"] = bench_portable(torch, mk, dev)
+        extra["arbitrary_length_prefill_bf16_NH16_256_256"] = bench_any_length(torch, mk, dev)
         extra["step_decode"] = bench_step(torch, mk, dev, peaks)
         extra["consttoken_sweep_65536_tokens"] = bench_sweep(torch, mk, dev, peaks)
         if world == 1 and not args.no_triton_ref:
@@ -747,6 +763,26 @@ def bench_triton_reference(torch, devin, leaf, L, flops_fw, flops_fwbw):
                              peak_extra_memory_gb=(torch.cuda.max_memory_allocated() - base) / 1e9)
         except Exception as e:  # noqa: BLE001
             out[name] = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
+    try:   # arbitrary-length prefill through the reference's own wrapper (chunk-size ladder + per-token tail loop)
+        from mlstm_kernels.torch.backend_module import mLSTMBackend, mLSTMBackendConfig
+        backend = mLSTMBackend(mLSTMBackendConfig(chunkwise_kernel="chunkwise--triton_xl_chunk",
+                                                   sequence_kernel="native_sequence__triton", step_kernel="triton",
+                                                   mode="inference", chunk_size=128, return_last_states=True,
+                                                   autocast_kernel_dtype="bfloat16", inference_state_dtype="float32"))
+        dev = devin["q"].device
+        for B, S in ((8, 500), (8, 8000 + 77)):
+            g = torch.Generator(device=dev).manual_seed(S)
+            mk_t = lambda *sh: torch.randn(*sh, device=dev, generator=g).bfloat16()  # noqa: E731
+            q, k, v = mk_t(B, 16, S, 256), mk_t(B, 16, S, 256), mk_t(B, 16, S, 256)
+            i, f = mk_t(B, 16, S), (3 + torch.randn(B, 16, S, device=dev, generator=g)).bfloat16()
+
+            def fw():
+                with torch.no_grad():
+                    backend(q, k, v, i, f)
+            ms = timed_local(torch, fw, 5, 3)
+            out[f"arbitrary_length_prefill_B{B}_S{S}"] = dict(fw_ms=ms, tokens_per_s=B * S / (ms * 1e-3))
+    except Exception as e:  # noqa: BLE001
+        out["arbitrary_length_prefill"] = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
     try:
         from mlstm_kernels.torch.recurrent.triton_step import mlstm_recurrent_step__triton
         NH, DHQK, DHHV = 8, 256, 512
@@ -763,6 +799,50 @@ def bench_triton_reference(torch, devin, leaf, L, flops_fw, flops_fwbw):
             out[f"step_B{B}"] = dict(us_per_step=ms * 1e3, tokens_per_s=B / (ms * 1e-3))
     except Exception as e:  # noqa: BLE001
         out["step"] = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
+    return out
+
+
+def bench_portable(torch, mk, dev):
+    """The CUDA-core kernels that take every case the tcgen05 path does not (f32 / f16 inputs, head dims that are no
+    multiples of 128): one f32 case in the reference's own test geometry, forward and forward+backward."""
+    B, NH, S, DHQK, DHHV, L = 4, 4, 2048, 64, 128, 64
+    g = torch.Generator(device=dev).manual_seed(3)
+    mk_t = lambda *sh: torch.randn(*sh, device=dev, generator=g)  # noqa: E731
+    q, k, v, i, f, dH = mk_t(B, NH, S, DHQK), mk_t(B, NH, S, DHQK), mk_t(B, NH, S, DHHV), mk_t(B, NH, S), 3 + mk_t(B, NH, S), mk_t(B, NH, S, DHHV)
+    leaf = [t.clone().requires_grad_(True) for t in (q, k, v, i, f)]
+
+    def fw():
+        with torch.no_grad():
+            mk.mlstm_chunkwise__b200_xl_chunk(q, k, v, i, f, chunk_size=L)
+
+    def fwbw():
+        for t in leaf:
+            t.grad = None
+        mk.mlstm_chunkwise__b200_xl_chunk(*leaf, chunk_size=L).backward(dH)
+    ms_fw, ms_fwbw = timed_local(torch, fw, 5, 3), timed_local(torch, fwbw, 5, 3)
+    ffw = fw_flops(B, NH, S, DHQK, DHHV, L)
+    ffb = ffw + bw_flops(B, NH, S, DHQK, DHHV, L)
+    return dict(fw_ms=ms_fw, fw_tflops=ffw / ms_fw / 1e9, fwbw_ms=ms_fwbw, fwbw_tflops=ffb / ms_fwbw / 1e9,
+                note="exact f32 arithmetic on CUDA cores (coverage path, not tuned)")
+
+
+def bench_any_length(torch, mk, dev):
+    """Prefill (forward with last states) of sequences whose length is no multiple of the chunk size, bf16, NH=16,
+    256/256, B=8: one call on the tcgen05 path with a ragged last chunk; no host-side padding, no chunk-size ladder."""
+    NH, DHQK, DHHV = 16, 256, 256
+    out = {}
+    for B, S in ((8, 500), (8, 8000 + 77)):
+        g = torch.Generator(device=dev).manual_seed(S)
+        mk_t = lambda *sh: torch.randn(*sh, device=dev, generator=g).bfloat16()  # noqa: E731
+        q, k, v = mk_t(B, NH, S, DHQK), mk_t(B, NH, S, DHQK), mk_t(B, NH, S, DHHV)
+        i, f = mk_t(B, NH, S), (3 + torch.randn(B, NH, S, device=dev, generator=g)).bfloat16()
+
+        def fw():
+            with torch.no_grad():
+                mk.mlstm_chunkwise__b200_xl_chunk(q, k, v, i, f, return_last_states=True, chunk_size=128)
+        ms = timed_local(torch, fw, 10, 3)
+        fl = fw_flops(B, NH, S, DHQK, DHHV, 128)
+        out[f"B{B}_S{S}"] = dict(fw_ms=ms, fw_tflops=fl / ms / 1e9, tokens_per_s=B * S / (ms * 1e-3))
     return out
 
 
@@ -873,6 +953,8 @@ def main():
     ap.add_argument("--no-triton-ref", action="store_true",
                     help="do not time the reference's Triton kernels on this GPU (they run by default at N=1 when the "
                          "reference package is importable)")
+    ap.add_argument("--e2e-slices", type=int, default=8,
+                    help="groups of (batch, head) units the end-to-end leg pipelines over PCIe (must divide B*NH)")
     ap.add_argument("--batch", type=int, default=None, help="override the batch size B of the workload (profiling)")
     ap.add_argument("--quick", action="store_true",
                     help="profiling mode: timed region only (no end-to-end leg, no per-kernel pass, no extras, no CPU leg)")
