@@ -58,7 +58,9 @@ constexpr int rec_smem_bytes(bool bwd) {
 // left columns d0.., d0+64.., right columns e0.., e0+64..).  A chunk is two stages; the product of a chunk is
 // accumulated over both before the state warps fold it in.  The ring is deeper than one chunk so that the load of
 // chunk s+2 is already in flight while chunk s is being gated and multiplied.
-template <bool BWD>
+// TN = columns of the state tile (128, or 64 for small problems: twice as many CTAs, so that a launch with few
+// (batch, head) units still covers the GPU).
+template <bool BWD, int TN>
 __global__ void __launch_bounds__(REC_THREADS, 1)
 rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUtensorMap mapR,
           const __grid_constant__ CUtensorMap mapS, RecParams p) {
@@ -74,9 +76,11 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // 1-D grid (no 65535 limit on batch x heads), state tiles of one (batch, head) next to each other
-  const int n_et = p.DHHV / 128, n_dt = p.DHQK / 128;
+  static_assert(TN == 128 || TN == 64, "state tile width");
+  constexpr int HC = TN / 2;   // columns each of the two state-warp groups owns
+  const int n_et = p.DHHV / TN, n_dt = p.DHQK / 128;
   const int et = blockIdx.x % n_et, dt = (blockIdx.x / n_et) % n_dt, bh = blockIdx.x / (n_et * n_dt);
-  const int e0 = et * 128, d0 = dt * 128;
+  const int e0 = et * TN, d0 = dt * 128;
   const int NC = p.NC, NH2 = 2 * p.NC;   // ring steps: two per chunk
   const bool do_n = (!BWD) && et == 0 && (p.n_states != nullptr || p.n_final != nullptr);
 
@@ -126,13 +130,13 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
         const int y = ck * CL + (h & 1) * REC_HALF;          // first token of this half chunk inside the sequence
         const size_t slot0 = (size_t)bh * p.SP + y;
         uint8_t* sl = smem + st * REC_STAGE_BYTES;
-        mbar_expect_tx(&bar_full[st], REC_STAGE_BYTES + (BWD ? 2 : 1) * REC_HALF * 4);
+        mbar_expect_tx(&bar_full[st], 16384 + TN * 128 + (BWD ? 2 : 1) * REC_HALF * 4);
         bulk_load(s_scale[st], p.lscale + slot0, REC_HALF * 4, &bar_full[st]);
         if (BWD) bulk_load(s_scale2[st], p.rscale + slot0, REC_HALF * 4, &bar_full[st]);
         tma_load_3d(sl, &mapL, &bar_full[st], d0, y, bh);
         tma_load_3d(sl + 8192, &mapL, &bar_full[st], d0 + 64, y, bh);
         tma_load_3d(sl + 16384, &mapR, &bar_full[st], e0, y, bh);
-        tma_load_3d(sl + 24576, &mapR, &bar_full[st], e0 + 64, y, bh);
+        if (TN == 128) tma_load_3d(sl + 24576, &mapR, &bar_full[st], e0 + 64, y, bh);
       }
       issued = h + 1;
     }
@@ -143,7 +147,7 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_bf16(128, 128, 1, 1);
+      constexpr uint32_t idesc = umma_idesc_bf16(128, TN, 1, 1);
       for (int h = 0; h < NH2; ++h) {
         const int st = h % REC_STAGES, s = h >> 1, buf = s & 1;
         if (!mbar_wait(&bar_scaled[st], (h / REC_STAGES) & 1, &s_abort, &g_sm100_status, 102)) break;
@@ -217,7 +221,7 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
         const int slot = BWD ? NC - n : n;
         const int y = (bh * (NC + 1) + slot) * p.DHQK + d0;
         tma_store_2d(&mapS, stage_base + ob * 32768, e0, y);
-        tma_store_2d(&mapS, stage_base + ob * 32768 + 16384, e0 + 64, y);
+        if (TN == 128) tma_store_2d(&mapS, stage_base + ob * 32768 + 16384, e0 + 64, y);
         tma_store_commit();
         asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");   // the previous tile has left its buffer
         if (n >= 1) mbar_arrive(&bar_out_free[ob ^ 1]);
@@ -254,15 +258,15 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
     // ---------------- state warps: fold each chunk's product into the running state, store it ----------------
     const int quarter = warp & 3, half = (warp - 10) >> 2;
     const int row = quarter * 32 + lane;           // state row (d)
-    const int d = d0 + row, ecol = e0 + half * 64;
-    float C[64];
+    const int d = d0 + row, ecol = e0 + half * HC;
+    float C[HC];
     if (p.c_init) {
       const float4* src = reinterpret_cast<const float4*>(p.c_init + ((size_t)bh * p.DHQK + d) * p.DHHV + ecol);
 #pragma unroll
-      for (int c = 0; c < 16; ++c) { float4 v = src[c]; C[4 * c] = v.x; C[4 * c + 1] = v.y; C[4 * c + 2] = v.z; C[4 * c + 3] = v.w; }
+      for (int c = 0; c < HC / 4; ++c) { float4 v = src[c]; C[4 * c] = v.x; C[4 * c + 1] = v.y; C[4 * c + 2] = v.z; C[4 * c + 3] = v.w; }
     } else {
 #pragma unroll
-      for (int c = 0; c < 64; ++c) C[c] = 0.f;
+      for (int c = 0; c < HC; ++c) C[c] = 0.f;
     }
     // The bf16 state tile goes to shared memory in the 128-byte-swizzled box layout and leaves with one TMA store
     // per 64-column box (coalesced, asynchronous); two staging buffers, one store group in flight.
@@ -272,13 +276,15 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
       if (p.c_states == nullptr) return true;
       const int ob = n_out & 1;
       if (n_out >= 2 && !mbar_wait(&bar_out_free[ob], ((n_out >> 1) - 1) & 1, &s_abort, &g_sm100_status, 107)) return false;
-      uint8_t* rowp = stage_base + ob * 32768 + half * 16384 + row * 128;
+      // TN = 128: each group fills its own 64-column box; TN = 64: the groups share one box (four 16-byte pieces each)
+      uint8_t* rowp = stage_base + ob * 32768 + (TN == 128 ? half * 16384 : 0) + row * 128;
+      const int piece0 = (TN == 128) ? 0 : half * 4;
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
+      for (int c = 0; c < HC / 8; ++c) {
         uint4 v;
         v.x = pack_bf16(C[8 * c], C[8 * c + 1]); v.y = pack_bf16(C[8 * c + 2], C[8 * c + 3]);
         v.z = pack_bf16(C[8 * c + 4], C[8 * c + 5]); v.w = pack_bf16(C[8 * c + 6], C[8 * c + 7]);
-        *reinterpret_cast<uint4*>(rowp + ((c ^ (row & 7)) << 4)) = v;
+        *reinterpret_cast<uint4*>(rowp + (((piece0 + c) ^ (row & 7)) << 4)) = v;
       }
       fence_proxy_async_smem();
       mbar_arrive(&bar_out_full[ob]);   // the store warp ships the tile
@@ -291,9 +297,9 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
       if (!mbar_wait(&bar_acc_full[buf], (s >> 1) & 1, &s_abort, &g_sm100_status, 104)) { ok = false; break; }
       tc_fence_after_sync();
       const float g = s_g[s & 7];
-      const uint32_t ta = tmem + ((uint32_t)(quarter * 32) << 16) + buf * 128 + half * 64;
+      const uint32_t ta = tmem + ((uint32_t)(quarter * 32) << 16) + buf * 128 + half * HC;
 #pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) {
+      for (int q4 = 0; q4 < HC / 16; ++q4) {
         uint32_t rr[16];
         tmem_ld16(ta + q4 * 16, rr);
         tmem_wait_ld();
@@ -307,7 +313,7 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
     if (ok && p.c_final) {
       float4* fd = reinterpret_cast<float4*>(p.c_final + ((size_t)bh * p.DHQK + d) * p.DHHV + ecol);
 #pragma unroll
-      for (int c = 0; c < 16; ++c) fd[c] = make_float4(C[4 * c], C[4 * c + 1], C[4 * c + 2], C[4 * c + 3]);
+      for (int c = 0; c < HC / 4; ++c) fd[c] = make_float4(C[4 * c], C[4 * c + 1], C[4 * c + 2], C[4 * c + 3]);
     }
   }
   tc_fence_before_sync();
@@ -910,6 +916,31 @@ static bool state_map(CUtensorMap* m, const void* base, const ChunkwiseDims& d, 
   return cached_map(m, base, (uint64_t)d.B * d.NH * (d.NC + 1) * d.DHQK, (uint64_t)d.DHHV, box_rows, 64);
 }
 
+template <bool BWD, int TN>
+static int launch_rec_tn(const CUtensorMap& mL, const CUtensorMap& mR, const CUtensorMap& mS, const RecParams& rp,
+                         const ChunkwiseDims& d, cudaStream_t st) {
+  auto kern = rec_sm100<BWD, TN>;
+  static bool attr_done[64] = {};
+  if (int rc = set_smem_once(kern, rec_smem_bytes(BWD), attr_done)) return rc;
+  const unsigned grid = (unsigned)(d.DHHV / TN) * (unsigned)(d.DHQK / 128) * (unsigned)(d.B * d.NH);
+  kern<<<grid, REC_THREADS, rec_smem_bytes(BWD), st>>>(mL, mR, mS, rp);
+  MLSTM_LAUNCH_CHECK();
+  return MLSTM_OK;
+}
+
+// number of SMs of the current device (queried once per device)
+static int sm_count() {
+  static int cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
 template <bool BWD>
 static int launch_rec(const void* left, const void* right, const RecParams& rp, const ChunkwiseDims& d, cudaStream_t st) {
   CUtensorMap mL, mR, mS;
@@ -917,13 +948,11 @@ static int launch_rec(const void* left, const void* right, const RecParams& rp, 
   if (!tok_map(&mL, left, d, d.DHQK, REC_HALF) || !tok_map(&mR, right, d, d.DHHV, REC_HALF)) return MLSTM_ERR_CUDA;
   // store map over the per-chunk states; when no states are wanted (segment summary) the map is never used
   if (!state_map(&mS, rp.c_states ? (const void*)rp.c_states : left, d, 128)) return MLSTM_ERR_CUDA;
-  auto kern = rec_sm100<BWD>;
-  static bool attr_done[64] = {};
-  if (int rc = set_smem_once(kern, rec_smem_bytes(BWD), attr_done)) return rc;
-  const unsigned grid = (unsigned)(d.DHHV / 128) * (unsigned)(d.DHQK / 128) * (unsigned)(d.B * d.NH);
-  kern<<<grid, REC_THREADS, rec_smem_bytes(BWD), st>>>(mL, mR, mS, rp);
-  MLSTM_LAUNCH_CHECK();
-  return MLSTM_OK;
+  // One CTA per SM walks all chunks of its state tile.  With 128-column tiles a launch of few (batch, head) units
+  // leaves SMs idle; 64-column tiles double the CTAs as long as they still fit one wave.
+  const long ctas128 = (long)(d.DHHV / 128) * (d.DHQK / 128) * d.B * d.NH;
+  if (2 * ctas128 <= sm_count()) return launch_rec_tn<BWD, 64>(mL, mR, mS, rp, d, st);
+  return launch_rec_tn<BWD, 128>(mL, mR, mS, rp, d, st);
 }
 
 int sm100_recurrent_fw(const void* k, const void* v, const GateBuffers& gb, const float* c_initial,
@@ -1016,7 +1045,8 @@ int sm100_wait_expiry_selftest(unsigned limit, int code, cudaStream_t st) {
 
 int sm100_force_load() {
   cudaFuncAttributes a;
-  MLSTM_CUDA_CHECK(cudaFuncGetAttributes(&a, rec_sm100<false>));
+  MLSTM_CUDA_CHECK(cudaFuncGetAttributes(&a, (rec_sm100<false, 128>)));
+  MLSTM_CUDA_CHECK(cudaFuncGetAttributes(&a, (rec_sm100<false, 64>)));
   MLSTM_CUDA_CHECK(cudaFuncGetAttributes(&a, par_fw_sm100));
   return MLSTM_OK;
 }

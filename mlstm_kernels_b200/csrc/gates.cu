@@ -202,17 +202,15 @@ gate_grad_rows_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
 // (the per-chunk totals telescope: <C_k, dP_k> - <P_k, dC_{k+1}> = <C_k, dC_k> - <C_{k+1}, dC_{k+1}> for
 // C_{k+1} = g C_k + P_k, dC_k = g dC_{k+1} + dP_k).  `anchors` holds those inner products for every
 // `anchor_tokens`-th token position (state_dot_kernel); the running sum of a token is then taken from the next anchor
-// instead of from the end of the sequence, which bounds the walk to one anchor interval.
+// instead of from the end of the sequence, which bounds the walk to one anchor interval (gate_grad_anchored_kernel).
+// gate_grad_scan_kernel is the plain form (portable path: f32 states, no anchors).
 constexpr int kScanThreads = 1024;
-constexpr int kMaxAnchors = 1024;
 template <typename T>
 __global__ void __launch_bounds__(kScanThreads)
 gate_grad_scan_kernel(const T* __restrict__ vecI, const T* __restrict__ vecF, const float* __restrict__ qdq,
                       const float* __restrict__ kdk, float* __restrict__ dI, float* __restrict__ dF,
-                      int S, int SP, int variant, int nparts, size_t part_stride, const float* __restrict__ anchors,
-                      int n_anchors, int anchor_tokens) {
+                      int S, int SP, int variant, int nparts, size_t part_stride) {
   __shared__ float s_part[kScanThreads];
-  __shared__ float s_run_at_anchor[kMaxAnchors];
   const int bh = blockIdx.x, t = threadIdx.x;
   const size_t base = (size_t)bh * S;      // gate logits and outputs: S tokens per (batch, head)
   const size_t pbase = (size_t)bh * SP;    // row sums: SP slots per (batch, head)
@@ -234,29 +232,57 @@ gate_grad_scan_kernel(const T* __restrict__ vecI, const T* __restrict__ vecF, co
     s_part[t] += y;
     __syncthreads();
   }
-  const float run0 = (t + 1 < kScanThreads) ? s_part[t + 1] : 0.f;
-  const bool anchored = anchors != nullptr;
-  if (anchored) {   // value of the plain running sum at every interior anchor position
-    float run = run0;
-    for (int s = s1 - 1; s >= s0; --s) {
-      run += parts(qdq, pbase + s) - parts(kdk, pbase + s);
-      if (s > 0 && s % anchor_tokens == 0) s_run_at_anchor[s / anchor_tokens] = run;
-    }
-    __syncthreads();
-  }
-  const float* anc = anchored ? anchors + (size_t)bh * n_anchors : nullptr;
-  float run = run0;
+  float run = (t + 1 < kScanThreads) ? s_part[t + 1] : 0.f;
   for (int s = s1 - 1; s >= s0; --s) {
     float di = parts(kdk, pbase + s);
     run += parts(qdq, pbase + s) - di;
-    float total = run;
-    if (anchored) {
-      const int a = s / anchor_tokens + 1;   // next anchor after this token; the last one is the end of the sequence
-      if (a < n_anchors - 1) total = (run - s_run_at_anchor[a]) + (anc[a] - anc[n_anchors - 1]);
-    }
-    dF[base + s] = total * sigmoid_f(-to_f32(vecF[base + s]));
+    dF[base + s] = run * sigmoid_f(-to_f32(vecF[base + s]));
     if (variant != MLSTM_EXP) di *= sigmoid_f(-to_f32(vecI[base + s]));
     dI[base + s] = di;
+  }
+}
+
+// The anchored form.  Between two anchors the running sum needs nothing from outside the interval: for a token t
+// with next anchor position p,  sum_{t' >= t} = sum_{t <= t' < p} (qdq - kdk)  +  anchors[p] - anchors[end]
+// (the last interval ends at the end of the sequence, where both anchor terms vanish).  So every interval of
+// `anchor_tokens` tokens is an independent CTA: grid (intervals, batch x heads), one token per thread, the suffix
+// sum inside the interval by warp shuffles in a fixed order.
+constexpr int kAnchorThreads = 512;
+template <typename T>
+__global__ void __launch_bounds__(kAnchorThreads)
+gate_grad_anchored_kernel(const T* __restrict__ vecI, const T* __restrict__ vecF, const float* __restrict__ qdq,
+                          const float* __restrict__ kdk, float* __restrict__ dI, float* __restrict__ dF, int S,
+                          int SP, int variant, int nparts, size_t part_stride,
+                          const float* __restrict__ anchors, int n_anchors) {
+  __shared__ float s_warp[kAnchorThreads / 32];
+  const int a = blockIdx.x, bh = blockIdx.y, t = threadIdx.x, lane = t & 31, warp = t >> 5;
+  const int s = a * kAnchorThreads + t;
+  const bool live = s < S;
+  float qd = 0.f, kd = 0.f;
+  if (live) {
+    const size_t idx = (size_t)bh * SP + s;
+    for (int pp = 0; pp < nparts; ++pp) { qd += qdq[pp * part_stride + idx]; kd += kdk[pp * part_stride + idx]; }
+  }
+  // inclusive suffix sum over the interval: inside the warp, then over the warps to the right
+  float x = qd - kd;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const float y = __shfl_down_sync(0xffffffffu, x, o);
+    if (lane + o < 32) x += y;
+  }
+  if (lane == 0) s_warp[warp] = x;
+  __syncthreads();
+  float right = 0.f;
+  for (int w = kAnchorThreads / 32 - 1; w > warp; --w) right += s_warp[w];
+  float total = x + right;
+  if (a + 1 < n_anchors - 1) {   // the interval ends at an interior anchor
+    const float* anc = anchors + (size_t)bh * n_anchors;
+    total += anc[a + 1] - anc[n_anchors - 1];
+  }
+  if (live) {
+    const size_t o = (size_t)bh * S + s;
+    dF[o] = total * sigmoid_f(-to_f32(vecF[o]));
+    dI[o] = (variant != MLSTM_EXP) ? kd * sigmoid_f(-to_f32(vecI[o])) : kd;
   }
 }
 
@@ -422,32 +448,34 @@ int launch_inv_den(const float* n_out, float* inv_den, const ChunkwiseDims& d, c
 }
 
 // Scan-only entry: the row sums were already produced (in f32, before rounding) by the backward kernels.
-// With `anchors` (see gate_grad_scan_kernel) the reverse sum restarts from an exact value every `anchor_tokens` tokens.
-int launch_gate_grad_scan(int dtype, const void* i, const void* f, const float* qdq, const float* kdk, int nparts,
-                          float* dI, float* dF, const ChunkwiseDims& d, cudaStream_t st, const float* anchors,
-                          int n_anchors, int anchor_tokens) {
+// With `anchors` (see above) the sum restarts from an exact value every `anchor_tokens` tokens and the intervals run
+// as independent CTAs; without, one CTA per (batch, head) scans the whole sequence.
+template <typename T>
+static int gate_grad_scan_t(const void* i, const void* f, const float* qdq, const float* kdk, int nparts, float* dI,
+                            float* dF, const ChunkwiseDims& d, cudaStream_t st, const float* anchors, int n_anchors,
+                            int anchor_tokens) {
   const size_t stride = (size_t)d.B * d.NH * d.SP;
-  if (n_anchors > kMaxAnchors) anchors = nullptr;   // sequences beyond kMaxAnchors intervals fall back to the plain sum
-  switch (dtype) {
-    case MLSTM_F32:
-      gate_grad_scan_kernel<float><<<d.B * d.NH, kScanThreads, 0, st>>>((const float*)i, (const float*)f, qdq, kdk,
-                                                                        dI, dF, d.S, d.SP, d.variant, nparts,
-                                                                        stride, anchors, n_anchors, anchor_tokens);
-      break;
-    case MLSTM_BF16:
-      gate_grad_scan_kernel<__nv_bfloat16><<<d.B * d.NH, kScanThreads, 0, st>>>(
-          (const __nv_bfloat16*)i, (const __nv_bfloat16*)f, qdq, kdk, dI, dF, d.S, d.SP, d.variant, nparts, stride,
-          anchors, n_anchors, anchor_tokens);
-      break;
-    case MLSTM_F16:
-      gate_grad_scan_kernel<__half><<<d.B * d.NH, kScanThreads, 0, st>>>((const __half*)i, (const __half*)f, qdq, kdk,
-                                                                         dI, dF, d.S, d.SP, d.variant, nparts,
-                                                                         stride, anchors, n_anchors, anchor_tokens);
-      break;
-    default: return MLSTM_ERR_DTYPE;
+  if (anchors != nullptr && anchor_tokens == kAnchorThreads) {
+    dim3 grid(ceil_div(d.S, kAnchorThreads), d.B * d.NH);
+    gate_grad_anchored_kernel<T><<<grid, kAnchorThreads, 0, st>>>((const T*)i, (const T*)f, qdq, kdk, dI, dF, d.S, d.SP,
+                                                                  d.variant, nparts, stride, anchors, n_anchors);
+  } else {
+    gate_grad_scan_kernel<T><<<d.B * d.NH, kScanThreads, 0, st>>>((const T*)i, (const T*)f, qdq, kdk, dI, dF, d.S, d.SP,
+                                                                  d.variant, nparts, stride);
   }
   MLSTM_LAUNCH_CHECK();
   return MLSTM_OK;
+}
+
+int launch_gate_grad_scan(int dtype, const void* i, const void* f, const float* qdq, const float* kdk, int nparts,
+                          float* dI, float* dF, const ChunkwiseDims& d, cudaStream_t st, const float* anchors,
+                          int n_anchors, int anchor_tokens) {
+  switch (dtype) {
+    case MLSTM_F32: return gate_grad_scan_t<float>(i, f, qdq, kdk, nparts, dI, dF, d, st, anchors, n_anchors, anchor_tokens);
+    case MLSTM_BF16: return gate_grad_scan_t<__nv_bfloat16>(i, f, qdq, kdk, nparts, dI, dF, d, st, anchors, n_anchors, anchor_tokens);
+    case MLSTM_F16: return gate_grad_scan_t<__half>(i, f, qdq, kdk, nparts, dI, dF, d, st, anchors, n_anchors, anchor_tokens);
+  }
+  return MLSTM_ERR_DTYPE;
 }
 
 // <C_k, dC_k> at every `every`-th chunk boundary and at the end (bf16 states of the tcgen05 path).

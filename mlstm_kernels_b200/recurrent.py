@@ -13,13 +13,31 @@ device guard is skipped when the tensors' device is already current.
 
 from __future__ import annotations
 
-import ctypes as C
-
 import torch
 
 from . import _lib
 
 _STATE_DTYPES = (torch.float32, torch.bfloat16)
+
+# cheapest routes to the current device ordinal and the current stream's handle
+_current_device = getattr(torch._C, "_cuda_getDevice", torch.cuda.current_device)
+_raw_stream_c = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
+def _raw_stream(device_index: int) -> int:
+    if _raw_stream_c is not None:
+        return _raw_stream_c(device_index)
+    return torch.cuda.current_stream(device_index).cuda_stream
+
+
+_STEP_FN = None
+
+
+def _step_fn():
+    global _STEP_FN
+    if _STEP_FN is None:
+        _STEP_FN = _lib.load().mlstm_b200_step
+    return _STEP_FN
 
 
 def _conform(t: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
@@ -50,11 +68,25 @@ def mlstm_recurrent_step__b200_fw(
     eps: float = 1e-6,
     dtype_state: torch.dtype = torch.float32,
     vecH_out: torch.Tensor = None,  # optional caller-owned output (B, NH, DHHV) in q's dtype
+    validate: bool = True,
     **kwargs,
 ):
+    """One decode step.  `validate=False` is for decode loops that own all their buffers: every tensor (the new-state
+    and `vecH_out` buffers included) must then be a contiguous CUDA tensor of the expected shape and element type on
+    the current device; nothing is checked or converted and the call costs little more than the launch itself."""
+    if not validate:
+        B, NH, DHQK = vecQ.shape
+        codes = _lib._DTYPE_CODE
+        rc = _step_fn()(vecQ.data_ptr(), vecK.data_ptr(), vecV.data_ptr(), scaI.data_ptr(), scaF.data_ptr(),
+                        matC_old.data_ptr(), vecN_old.data_ptr(), scaM_old.data_ptr(), vecH_out.data_ptr(),
+                        matC_new.data_ptr(), vecN_new.data_ptr(), scaM_new.data_ptr(), B, NH, DHQK,
+                        vecV.shape[-1], codes[vecQ.dtype], codes[scaI.dtype], codes[dtype_state], eps,
+                        _raw_stream(vecQ.device.index))
+        if rc != 0:
+            _lib.check(rc, "mlstm_b200_step")
+        return vecH_out, (matC_new, vecN_new, scaM_new)
     if not (vecQ.is_cuda and matC_old.is_cuda):
         raise RuntimeError("mlstm_kernels_b200 kernels run on CUDA tensors only (there is no CPU fallback)")
-    lib = _lib.load()
     B, NH, DHQK = vecQ.shape
     DHHV = vecV.shape[-1]
     assert vecQ.shape == vecK.shape, "q and k must have the same shape"
@@ -66,12 +98,20 @@ def mlstm_recurrent_step__b200_fw(
     if dtype_state not in _STATE_DTYPES:
         raise ValueError(f"Unsupported state dtype {dtype_state}.")
     qdt = vecQ.dtype
-    dt = _lib.dtype_code(qdt)
+    codes = _lib._DTYPE_CODE
+    dt = codes.get(qdt)
+    if dt is None:
+        raise ValueError(f"Unsupported kernel dtype {qdt}.")
+    # tensors that already conform are passed through untouched
     q = vecQ if vecQ.is_contiguous() else vecQ.contiguous()
-    k, v = _conform(vecK, qdt), _conform(vecV, qdt)
-    gi = _gate(scaI)
-    gf = _gate(scaF) if scaF.dtype is gi.dtype else _conform(scaF, gi.dtype)
-    c, n, m = _conform(matC_old, dtype_state), _conform(vecN_old, dtype_state), _conform(scaM_old, dtype_state)
+    k = vecK if (vecK.dtype is qdt and vecK.is_contiguous()) else _conform(vecK, qdt)
+    v = vecV if (vecV.dtype is qdt and vecV.is_contiguous()) else _conform(vecV, qdt)
+    gi = scaI if (scaI.dtype in codes and scaI.is_contiguous()) else _gate(scaI)
+    gdt = gi.dtype
+    gf = scaF if (scaF.dtype is gdt and scaF.is_contiguous()) else _conform(scaF, gdt)
+    c = matC_old if (matC_old.dtype is dtype_state and matC_old.is_contiguous()) else _conform(matC_old, dtype_state)
+    n = vecN_old if (vecN_old.dtype is dtype_state and vecN_old.is_contiguous()) else _conform(vecN_old, dtype_state)
+    m = scaM_old if (scaM_old.dtype is dtype_state and scaM_old.is_contiguous()) else _conform(scaM_old, dtype_state)
     if matC_new is None:
         assert vecN_new is None and scaM_new is None, "Initial states must be provided together."
         matC_new, vecN_new, scaM_new = torch.empty_like(c), torch.empty_like(n), torch.empty_like(m)
@@ -86,17 +126,19 @@ def mlstm_recurrent_step__b200_fw(
         h = vecH_out
         if h.dtype is not qdt or h.shape != v.shape or not h.is_contiguous():
             raise ValueError("vecH_out must be a contiguous (B, NH, DHHV) tensor of q's dtype")
-    dev = q.device
-    VP = C.c_void_p
-    args = (VP(q.data_ptr()), VP(k.data_ptr()), VP(v.data_ptr()), VP(gi.data_ptr()), VP(gf.data_ptr()),
-            VP(c.data_ptr()), VP(n.data_ptr()), VP(m.data_ptr()), VP(h.data_ptr()),
-            VP(matC_new.data_ptr()), VP(vecN_new.data_ptr()), VP(scaM_new.data_ptr()),
-            B, NH, DHQK, DHHV, dt, _lib._DTYPE_CODE[gi.dtype], _lib._DTYPE_CODE[dtype_state], eps)
-    if torch.cuda.current_device() == dev.index:
-        rc = lib.mlstm_b200_step(*args, VP(torch.cuda.current_stream().cuda_stream))
+    # raw addresses go to ctypes as plain integers (the argument types are declared once in _lib.SIGNATURES)
+    dev_index = q.device.index
+    if _current_device() == dev_index:
+        rc = _step_fn()(q.data_ptr(), k.data_ptr(), v.data_ptr(), gi.data_ptr(), gf.data_ptr(), c.data_ptr(),
+                        n.data_ptr(), m.data_ptr(), h.data_ptr(), matC_new.data_ptr(), vecN_new.data_ptr(),
+                        scaM_new.data_ptr(), B, NH, DHQK, DHHV, dt, codes[gdt], codes[dtype_state], eps,
+                        _raw_stream(dev_index))
     else:
-        with torch.cuda.device(dev):
-            rc = lib.mlstm_b200_step(*args, VP(torch.cuda.current_stream(dev).cuda_stream))
+        with torch.cuda.device(q.device):
+            rc = _step_fn()(q.data_ptr(), k.data_ptr(), v.data_ptr(), gi.data_ptr(), gf.data_ptr(), c.data_ptr(),
+                            n.data_ptr(), m.data_ptr(), h.data_ptr(), matC_new.data_ptr(), vecN_new.data_ptr(),
+                            scaM_new.data_ptr(), B, NH, DHQK, DHHV, dt, codes[gdt], codes[dtype_state], eps,
+                            _raw_stream(dev_index))
     if rc != 0:
         _lib.check(rc, "mlstm_b200_step")
     return h, (matC_new, vecN_new, scaM_new)

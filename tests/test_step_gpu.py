@@ -100,6 +100,13 @@ def test_step_bf16_state_and_out_buffers():
                                                         vecN_new=nb, scaM_new=mb)
     assert c3.data_ptr() == cf.data_ptr()
     assert max_rel_err(npy(h3), ho) < 2e-2
+    # decode loop that owns its buffers: validation off, same result
+    cf2, nf2, mf2 = c.float(), n.float(), m.float()
+    co, no, mo, hf = torch.empty_like(cf2), torch.empty_like(nf2), torch.empty_like(mf2), torch.empty_like(v)
+    h5, (c5, _, _) = mk.mlstm_recurrent_step__b200_fw(cf2, nf2, mf2, q, k, v, i, f, matC_new=co, vecN_new=no,
+                                                      scaM_new=mo, vecH_out=hf, validate=False)
+    h6, (c6, _, _) = mk.mlstm_recurrent_step__b200_fw(cf2, nf2, mf2, q, k, v, i, f)
+    assert torch.equal(h5, h6) and torch.equal(c5, c6)
     # caller-owned h
     hb = torch.empty_like(v)
     h4, _ = mk.mlstm_recurrent_step__b200_fw(c.float(), n.float(), m.float(), q, k, v, i, f, vecH_out=hb)
