@@ -48,7 +48,7 @@ METRIC = "chunkwise_fwbw_tflops_64k_tokens"
 
 # measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum) at NH=16, 256/256, chunk 128, bf16 on a quarter
 # batch, divided by its 2048 chunks; the ncu summaries are kept under profiles/
-NCU_DRAM_BYTES_PER_CHUNK = {"recurrent_fw": 245839, "parallel_fw": 389908, "recurrent_bw": 242707, "parallel_bw": 718655}
+NCU_DRAM_BYTES_PER_CHUNK = {"recurrent_fw": 246736, "parallel_fw": 389655, "recurrent_bw": 244795, "parallel_bw": 717398}
 
 
 def fw_flops(B, NH, S, DHQK, DHHV, L):
