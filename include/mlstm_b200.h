@@ -89,7 +89,7 @@ int mlstm_b200_profile_read(float* total_ms, int* count);
 /* 1 if the tcgen05 path covers this chunkwise case, else 0. */
 int mlstm_b200_chunkwise_has_tcgen05(int S, int DHQK, int DHHV, int L, int dtype);
 
-/* Element type (MLSTM_F32 or MLSTM_BF16) of the per-chunk C state buffer that
+/* Element type (MLSTM_F32, or the 16-bit input type on the tcgen05 path) of the per-chunk C state buffer that
  * mlstm_b200_chunkwise_fw writes and mlstm_b200_chunkwise_bw reads, for the given
  * case and implementation choice. */
 int mlstm_b200_chunkwise_state_dtype(int S, int DHQK, int DHHV, int L, int dtype, int impl);
@@ -114,8 +114,8 @@ size_t mlstm_b200_chunkwise_workspace_bytes(int B, int NH, int S, int DHQK, int 
  *                                        before chunk k, slot NC = final state
  *   n_states    (B,NH,NC+1,DHQK) f32 out,  m_states (B,NH,NC+1) f32 out
  *   c_last,n_last,m_last  f32 copies of the final state (B,NH,DHQK,DHHV),(B,NH,DHQK),(B,NH); each may be NULL
- *   L a power of two >= 16.  S % L == 0 for the portable kernels.  Where the tcgen05 kernels run (bf16, L = 128,
- *   head dims multiples of 128) S may be ANY length >= 1: NC = ceil(S / L) and the last chunk is ragged - its
+ *   L a power of two >= 16.  S % L == 0 for the portable kernels.  Where the tcgen05 kernels run (bf16 or f16,
+ *   L = 128, head dims multiples of 128) S may be ANY length >= 1: NC = ceil(S / L) and the last chunk is ragged - its
  *   missing tokens are read as zeros and switched off in the gates, no output row past S is written.  This
  *   replaces the host-side zero padding of wrap_chunkwise__pad_zeros and the chunk-size ladder 64/32/16 of
  *   wrap_chunkwise__arbitrary_sequence_length (mlstm_kernels/torch/kernel_wrappers.py:76-171,206-267).

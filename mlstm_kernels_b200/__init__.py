@@ -12,6 +12,7 @@ from .chunkwise import (
     resolve_chunk_size,
     mlstm_siging_chunkwise__b200_xl_chunk,
     select_chunk_size,
+    tcgen05_applies,
 )
 from .recurrent import (
     mlstm_recurrent_sequence__b200,
@@ -31,6 +32,7 @@ __all__ = [
     "chunkwise_states_raw",
     "select_chunk_size",
     "kernel_chunk_size",
+    "tcgen05_applies",
     "resolve_chunk_size",
     "get_kernel",
     "register_with_mlstm_kernels",

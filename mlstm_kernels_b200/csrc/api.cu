@@ -221,7 +221,7 @@ int mlstm_b200_chunkwise_has_tcgen05(int S, int DHQK, int DHHV, int L, int dtype
 int mlstm_b200_chunkwise_state_dtype(int S, int DHQK, int DHHV, int L, int dtype, int impl) {
   bool use_sm100 = false;
   if (resolve_impl(impl, 1, 1, S, DHQK, DHHV, L, dtype, &use_sm100) != MLSTM_OK) return MLSTM_F32;
-  return use_sm100 ? MLSTM_BF16 : MLSTM_F32;
+  return use_sm100 ? dtype : MLSTM_F32;   // tcgen05 path: 16-bit states of the input type
 }
 
 size_t mlstm_b200_chunkwise_workspace_bytes(int B, int NH, int S, int DHQK, int DHHV, int L, int dtype, int variant,
@@ -233,7 +233,7 @@ size_t mlstm_b200_chunkwise_workspace_bytes(int B, int NH, int S, int DHQK, int 
   const int NC = (S + L - 1) / L, SP = NC * L;
   if (backward == 2) return carve_summary(nullptr, B * NH, SP, NC).bytes;
   if (!backward) return carve_fw(nullptr, B * NH, SP, NC).bytes;
-  return carve_bw(nullptr, B * NH, SP, NC, DHQK, DHHV, dtype_size(use_sm100 ? MLSTM_BF16 : MLSTM_F32)).bytes;
+  return carve_bw(nullptr, B * NH, SP, NC, DHQK, DHHV, dtype_size(use_sm100 ? dtype : MLSTM_F32)).bytes;
 }
 
 int mlstm_b200_chunkwise_fw(const void* q, const void* k, const void* v, const void* i, const void* f,
@@ -255,7 +255,7 @@ int mlstm_b200_chunkwise_fw(const void* q, const void* k, const void* v, const v
   bool use_sm100 = false;
   if ((rc = resolve_impl(impl, B, NH, S, DHQK, DHHV, L, dtype, &use_sm100)) != MLSTM_OK) return rc;
 
-  const ChunkwiseDims d = make_dims(B, NH, S, DHQK, DHHV, L, variant, eps);
+  const ChunkwiseDims d = make_dims(B, NH, S, DHQK, DHHV, L, variant, eps, dtype);
   FwLayout lay = carve_fw(workspace, B * NH, d.SP, d.NC);
   if (workspace_bytes < lay.bytes) return MLSTM_ERR_WORKSPACE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -298,8 +298,8 @@ static int bw_impl(const void* q, const void* k, const void* v, const void* i, c
   bool use_sm100 = false;
   if ((rc = resolve_impl(impl, B, NH, S, DHQK, DHHV, L, dtype, &use_sm100)) != MLSTM_OK) return rc;
 
-  const ChunkwiseDims d = make_dims(B, NH, S, DHQK, DHHV, L, variant, eps);
-  const int sdt = use_sm100 ? MLSTM_BF16 : MLSTM_F32;
+  const ChunkwiseDims d = make_dims(B, NH, S, DHQK, DHHV, L, variant, eps, dtype);
+  const int sdt = use_sm100 ? dtype : MLSTM_F32;
   BwLayout lay = carve_bw(workspace, B * NH, d.SP, d.NC, DHQK, DHHV, dtype_size(sdt));
   if (workspace_bytes < lay.bytes) return MLSTM_ERR_WORKSPACE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -376,7 +376,7 @@ int mlstm_b200_chunkwise_states(const void* k, const void* v, const void* i, con
   for (const void* p : ptrs) if (p && !aligned16(p)) return MLSTM_ERR_ALIGN;
   bool use_sm100 = false;
   if ((rc = resolve_impl(impl, B, NH, S, DHQK, DHHV, L, dtype, &use_sm100)) != MLSTM_OK) return rc;
-  const ChunkwiseDims d = make_dims(B, NH, S, DHQK, DHHV, L, variant, 1e-6f);
+  const ChunkwiseDims d = make_dims(B, NH, S, DHQK, DHHV, L, variant, 1e-6f, dtype);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   GateBuffers gb;
   if (fw_workspace != nullptr) {   // the forward's gate vectors are still there: only abar and gbar are read
@@ -408,7 +408,7 @@ int mlstm_b200_chunkwise_summary(const void* k, const void* v, const void* i, co
   for (const void* p : ptrs) if (p && !aligned16(p)) return MLSTM_ERR_ALIGN;
   bool use_sm100 = false;
   if ((rc = resolve_impl(impl, B, NH, S, DHQK, DHHV, L, dtype, &use_sm100)) != MLSTM_OK) return rc;
-  const ChunkwiseDims d = make_dims(B, NH, S, DHQK, DHHV, L, variant, 1e-6f);
+  const ChunkwiseDims d = make_dims(B, NH, S, DHQK, DHHV, L, variant, 1e-6f, dtype);
   SumLayout lay = carve_summary(workspace, B * NH, d.SP, d.NC);
   if (workspace_bytes < lay.bytes) return MLSTM_ERR_WORKSPACE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);

@@ -1,5 +1,5 @@
 // tcgen05 / TMEM / TMA implementation of the chunkwise mLSTM kernels for B200 (sm_100a).
-// bf16 operands, f32 accumulation in tensor memory, chunk size 128, head dims multiples of 128.
+// bf16 or f16 operands, f32 accumulation in tensor memory, chunk size 128, head dims multiples of 128.
 //
 //   rec_sm100<BWD>   inter-chunk recurrence (forward C_k, n_k; backward deltaC_k).  A CTA owns a 128 x 128 tile
 //                    of the state for one (batch, head) and walks the chunks in order; per chunk one
@@ -36,7 +36,7 @@ struct RecParams {
   const float* gbar;    // (BNH, NC)
   const float* c_init;  // (BNH, DHQK, DHHV) f32 or nullptr
   const float* n_init;  // (BNH, DHQK) or nullptr
-  __nv_bfloat16* c_states;  // (BNH, NC+1, DHQK, DHHV)
+  void* c_states;           // (BNH, NC+1, DHQK, DHHV), 16-bit elements of the input type
   float* n_states;          // (BNH, NC+1, DHQK) or nullptr
   float* c_final;           // (BNH, DHQK, DHHV) f32 or nullptr
   float* n_final;
@@ -60,7 +60,8 @@ constexpr int rec_smem_bytes(bool bwd) {
 // chunk s+2 is already in flight while chunk s is being gated and multiplied.
 // TN = columns of the state tile (128, or 64 for small problems: twice as many CTAs, so that a launch with few
 // (batch, head) units still covers the GPU).
-template <bool BWD, int TN>
+// F16: the 16-bit element type is IEEE half instead of bf16 (operands, gated tiles, stored states, outputs).
+template <bool BWD, int TN, bool F16>
 __global__ void __launch_bounds__(REC_THREADS, 1)
 rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUtensorMap mapR,
           const __grid_constant__ CUtensorMap mapS, RecParams p) {
@@ -147,7 +148,7 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_bf16(128, TN, 1, 1);
+      constexpr uint32_t idesc = umma_idesc_16(F16, 128, TN, 1, 1);
       for (int h = 0; h < NH2; ++h) {
         const int st = h % REC_STAGES, s = h >> 1, buf = s & 1;
         if (!mbar_wait(&bar_scaled[st], (h / REC_STAGES) & 1, &s_abort, &g_sm100_status, 102)) break;
@@ -188,10 +189,11 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
         uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          __nv_bfloat162 h2 = *reinterpret_cast<__nv_bfloat162*>(&w[e]);
-          const float lo = __low2float(h2) * sc, hi = __high2float(h2) * sc;
+          float lo, hi;
+          Pair16<F16>::unpack(w[e], lo, hi);
+          lo *= sc; hi *= sc;
           ns[u >> 1][2 * e] += lo; ns[u >> 1][2 * e + 1] += hi;
-          w[e] = pack_bf16(lo, hi);
+          w[e] = Pair16<F16>::pack(lo, hi);
         }
         *ptr = make_uint4(w[0], w[1], w[2], w[3]);
       }
@@ -282,8 +284,8 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
 #pragma unroll
       for (int c = 0; c < HC / 8; ++c) {
         uint4 v;
-        v.x = pack_bf16(C[8 * c], C[8 * c + 1]); v.y = pack_bf16(C[8 * c + 2], C[8 * c + 3]);
-        v.z = pack_bf16(C[8 * c + 4], C[8 * c + 5]); v.w = pack_bf16(C[8 * c + 6], C[8 * c + 7]);
+        v.x = Pair16<F16>::pack(C[8 * c], C[8 * c + 1]); v.y = Pair16<F16>::pack(C[8 * c + 2], C[8 * c + 3]);
+        v.z = Pair16<F16>::pack(C[8 * c + 4], C[8 * c + 5]); v.w = Pair16<F16>::pack(C[8 * c + 6], C[8 * c + 7]);
         *reinterpret_cast<uint4*>(rowp + (((piece0 + c) ^ (row & 7)) << 4)) = v;
       }
       fence_proxy_async_smem();
@@ -346,7 +348,7 @@ enum { PM_H = 0, PM_DV = 1, PM_DK = 2, PM_DQ = 3 };
 struct ParParams {
   const float *vecB, *iota, *m_tok, *abar, *bbar, *inv_den;  // per token, f32
   const float* n_states;                                     // H only
-  __nv_bfloat16 *out_h, *out_dv, *out_dk, *out_dq;
+  uint16_t *out_h, *out_dv, *out_dk, *out_dq;   // 16-bit elements of the input type
   float* n_out;               // H only
   float *rowdot_q, *rowdot_k; // sum_d q dq (from DQ), sum_d k dk (from DK); one partial per output tile: [DHQK/128][tokens]
   size_t nslots;              // B * NH * SP
@@ -386,6 +388,7 @@ struct ParShared {
 // underflows the exact value is below 2^-100 as well.  The diagonal block keeps the exact per-element form (its
 // masked columns may carry arbitrarily large colE).  The special-function unit (16 results per clock and SM) was
 // the limit of the gating phase before: the warps of the busiest row quarter share one SM sub-partition.
+template <bool F16>
 __device__ __forceinline__ void
 par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const CUtensorMap* mapX,
          const CUtensorMap* mapSt, const CUtensorMap* mapE, const ParParams& p,
@@ -510,9 +513,9 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);
-      const uint32_t idesc_st = ST_MN ? umma_idesc_bf16(128, 128, 0, 1) : umma_idesc_bf16(128, 128, 0, 0);
-      constexpr uint32_t idesc_x = umma_idesc_bf16(128, 128, 0, 1);
+      constexpr uint32_t idesc_s = umma_idesc_16(F16, 128, 128, 0, 0);
+      const uint32_t idesc_st = ST_MN ? umma_idesc_16(F16, 128, 128, 0, 1) : umma_idesc_16(F16, 128, 128, 0, 0);
+      constexpr uint32_t idesc_x = umma_idesc_16(F16, 128, 128, 0, 1);
       bool ok = true;
       for (int ld = 0; ld < ND; ++ld) {            // score: S = A . B^T
         const int st = ld % PAR_NST;
@@ -605,9 +608,10 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
           const float* nn = sh.s_n + it * 64 + lc * 8;
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const __nv_bfloat162 h2 = *reinterpret_cast<const __nv_bfloat162*>(&w[e]);
-            qn = fmaf(__low2float(h2), nn[2 * e], qn);
-            qn = fmaf(__high2float(h2), nn[2 * e + 1], qn);
+            float lo, hi;
+            Pair16<F16>::unpack(w[e], lo, hi);
+            qn = fmaf(lo, nn[2 * e], qn);
+            qn = fmaf(hi, nn[2 * e + 1], qn);
           }
         }
         fence_proxy_async_smem();   // generic-proxy reads ordered before the TMA refill of the stage
@@ -660,8 +664,8 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
                   g4[e] = val;
                   rowsum += val;
                 }
-                pk[u][8 * hh + 2 * c4] = pack_bf16(g4[0], g4[1]);
-                pk[u][8 * hh + 2 * c4 + 1] = pack_bf16(g4[2], g4[3]);
+                pk[u][8 * hh + 2 * c4] = Pair16<F16>::pack(g4[0], g4[1]);
+                pk[u][8 * hh + 2 * c4 + 1] = Pair16<F16>::pack(g4[2], g4[3]);
               }
             } else {
               const float rf = ex2_approx(rowE + sh.s_colP[cq]);
@@ -672,8 +676,8 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
                 const float g0 = __uint_as_float(v[4 * c4]) * (rf * f4.x), g1 = __uint_as_float(v[4 * c4 + 1]) * (rf * f4.y);
                 const float g2 = __uint_as_float(v[4 * c4 + 2]) * (rf * f4.z), g3 = __uint_as_float(v[4 * c4 + 3]) * (rf * f4.w);
                 rowsum += (g0 + g1) + (g2 + g3);
-                pk[u][8 * hh + 2 * c4] = pack_bf16(g0, g1);
-                pk[u][8 * hh + 2 * c4 + 1] = pack_bf16(g2, g3);
+                pk[u][8 * hh + 2 * c4] = Pair16<F16>::pack(g0, g1);
+                pk[u][8 * hh + 2 * c4 + 1] = Pair16<F16>::pack(g2, g3);
               }
             }
           }
@@ -762,14 +766,15 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
             const uint32_t w[4] = {ev.x, ev.y, ev.z, ev.w};
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-              const __nv_bfloat162 h2 = *reinterpret_cast<const __nv_bfloat162*>(&w[e]);
-              dot4[e] = fmaf(__low2float(h2), x[2 * e], dot4[e]);
-              dot4[e] = fmaf(__high2float(h2), x[2 * e + 1], dot4[e]);
+              float lo, hi;
+              Pair16<F16>::unpack(w[e], lo, hi);
+              dot4[e] = fmaf(lo, x[2 * e], dot4[e]);
+              dot4[e] = fmaf(hi, x[2 * e + 1], dot4[e]);
             }
           }
           uint4 o;
-          o.x = pack_bf16(x[0], x[1]); o.y = pack_bf16(x[2], x[3]);
-          o.z = pack_bf16(x[4], x[5]); o.w = pack_bf16(x[6], x[7]);
+          o.x = Pair16<F16>::pack(x[0], x[1]); o.y = Pair16<F16>::pack(x[2], x[3]);
+          o.z = Pair16<F16>::pack(x[4], x[5]); o.w = Pair16<F16>::pack(x[6], x[7]);
           *reinterpret_cast<uint4*>(orow + sw) = o;
         }
       }
@@ -781,7 +786,7 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
       mbar_arrive(&sh.bar_out);
       if (!mbar_wait(&sh.bar_out, sub & 1, &sh.abort, &g_sm100_status, 211)) { ok = false; break; }
       {
-        __nv_bfloat16* outp = (mode == PM_H) ? p.out_h : (mode == PM_DV) ? p.out_dv : (mode == PM_DK) ? p.out_dk : p.out_dq;
+        uint16_t* outp = (mode == PM_H) ? p.out_h : (mode == PM_DV) ? p.out_dv : (mode == PM_DK) ? p.out_dk : p.out_dq;
         uint8_t* gbase = reinterpret_cast<uint8_t*>(outp + out_row0 * DO + o0);
         const int ew = warp - 2, j = lane & 15;          // 16-byte piece j of the 256-byte tile row
 #pragma unroll
@@ -813,6 +818,7 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
   if (warp == 1) tmem_dealloc(tmem, 256);
 }
 
+template <bool F16>
 __global__ void __launch_bounds__(PAR_THREADS, 2)
 par_fw_sm100(const __grid_constant__ CUtensorMap mQ, const __grid_constant__ CUtensorMap mK,
              const __grid_constant__ CUtensorMap mV, const __grid_constant__ CUtensorMap mC,
@@ -823,12 +829,13 @@ par_fw_sm100(const __grid_constant__ CUtensorMap mQ, const __grid_constant__ CUt
   const int gx = (T + PAR_MAXSUB - 1) / PAR_MAXSUB;
   const int x = blockIdx.x % gx, ck = (blockIdx.x / gx) % p.NC, bh = blockIdx.x / (gx * p.NC);
   const int t0 = PAR_MAXSUB * x;
-  par_body(PM_H, &mQ, &mK, &mV, &mC, &mV, p, sh, t0, min(PAR_MAXSUB, T - t0), ck, bh);
+  par_body<F16>(PM_H, &mQ, &mK, &mV, &mC, &mV, p, sh, t0, min(PAR_MAXSUB, T - t0), ck, bh);
 }
 
 // deltaV, deltaK and deltaQ of one chunk in ONE launch: blockIdx.x enumerates the 128-wide output tiles of the three
 // results, so the CTAs that read the same q, k, v, deltaH and state tiles of a chunk are scheduled next to each other
 // and share them through L2 instead of re-reading them from HBM in three separate launches.
+template <bool F16>
 __global__ void __launch_bounds__(PAR_THREADS, 2)
 par_bw_sm100(const __grid_constant__ CUtensorMap mQ, const __grid_constant__ CUtensorMap mK,
              const __grid_constant__ CUtensorMap mV, const __grid_constant__ CUtensorMap mDH,
@@ -845,7 +852,7 @@ par_bw_sm100(const __grid_constant__ CUtensorMap mQ, const __grid_constant__ CUt
   if (x < c_dv) { mode = PM_DV; pair = x; T = T_dv; a = &mK; b = &mQ; xm = &mDH; stm = &mdC_mn; e = &mDH; }
   else if (x < c_dv + c_dk) { mode = PM_DK; pair = x - c_dv; T = T_dk; a = &mV; b = &mDH; xm = &mQ; stm = &mdC_k; e = &mK; }
   else { mode = PM_DQ; pair = x - c_dv - c_dk; T = T_dk; a = &mDH; b = &mV; xm = &mK; stm = &mC_k; e = &mQ; }
-  par_body(mode, a, b, xm, stm, e, p, sh, PAR_MAXSUB * pair, min(PAR_MAXSUB, T - PAR_MAXSUB * pair), ck, bh);
+  par_body<F16>(mode, a, b, xm, stm, e, p, sh, PAR_MAXSUB * pair, min(PAR_MAXSUB, T - PAR_MAXSUB * pair), ck, bh);
 }
 
 // =====================================================================================================
@@ -853,7 +860,7 @@ par_bw_sm100(const __grid_constant__ CUtensorMap mQ, const __grid_constant__ CUt
 // =====================================================================================================
 bool sm100_supported(int S, int DHQK, int DHHV, int L, int dtype) {
   // any sequence length: a ragged last chunk is handled by zero-filled loads and masked stores
-  return dtype == MLSTM_BF16 && L == CL && S >= 1 && DHQK % 128 == 0 && DHHV % 128 == 0 && DHQK <= 512 &&
+  return (dtype == MLSTM_BF16 || dtype == MLSTM_F16) && L == CL && S >= 1 && DHQK % 128 == 0 && DHHV % 128 == 0 && DHQK <= 512 &&
          DHHV <= 1024;
 }
 
@@ -881,10 +888,10 @@ static int set_smem_once(K kern, int bytes, bool (&done)[64]) {
 
 // Tensor maps depend only on (base pointer, rows, columns, box): a training loop calls with the same buffers over
 // and over, so the last few encodings are kept per thread instead of calling the driver 3-7 times per launch.
-struct MapKey { const void* base; uint64_t rows, cols, slabs; uint32_t box_rows, box_cols; };
-// slabs == 0: plain 2-D matrix [rows x cols]; otherwise a 3-D tensor [slabs x rows x cols]
+struct MapKey { const void* base; uint64_t rows, cols, slabs; uint32_t box_rows, box_cols; bool f16; };
+// slabs == 0: plain 2-D matrix [rows x cols]; otherwise a 3-D tensor [slabs x rows x cols]; f16: IEEE half, else bf16
 static bool cached_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
-                       uint32_t box_cols, uint64_t slabs = 0) {
+                       uint32_t box_cols, uint64_t slabs, bool f16) {
   constexpr int N = 32;
   static thread_local MapKey keys[N];
   static thread_local CUtensorMap maps[N];
@@ -892,15 +899,15 @@ static bool cached_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t
   for (int i = 0; i < used; ++i) {
     const MapKey& k = keys[i];
     if (k.base == base && k.rows == rows && k.cols == cols && k.slabs == slabs && k.box_rows == box_rows &&
-        k.box_cols == box_cols) {
+        k.box_cols == box_cols && k.f16 == f16) {
       *m = maps[i];
       return true;
     }
   }
-  const bool ok = slabs == 0 ? sm100_host::make_map_bf16(m, base, rows, cols, box_rows, box_cols)
-                             : sm100_host::make_map_bf16_3d(m, base, slabs, rows, cols, box_rows, box_cols);
+  const bool ok = slabs == 0 ? sm100_host::make_map_bf16(m, base, rows, cols, box_rows, box_cols, f16)
+                             : sm100_host::make_map_bf16_3d(m, base, slabs, rows, cols, box_rows, box_cols, f16);
   if (!ok) return false;
-  keys[next] = MapKey{base, rows, cols, slabs, box_rows, box_cols};
+  keys[next] = MapKey{base, rows, cols, slabs, box_rows, box_cols, f16};
   maps[next] = *m;
   next = (next + 1) % N;
   if (used < N) ++used;
@@ -910,16 +917,17 @@ static bool cached_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t
 // token tensors (q, k, v, deltaH): one slab of S rows per (batch, head), so that a box hanging over the end of a
 // sequence (ragged last chunk) reads zeros instead of the next head's tokens
 static bool tok_map(CUtensorMap* m, const void* base, const ChunkwiseDims& d, int cols, int box_rows = 128) {
-  return cached_map(m, base, (uint64_t)d.S, (uint64_t)cols, box_rows, 64, (uint64_t)d.B * d.NH);
+  return cached_map(m, base, (uint64_t)d.S, (uint64_t)cols, box_rows, 64, (uint64_t)d.B * d.NH, d.dtype == MLSTM_F16);
 }
 static bool state_map(CUtensorMap* m, const void* base, const ChunkwiseDims& d, int box_rows) {
-  return cached_map(m, base, (uint64_t)d.B * d.NH * (d.NC + 1) * d.DHQK, (uint64_t)d.DHHV, box_rows, 64);
+  return cached_map(m, base, (uint64_t)d.B * d.NH * (d.NC + 1) * d.DHQK, (uint64_t)d.DHHV, box_rows, 64, 0,
+                    d.dtype == MLSTM_F16);
 }
 
-template <bool BWD, int TN>
+template <bool BWD, int TN, bool F16>
 static int launch_rec_tn(const CUtensorMap& mL, const CUtensorMap& mR, const CUtensorMap& mS, const RecParams& rp,
                          const ChunkwiseDims& d, cudaStream_t st) {
-  auto kern = rec_sm100<BWD, TN>;
+  auto kern = rec_sm100<BWD, TN, F16>;
   static bool attr_done[64] = {};
   if (int rc = set_smem_once(kern, rec_smem_bytes(BWD), attr_done)) return rc;
   const unsigned grid = (unsigned)(d.DHHV / TN) * (unsigned)(d.DHQK / 128) * (unsigned)(d.B * d.NH);
@@ -951,15 +959,17 @@ static int launch_rec(const void* left, const void* right, const RecParams& rp, 
   // One CTA per SM walks all chunks of its state tile.  With 128-column tiles a launch of few (batch, head) units
   // leaves SMs idle; 64-column tiles double the CTAs as long as they still fit one wave.
   const long ctas128 = (long)(d.DHHV / 128) * (d.DHQK / 128) * d.B * d.NH;
-  if (2 * ctas128 <= sm_count()) return launch_rec_tn<BWD, 64>(mL, mR, mS, rp, d, st);
-  return launch_rec_tn<BWD, 128>(mL, mR, mS, rp, d, st);
+  const bool f16 = d.dtype == MLSTM_F16;
+  if (2 * ctas128 <= sm_count())
+    return f16 ? launch_rec_tn<BWD, 64, true>(mL, mR, mS, rp, d, st) : launch_rec_tn<BWD, 64, false>(mL, mR, mS, rp, d, st);
+  return f16 ? launch_rec_tn<BWD, 128, true>(mL, mR, mS, rp, d, st) : launch_rec_tn<BWD, 128, false>(mL, mR, mS, rp, d, st);
 }
 
 int sm100_recurrent_fw(const void* k, const void* v, const GateBuffers& gb, const float* c_initial,
                        const float* n_initial, void* c_states, float* n_states, float* c_last, float* n_last,
                        const ChunkwiseDims& d, cudaStream_t st) {
   PhaseScope ps(PH_REC_FW, st);
-  RecParams rp{gb.abar, nullptr, 1.f, gb.gbar, c_initial, n_initial, (__nv_bfloat16*)c_states,
+  RecParams rp{gb.abar, nullptr, 1.f, gb.gbar, c_initial, n_initial, c_states,
                d.variant == MLSTM_SIG_NONORM ? nullptr : n_states, c_last, d.variant == MLSTM_SIG_NONORM ? nullptr : n_last, d.S, d.SP, d.NC, d.DHQK, d.DHHV};
   return launch_rec<false>(k, v, rp, d, st);
 }
@@ -967,7 +977,7 @@ int sm100_recurrent_fw(const void* k, const void* v, const GateBuffers& gb, cons
 int sm100_recurrent_bw(const void* q, const void* dh, const GateBuffers& gb, const float* dc_last, void* dc_states,
                        float* dc_initial, const ChunkwiseDims& d, cudaStream_t st) {
   PhaseScope ps(PH_REC_BW, st);
-  RecParams rp{gb.bbar, gb.inv_den, d.qk_scale, gb.gbar, dc_last, nullptr, (__nv_bfloat16*)dc_states, nullptr,
+  RecParams rp{gb.bbar, gb.inv_den, d.qk_scale, gb.gbar, dc_last, nullptr, dc_states, nullptr,
                dc_initial, nullptr, d.S, d.SP, d.NC, d.DHQK, d.DHHV};
   return launch_rec<true>(q, dh, rp, d, st);
 }
@@ -990,12 +1000,15 @@ int sm100_parallel_fw(const void* q, const void* k, const void* v, const GateBuf
       !state_map(&mC, c_states, d, 64))
     return MLSTM_ERR_CUDA;
   ParParams pp = base_params(gb, d);
-  pp.n_states = n_states; pp.out_h = (__nv_bfloat16*)h; pp.n_out = n_out;
-  static bool attr_done[64] = {};
-  if (int rc = set_smem_once(par_fw_sm100, PAR_SMEM, attr_done)) return rc;
+  pp.n_states = n_states; pp.out_h = (uint16_t*)h; pp.n_out = n_out;
+  const bool f16 = d.dtype == MLSTM_F16;
+  static bool attr_done[2][64] = {};
+  if (int rc = f16 ? set_smem_once(par_fw_sm100<true>, PAR_SMEM, attr_done[1])
+                   : set_smem_once(par_fw_sm100<false>, PAR_SMEM, attr_done[0])) return rc;
   // up to PAR_MAXSUB output tiles per CTA
   const unsigned grid = (unsigned)((d.DHHV / 128 + PAR_MAXSUB - 1) / PAR_MAXSUB) * (unsigned)d.NC * (unsigned)(d.B * d.NH);
-  par_fw_sm100<<<grid, PAR_THREADS, PAR_SMEM, st>>>(mQ, mK, mV, mC, pp);
+  if (f16) par_fw_sm100<true><<<grid, PAR_THREADS, PAR_SMEM, st>>>(mQ, mK, mV, mC, pp);
+  else par_fw_sm100<false><<<grid, PAR_THREADS, PAR_SMEM, st>>>(mQ, mK, mV, mC, pp);
   MLSTM_LAUNCH_CHECK();
   return MLSTM_OK;
 }
@@ -1010,14 +1023,17 @@ int sm100_parallel_bw(const void* q, const void* k, const void* v, const void* d
       !state_map(&mdC_k, dc_states, d, 128))
     return MLSTM_ERR_CUDA;
   ParParams pp = base_params(gb, d);
-  pp.out_dv = (__nv_bfloat16*)dv; pp.out_dk = (__nv_bfloat16*)dk; pp.out_dq = (__nv_bfloat16*)dq;
+  pp.out_dv = (uint16_t*)dv; pp.out_dk = (uint16_t*)dk; pp.out_dq = (uint16_t*)dq;
   pp.rowdot_q = qdq_parts; pp.rowdot_k = kdk_parts;
-  static bool attr_done[64] = {};
-  if (int rc = set_smem_once(par_bw_sm100, PAR_SMEM, attr_done)) return rc;
+  const bool f16 = d.dtype == MLSTM_F16;
+  static bool attr_done[2][64] = {};
+  if (int rc = f16 ? set_smem_once(par_bw_sm100<true>, PAR_SMEM, attr_done[1])
+                   : set_smem_once(par_bw_sm100<false>, PAR_SMEM, attr_done[0])) return rc;
   // up to PAR_MAXSUB output tiles per CTA
   const unsigned grid = (unsigned)((d.DHHV / 128 + PAR_MAXSUB - 1) / PAR_MAXSUB + 2 * ((d.DHQK / 128 + PAR_MAXSUB - 1) / PAR_MAXSUB)) *
                         (unsigned)d.NC * (unsigned)(d.B * d.NH);
-  par_bw_sm100<<<grid, PAR_THREADS, PAR_SMEM, st>>>(mQ, mK, mV, mDH, mC_k, mdC_mn, mdC_k, pp);
+  if (f16) par_bw_sm100<true><<<grid, PAR_THREADS, PAR_SMEM, st>>>(mQ, mK, mV, mDH, mC_k, mdC_mn, mdC_k, pp);
+  else par_bw_sm100<false><<<grid, PAR_THREADS, PAR_SMEM, st>>>(mQ, mK, mV, mDH, mC_k, mdC_mn, mdC_k, pp);
   MLSTM_LAUNCH_CHECK();
   return MLSTM_OK;
 }
@@ -1045,9 +1061,12 @@ int sm100_wait_expiry_selftest(unsigned limit, int code, cudaStream_t st) {
 
 int sm100_force_load() {
   cudaFuncAttributes a;
-  MLSTM_CUDA_CHECK(cudaFuncGetAttributes(&a, (rec_sm100<false, 128>)));
-  MLSTM_CUDA_CHECK(cudaFuncGetAttributes(&a, (rec_sm100<false, 64>)));
-  MLSTM_CUDA_CHECK(cudaFuncGetAttributes(&a, par_fw_sm100));
+  MLSTM_CUDA_CHECK(cudaFuncGetAttributes(&a, (rec_sm100<false, 128, false>)));
+  MLSTM_CUDA_CHECK(cudaFuncGetAttributes(&a, (rec_sm100<false, 64, false>)));
+  MLSTM_CUDA_CHECK(cudaFuncGetAttributes(&a, par_fw_sm100<false>));
+  MLSTM_CUDA_CHECK(cudaFuncGetAttributes(&a, (rec_sm100<false, 128, true>)));
+  MLSTM_CUDA_CHECK(cudaFuncGetAttributes(&a, (rec_sm100<false, 64, true>)));
+  MLSTM_CUDA_CHECK(cudaFuncGetAttributes(&a, par_fw_sm100<true>));
   return MLSTM_OK;
 }
 

@@ -83,10 +83,11 @@ struct ChunkwiseDims {
   float eps;
   float qk_scale;
   int SP;       // NC * L
+  int dtype;    // element type of q, k, v, h and the gradients (MLSTM_F32 / MLSTM_BF16 / MLSTM_F16)
 };
-inline ChunkwiseDims make_dims(int B, int NH, int S, int DHQK, int DHHV, int L, int variant, float eps) {
+inline ChunkwiseDims make_dims(int B, int NH, int S, int DHQK, int DHHV, int L, int variant, float eps, int dtype) {
   const int NC = (S + L - 1) / L;
-  return ChunkwiseDims{B, NH, S, DHQK, DHHV, L, NC, variant, eps, 1.0f / sqrtf((float)DHQK), NC * L};
+  return ChunkwiseDims{B, NH, S, DHQK, DHHV, L, NC, variant, eps, 1.0f / sqrtf((float)DHQK), NC * L, dtype};
 }
 
 // Per-token / per-chunk gate vectors produced by the gate pre-pass (all f32, device memory).

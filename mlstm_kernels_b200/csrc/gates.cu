@@ -288,8 +288,9 @@ gate_grad_anchored_kernel(const T* __restrict__ vecI, const T* __restrict__ vecF
 
 // anchors[bh][a] = <C_k, dC_k> over the whole DHQK x DHHV state, k = min(a * every, NC), a = 1 .. n_anchors - 1
 // (a = 0 is never read).  One CTA per (anchor, batch x head); the partial sums are added in a fixed order.
+template <typename TS>
 __global__ void __launch_bounds__(256)
-state_dot_kernel(const __nv_bfloat16* __restrict__ c_states, const __nv_bfloat16* __restrict__ dc_states,
+state_dot_kernel(const TS* __restrict__ c_states, const TS* __restrict__ dc_states,
                  float* __restrict__ anchors, int NC, int every, int n_anchors, size_t state_elems) {
   __shared__ float s_w[8];
   const int bh = blockIdx.y, a = blockIdx.x + 1;
@@ -303,10 +304,10 @@ state_dot_kernel(const __nv_bfloat16* __restrict__ c_states, const __nv_bfloat16
     const uint32_t xw[4] = {x.x, x.y, x.z, x.w}, yw[4] = {y.x, y.y, y.z, y.w};
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      const __nv_bfloat162 xa = *reinterpret_cast<const __nv_bfloat162*>(&xw[e]);
-      const __nv_bfloat162 ya = *reinterpret_cast<const __nv_bfloat162*>(&yw[e]);
-      acc[e] = fmaf(__low2float(xa), __low2float(ya), acc[e]);
-      acc[e] = fmaf(__high2float(xa), __high2float(ya), acc[e]);
+      const TS* xa = reinterpret_cast<const TS*>(&xw[e]);
+      const TS* ya = reinterpret_cast<const TS*>(&yw[e]);
+      acc[e] = fmaf(to_f32(xa[0]), to_f32(ya[0]), acc[e]);
+      acc[e] = fmaf(to_f32(xa[1]), to_f32(ya[1]), acc[e]);
     }
   }
   float v = warp_sum((acc[0] + acc[1]) + (acc[2] + acc[3]));
@@ -478,13 +479,17 @@ int launch_gate_grad_scan(int dtype, const void* i, const void* f, const float* 
   return MLSTM_ERR_DTYPE;
 }
 
-// <C_k, dC_k> at every `every`-th chunk boundary and at the end (bf16 states of the tcgen05 path).
+// <C_k, dC_k> at every `every`-th chunk boundary and at the end (16-bit states of the tcgen05 path).
 int launch_state_dot(const void* c_states, const void* dc_states, float* anchors, int every, int n_anchors,
                      const ChunkwiseDims& d, cudaStream_t st) {
   if (n_anchors < 2) return MLSTM_OK;
   dim3 grid(n_anchors - 1, d.B * d.NH);
-  state_dot_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)c_states, (const __nv_bfloat16*)dc_states, anchors, d.NC,
-                                         every, n_anchors, (size_t)d.DHQK * d.DHHV);
+  if (d.dtype == MLSTM_F16)
+    state_dot_kernel<__half><<<grid, 256, 0, st>>>((const __half*)c_states, (const __half*)dc_states, anchors, d.NC,
+                                                   every, n_anchors, (size_t)d.DHQK * d.DHHV);
+  else
+    state_dot_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)c_states, (const __nv_bfloat16*)dc_states,
+                                                          anchors, d.NC, every, n_anchors, (size_t)d.DHQK * d.DHHV);
   MLSTM_LAUNCH_CHECK();
   return MLSTM_OK;
 }

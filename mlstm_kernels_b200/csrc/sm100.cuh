@@ -3,6 +3,7 @@
 // Every wait is bounded: after the limit the waiter records an error code and the kernel drains.
 #pragma once
 #include <cuda.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -120,11 +121,12 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr, uint32_t
   d |= (uint64_t)2 << 61;  // SWIZZLE_128B
   return d;
 }
-// Instruction descriptor, kind::f16, bf16 x bf16 -> f32.  a_mn / b_mn: 1 = MN-major operand.
-__host__ __device__ constexpr uint32_t umma_idesc_bf16(int M, int N, int a_mn, int b_mn) {
+// Instruction descriptor, kind::f16, 16-bit x 16-bit -> f32.  a_mn / b_mn: 1 = MN-major operand.
+// f16 = false: both operands bf16 (format code 1); f16 = true: both operands IEEE half (format code 0).
+__host__ __device__ constexpr uint32_t umma_idesc_16(bool f16, int M, int N, int a_mn, int b_mn) {
   return (1u << 4)                      // D format f32
-         | (1u << 7)                    // A format bf16
-         | (1u << 10)                   // B format bf16
+         | ((f16 ? 0u : 1u) << 7)       // A format
+         | ((f16 ? 0u : 1u) << 10)      // B format
          | ((uint32_t)a_mn << 15) | ((uint32_t)b_mn << 16)
          | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
@@ -209,6 +211,23 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
   return r;
 }
+__device__ __forceinline__ uint32_t pack_f16(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+// Two 16-bit elements in one 32-bit word (low half first), bf16 or IEEE half.
+template <bool F16> struct Pair16 {
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) { return F16 ? pack_f16(lo, hi) : pack_bf16(lo, hi); }
+  static __device__ __forceinline__ void unpack(uint32_t w, float& lo, float& hi) {
+    if (F16) {
+      const __half2 h2 = *reinterpret_cast<const __half2*>(&w);
+      lo = __low2float(h2); hi = __high2float(h2);
+    } else {   // bf16 -> f32 is a 16-bit shift
+      lo = __uint_as_float(w << 16); hi = __uint_as_float(w & 0xffff0000u);
+    }
+  }
+};
 
 }  // namespace sm100
 
@@ -234,14 +253,14 @@ inline EncodeTiledFn get_encode_fn() {
 // bf16 row-major matrix [rows x cols] (cols contiguous); box = box_cols x box_rows; 128-byte swizzle
 // (box_cols * 2 bytes must be 128).
 inline bool make_map_bf16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
-                          uint32_t box_cols) {
+                          uint32_t box_cols, bool f16 = false) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return false;
   cuuint64_t dims[2] = {cols, rows};
   cuuint64_t strides[1] = {cols * 2};
   cuuint32_t box[2] = {box_cols, box_rows};
   cuuint32_t estr[2] = {1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+  return fn(map, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -249,14 +268,14 @@ inline bool make_map_bf16(CUtensorMap* map, const void* base, uint64_t rows, uin
 // bf16 tensor [slabs x rows x cols] (cols contiguous, slabs rows * cols elements apart); box = box_cols x box_rows x 1;
 // 128-byte swizzle.  Out-of-range rows read as zero.
 inline bool make_map_bf16_3d(CUtensorMap* map, const void* base, uint64_t slabs, uint64_t rows, uint64_t cols,
-                             uint32_t box_rows, uint32_t box_cols) {
+                             uint32_t box_rows, uint32_t box_cols, bool f16 = false) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return false;
   cuuint64_t dims[3] = {cols, rows, slabs};
   cuuint64_t strides[2] = {cols * 2, rows * cols * 2};
   cuuint32_t box[3] = {box_cols, box_rows, 1};
   cuuint32_t estr[3] = {1, 1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+  return fn(map, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }

@@ -412,3 +412,26 @@ def test_ragged_tail_writes_nothing_past_the_sequence():
         alone = run_cuda_fwbw(one, 128, dtype=torch.bfloat16)
         for key in ("H", "dQ", "dK", "dV", "dI", "dF"):
             assert np.array_equal(full[key][:, h:h + 1], alone[key]), (h, key)
+
+
+@pytest.mark.parametrize("shape", [(2, 2, 512, 256, 256), (1, 2, 300, 128, 256), (1, 1, 1024, 256, 512)])
+@pytest.mark.parametrize("variant", ["exp", "sig", "sig_nonorm"])
+def test_tcgen05_fp16(shape, variant):
+    """IEEE half inputs take the tensor-core path as well (f16 operands, f16 per-chunk states, f32 accumulation):
+    against the oracle on the f16-rounded inputs, with initial states, an incoming state gradient and a ragged length.
+    f16 carries three more mantissa bits than bf16, so the bound is tighter: 2e-3 (measured 2-6e-4)."""
+    B, NH, S, DHQK, DHHV = shape
+    inp = case_inputs(81, B, NH, S, DHQK, DHHV, init=True, dC_last=True)
+    siging, normalize = variant != "exp", variant != "sig_nonorm"
+    q, v = to_dev(inp["q"], torch.float16), to_dev(inp["v"], torch.float16)
+    assert mk.tcgen05_applies(q, v)
+    got = run_cuda_fwbw(inp, 128, dtype=torch.float16, siging=siging, normalize=normalize, impl="tcgen05")
+    ref = run_oracle_fwbw(inp, _largest_divisor_up_to(S, 128), dtype=torch.float16, siging=siging, normalize=normalize)
+    worst = {k_: max_rel_err(got[k_], ref[k_]) for k_ in ("H", "dQ", "dK", "dV", "dI", "dF", "dC_initial")}
+    print("\nfp16", shape, variant, {k_: f"{e:.2e}" for k_, e in worst.items()})
+    compare(got, ref, 2e-3, 2e-3, keys_fw=("H",))
+    if siging:
+        assert max_rel_err(got["C_last"], ref["C_last"]) < 2e-3
+    else:
+        sg, sr = np.exp(got["m_last"]), np.exp(ref["m_last"])
+        assert max_rel_err(got["C_last"] * sg[..., None], ref["C_last"] * sr[..., None]) < 2e-3
