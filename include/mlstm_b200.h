@@ -231,6 +231,12 @@ int mlstm_b200_chunkwise_states(const void* k, const void* v, const void* i, con
  *   (m terms are zero for the sigmoid input gate).  c_in / n_in / m_in may be NULL (zero state, m = 0).
  *   The result equals what the single-device recurrence holds at the segment's end
  *   (mlstm_kernels/triton/chunkwise/xl_chunk/fw_kernel_recurrent.py:175-196 applied per segment).
+ * mlstm_b200_chunkwise_dc_summary: the backward twin of the summary.  The state-gradient recurrence of ONE segment
+ *   started from a zero incoming gradient: dc_initial (B,NH,DHQK,DHHV) f32 = the segment's own contribution to the
+ *   gradient of the state that entered it.  The recurrence is linear, so with dC_right the gradient of the state the
+ *   segment handed on,  dC_left = exp(G + m_in - m_out) dC_right + dc_initial  (G, m_in, m_out: total log forget
+ *   gate and max state at the two ends of the segment; exp(G) for the sigmoid input gate).  Needs the forward's
+ *   scratch buffer (gate vectors) and n_out; `workspace` of B*NH*ceil(S/L)*L floats.  No per-chunk states are written.
  */
 int mlstm_b200_chunkwise_summary(const void* k, const void* v, const void* i, const void* f,
                                  float* c_last, float* n_last, float* m_last, float* g_total,
@@ -241,6 +247,11 @@ int mlstm_b200_state_combine(const float* c_in, const float* n_in, const float* 
                              const float* c_loc, const float* n_loc, const float* m_loc, const float* g_total,
                              float* c_out, float* n_out, float* m_out,
                              int B, int NH, int DHQK, int DHHV, int variant, void* stream);
+int mlstm_b200_chunkwise_dc_summary(const void* q, const void* dh, const float* n_out,
+                                    const void* fw_workspace, size_t fw_workspace_bytes,
+                                    float* dc_initial, void* workspace, size_t workspace_bytes,
+                                    int B, int NH, int S, int DHQK, int DHHV, int L,
+                                    int dtype, int variant, int impl, float eps, void* stream);
 
 /*
  * One recurrent decode step.  Replaces mlstm_recurrent_step__triton_fw

@@ -393,6 +393,33 @@ int mlstm_b200_chunkwise_states(const void* k, const void* v, const void* i, con
   return simt_recurrent_fw(dtype, MLSTM_F32, k, v, gb, c_initial, nullptr, c_states, nullptr, nullptr, nullptr, d, st);
 }
 
+int mlstm_b200_chunkwise_dc_summary(const void* q, const void* dh, const float* n_out, const void* fw_workspace,
+                                    size_t fw_workspace_bytes, float* dc_initial, void* workspace,
+                                    size_t workspace_bytes, int B, int NH, int S, int DHQK, int DHHV, int L, int dtype,
+                                    int variant, int impl, float eps, void* stream) {
+  int rc = check_dims(B, NH, S, DHQK, DHHV, L);
+  if (rc != MLSTM_OK) return rc;
+  if (dtype != MLSTM_F32 && dtype != MLSTM_BF16 && dtype != MLSTM_F16) return MLSTM_ERR_DTYPE;
+  if (variant < MLSTM_EXP || variant > MLSTM_SIG_NONORM) return MLSTM_ERR_UNSUPPORTED;
+  if (!q || !dh || !fw_workspace || !dc_initial || !workspace) return MLSTM_ERR_NULL;
+  if (variant != MLSTM_SIG_NONORM && !n_out) return MLSTM_ERR_NULL;
+  const void* ptrs[] = {q, dh, n_out, fw_workspace, dc_initial, workspace};
+  for (const void* p : ptrs) if (p && !aligned16(p)) return MLSTM_ERR_ALIGN;
+  bool use_sm100 = false;
+  if ((rc = resolve_impl(impl, B, NH, S, DHQK, DHHV, L, dtype, &use_sm100)) != MLSTM_OK) return rc;
+  const ChunkwiseDims d = make_dims(B, NH, S, DHQK, DHHV, L, variant, eps, dtype);
+  FwLayout fl = carve_fw(const_cast<void*>(fw_workspace), B * NH, d.SP, d.NC);
+  if (fw_workspace_bytes < fl.bytes) return MLSTM_ERR_WORKSPACE;
+  const size_t need = align_up((size_t)B * NH * d.SP * sizeof(float), 256);
+  if (workspace_bytes < need) return MLSTM_ERR_WORKSPACE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  GateBuffers gb = fl.gb;
+  gb.inv_den = static_cast<float*>(workspace);
+  if ((rc = launch_inv_den(n_out, gb.inv_den, d, st)) != MLSTM_OK) return rc;
+  if (use_sm100) return sm100_recurrent_bw(q, dh, gb, nullptr, nullptr, dc_initial, d, st);
+  return simt_recurrent_bw(dtype, MLSTM_F32, q, dh, gb, nullptr, nullptr, dc_initial, d, st);
+}
+
 int mlstm_b200_chunkwise_summary(const void* k, const void* v, const void* i, const void* f, float* c_last,
                                  float* n_last, float* m_last, float* g_total, void* workspace,
                                  size_t workspace_bytes, int B, int NH, int S, int DHQK, int DHHV, int L, int dtype,

@@ -14,11 +14,18 @@ c_initial / n_initial / m_initial in, last states out: mlstm_kernels/torch/kerne
   forward of their segment, concurrently, from the true incoming state.  "chain" mode is the plain
   serial hand-off (segment r starts when r-1 has finished its recurrence).  Both reproduce the
   single-GPU (C, n, m) path.
-  The call is differentiable: the backward runs the chain the other way.  Rank r receives, from rank r+1, the
+  The call is differentiable.  "chain" mode runs the chain the other way: rank r receives, from rank r+1, the
   gradient of the state it handed over and the sum of (q . dq - k . dk) over all later tokens of each head
   (the forget-gate gradient of a token is sigmoid(-f) times that sum over all tokens from it to the end of the
   WHOLE sequence: mlstm_kernels/torch/chunkwise/triton_xl_chunk/chunkwise_gates.py:75-95), runs the backward of its
   segment, and passes both on to rank r-1.
+  "scan" mode keeps the segment backwards concurrent as well.  The state-gradient recurrence is linear in the
+  gradient that enters it on the right, dC_left = a dC_right + dC_own with a = exp(G + m_in - m_out) per head
+  (exp(G) for the sigmoid input gate), so (1) all ranks compute dC_own (`segment_dc_summary`: the light recurrence
+  only, from a zero gradient), (2) only the (B, NH, DHQK, DHHV) boundary gradient travels along the chain, one
+  multiply-add per hop, (3) all ranks run the full backward of their segment from the true dC_right.  The sum over
+  all later tokens needs no message: summed from a chunk boundary to the end of the sequence,
+  q . dq - k . dk = <C, dC> at that boundary, so it is <C_last, dC_right> of the rank's own segment.
 """
 
 from __future__ import annotations
@@ -111,6 +118,29 @@ def _segment_backward(q, k, v, i, f, saved, dh, dc_last, *, chunk_size, eps, var
                             m_out=saved["m_out"], fw_workspace=saved["workspace"])
 
 
+def segment_dc_summary(q, dh, saved, *, chunk_size, eps, variant, impl="auto"):
+    """The segment's own contribution to the gradient of the state that entered it: its state-gradient recurrence
+    started from a zero gradient on the right.  (B, NH, DHQK, DHHV) f32.  No per-chunk states are written."""
+    _lib.require_cuda(q, dh)
+    lib = _lib.load()
+    B, NH, S, DHQK = q.shape
+    DHHV = dh.shape[-1]
+    dt, im = _lib.dtype_code(q.dtype), _lib.IMPL[impl]
+    q, dh = q.contiguous(), dh.to(q.dtype).contiguous()
+    dev = q.device
+    dc = torch.empty((B, NH, DHQK, DHHV), dtype=torch.float32, device=dev)
+    sp = -(-S // chunk_size) * chunk_size
+    ws = torch.empty((max(B * NH * sp * 4 + 256, 256),), dtype=torch.uint8, device=dev)
+    fw_ws = saved["workspace"]
+    with torch.cuda.device(dev):
+        rc = lib.mlstm_b200_chunkwise_dc_summary(
+            _lib.ptr(q), _lib.ptr(dh), None if variant == _lib.SIG_NONORM else _lib.ptr(saved["n_out"]),
+            _lib.ptr(fw_ws), fw_ws.numel(), _lib.ptr(dc), _lib.ptr(ws), ws.numel(),
+            B, NH, S, DHQK, DHHV, chunk_size, dt, variant, im, eps, _lib.stream_handle(dev))
+    _lib.check(rc, "mlstm_b200_chunkwise_dc_summary")
+    return dc
+
+
 def _segment_gate_sum(q, k, f, dq, dk, df_local):
     """Sum over the segment's tokens of (q . dq - k . dk), per (batch, head).
     The kernels form these sums in f32 from their f32 accumulators and return them inside the forget-gate gradient:
@@ -147,6 +177,9 @@ class _SequenceParallelFn(torch.autograd.Function):
                 _send_state(last, next_rank, group)
             h, _, saved = _segment_forward_saved(q, k, v, i, f, state_in, chunk_size=L, eps=eps, variant=variant,
                                                  impl=impl)
+            # per-head decay of a state gradient across the whole segment, and the state at its right end
+            log_a = summary[3] + (state_in[2] - last[2]).reshape(summary[3].shape) if variant == _lib.EXP else summary[3]
+            saved["decay"], saved["c_last"] = torch.exp(log_a), last[0]
         ctx.opts, ctx.saved = opts, saved
         ctx.save_for_backward(q, k, v, i, f)
         ctx.mark_non_differentiable(*last)
@@ -161,6 +194,24 @@ class _SequenceParallelFn(torch.autograd.Function):
         next_rank = ranks[rank + 1] if rank < world - 1 else None
         B, NH, S, DHQK = q.shape
         DHHV = v.shape[-1]
+        if opts["mode"] == "scan":
+            kw = dict(chunk_size=opts["L"], eps=opts["eps"], variant=opts["variant"], impl=opts["impl"])
+            dh = dh.contiguous()
+            dc_right = None
+            if prev_rank is not None:   # rank 0 hands nothing on: it needs no summary
+                dc_left = segment_dc_summary(q, dh, ctx.saved, **kw)
+            if next_rank is not None:
+                like = (torch.empty((B, NH, DHQK, DHHV), dtype=torch.float32, device=q.device),)
+                (dc_right,) = _recv_state(like, next_rank, group)
+                if prev_rank is not None:
+                    dc_left = dc_left + ctx.saved["decay"][..., None, None] * dc_right
+            if prev_rank is not None:
+                _send_state((dc_left,), prev_rank, group)
+            dq, dk, dv, di, df, _ = _segment_backward(q, k, v, i, f, ctx.saved, dh, dc_right, **kw)
+            if dc_right is not None:
+                tail = (ctx.saved["c_last"] * dc_right).sum(dim=(-1, -2))
+                df = df + torch.sigmoid(-f.float()) * tail[..., None]
+            return dq, dk, dv, di.to(i.dtype), df.to(f.dtype), None, None
         dc_last, tail = None, None
         if next_rank is not None:   # gradient of the state handed to rank r+1, and the sum over all later tokens
             like = (torch.empty((B, NH, DHQK, DHHV), dtype=torch.float32, device=q.device),
@@ -225,7 +276,7 @@ def mlstm_chunkwise_sequence_parallel(
     """Forward (prefill) of one long sequence whose segments live on the ranks of `group`.
     Returns this rank's H (B, NH, S_local, DHHV) and, if requested, the state after the LAST segment
     (identical on every rank).  Ranks are ordered along the sequence: global rank order of the group.
-    Differentiable with respect to q, k, v, i, f (every rank must then run the backward: it is a chain of
+    Differentiable with respect to q, k, v, i, f (every rank must then run the backward: it exchanges
     point-to-point messages from the last rank to the first)."""
     if mode not in ("scan", "chain"):
         raise ValueError(f"unknown mode {mode}")
@@ -248,7 +299,9 @@ def mlstm_chunkwise_sequence_parallel(
     h, last = out[0], out[1:]
     if not return_last_states:
         return h
-    last = tuple(t.contiguous() for t in last)
+    # receive into copies: the state at the end of THIS rank's segment stays as the backward saved it
+    last = tuple(t.contiguous() if rank == world - 1 else torch.empty_like(t, memory_format=torch.contiguous_format)
+                 for t in last)
     for t in last:
         dist.broadcast(t, src=ranks[world - 1], group=group)
     if siging:

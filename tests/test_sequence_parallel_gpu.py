@@ -99,6 +99,59 @@ def test_backward_chain_emulated_on_one_gpu(dtype, L, dims, siging):
         assert max_rel_err(npy(got), npy(leaves[j].grad)) < tol, name
 
 
+@pytest.mark.parametrize("dtype,L,dims", [(torch.float32, 32, (16, 32)), (torch.bfloat16, 128, (256, 256)),
+                                          (torch.float16, 128, (128, 256))])
+@pytest.mark.parametrize("variant", [_lib.EXP, _lib.SIG, _lib.SIG_NONORM])
+def test_backward_scan_emulated_on_one_gpu(dtype, L, dims, variant):
+    """Scan form of the backward, ranks emulated in one process: (1) every segment's own state-gradient summary,
+    (2) the boundary gradients by dC_left = a dC_right + dC_own, (3) every segment's full backward from its true
+    dC_right, with the forget-gate tail <C_last, dC_right>.  Compared with the single pass over the whole sequence;
+    the summary is also compared with the dC_initial that the full segment backward returns."""
+    DHQK, DHHV = dims
+    P, S = 4, 4 * max(L, 128)
+    inp = case_inputs(35, 1, 2, S, DHQK, DHHV, f_offset=1.0)
+    q, k, v, i, f = (to_dev(inp[n], dtype) for n in "qkvif")
+    dh = to_dev(inp["dH"], dtype)
+    siging = variant != _lib.EXP
+    kw = dict(chunk_size=L)
+    if siging:
+        kw["normalize"] = variant == _lib.SIG
+    fn = mk.mlstm_siging_chunkwise__b200_xl_chunk if siging else mk.mlstm_chunkwise__b200_xl_chunk
+    leaves = [t.detach().clone().requires_grad_(True) for t in (q, k, v, i, f)]
+    fn(*leaves, **kw).backward(dh)
+    Lk = mk.kernel_chunk_size(q, v, L)
+    seg = S // P
+    opt = dict(chunk_size=Lk, eps=1e-6, variant=variant, impl="auto")
+    cut = lambda t, r: t[:, :, r * seg:(r + 1) * seg].contiguous()  # noqa: E731
+    state, saved, ends, decay = (None, None, None), [], [], []
+    for r in range(P):
+        g = torch.nn.functional.logsigmoid(cut(f, r).float()).sum(-1)
+        m_in = torch.zeros_like(g) if state[2] is None else state[2].reshape(g.shape)
+        _, state, sv = sharding._segment_forward_saved(*(cut(t, r) for t in (q, k, v, i, f)), state, **opt)
+        saved.append(sv)
+        ends.append(state[0])
+        decay.append(torch.exp(g + m_in - state[2].reshape(g.shape)) if variant == _lib.EXP else torch.exp(g))
+    own = [sharding.segment_dc_summary(cut(q, r), cut(dh, r), saved[r], **opt) for r in range(P)]
+    dc_right = [None] * P
+    for r in reversed(range(P - 1)):
+        nxt = own[r + 1] if dc_right[r + 1] is None else own[r + 1] + decay[r + 1][..., None, None] * dc_right[r + 1]
+        dc_right[r] = nxt
+    grads = []
+    for r in range(P):
+        dq, dk, dv, di, df, dc0 = sharding._segment_backward(*(cut(t, r) for t in (q, k, v, i, f)), saved[r], cut(dh, r),
+                                                             dc_right[r], **opt)
+        if dc_right[r] is not None:
+            tail = (ends[r] * dc_right[r]).sum(dim=(-1, -2))
+            df = df + torch.sigmoid(-cut(f, r).float()) * tail[..., None]
+        else:   # last segment: its own summary IS the gradient of the state it received
+            assert max_rel_err(npy(own[r]), npy(dc0)) < 1e-5
+        grads.append((dq, dk, dv, di, df))
+    tol = 1e-4 if dtype == torch.float32 else 2e-2
+    for j, name in enumerate("qkvif"):
+        got = torch.cat([g_[j] for g_ in grads], 2)
+        assert max_rel_err(npy(got), npy(leaves[j].grad)) < tol, name
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least two GPUs")
 @pytest.mark.parametrize("mode", ["scan", "chain"])
 def test_sequence_parallel_torchrun(tmp_path, mode):

@@ -69,6 +69,7 @@ def fake_segment_forward_saved(q, k, v, i, f, state_in, *, chunk_size, eps, vari
                         None if siging else _np(state_in[2]), chunk_size=chunk_size, eps=eps, siging=siging,
                         normalize=variant != 2)
     t = lambda x: torch.from_numpy(np.ascontiguousarray(x)).float()  # noqa: E731
+    fw.update(_k=_np(k), _v=_np(v), _i=_np(i), _f=_np(f))
     return t(fw["H"]), (t(fw["C_last"]), t(fw["n_last"]), t(fw["m_last"])), dict(fw=fw)
 
 
@@ -78,6 +79,15 @@ def fake_segment_backward(q, k, v, i, f, saved, dh, dc_last, *, chunk_size, eps,
                         chunk_size=chunk_size, eps=eps, siging=siging, normalize=variant != 2)
     t = lambda x: torch.from_numpy(np.ascontiguousarray(x)).float()  # noqa: E731
     return t(bw["dQ"]), t(bw["dK"]), t(bw["dV"]), t(bw["dI"]), t(bw["dF"]), t(bw["dC_initial"])
+
+
+def fake_segment_dc_summary(q, dh, saved, *, chunk_size, eps, variant, impl="auto"):
+    siging = variant != 0
+    fw = saved["fw"]
+    # only the state-gradient recurrence matters here: it reads q, dh and the forward's gates and normaliser
+    bw = O.chunkwise_bw(_np(q), fw["_k"], fw["_v"], fw["_i"], fw["_f"], _np(dh), fw, None, True,
+                        chunk_size=chunk_size, eps=eps, siging=siging, normalize=variant != 2)
+    return torch.from_numpy(np.ascontiguousarray(bw["dC_initial"])).float()
 
 
 CASE = dict(seed=17, B=1, NH=2, S=256, DHQK=16, DHHV=32, f_offset=1.0)
@@ -91,6 +101,7 @@ def _worker(rank, world, port, mode, siging, out_dir):
     sharding.state_combine = fake_state_combine
     sharding._segment_forward_saved = fake_segment_forward_saved
     sharding._segment_backward = fake_segment_backward
+    sharding.segment_dc_summary = fake_segment_dc_summary
     inp = make_chunkwise_inputs(CASE)
     seg = CASE["S"] // world
     sl = slice(rank * seg, (rank + 1) * seg)
@@ -110,10 +121,9 @@ def _free_port():
         return s.getsockname()[1]
 
 
-@pytest.mark.parametrize("mode", ["scan", "chain"])
+@pytest.mark.parametrize("mode,world", [("scan", 2), ("chain", 2), ("scan", 4)])
 @pytest.mark.parametrize("siging", [False, True])
-def test_sequence_parallel_two_ranks_gloo(tmp_path, mode, siging):
-    world = 2
+def test_sequence_parallel_gloo_ranks(tmp_path, mode, world, siging):
     mp.spawn(_worker, args=(world, _free_port(), mode, siging, str(tmp_path)), nprocs=world, join=True)
     inp = make_chunkwise_inputs(CASE)
     full, full_bw = O.chunkwise_fwbw(inp["q"], inp["k"], inp["v"], inp["i"], inp["f"], inp["dH"], chunk_size=32,
