@@ -120,6 +120,12 @@ size_t mlstm_b200_chunkwise_workspace_bytes(int B, int NH, int S, int DHQK, int 
  *   replaces the host-side zero padding of wrap_chunkwise__pad_zeros and the chunk-size ladder 64/32/16 of
  *   wrap_chunkwise__arbitrary_sequence_length (mlstm_kernels/torch/kernel_wrappers.py:76-171,206-267).
  */
+/* Large problems (more recurrence CTAs than SMs) are run as two halves of the (batch, head) units on two streams: the
+ * caller's and one the library creates per device on first use, forked and joined with events, so that one half's
+ * last, partly filled wave of CTAs overlaps the other half's work.  Legal under stream capture.  on = 0 keeps every
+ * launch on the caller's stream; returns the previous setting.  mlstm_b200_chunkwise_fw_static never splits. */
+int mlstm_b200_set_unit_split(int on);
+
 int mlstm_b200_chunkwise_fw(const void* q, const void* k, const void* v, const void* i, const void* f,
                             const float* c_initial, const float* n_initial, const float* m_initial,
                             void* h, float* n_out, float* m_out,

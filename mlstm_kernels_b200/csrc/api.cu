@@ -47,6 +47,49 @@ PhaseScope::~PhaseScope() {
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// ---- the (batch, head) units as two chains of launches on two streams ---------------------------------
+// Each recurrence CTA walks a whole sequence, so a launch whose CTA count is not a multiple of the SM count ends with
+// a partly filled wave, and the intra-chunk kernel behind it waits for that wave.  The units are independent: the
+// first half runs on the caller's stream and the second half on a stream of the library, forked and joined with
+// events (the pattern stream capture allows), and the block scheduler fills the idle SMs of one chain's last wave
+// with the other chain's CTAs.  No kernel waits for another one: the order is the streams' and events' only.
+struct SideStream { cudaStream_t st = nullptr; cudaEvent_t fork = nullptr, join = nullptr; };
+static std::mutex g_side_mu;          // held while a split call enqueues: one stream and one event pair per device
+static SideStream g_side[64];
+static std::atomic<int> g_split_on{1};
+
+static SideStream* side_stream_for_current_device() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  SideStream& s = g_side[dev];
+  if (s.st == nullptr) {
+    cudaStream_t st = nullptr;
+    cudaEvent_t a = nullptr, b = nullptr;
+    // default priority: giving this stream a higher one (so that the second half's recurrence CTAs are placed before
+    // the first half's intra-chunk CTAs) measured slower
+    if (cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&a, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&b, cudaEventDisableTiming) != cudaSuccess) {
+      (void)cudaGetLastError();
+      if (st) cudaStreamDestroy(st);
+      if (a) cudaEventDestroy(a);
+      if (b) cudaEventDestroy(b);
+      return nullptr;
+    }
+    s.st = st; s.fork = a; s.join = b;
+  }
+  return &s;
+}
+
+// worth it only when the recurrence needs more than one wave of CTAs and the last one is far from full (and never
+// while phases are being timed)
+static bool want_unit_split(const ChunkwiseDims& d, bool allow) {
+  if (!allow || g_split_on.load(std::memory_order_relaxed) == 0 || g_prof_on || d.B * d.NH < 2) return false;
+  const long ctas = sm100_recurrence_ctas(d), sms = sm100_sm_count();
+  const long waves = (ctas + sms - 1) / sms;
+  return waves > 1 && ctas * 100 < waves * sms * 95;   // the last wave leaves more than 5 % of the SM time idle
+}
+
 // S need not be a multiple of L where the tcgen05 kernels run (they mask a ragged last chunk); resolve_impl refuses
 // that case for the portable kernels.
 static int check_dims(int B, int NH, int S, int DHQK, int DHHV, int L) {
@@ -236,12 +279,28 @@ size_t mlstm_b200_chunkwise_workspace_bytes(int B, int NH, int S, int DHQK, int 
   return carve_bw(nullptr, B * NH, SP, NC, DHQK, DHHV, dtype_size(use_sm100 ? dtype : MLSTM_F32)).bytes;
 }
 
+int mlstm_b200_set_unit_split(int on) { return g_split_on.exchange(on != 0 ? 1 : 0); }
+
 int mlstm_b200_chunkwise_fw(const void* q, const void* k, const void* v, const void* i, const void* f,
                             const float* c_initial, const float* n_initial, const float* m_initial, void* h,
                             float* n_out, float* m_out, void* c_states, float* n_states, float* m_states,
                             float* c_last, float* n_last, float* m_last, void* workspace, size_t workspace_bytes,
                             int B, int NH, int S, int DHQK, int DHHV, int L, int dtype, int gate_dtype, int variant,
                             int impl, float eps, void* stream) {
+  return chunkwise_fw_body(q, k, v, i, f, c_initial, n_initial, m_initial, h, n_out, m_out, c_states, n_states, m_states,
+                           c_last, n_last, m_last, workspace, workspace_bytes, B, NH, S, DHQK, DHHV, L, dtype,
+                           gate_dtype, variant, impl, eps, stream, true);
+}
+
+}  // extern "C"
+
+namespace mlstm {
+int chunkwise_fw_body(const void* q, const void* k, const void* v, const void* i, const void* f,
+                      const float* c_initial, const float* n_initial, const float* m_initial, void* h,
+                      float* n_out, float* m_out, void* c_states, float* n_states, float* m_states,
+                      float* c_last, float* n_last, float* m_last, void* workspace, size_t workspace_bytes,
+                      int B, int NH, int S, int DHQK, int DHHV, int L, int dtype, int gate_dtype, int variant,
+                      int impl, float eps, void* stream, bool allow_split) {
   int rc = check_dims(B, NH, S, DHQK, DHHV, L);
   if (rc != MLSTM_OK) return rc;
   if (dtype != MLSTM_F32 && dtype != MLSTM_BF16 && dtype != MLSTM_F16) return MLSTM_ERR_DTYPE;
@@ -262,8 +321,22 @@ int mlstm_b200_chunkwise_fw(const void* q, const void* k, const void* v, const v
 
   if ((rc = launch_gates(gate_dtype, i, f, variant == MLSTM_EXP ? m_initial : nullptr, nullptr, m_out, lay.gb, m_states, d, st)) != MLSTM_OK) return rc;
   if (use_sm100) {
-    if ((rc = sm100_recurrent_fw(k, v, lay.gb, c_initial, n_initial, c_states, n_states, c_last, n_last, d, st)) != MLSTM_OK) return rc;
-    if ((rc = sm100_parallel_fw(q, k, v, lay.gb, c_states, n_states, h, n_out, d, st)) != MLSTM_OK) return rc;
+    std::unique_lock<std::mutex> lk(g_side_mu, std::defer_lock);
+    SideStream* side = nullptr;
+    if (want_unit_split(d, allow_split)) { lk.lock(); side = side_stream_for_current_device(); }
+    const UnitRange first{0, side ? (B * NH + 1) / 2 : B * NH}, second{first.count, -1};
+    if (side) {
+      MLSTM_CUDA_CHECK(cudaEventRecord(side->fork, st));
+      MLSTM_CUDA_CHECK(cudaStreamWaitEvent(side->st, side->fork, 0));
+    }
+    if ((rc = sm100_recurrent_fw(k, v, lay.gb, c_initial, n_initial, c_states, n_states, c_last, n_last, d, st, first)) != MLSTM_OK) return rc;
+    if (side && (rc = sm100_recurrent_fw(k, v, lay.gb, c_initial, n_initial, c_states, n_states, c_last, n_last, d, side->st, second)) != MLSTM_OK) return rc;
+    if ((rc = sm100_parallel_fw(q, k, v, lay.gb, c_states, n_states, h, n_out, d, st, first)) != MLSTM_OK) return rc;
+    if (side) {
+      if ((rc = sm100_parallel_fw(q, k, v, lay.gb, c_states, n_states, h, n_out, d, side->st, second)) != MLSTM_OK) return rc;
+      MLSTM_CUDA_CHECK(cudaEventRecord(side->join, side->st));
+      MLSTM_CUDA_CHECK(cudaStreamWaitEvent(st, side->join, 0));
+    }
   } else {
     if ((rc = simt_recurrent_fw(dtype, MLSTM_F32, k, v, lay.gb, c_initial, n_initial, c_states, n_states, c_last, n_last, d, st)) != MLSTM_OK) return rc;
     if ((rc = simt_parallel_fw(dtype, MLSTM_F32, q, k, v, lay.gb, c_states, n_states, h, n_out, d, st)) != MLSTM_OK) return rc;
@@ -274,8 +347,7 @@ int mlstm_b200_chunkwise_fw(const void* q, const void* k, const void* v, const v
   }
   return MLSTM_OK;
 }
-
-}  // extern "C"
+}  // namespace mlstm
 
 // Backward body.  With `fw_workspace` (the scratch buffer the forward call of the same problem left behind, still
 // intact) and `m_out` the gate pre-pass is not run again: its vectors are read from that buffer.
@@ -316,8 +388,24 @@ static int bw_impl(const void* q, const void* k, const void* v, const void* i, c
     if ((rc = launch_gates(gate_dtype, i, f, variant == MLSTM_EXP ? m_initial : nullptr, n_out, nullptr, lay.gb, lay.m_states, d, st)) != MLSTM_OK) return rc;
   }
   if (use_sm100) {
-    if ((rc = sm100_recurrent_bw(q, dh, lay.gb, dc_last, lay.dc_states, dc_initial, d, st)) != MLSTM_OK) return rc;
-    if ((rc = sm100_parallel_bw(q, k, v, dh, lay.gb, c_states, lay.dc_states, dq, dk, dv, lay.acc, lay.kdk, d, st)) != MLSTM_OK) return rc;
+    {
+      std::unique_lock<std::mutex> lk(g_side_mu, std::defer_lock);
+      SideStream* side = nullptr;
+      if (want_unit_split(d, true)) { lk.lock(); side = side_stream_for_current_device(); }
+      const UnitRange first{0, side ? (B * NH + 1) / 2 : B * NH}, second{first.count, -1};
+      if (side) {
+        MLSTM_CUDA_CHECK(cudaEventRecord(side->fork, st));
+        MLSTM_CUDA_CHECK(cudaStreamWaitEvent(side->st, side->fork, 0));
+      }
+      if ((rc = sm100_recurrent_bw(q, dh, lay.gb, dc_last, lay.dc_states, dc_initial, d, st, first)) != MLSTM_OK) return rc;
+      if (side && (rc = sm100_recurrent_bw(q, dh, lay.gb, dc_last, lay.dc_states, dc_initial, d, side->st, second)) != MLSTM_OK) return rc;
+      if ((rc = sm100_parallel_bw(q, k, v, dh, lay.gb, c_states, lay.dc_states, dq, dk, dv, lay.acc, lay.kdk, d, st, first)) != MLSTM_OK) return rc;
+      if (side) {
+        if ((rc = sm100_parallel_bw(q, k, v, dh, lay.gb, c_states, lay.dc_states, dq, dk, dv, lay.acc, lay.kdk, d, side->st, second)) != MLSTM_OK) return rc;
+        MLSTM_CUDA_CHECK(cudaEventRecord(side->join, side->st));
+        MLSTM_CUDA_CHECK(cudaStreamWaitEvent(st, side->join, 0));
+      }
+    }
     {
       PhaseScope ps(PH_GATE_GRADS, st);
       const int n_anchors = anchor_count(d.NC);

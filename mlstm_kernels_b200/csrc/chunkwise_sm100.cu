@@ -41,6 +41,7 @@ struct RecParams {
   float* c_final;           // (BNH, DHQK, DHHV) f32 or nullptr
   float* n_final;
   int S, SP, NC, DHQK, DHHV;   // SP = NC * 128: slots per (batch, head) of the per-token scale vectors
+  int bh0;                     // first (batch, head) unit of this launch (a launch may cover a sub-range of the units)
 };
 
 constexpr int REC_THREADS = 640;                 // warp 0 TMA, 1 MMA, 2..9 gate the left tile, 10..17 own the state, 18 stores it, 19 keeps n
@@ -80,7 +81,7 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
   static_assert(TN == 128 || TN == 64, "state tile width");
   constexpr int HC = TN / 2;   // columns each of the two state-warp groups owns
   const int n_et = p.DHHV / TN, n_dt = p.DHQK / 128;
-  const int et = blockIdx.x % n_et, dt = (blockIdx.x / n_et) % n_dt, bh = blockIdx.x / (n_et * n_dt);
+  const int et = blockIdx.x % n_et, dt = (blockIdx.x / n_et) % n_dt, bh = p.bh0 + blockIdx.x / (n_et * n_dt);
   const int e0 = et * TN, d0 = dt * 128;
   const int NC = p.NC, NH2 = 2 * p.NC;   // ring steps: two per chunk
   const bool do_n = (!BWD) && et == 0 && (p.n_states != nullptr || p.n_final != nullptr);
@@ -354,6 +355,7 @@ struct ParParams {
   size_t nslots;              // B * NH * SP
   int S, SP, NC, DHQK, DHHV, variant;   // SP = NC * 128: slots per (batch, head) of the per-token gate vectors
   float eps, qk_scale;
+  int bh0;                    // first (batch, head) unit of this launch
 };
 
 constexpr int PAR_THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2..9 element-wise
@@ -827,7 +829,7 @@ par_fw_sm100(const __grid_constant__ CUtensorMap mQ, const __grid_constant__ CUt
   const int T = p.DHHV / 128;                         // output tiles per chunk; a CTA takes up to PAR_MAXSUB of them
   // 1-D grid in the order (tile group, chunk, batch x head): no 65535 limit on chunks or batch x heads
   const int gx = (T + PAR_MAXSUB - 1) / PAR_MAXSUB;
-  const int x = blockIdx.x % gx, ck = (blockIdx.x / gx) % p.NC, bh = blockIdx.x / (gx * p.NC);
+  const int x = blockIdx.x % gx, ck = (blockIdx.x / gx) % p.NC, bh = p.bh0 + blockIdx.x / (gx * p.NC);
   const int t0 = PAR_MAXSUB * x;
   par_body<F16>(PM_H, &mQ, &mK, &mV, &mC, &mV, p, sh, t0, min(PAR_MAXSUB, T - t0), ck, bh);
 }
@@ -846,7 +848,7 @@ par_bw_sm100(const __grid_constant__ CUtensorMap mQ, const __grid_constant__ CUt
   const int T_dv = p.DHHV / 128, T_dk = p.DHQK / 128;         // output tiles per chunk of dV, and of dK / dQ
   const int c_dv = (T_dv + PAR_MAXSUB - 1) / PAR_MAXSUB, c_dk = (T_dk + PAR_MAXSUB - 1) / PAR_MAXSUB;   // CTAs per mode
   const int gx = c_dv + 2 * c_dk;   // 1-D grid in the order (mode and tile group, chunk, batch x head)
-  const int x = blockIdx.x % gx, ck = (blockIdx.x / gx) % p.NC, bh = blockIdx.x / (gx * p.NC);
+  const int x = blockIdx.x % gx, ck = (blockIdx.x / gx) % p.NC, bh = p.bh0 + blockIdx.x / (gx * p.NC);
   int mode, pair, T;
   const CUtensorMap *a, *b, *xm, *stm, *e;
   if (x < c_dv) { mode = PM_DV; pair = x; T = T_dv; a = &mK; b = &mQ; xm = &mDH; stm = &mdC_mn; e = &mDH; }
@@ -926,11 +928,11 @@ static bool state_map(CUtensorMap* m, const void* base, const ChunkwiseDims& d, 
 
 template <bool BWD, int TN, bool F16>
 static int launch_rec_tn(const CUtensorMap& mL, const CUtensorMap& mR, const CUtensorMap& mS, const RecParams& rp,
-                         const ChunkwiseDims& d, cudaStream_t st) {
+                         const ChunkwiseDims& d, int units, cudaStream_t st) {
   auto kern = rec_sm100<BWD, TN, F16>;
   static bool attr_done[64] = {};
   if (int rc = set_smem_once(kern, rec_smem_bytes(BWD), attr_done)) return rc;
-  const unsigned grid = (unsigned)(d.DHHV / TN) * (unsigned)(d.DHQK / 128) * (unsigned)(d.B * d.NH);
+  const unsigned grid = (unsigned)(d.DHHV / TN) * (unsigned)(d.DHQK / 128) * (unsigned)units;
   kern<<<grid, REC_THREADS, rec_smem_bytes(BWD), st>>>(mL, mR, mS, rp);
   MLSTM_LAUNCH_CHECK();
   return MLSTM_OK;
@@ -949,8 +951,15 @@ static int sm_count() {
   return cached[dev];
 }
 
+long sm100_recurrence_ctas(const ChunkwiseDims& d) { return (long)(d.DHHV / 128) * (d.DHQK / 128) * d.B * d.NH; }
+int sm100_sm_count() { return sm_count(); }
+
 template <bool BWD>
-static int launch_rec(const void* left, const void* right, const RecParams& rp, const ChunkwiseDims& d, cudaStream_t st) {
+static int launch_rec(const void* left, const void* right, RecParams rp, const ChunkwiseDims& d, UnitRange ur,
+                      cudaStream_t st) {
+  rp.bh0 = ur.first;
+  const int units = ur.count < 0 ? d.B * d.NH - ur.first : ur.count;
+  if (units <= 0) return MLSTM_OK;
   CUtensorMap mL, mR, mS;
   // recurrence operands arrive in half-chunk boxes (64 tokens x 64 columns)
   if (!tok_map(&mL, left, d, d.DHQK, REC_HALF) || !tok_map(&mR, right, d, d.DHHV, REC_HALF)) return MLSTM_ERR_CUDA;
@@ -961,25 +970,25 @@ static int launch_rec(const void* left, const void* right, const RecParams& rp, 
   const long ctas128 = (long)(d.DHHV / 128) * (d.DHQK / 128) * d.B * d.NH;
   const bool f16 = d.dtype == MLSTM_F16;
   if (2 * ctas128 <= sm_count())
-    return f16 ? launch_rec_tn<BWD, 64, true>(mL, mR, mS, rp, d, st) : launch_rec_tn<BWD, 64, false>(mL, mR, mS, rp, d, st);
-  return f16 ? launch_rec_tn<BWD, 128, true>(mL, mR, mS, rp, d, st) : launch_rec_tn<BWD, 128, false>(mL, mR, mS, rp, d, st);
+    return f16 ? launch_rec_tn<BWD, 64, true>(mL, mR, mS, rp, d, units, st) : launch_rec_tn<BWD, 64, false>(mL, mR, mS, rp, d, units, st);
+  return f16 ? launch_rec_tn<BWD, 128, true>(mL, mR, mS, rp, d, units, st) : launch_rec_tn<BWD, 128, false>(mL, mR, mS, rp, d, units, st);
 }
 
 int sm100_recurrent_fw(const void* k, const void* v, const GateBuffers& gb, const float* c_initial,
                        const float* n_initial, void* c_states, float* n_states, float* c_last, float* n_last,
-                       const ChunkwiseDims& d, cudaStream_t st) {
+                       const ChunkwiseDims& d, cudaStream_t st, UnitRange ur) {
   PhaseScope ps(PH_REC_FW, st);
   RecParams rp{gb.abar, nullptr, 1.f, gb.gbar, c_initial, n_initial, c_states,
-               d.variant == MLSTM_SIG_NONORM ? nullptr : n_states, c_last, d.variant == MLSTM_SIG_NONORM ? nullptr : n_last, d.S, d.SP, d.NC, d.DHQK, d.DHHV};
-  return launch_rec<false>(k, v, rp, d, st);
+               d.variant == MLSTM_SIG_NONORM ? nullptr : n_states, c_last, d.variant == MLSTM_SIG_NONORM ? nullptr : n_last, d.S, d.SP, d.NC, d.DHQK, d.DHHV, 0};
+  return launch_rec<false>(k, v, rp, d, ur, st);
 }
 
 int sm100_recurrent_bw(const void* q, const void* dh, const GateBuffers& gb, const float* dc_last, void* dc_states,
-                       float* dc_initial, const ChunkwiseDims& d, cudaStream_t st) {
+                       float* dc_initial, const ChunkwiseDims& d, cudaStream_t st, UnitRange ur) {
   PhaseScope ps(PH_REC_BW, st);
   RecParams rp{gb.bbar, gb.inv_den, d.qk_scale, gb.gbar, dc_last, nullptr, dc_states, nullptr,
-               dc_initial, nullptr, d.S, d.SP, d.NC, d.DHQK, d.DHHV};
-  return launch_rec<true>(q, dh, rp, d, st);
+               dc_initial, nullptr, d.S, d.SP, d.NC, d.DHQK, d.DHHV, 0};
+  return launch_rec<true>(q, dh, rp, d, ur, st);
 }
 
 static ParParams base_params(const GateBuffers& gb, const ChunkwiseDims& d) {
@@ -993,7 +1002,10 @@ static ParParams base_params(const GateBuffers& gb, const ChunkwiseDims& d) {
 }
 
 int sm100_parallel_fw(const void* q, const void* k, const void* v, const GateBuffers& gb, const void* c_states,
-                      const float* n_states, void* h, float* n_out, const ChunkwiseDims& d, cudaStream_t st) {
+                      const float* n_states, void* h, float* n_out, const ChunkwiseDims& d, cudaStream_t st,
+                      UnitRange ur) {
+  const int units = ur.count < 0 ? d.B * d.NH - ur.first : ur.count;
+  if (units <= 0) return MLSTM_OK;
   PhaseScope ps(PH_PAR_FW, st);
   CUtensorMap mQ, mK, mV, mC;
   if (!tok_map(&mQ, q, d, d.DHQK) || !tok_map(&mK, k, d, d.DHQK) || !tok_map(&mV, v, d, d.DHHV) ||
@@ -1001,12 +1013,13 @@ int sm100_parallel_fw(const void* q, const void* k, const void* v, const GateBuf
     return MLSTM_ERR_CUDA;
   ParParams pp = base_params(gb, d);
   pp.n_states = n_states; pp.out_h = (uint16_t*)h; pp.n_out = n_out;
+  pp.bh0 = ur.first;
   const bool f16 = d.dtype == MLSTM_F16;
   static bool attr_done[2][64] = {};
   if (int rc = f16 ? set_smem_once(par_fw_sm100<true>, PAR_SMEM, attr_done[1])
                    : set_smem_once(par_fw_sm100<false>, PAR_SMEM, attr_done[0])) return rc;
   // up to PAR_MAXSUB output tiles per CTA
-  const unsigned grid = (unsigned)((d.DHHV / 128 + PAR_MAXSUB - 1) / PAR_MAXSUB) * (unsigned)d.NC * (unsigned)(d.B * d.NH);
+  const unsigned grid = (unsigned)((d.DHHV / 128 + PAR_MAXSUB - 1) / PAR_MAXSUB) * (unsigned)d.NC * (unsigned)units;
   if (f16) par_fw_sm100<true><<<grid, PAR_THREADS, PAR_SMEM, st>>>(mQ, mK, mV, mC, pp);
   else par_fw_sm100<false><<<grid, PAR_THREADS, PAR_SMEM, st>>>(mQ, mK, mV, mC, pp);
   MLSTM_LAUNCH_CHECK();
@@ -1015,7 +1028,9 @@ int sm100_parallel_fw(const void* q, const void* k, const void* v, const GateBuf
 
 int sm100_parallel_bw(const void* q, const void* k, const void* v, const void* dh, const GateBuffers& gb,
                       const void* c_states, const void* dc_states, void* dq, void* dk, void* dv, float* qdq_parts,
-                      float* kdk_parts, const ChunkwiseDims& d, cudaStream_t st) {
+                      float* kdk_parts, const ChunkwiseDims& d, cudaStream_t st, UnitRange ur) {
+  const int units = ur.count < 0 ? d.B * d.NH - ur.first : ur.count;
+  if (units <= 0) return MLSTM_OK;
   PhaseScope ps(PH_PAR_BW, st);
   CUtensorMap mQ, mK, mV, mDH, mC_k, mdC_mn, mdC_k;
   if (!tok_map(&mQ, q, d, d.DHQK) || !tok_map(&mK, k, d, d.DHQK) || !tok_map(&mV, v, d, d.DHHV) ||
@@ -1025,13 +1040,14 @@ int sm100_parallel_bw(const void* q, const void* k, const void* v, const void* d
   ParParams pp = base_params(gb, d);
   pp.out_dv = (uint16_t*)dv; pp.out_dk = (uint16_t*)dk; pp.out_dq = (uint16_t*)dq;
   pp.rowdot_q = qdq_parts; pp.rowdot_k = kdk_parts;
+  pp.bh0 = ur.first;
   const bool f16 = d.dtype == MLSTM_F16;
   static bool attr_done[2][64] = {};
   if (int rc = f16 ? set_smem_once(par_bw_sm100<true>, PAR_SMEM, attr_done[1])
                    : set_smem_once(par_bw_sm100<false>, PAR_SMEM, attr_done[0])) return rc;
   // up to PAR_MAXSUB output tiles per CTA
   const unsigned grid = (unsigned)((d.DHHV / 128 + PAR_MAXSUB - 1) / PAR_MAXSUB + 2 * ((d.DHQK / 128 + PAR_MAXSUB - 1) / PAR_MAXSUB)) *
-                        (unsigned)d.NC * (unsigned)(d.B * d.NH);
+                        (unsigned)d.NC * (unsigned)units;
   if (f16) par_bw_sm100<true><<<grid, PAR_THREADS, PAR_SMEM, st>>>(mQ, mK, mV, mDH, mC_k, mdC_mn, mdC_k, pp);
   else par_bw_sm100<false><<<grid, PAR_THREADS, PAR_SMEM, st>>>(mQ, mK, mV, mDH, mC_k, mdC_mn, mdC_k, pp);
   MLSTM_LAUNCH_CHECK();

@@ -39,16 +39,32 @@ int simt_parallel_bw(int dtype, int state_dtype, const void* q, const void* k, c
 // chunkwise_sm100.cu : tcgen05 + TMA kernels (bf16, L = 128, head dims multiples of 128)
 bool sm100_supported(int S, int DHQK, int DHHV, int L, int dtype);
 bool sm100_sizes_ok(int B, int NH, int S, int DHQK, int DHHV);
+// A launch may cover a sub-range of the B * NH independent (batch, head) units; all pointers stay those of the whole
+// problem.  count < 0: every unit from `first` on.
+struct UnitRange { int first = 0; int count = -1; };
 int sm100_recurrent_fw(const void* k, const void* v, const GateBuffers& gb, const float* c_initial,
                        const float* n_initial, void* c_states, float* n_states, float* c_last, float* n_last,
-                       const ChunkwiseDims& d, cudaStream_t st);
+                       const ChunkwiseDims& d, cudaStream_t st, UnitRange ur = UnitRange());
 int sm100_parallel_fw(const void* q, const void* k, const void* v, const GateBuffers& gb, const void* c_states,
-                      const float* n_states, void* h, float* n_out, const ChunkwiseDims& d, cudaStream_t st);
+                      const float* n_states, void* h, float* n_out, const ChunkwiseDims& d, cudaStream_t st,
+                      UnitRange ur = UnitRange());
 int sm100_recurrent_bw(const void* q, const void* dh, const GateBuffers& gb, const float* dc_last, void* dc_states,
-                       float* dc_initial, const ChunkwiseDims& d, cudaStream_t st);
+                       float* dc_initial, const ChunkwiseDims& d, cudaStream_t st, UnitRange ur = UnitRange());
 int sm100_parallel_bw(const void* q, const void* k, const void* v, const void* dh, const GateBuffers& gb,
                       const void* c_states, const void* dc_states, void* dq, void* dk, void* dv, float* qdq_parts,
-                      float* kdk_parts, const ChunkwiseDims& d, cudaStream_t st);
+                      float* kdk_parts, const ChunkwiseDims& d, cudaStream_t st, UnitRange ur = UnitRange());
+// number of CTAs the recurrence launches for the whole problem with 128-column state tiles, and SMs of the device
+long sm100_recurrence_ctas(const ChunkwiseDims& d);
+int sm100_sm_count();
+
+// Forward of mlstm_b200_chunkwise_fw; `allow_split` = false keeps every launch on the caller's stream (no stream or
+// event of the library is created or used).
+int chunkwise_fw_body(const void* q, const void* k, const void* v, const void* i, const void* f,
+                      const float* c_initial, const float* n_initial, const float* m_initial, void* h,
+                      float* n_out, float* m_out, void* c_states, float* n_states, float* m_states,
+                      float* c_last, float* n_last, float* m_last, void* workspace, size_t workspace_bytes,
+                      int B, int NH, int S, int DHQK, int DHHV, int L, int dtype, int gate_dtype, int variant,
+                      int impl, float eps, void* stream, bool allow_split);
 
 int sm100_device_status(int reset, int* status);
 int sm100_wait_expiry_selftest(unsigned limit, int code, cudaStream_t st);

@@ -76,9 +76,11 @@ int mlstm_b200_chunkwise_fw_static(const void* q, const void* k, const void* v, 
   if (rc != MLSTM_OK) return rc;
   if ((rc = scratch_for_current_device(&scratch)) != MLSTM_OK) return rc;
   // The forward writes every scratch word before it reads it, so nothing has to be cleared between calls.
-  return mlstm_b200_chunkwise_fw(q, k, v, i, f, c_initial, n_initial, m_initial, h, n_out, m_out, c_states, n_states,
-                                 m_states, c_last, n_last, m_last, scratch, kStaticScratchBytes, B, NH, S, DHQK, DHHV,
-                                 L, dtype, gate_dtype, variant, impl, eps, stream);
+  // Single-stream form of the forward: the two-stream split of the regular entry point would create a stream and two
+  // events on its first use, which is driver memory this entry point promises not to take.
+  return mlstm::chunkwise_fw_body(q, k, v, i, f, c_initial, n_initial, m_initial, h, n_out, m_out, c_states, n_states,
+                                  m_states, c_last, n_last, m_last, scratch, kStaticScratchBytes, B, NH, S, DHQK, DHHV,
+                                  L, dtype, gate_dtype, variant, impl, eps, stream, false);
 }
 
 }  // extern "C"

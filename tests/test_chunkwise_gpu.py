@@ -259,6 +259,50 @@ def test_forward_backward_capture_in_cuda_graph():
         assert torch.equal(a, b)
 
 
+@pytest.mark.parametrize("odd", [False, True])
+def test_two_stream_unit_split_is_bit_identical_and_capturable(odd):
+    """With more recurrence CTAs than SMs and a poorly filled last wave, the library runs the two halves of the
+    (batch, head) units on two streams.  Same kernels on the same data: every output must be bit-identical to the
+    single-stream run, with an odd number of units too, and the forked launches must survive a graph capture."""
+    from mlstm_kernels_b200 import _lib
+    lib = _lib.load()
+    B, NH = (3, 67) if odd else (2, 100)          # 201 / 200 state tiles of 128 x 128 on 148 SMs: two waves, 68 % full
+    g = torch.Generator(device="cuda").manual_seed(11)
+    rnd = lambda *s: torch.randn(*s, device="cuda", generator=g)  # noqa: E731
+    q, k, v = (rnd(B, NH, 300, 128).bfloat16() for _ in range(3))
+    i, f = rnd(B, NH, 300).bfloat16(), (3 + rnd(B, NH, 300)).bfloat16()
+    dh = rnd(B, NH, 300, 128).bfloat16()
+
+    def step():
+        leaves = [t.detach().requires_grad_(True) for t in (q, k, v, i, f)]
+        h, last = mk.mlstm_chunkwise__b200_xl_chunk(*leaves, chunk_size=128, return_last_states=True)
+        grads = torch.autograd.grad(h, leaves, dh)
+        return (h.detach(),) + tuple(last) + grads
+
+    prev = lib.mlstm_b200_set_unit_split(0)
+    try:
+        single = [t.clone() for t in step()]
+        lib.mlstm_b200_set_unit_split(1)
+        split = [t.clone() for t in step()]
+        for a, b in zip(single, split):
+            assert torch.equal(a, b)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            step()
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            outs = step()
+        for _ in range(2):
+            graph.replay()
+        torch.cuda.synchronize()
+        for a, b in zip(single, outs):
+            assert torch.equal(a, b)
+    finally:
+        lib.mlstm_b200_set_unit_split(prev)
+
+
 def test_benchmark_size_properties():
     """At the benchmark size (B=8, S=8192, NH=16, 256/256, bf16: too large for the oracle) the kernels are checked
     through properties that do not depend on the size: reruns are bit-identical (forward and all five gradients),
