@@ -504,6 +504,18 @@ def run_b200(args):
             "True (the reference's default)": dict(ms=ms_rec, tflops=flops_fwbw / (ms_rec * 1e-3) / 1e12,
                                                    **memory(True)),
             "note": "memory above the resident inputs (H and the input gradients included); timed back to back"}
+        # the same step with every launch on one stream (the library's two-stream split of the units switched off)
+        lib = _lib.load()
+        prev_split = lib.mlstm_b200_set_unit_split(0)
+        try:
+            ms_one, ms_one_fw = timed_local(torch, step_resident, 5, 3), timed_local(torch, fw_only, 5, 3)
+        finally:
+            lib.mlstm_b200_set_unit_split(prev_split)
+        ms_two, ms_two_fw = timed_local(torch, step_resident, 5, 3), timed_local(torch, fw_only, 5, 3)
+        extra["two_stream_unit_split"] = {
+            "on (default)": dict(fwbw_ms=ms_two, fw_ms=ms_two_fw), "off": dict(fwbw_ms=ms_one, fw_ms=ms_one_fw),
+            "note": "when the recurrence's last wave of CTAs is poorly filled, the two halves of the (batch, head) "
+                    "units run as two chains of launches on two streams; timed back to back"}
         sig_step = make_step(mk.mlstm_siging_chunkwise__b200_xl_chunk, normalize=True)
         ms_sig = timed_local(torch, sig_step, 5, 3)
         extra["fwbw_mLSTMsig"] = dict(ms=ms_sig, tflops=flops_fwbw / (ms_sig * 1e-3) / 1e12)
@@ -539,7 +551,9 @@ def run_b200(args):
                                 "batch split over the ranks is under extra.strong_scaling_fixed_batch",
                     "l2": "inputs (2.2 GB per step) larger than L2; no flush (a flushed variant is under "
                           "extra.reference_protocol_fwbw)",
-                    "recompute_states_in_bw": RECOMPUTE, "impl": impl_used},
+                    "recompute_states_in_bw": RECOMPUTE, "impl": impl_used,
+                    "streams": "two chains of launches (two halves of the units) when the recurrence's last wave is "
+                               "poorly filled; extra.two_stream_unit_split times it on and off"},
             "roofline": roofline, "cpu_baseline": cpu,
             "e2e": {"value": e2e_val, "unit": "TFLOP/s", "ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h},
@@ -679,7 +693,7 @@ def bench_sequence_parallel(torch, dist, mk, dev, world, rank, barrier, max_over
         d = (a.float() - b.float()).abs().max() / b.float().abs().max().clamp_min(1e-30)
         return max_over_ranks(float(d))
 
-    for mode in ("scan", "chain"):
+    for mode in ("gather", "scan", "chain"):
         def sp_fw():
             with torch.no_grad():
                 return mlstm_chunkwise_sequence_parallel(*mine, return_last_states=True, chunk_size=Lreq, mode=mode)
@@ -700,7 +714,7 @@ def bench_sequence_parallel(torch, dist, mk, dev, world, rank, barrier, max_over
                    C_last_max_rel_err=max_err(last_sp[0], last_ref[0]),
                    n_last_max_rel_err=max_err(last_sp[1], last_ref[1]),
                    m_last_max_abs_err=max_over_ranks(float((last_sp[2] - last_ref[2]).abs().max())))
-        # forward + backward: the backward is the chain run right to left
+        # forward + backward (gather, scan: the segments' backwards run concurrently; chain: right to left)
         lv = [t.clone().requires_grad_(True) for t in mine]
 
         def sp_fwbw():
@@ -719,7 +733,9 @@ def bench_sequence_parallel(torch, dist, mk, dev, world, rank, barrier, max_over
         for name, a, b in zip(("dQ", "dK", "dV", "dI", "dF"), lv, grads_ref):
             res[f"{name}_max_rel_err_vs_single_gpu"] = max_err(a.grad, b[:, :, sl])
         out[mode] = res
-    out["exchange"] = "(C, n, m) packed into one NCCL point-to-point message per hop (4.2 MB per head pair); NVLS off"
+    out["exchange"] = ("gather: one NCCL all-gather of the packed segment summaries (forward) and of the packed "
+                       "(dC_own, decay) pairs (backward), folded locally in rank order; scan / chain: (C, n, m) packed "
+                       "into one NCCL point-to-point message per hop (4.2 MB); segments concurrent in gather and scan")
     return out
 
 

@@ -26,6 +26,11 @@ c_initial / n_initial / m_initial in, last states out: mlstm_kernels/torch/kerne
   multiply-add per hop, (3) all ranks run the full backward of their segment from the true dC_right.  The sum over
   all later tokens needs no message: summed from a chunk boundary to the end of the sequence,
   q . dq - k . dk = <C, dC> at that boundary, so it is <C_last, dC_right> of the rank's own segment.
+  "gather" mode (the default) replaces both chains by one all-gather each: every rank receives all segment summaries
+  and folds those of the ranks before it itself, in rank order (the same arithmetic in the same order as the chain,
+  so the same bits); in the backward every rank receives all (dC_own, a) pairs and folds those of the ranks after it.
+  The hops of a chain are serial - each costs a message latency plus the launches around it, seven of them on eight
+  GPUs - while the folds are a few small kernels on data that one collective over NVSwitch has already delivered.
 """
 
 from __future__ import annotations
@@ -171,10 +176,22 @@ class _SequenceParallelFn(torch.autograd.Function):
                 _send_state(last, next_rank, group)
         else:
             summary = segment_summary(k, v, i, f, chunk_size=L, variant=variant, impl=impl)
-            state_in = first_state if rank == 0 else _recv_state(like, prev_rank, group)
-            last = state_combine(state_in, summary, variant=variant)
-            if next_rank is not None:
-                _send_state(last, next_rank, group)
+            if mode == "gather":
+                # rank 0 contributes the state at the end of its segment (the initial state of the whole sequence
+                # folded in), every other rank its summary; rank r folds entries 1 .. r-1 onto entry 0
+                mine = state_combine(first_state, summary, variant=variant) + (summary[3],) if rank == 0 else summary
+                entries = _all_gather_packed(mine, world, group)
+                state_in = first_state
+                if rank > 0:
+                    state_in = tuple(entries[0][:3])
+                    for r in range(1, rank):
+                        state_in = state_combine(state_in, entries[r], variant=variant)
+                last = tuple(mine[:3]) if rank == 0 else state_combine(state_in, summary, variant=variant)
+            else:
+                state_in = first_state if rank == 0 else _recv_state(like, prev_rank, group)
+                last = state_combine(state_in, summary, variant=variant)
+                if next_rank is not None:
+                    _send_state(last, next_rank, group)
             h, _, saved = _segment_forward_saved(q, k, v, i, f, state_in, chunk_size=L, eps=eps, variant=variant,
                                                  impl=impl)
             # per-head decay of a state gradient across the whole segment, and the state at its right end
@@ -194,10 +211,23 @@ class _SequenceParallelFn(torch.autograd.Function):
         next_rank = ranks[rank + 1] if rank < world - 1 else None
         B, NH, S, DHQK = q.shape
         DHHV = v.shape[-1]
-        if opts["mode"] == "scan":
+        if opts["mode"] in ("scan", "gather"):
             kw = dict(chunk_size=opts["L"], eps=opts["eps"], variant=opts["variant"], impl=opts["impl"])
             dh = dh.contiguous()
             dc_right = None
+            if opts["mode"] == "gather":
+                # every rank receives every (dC_own, a) and folds those of the ranks after it, last rank first
+                own = (segment_dc_summary(q, dh, ctx.saved, **kw) if rank > 0 else
+                       torch.zeros((B, NH, DHQK, DHHV), dtype=torch.float32, device=q.device))
+                entries = _all_gather_packed((own, ctx.saved["decay"]), world, group)
+                for r in range(world - 1, rank, -1):
+                    own_r, decay_r = entries[r]
+                    dc_right = own_r if dc_right is None else own_r + decay_r[..., None, None] * dc_right
+                dq, dk, dv, di, df, _ = _segment_backward(q, k, v, i, f, ctx.saved, dh, dc_right, **kw)
+                if dc_right is not None:
+                    tail = (ctx.saved["c_last"] * dc_right).sum(dim=(-1, -2))
+                    df = df + torch.sigmoid(-f.float()) * tail[..., None]
+                return dq, dk, dv, di.to(i.dtype), df.to(f.dtype), None, None
             if prev_rank is not None:   # rank 0 hands nothing on: it needs no summary
                 dc_left = segment_dc_summary(q, dh, ctx.saved, **kw)
             if next_rank is not None:
@@ -245,6 +275,16 @@ def _unpack(flat, like):
     return tuple(out)
 
 
+def _all_gather_packed(tensors, world, group):
+    """All-gather of a tuple of tensors (packed into one f32 buffer per rank, one collective); returns, per rank of
+    the group, the tuple of that rank's tensors."""
+    flat = _pack(tensors)
+    n = flat.numel()
+    out = torch.empty(world * n, dtype=torch.float32, device=flat.device)
+    dist.all_gather_into_tensor(out, flat, group=group)
+    return [_unpack(out[r * n:(r + 1) * n], tensors) for r in range(world)]
+
+
 def _send_state(state, dst, group):
     dist.send(_pack(state), dst=dst, group=group)
 
@@ -269,7 +309,7 @@ def mlstm_chunkwise_sequence_parallel(
     chunk_size: int = 128,
     siging: bool = False,
     normalize: bool = True,
-    mode: str = "scan",
+    mode: str = "gather",
     group=None,
     impl: str = "auto",
 ):
@@ -278,7 +318,7 @@ def mlstm_chunkwise_sequence_parallel(
     (identical on every rank).  Ranks are ordered along the sequence: global rank order of the group.
     Differentiable with respect to q, k, v, i, f (every rank must then run the backward: it exchanges
     point-to-point messages from the last rank to the first)."""
-    if mode not in ("scan", "chain"):
+    if mode not in ("gather", "scan", "chain"):
         raise ValueError(f"unknown mode {mode}")
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
@@ -299,11 +339,12 @@ def mlstm_chunkwise_sequence_parallel(
     h, last = out[0], out[1:]
     if not return_last_states:
         return h
-    # receive into copies: the state at the end of THIS rank's segment stays as the backward saved it
-    last = tuple(t.contiguous() if rank == world - 1 else torch.empty_like(t, memory_format=torch.contiguous_format)
-                 for t in last)
-    for t in last:
-        dist.broadcast(t, src=ranks[world - 1], group=group)
+    # one broadcast of the packed state, received into a buffer of its own: the state at the end of THIS rank's
+    # segment stays as the backward saved it
+    flat = _pack(last) if rank == world - 1 else torch.empty(sum(t.numel() for t in last), dtype=torch.float32,
+                                                             device=dev)
+    dist.broadcast(flat, src=ranks[world - 1], group=group)
+    last = tuple(t.clone() for t in _unpack(flat, last))
     if siging:
         return h, (last[0], last[1])
     return h, last

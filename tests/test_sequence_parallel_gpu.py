@@ -153,7 +153,7 @@ def test_backward_scan_emulated_on_one_gpu(dtype, L, dims, variant):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least two GPUs")
-@pytest.mark.parametrize("mode", ["scan", "chain"])
+@pytest.mark.parametrize("mode", ["gather", "scan", "chain"])
 def test_sequence_parallel_torchrun(tmp_path, mode):
     n = min(torch.cuda.device_count(), 4)
     script = os.path.join(os.path.dirname(os.path.abspath(__file__)), "run_sequence_parallel.py")

@@ -121,7 +121,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-@pytest.mark.parametrize("mode,world", [("scan", 2), ("chain", 2), ("scan", 4)])
+@pytest.mark.parametrize("mode,world", [("gather", 2), ("scan", 2), ("chain", 2), ("scan", 4), ("gather", 4)])
 @pytest.mark.parametrize("siging", [False, True])
 def test_sequence_parallel_gloo_ranks(tmp_path, mode, world, siging):
     mp.spawn(_worker, args=(world, _free_port(), mode, siging, str(tmp_path)), nprocs=world, join=True)
