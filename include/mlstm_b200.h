@@ -221,6 +221,21 @@ int mlstm_b200_chunkwise_states(const void* k, const void* v, const void* i, con
                                 int B, int NH, int S, int DHQK, int DHHV, int L,
                                 int dtype, int gate_dtype, int variant, int impl, void* stream);
 
+/* Backward for a forward that did not keep its per-chunk states (the reference's recompute_states_in_bw = True,
+ * mlstm_kernels/torch/chunkwise/triton_xl_chunk/bw.py:76-112): as mlstm_b200_chunkwise_bw_cached, but `c_states_scratch`
+ * (same size and element type as the forward's c_states) arrives unwritten and the forward's recurrence is run again, from
+ * `c_initial` (f32 or NULL) and the forward's gate vectors, inside the backward's own chains of launches - so that
+ * its last wave of CTAs overlaps the state-gradient recurrence instead of standing alone in front of the call. */
+int mlstm_b200_chunkwise_bw_recompute(const void* q, const void* k, const void* v, const void* i, const void* f,
+                                      const float* m_initial, const float* c_initial, void* c_states_scratch,
+                                      const float* n_out, const float* m_out,
+                                      const void* fw_workspace, size_t fw_workspace_bytes,
+                                      const void* dh, const float* dc_last,
+                                      void* dq, void* dk, void* dv, float* di, float* df, float* dc_initial,
+                                      void* workspace, size_t workspace_bytes,
+                                      int B, int NH, int S, int DHQK, int DHHV, int L,
+                                      int dtype, int gate_dtype, int variant, int impl, float eps, void* stream);
+
 /*
  * Sequence-parallel prefill: a long sequence is split into contiguous segments, one per GPU.
  * The reference has no multi-device code; these two entry points implement its state-passing

@@ -47,6 +47,8 @@ SIGNATURES = {
                                 + [_vp, _sz] + [_i] * 6 + [_i, _i, _i, _i, _f, _vp]),
     "mlstm_b200_chunkwise_bw_cached": (_i, [_vp] * 5 + [_fp, _vp, _fp, _fp, _vp, _sz, _vp, _fp] + [_vp] * 3 + [_fp] * 3
                                        + [_vp, _sz] + [_i] * 6 + [_i, _i, _i, _i, _f, _vp]),
+    "mlstm_b200_chunkwise_bw_recompute": (_i, [_vp] * 5 + [_fp, _fp, _vp, _fp, _fp, _vp, _sz, _vp, _fp] + [_vp] * 3
+                                          + [_fp] * 3 + [_vp, _sz] + [_i] * 6 + [_i, _i, _i, _i, _f, _vp]),
     "mlstm_b200_chunkwise_states": (_i, [_vp] * 4 + [_fp, _fp, _vp, _vp, _sz, _vp, _sz] + [_i] * 6 + [_i, _i, _i, _i, _vp]),
     "mlstm_b200_chunkwise_summary": (_i, [_vp] * 4 + [_fp] * 4 + [_vp, _sz] + [_i] * 6 + [_i, _i, _i, _i, _vp]),
     "mlstm_b200_set_unit_split": (_i, [_i]),

@@ -160,9 +160,11 @@ def chunkwise_states_raw(k, v, i, f, c_initial=None, m_initial=None, *, chunk_si
 
 
 def chunkwise_bw_raw(q, k, v, i, f, m_initial, c_states, n_out, dh, dc_last=None, *, chunk_size: int, eps: float,
-                     variant: int, impl: str = "auto", want_dc_initial: bool = False, m_out=None, fw_workspace=None):
+                     variant: int, impl: str = "auto", want_dc_initial: bool = False, m_out=None, fw_workspace=None,
+                     recompute_c_initial=None):
     """Run the backward kernels.  Returns (dq, dk, dv, di, df, dc_initial).  With `m_out` and `fw_workspace` (both
-    as returned by chunkwise_fw_raw for the same inputs) the gate pre-pass is not repeated."""
+    as returned by chunkwise_fw_raw for the same inputs) the gate pre-pass is not repeated.  With c_states = None
+    (needs fw_workspace) the per-chunk states are recomputed inside the call, from `recompute_c_initial`."""
     _lib.require_cuda(q, k, v, i, f, dh)
     lib = _lib.load()
     B, NH, S, DHQK = q.shape
@@ -185,7 +187,20 @@ def chunkwise_bw_raw(q, k, v, i, f, m_initial, c_states, n_out, dh, dc_last=None
     ws_bytes = lib.mlstm_b200_chunkwise_workspace_bytes(B, NH, S, DHQK, DHHV, L, dt, variant, im, 1)
     ws = torch.empty((max(ws_bytes, 256),), dtype=torch.uint8, device=dev)
     with torch.cuda.device(dev):
-        if fw_workspace is not None and m_out is not None:
+        if c_states is None:
+            if fw_workspace is None:
+                raise ValueError("recomputing the states inside the backward needs the forward's workspace")
+            sdt = _lib.code_dtype(lib.mlstm_b200_chunkwise_state_dtype(S, DHQK, DHHV, L, dt, im))
+            c_states = torch.empty((B, NH, -(-S // L) + 1, DHQK, DHHV), dtype=sdt, device=dev)
+            c0 = _f32c(recompute_c_initial)
+            rc = lib.mlstm_b200_chunkwise_bw_recompute(
+                _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(i), _lib.ptr(f),
+                _lib.ptr(m0), _lib.ptr(c0), _lib.ptr(c_states), _lib.ptr(n_out), _lib.ptr(m_out),
+                _lib.ptr(fw_workspace), fw_workspace.numel(), _lib.ptr(dh), _lib.ptr(dcl),
+                _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(di), _lib.ptr(df), _lib.ptr(dc0),
+                _lib.ptr(ws), ws_bytes, B, NH, S, DHQK, DHHV, L, dt, gdt, variant, im, float(eps),
+                _lib.stream_handle(dev))
+        elif fw_workspace is not None and m_out is not None:
             rc = lib.mlstm_b200_chunkwise_bw_cached(
                 _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(i), _lib.ptr(f),
                 _lib.ptr(m0), _lib.ptr(c_states), _lib.ptr(n_out), _lib.ptr(m_out), _lib.ptr(fw_workspace),
@@ -234,12 +249,11 @@ def _make_fwbw(autocast_kernel_dtype: torch.dtype, variant: int):
         def backward(ctx, dH, dC_last, dN_last, dM_last):
             q, k, v, i, f, c_initial, m_initial, c_states, n_out, m_out, fw_ws = ctx.saved_tensors
             L, eps, impl, has_c0, has_n0, has_m0, c0_dtype, n0_dtype = ctx.cfg
-            if c_states is None:
-                c_states = chunkwise_states_raw(k, v, i, f, c_initial, m_initial, chunk_size=L, variant=variant,
-                                                impl=impl, fw_workspace=fw_ws)
+            # c_states is None: the forward did not keep them; the call runs the recurrence again in front of its own
+            # chains of launches
             dq, dk, dv, di, df, dc0 = chunkwise_bw_raw(
                 q, k, v, i, f, m_initial, c_states, n_out, dH, dC_last, chunk_size=L, eps=eps, variant=variant,
-                impl=impl, want_dc_initial=has_c0, m_out=m_out, fw_workspace=fw_ws)
+                impl=impl, want_dc_initial=has_c0, m_out=m_out, fw_workspace=fw_ws, recompute_c_initial=c_initial)
             B, NH, S, DHQK = q.shape
             dn0 = torch.zeros((B, NH, DHQK), dtype=n0_dtype, device=q.device) if has_n0 else None
             dm0 = torch.zeros_like(m_initial) if has_m0 else None

@@ -356,7 +356,8 @@ static int bw_impl(const void* q, const void* k, const void* v, const void* i, c
                    const float* dc_last, void* dq, void* dk, void* dv, float* di, float* df,
                    float* dc_initial, void* workspace, size_t workspace_bytes, int B, int NH, int S, int DHQK,
                    int DHHV, int L, int dtype, int gate_dtype, int variant, int impl, float eps, void* stream,
-                   const void* fw_workspace, size_t fw_workspace_bytes, const float* m_out) {
+                   const void* fw_workspace, size_t fw_workspace_bytes, const float* m_out,
+                   void* recompute_into = nullptr, const float* recompute_c_initial = nullptr) {
   int rc = check_dims(B, NH, S, DHQK, DHHV, L);
   if (rc != MLSTM_OK) return rc;
   if (dtype != MLSTM_F32 && dtype != MLSTM_BF16 && dtype != MLSTM_F16) return MLSTM_ERR_DTYPE;
@@ -365,8 +366,12 @@ static int bw_impl(const void* q, const void* k, const void* v, const void* i, c
   if (!q || !k || !v || !i || !f || !c_states || !dh || !dq || !dk || !dv || !di || !df || !workspace)
     return MLSTM_ERR_NULL;
   if (variant != MLSTM_SIG_NONORM && !n_out) return MLSTM_ERR_NULL;
-  const void* ptrs[] = {q, k, v, i, f, m_initial, c_states, n_out, dh, dc_last, dq, dk, dv, di, df, dc_initial, workspace};
+  const void* ptrs[] = {q, k, v, i, f, m_initial, c_states, n_out, dh, dc_last, dq, dk, dv, di, df, dc_initial, workspace,
+                        recompute_c_initial};
   for (const void* p : ptrs) if (p && !aligned16(p)) return MLSTM_ERR_ALIGN;
+  // recompute_into (== c_states, writable): the per-chunk states are not there yet; the forward's recurrence is run
+  // again in front of each chain of backward launches.  Needs the forward's gate vectors (fw_workspace).
+  if (recompute_into != nullptr && fw_workspace == nullptr) return MLSTM_ERR_NULL;
   bool use_sm100 = false;
   if ((rc = resolve_impl(impl, B, NH, S, DHQK, DHHV, L, dtype, &use_sm100)) != MLSTM_OK) return rc;
 
@@ -397,6 +402,10 @@ static int bw_impl(const void* q, const void* k, const void* v, const void* i, c
         MLSTM_CUDA_CHECK(cudaEventRecord(side->fork, st));
         MLSTM_CUDA_CHECK(cudaStreamWaitEvent(side->st, side->fork, 0));
       }
+      if (recompute_into) {
+        if ((rc = sm100_recurrent_fw(k, v, lay.gb, recompute_c_initial, nullptr, recompute_into, nullptr, nullptr, nullptr, d, st, first)) != MLSTM_OK) return rc;
+        if (side && (rc = sm100_recurrent_fw(k, v, lay.gb, recompute_c_initial, nullptr, recompute_into, nullptr, nullptr, nullptr, d, side->st, second)) != MLSTM_OK) return rc;
+      }
       if ((rc = sm100_recurrent_bw(q, dh, lay.gb, dc_last, lay.dc_states, dc_initial, d, st, first)) != MLSTM_OK) return rc;
       if (side && (rc = sm100_recurrent_bw(q, dh, lay.gb, dc_last, lay.dc_states, dc_initial, d, side->st, second)) != MLSTM_OK) return rc;
       if ((rc = sm100_parallel_bw(q, k, v, dh, lay.gb, c_states, lay.dc_states, dq, dk, dv, lay.acc, lay.kdk, d, st, first)) != MLSTM_OK) return rc;
@@ -416,6 +425,8 @@ static int bw_impl(const void* q, const void* k, const void* v, const void* i, c
                                       n_anchors, kAnchorEvery * L)) != MLSTM_OK) return rc;
     }
   } else {
+    if (recompute_into &&
+        (rc = simt_recurrent_fw(dtype, MLSTM_F32, k, v, lay.gb, recompute_c_initial, nullptr, recompute_into, nullptr, nullptr, nullptr, d, st)) != MLSTM_OK) return rc;
     if ((rc = simt_recurrent_bw(dtype, sdt, q, dh, lay.gb, dc_last, lay.dc_states, dc_initial, d, st)) != MLSTM_OK) return rc;
     if ((rc = simt_parallel_bw(dtype, sdt, q, k, v, dh, lay.gb, c_states, lay.dc_states, dq, dk, dv, d, st)) != MLSTM_OK) return rc;
     if ((rc = launch_gate_grads(dtype, gate_dtype, q, k, dq, dk, i, f, lay.acc, lay.kdk, di, df, d, st)) != MLSTM_OK) return rc;
@@ -446,6 +457,19 @@ int mlstm_b200_chunkwise_bw_cached(const void* q, const void* k, const void* v, 
   return bw_impl(q, k, v, i, f, m_initial, c_states, n_out, dh, dc_last, dq, dk, dv, di, df, dc_initial, workspace,
                  workspace_bytes, B, NH, S, DHQK, DHHV, L, dtype, gate_dtype, variant, impl, eps, stream, fw_workspace,
                  fw_workspace_bytes, m_out);
+}
+
+int mlstm_b200_chunkwise_bw_recompute(const void* q, const void* k, const void* v, const void* i, const void* f,
+                                      const float* m_initial, const float* c_initial, void* c_states_scratch,
+                                      const float* n_out, const float* m_out, const void* fw_workspace,
+                                      size_t fw_workspace_bytes, const void* dh, const float* dc_last, void* dq,
+                                      void* dk, void* dv, float* di, float* df, float* dc_initial, void* workspace,
+                                      size_t workspace_bytes, int B, int NH, int S, int DHQK, int DHHV, int L,
+                                      int dtype, int gate_dtype, int variant, int impl, float eps, void* stream) {
+  if (!fw_workspace || !c_states_scratch) return MLSTM_ERR_NULL;
+  return bw_impl(q, k, v, i, f, m_initial, c_states_scratch, n_out, dh, dc_last, dq, dk, dv, di, df, dc_initial,
+                 workspace, workspace_bytes, B, NH, S, DHQK, DHHV, L, dtype, gate_dtype, variant, impl, eps, stream,
+                 fw_workspace, fw_workspace_bytes, m_out, c_states_scratch, c_initial);
 }
 
 int mlstm_b200_chunkwise_states(const void* k, const void* v, const void* i, const void* f, const float* c_initial,

@@ -259,6 +259,28 @@ def test_forward_backward_capture_in_cuda_graph():
         assert torch.equal(a, b)
 
 
+@pytest.mark.parametrize("dtype,dims,L,S", [(torch.bfloat16, (256, 256), 128, 1024), (torch.float32, (32, 64), 64, 512)])
+@pytest.mark.parametrize("gates", [(8.0, 0.0), (4.0, -6.0), (1.0, 12.0)])
+@pytest.mark.parametrize("variant", ["exp", "sig"])
+def test_extreme_gate_values(dtype, dims, L, S, gates, variant):
+    """Gate pre-activations far outside the benchmark's distribution: input gates 8 N(0,1) (single tokens dominate a
+    whole chunk), forget gates around -6 (the state is wiped at nearly every step) and around +12 (nothing decays).
+    Nothing may overflow or lose the stabilisation.  Tolerance: f32 1e-3; bf16 3e-2 - with a handful of dominant terms
+    per output the bf16 roundings of the gated tile no longer average out (the same inputs in fp16 give 1e-3)."""
+    scale, offset = gates
+    inp = case_inputs(77, 1, 2, S, dims[0], dims[1])
+    rng = np.random.default_rng(5)
+    inp["i"] = (scale * rng.standard_normal(inp["i"].shape)).astype(np.float32)
+    inp["f"] = (offset + scale * rng.standard_normal(inp["f"].shape)).astype(np.float32)
+    siging = variant == "sig"
+    got = run_cuda_fwbw(inp, L, dtype=dtype, siging=siging)
+    ref = run_oracle_fwbw(inp, L, dtype=dtype, siging=siging)
+    tol = 1e-3 if dtype == torch.float32 else 3e-2
+    for key in ("H", "C_last", "dQ", "dK", "dV", "dI", "dF"):
+        assert np.isfinite(got[key]).all(), key
+        assert max_rel_err(got[key], ref[key]) < tol, key
+
+
 @pytest.mark.parametrize("odd", [False, True])
 def test_two_stream_unit_split_is_bit_identical_and_capturable(odd):
     """With more recurrence CTAs than SMs and a poorly filled last wave, the library runs the two halves of the
