@@ -281,11 +281,13 @@ def test_extreme_gate_values(dtype, dims, L, S, gates, variant):
         assert max_rel_err(got[key], ref[key]) < tol, key
 
 
+@pytest.mark.parametrize("recompute", [True, False])
 @pytest.mark.parametrize("odd", [False, True])
-def test_two_stream_unit_split_is_bit_identical_and_capturable(odd):
+def test_two_stream_unit_split_is_bit_identical_and_capturable(odd, recompute):
     """With more recurrence CTAs than SMs and a poorly filled last wave, the library runs the two halves of the
     (batch, head) units on two streams.  Same kernels on the same data: every output must be bit-identical to the
-    single-stream run, with an odd number of units too, and the forked launches must survive a graph capture."""
+    single-stream run, with an odd number of units too and with either way of getting the per-chunk states in the
+    backward (kept, or recomputed inside the launch chains), and the forked launches must survive a graph capture."""
     from mlstm_kernels_b200 import _lib
     lib = _lib.load()
     B, NH = (3, 67) if odd else (2, 100)          # 201 / 200 state tiles of 128 x 128 on 148 SMs: two waves, 68 % full
@@ -297,7 +299,8 @@ def test_two_stream_unit_split_is_bit_identical_and_capturable(odd):
 
     def step():
         leaves = [t.detach().requires_grad_(True) for t in (q, k, v, i, f)]
-        h, last = mk.mlstm_chunkwise__b200_xl_chunk(*leaves, chunk_size=128, return_last_states=True)
+        h, last = mk.mlstm_chunkwise__b200_xl_chunk(*leaves, chunk_size=128, return_last_states=True,
+                                                    recompute_states_in_bw=recompute)
         grads = torch.autograd.grad(h, leaves, dh)
         return (h.detach(),) + tuple(last) + grads
 
