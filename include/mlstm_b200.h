@@ -115,7 +115,7 @@ size_t mlstm_b200_chunkwise_workspace_bytes(int B, int NH, int S, int DHQK, int 
  *   n_states    (B,NH,NC+1,DHQK) f32 out,  m_states (B,NH,NC+1) f32 out
  *   c_last,n_last,m_last  f32 copies of the final state (B,NH,DHQK,DHHV),(B,NH,DHQK),(B,NH); each may be NULL
  *   L a power of two >= 16.  S % L == 0 for the portable kernels.  Where the tcgen05 kernels run (bf16 or f16,
- *   L = 128, head dims multiples of 128) S may be ANY length >= 1: NC = ceil(S / L) and the last chunk is ragged - its
+ *   L = 128, head dims multiples of 8 up to 512 / 1024) S may be ANY length >= 1: NC = ceil(S / L) and the last chunk is ragged - its
  *   missing tokens are read as zeros and switched off in the gates, no output row past S is written.  This
  *   replaces the host-side zero padding of wrap_chunkwise__pad_zeros and the chunk-size ladder 64/32/16 of
  *   wrap_chunkwise__arbitrary_sequence_length (mlstm_kernels/torch/kernel_wrappers.py:76-171,206-267).

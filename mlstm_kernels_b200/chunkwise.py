@@ -49,7 +49,8 @@ def select_chunk_size(sequence_length: int, target_chunk_size: int) -> int:
 
 
 def tcgen05_applies(q: torch.Tensor, v: torch.Tensor, impl: str = "auto") -> bool:
-    """True where the tcgen05 kernels run: bf16 or fp16, head dims multiples of 128 (any sequence length)."""
+    """True where the tcgen05 kernels run: bf16 or fp16, head dims multiples of 8 up to 512 (qk) / 1024 (v),
+    any sequence length."""
     if impl == "simt" or not q.is_cuda or q.dtype not in _lib._DTYPE_CODE:
         return False
     lib = _lib.load()
@@ -57,7 +58,7 @@ def tcgen05_applies(q: torch.Tensor, v: torch.Tensor, impl: str = "auto") -> boo
 
 
 def kernel_chunk_size(q: torch.Tensor, v: torch.Tensor, chunk_size: int, impl: str = "auto") -> int:
-    """Chunk size the kernels run with.  Where the tcgen05 path applies (bf16 or fp16, head dims multiples of 128) every
+    """Chunk size the kernels run with.  Where the tcgen05 path applies (bf16 or fp16, head dims multiples of 8) every
     requested chunk size runs as chunks of 128, the last one ragged if the sequence length is no multiple of 128
     (H does not depend on the chunk size; the reference does the same for its inter-chunk kernel:
     chunk_size_inter = min(128, chunk_size), mlstm_kernels/triton/chunkwise/kernel_param_heuristics.py:96-121)."""

@@ -421,7 +421,7 @@ static int bw_impl(const void* q, const void* k, const void* v, const void* i, c
       // (sequences of up to kAnchorEvery chunks have no interior anchor: nothing to compute)
       if (n_anchors > 2 &&
           (rc = launch_state_dot(c_states, lay.dc_states, lay.anchors, kAnchorEvery, n_anchors, d, st)) != MLSTM_OK) return rc;
-      if ((rc = launch_gate_grad_scan(gate_dtype, i, f, lay.acc, lay.kdk, DHQK / 128, di, df, d, st, lay.anchors,
+      if ((rc = launch_gate_grad_scan(gate_dtype, i, f, lay.acc, lay.kdk, (DHQK + 127) / 128, di, df, d, st, lay.anchors,
                                       n_anchors, kAnchorEvery * L)) != MLSTM_OK) return rc;
     }
   } else {

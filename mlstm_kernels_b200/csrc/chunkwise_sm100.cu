@@ -1,5 +1,6 @@
 // tcgen05 / TMEM / TMA implementation of the chunkwise mLSTM kernels for B200 (sm_100a).
-// bf16 or f16 operands, f32 accumulation in tensor memory, chunk size 128, head dims multiples of 128.
+// bf16 or f16 operands, f32 accumulation in tensor memory, chunk size 128, head dims multiples of 8 (tiles of 128: a tile
+// hanging over the edge of a head dim is zero-padded by TMA on the way in, masked or clipped on the way out).
 //
 //   rec_sm100<BWD>   inter-chunk recurrence (forward C_k, n_k; backward deltaC_k).  A CTA owns a 128 x 128 tile
 //                    of the state for one (batch, head) and walks the chunks in order; per chunk one
@@ -80,7 +81,9 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
   // 1-D grid (no 65535 limit on batch x heads), state tiles of one (batch, head) next to each other
   static_assert(TN == 128 || TN == 64, "state tile width");
   constexpr int HC = TN / 2;   // columns each of the two state-warp groups owns
-  const int n_et = p.DHHV / TN, n_dt = p.DHQK / 128;
+  // head dims need not be multiples of the tile: the last tile hangs over the edge, where loads read zeros (the
+  // tensor maps know the true extents), plain accesses are masked and the state store is clipped
+  const int n_et = (p.DHHV + TN - 1) / TN, n_dt = (p.DHQK + 127) / 128;
   const int et = blockIdx.x % n_et, dt = (blockIdx.x / n_et) % n_dt, bh = p.bh0 + blockIdx.x / (n_et * n_dt);
   const int e0 = et * TN, d0 = dt * 128;
   const int NC = p.NC, NH2 = 2 * p.NC;   // ring steps: two per chunk
@@ -222,9 +225,9 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
         const int ob = n & 1;
         if (!mbar_wait(&bar_out_full[ob], (n >> 1) & 1, &s_abort, &g_sm100_status, 108)) break;
         const int slot = BWD ? NC - n : n;
-        const int y = (bh * (NC + 1) + slot) * p.DHQK + d0;
-        tma_store_2d(&mapS, stage_base + ob * 32768, e0, y);
-        if (TN == 128) tma_store_2d(&mapS, stage_base + ob * 32768 + 16384, e0 + 64, y);
+        const int z = bh * (NC + 1) + slot;
+        tma_store_3d(&mapS, stage_base + ob * 32768, e0, d0, z);
+        if (TN == 128 && e0 + 64 < p.DHHV) tma_store_3d(&mapS, stage_base + ob * 32768 + 16384, e0 + 64, d0, z);
         tma_store_commit();
         asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");   // the previous tile has left its buffer
         if (n >= 1) mbar_arrive(&bar_out_free[ob ^ 1]);
@@ -237,8 +240,9 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
     // depend on scheduling.
     if (do_n) {
       float4 nv = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (p.n_init) nv = *reinterpret_cast<const float4*>(p.n_init + (size_t)bh * p.DHQK + d0 + 4 * lane);
-      if (p.n_states != nullptr)
+      const bool d_in = d0 + 4 * lane < p.DHQK;   // the lane's four rows exist (DHQK is a multiple of 8)
+      if (p.n_init && d_in) nv = *reinterpret_cast<const float4*>(p.n_init + (size_t)bh * p.DHQK + d0 + 4 * lane);
+      if (p.n_states != nullptr && d_in)
         *reinterpret_cast<float4*>(p.n_states + ((size_t)bh * (NC + 1)) * p.DHQK + d0 + 4 * lane) = nv;
       bool ok = true;
       for (int s = 0; s < NC; ++s) {
@@ -252,10 +256,10 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
         if (lane == 0) mbar_arrive(&bar_nread[nb]);
         const float g = s_g[s & 7];
         nv.x = fmaf(g, nv.x, cs.x); nv.y = fmaf(g, nv.y, cs.y); nv.z = fmaf(g, nv.z, cs.z); nv.w = fmaf(g, nv.w, cs.w);
-        if (p.n_states != nullptr)
+        if (p.n_states != nullptr && d_in)
           *reinterpret_cast<float4*>(p.n_states + ((size_t)bh * (NC + 1) + s + 1) * p.DHQK + d0 + 4 * lane) = nv;
       }
-      if (ok && p.n_final) *reinterpret_cast<float4*>(p.n_final + (size_t)bh * p.DHQK + d0 + 4 * lane) = nv;
+      if (ok && p.n_final && d_in) *reinterpret_cast<float4*>(p.n_final + (size_t)bh * p.DHQK + d0 + 4 * lane) = nv;
     }
   } else {
     // ---------------- state warps: fold each chunk's product into the running state, store it ----------------
@@ -266,7 +270,11 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
     if (p.c_init) {
       const float4* src = reinterpret_cast<const float4*>(p.c_init + ((size_t)bh * p.DHQK + d) * p.DHHV + ecol);
 #pragma unroll
-      for (int c = 0; c < HC / 4; ++c) { float4 v = src[c]; C[4 * c] = v.x; C[4 * c + 1] = v.y; C[4 * c + 2] = v.z; C[4 * c + 3] = v.w; }
+      for (int c = 0; c < HC / 4; ++c) {
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (d < p.DHQK && ecol + 4 * c < p.DHHV) v = src[c];
+        C[4 * c] = v.x; C[4 * c + 1] = v.y; C[4 * c + 2] = v.z; C[4 * c + 3] = v.w;
+      }
     } else {
 #pragma unroll
       for (int c = 0; c < HC; ++c) C[c] = 0.f;
@@ -316,7 +324,8 @@ rec_sm100(const __grid_constant__ CUtensorMap mapL, const __grid_constant__ CUte
     if (ok && p.c_final) {
       float4* fd = reinterpret_cast<float4*>(p.c_final + ((size_t)bh * p.DHQK + d) * p.DHHV + ecol);
 #pragma unroll
-      for (int c = 0; c < HC / 4; ++c) fd[c] = make_float4(C[4 * c], C[4 * c + 1], C[4 * c + 2], C[4 * c + 3]);
+      for (int c = 0; c < HC / 4; ++c)
+        if (d < p.DHQK && ecol + 4 * c < p.DHHV) fd[c] = make_float4(C[4 * c], C[4 * c + 1], C[4 * c + 2], C[4 * c + 3]);
     }
   }
   tc_fence_before_sync();
@@ -405,7 +414,7 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
   const int o00 = o_tile0 * 128;   // first output column of the CTA's first tile
   const int DI = (mode == PM_H || mode == PM_DV) ? p.DHQK : p.DHHV;   // contraction dim of the score product
   const int DO = (mode == PM_H || mode == PM_DV) ? p.DHHV : p.DHQK;   // output width
-  const int NC = p.NC, ND = DI / 64;
+  const int NC = p.NC, ND = (DI + 63) / 64;   // slices of 64 columns; a last partial slice is padded with zeros by TMA
   const int y0 = ck * CL;                         // first token of the chunk inside its sequence
   const int valid = min(CL, p.S - y0);            // tokens of the chunk that exist (ragged last chunk: < 128)
   const size_t out_row0 = (size_t)bh * p.S + y0;  // first row of the chunk in the (B*NH*S)-row token tensors
@@ -453,7 +462,7 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
     // ---------------- TMA producer ----------------
     if (lane == 0) {
       const int slot = LOWER ? ck : ck + 1;
-      const int srow = (bh * (NC + 1) + slot) * p.DHQK;
+      const int sz = bh * (NC + 1) + slot;   // slab of the state tensor (one DHQK x DHHV matrix per chunk boundary)
       int issued = 0;
       // Per stage: uses handed back by an MMA commit so far (phase counter of bar_empty) and score pairs read for
       // q . n so far (phase counter of bar_qdone).  Scalars picked by comparisons, not arrays: a dynamically indexed
@@ -490,10 +499,10 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
         } else if (kind == LK_STATE) {
           tma_load_3d(sb, mapA, &sh.bar_full[st], 64 * it, y0, bh);
           if (ST_MN) {
-            tma_load_2d(sb + 16384, mapSt, &sh.bar_full[st], o0, srow + 64 * it);
-            tma_load_2d(sb + 16384 + 8192, mapSt, &sh.bar_full[st], o0 + 64, srow + 64 * it);
+            tma_load_3d(sb + 16384, mapSt, &sh.bar_full[st], o0, 64 * it, sz);
+            tma_load_3d(sb + 16384 + 8192, mapSt, &sh.bar_full[st], o0 + 64, 64 * it, sz);
           } else {
-            tma_load_2d(sb + 16384, mapSt, &sh.bar_full[st], 64 * it, srow + o0);
+            tma_load_3d(sb + 16384, mapSt, &sh.bar_full[st], 64 * it, o0, sz);
           }
         } else {
           const CUtensorMap* m = (kind == LK_X) ? mapX : mapE;
@@ -589,7 +598,7 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
     else rowscale = p.abar[tok];
     if (use_n) {
       const float* nsrc = p.n_states + ((size_t)bh * (NC + 1) + ck) * p.DHQK;
-      for (int dd = tid - 64; dd < p.DHQK; dd += 256) sh.s_n[dd] = nsrc[dd];
+      for (int dd = tid - 64; dd < ND * 64; dd += 256) sh.s_n[dd] = dd < p.DHQK ? nsrc[dd] : 0.f;   // zero padding
     }
     asm volatile("bar.sync 1, 256;" ::: "memory");  // gate vectors and n visible to the element-wise warps
 
@@ -795,7 +804,7 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
         for (int i2 = 0; i2 < 8; ++i2) {
           const int orow_i = 16 * i2 + 2 * ew + (lane >> 4);
           const uint4 o = *reinterpret_cast<const uint4*>(ostage + (j >> 3) * 16384 + orow_i * 128 + (((j & 7) ^ (orow_i & 7)) << 4));
-          if (orow_i < valid) *reinterpret_cast<uint4*>(gbase + (size_t)orow_i * DO * 2 + j * 16) = o;
+          if (orow_i < valid && o0 + j * 8 < DO) *reinterpret_cast<uint4*>(gbase + (size_t)orow_i * DO * 2 + j * 16) = o;
         }
       }
       if (HAS_E) {
@@ -826,7 +835,7 @@ par_fw_sm100(const __grid_constant__ CUtensorMap mQ, const __grid_constant__ CUt
              const __grid_constant__ CUtensorMap mV, const __grid_constant__ CUtensorMap mC,
              const __grid_constant__ ParParams p) {
   __shared__ ParShared sh;
-  const int T = p.DHHV / 128;                         // output tiles per chunk; a CTA takes up to PAR_MAXSUB of them
+  const int T = (p.DHHV + 127) / 128;                 // output tiles per chunk; a CTA takes up to PAR_MAXSUB of them
   // 1-D grid in the order (tile group, chunk, batch x head): no 65535 limit on chunks or batch x heads
   const int gx = (T + PAR_MAXSUB - 1) / PAR_MAXSUB;
   const int x = blockIdx.x % gx, ck = (blockIdx.x / gx) % p.NC, bh = p.bh0 + blockIdx.x / (gx * p.NC);
@@ -845,7 +854,7 @@ par_bw_sm100(const __grid_constant__ CUtensorMap mQ, const __grid_constant__ CUt
              const __grid_constant__ CUtensorMap mdC_k,
              const __grid_constant__ ParParams p) {
   __shared__ ParShared sh;
-  const int T_dv = p.DHHV / 128, T_dk = p.DHQK / 128;         // output tiles per chunk of dV, and of dK / dQ
+  const int T_dv = (p.DHHV + 127) / 128, T_dk = (p.DHQK + 127) / 128;   // output tiles per chunk of dV, and of dK / dQ
   const int c_dv = (T_dv + PAR_MAXSUB - 1) / PAR_MAXSUB, c_dk = (T_dk + PAR_MAXSUB - 1) / PAR_MAXSUB;   // CTAs per mode
   const int gx = c_dv + 2 * c_dk;   // 1-D grid in the order (mode and tile group, chunk, batch x head)
   const int x = blockIdx.x % gx, ck = (blockIdx.x / gx) % p.NC, bh = p.bh0 + blockIdx.x / (gx * p.NC);
@@ -862,8 +871,10 @@ par_bw_sm100(const __grid_constant__ CUtensorMap mQ, const __grid_constant__ CUt
 // =====================================================================================================
 bool sm100_supported(int S, int DHQK, int DHHV, int L, int dtype) {
   // any sequence length: a ragged last chunk is handled by zero-filled loads and masked stores
-  return (dtype == MLSTM_BF16 || dtype == MLSTM_F16) && L == CL && S >= 1 && DHQK % 128 == 0 && DHHV % 128 == 0 && DHQK <= 512 &&
-         DHHV <= 1024;
+  // head dims: multiples of 8 (16-byte rows for TMA and the vector stores); tiles that hang over the edge of a head
+  // dim are padded with zeros by TMA on the way in and masked or clipped on the way out
+  return (dtype == MLSTM_BF16 || dtype == MLSTM_F16) && L == CL && S >= 1 && DHQK % 8 == 0 && DHHV % 8 == 0 &&
+         DHQK >= 8 && DHHV >= 8 && DHQK <= 512 && DHHV <= 1024;
 }
 
 // The kernels address token rows and state rows with 32-bit TMA coordinates and use 1-D grids: both row counts and
@@ -871,9 +882,9 @@ bool sm100_supported(int S, int DHQK, int DHHV, int L, int dtype) {
 bool sm100_sizes_ok(int B, int NH, int S, int DHQK, int DHHV) {
   const uint64_t lim = 0x7fffffffull;
   const uint64_t bnh = (uint64_t)B * NH, nc = ((uint64_t)S + CL - 1) / CL;
-  const uint64_t tiles = (uint64_t)(DHHV / 128 + 2 * (DHQK / 128));
+  const uint64_t tiles = (uint64_t)((DHHV + 127) / 128 + 2 * ((DHQK + 127) / 128));
   return bnh * S < lim && bnh * (nc + 1) * DHQK < lim && bnh * nc * tiles < lim &&
-         bnh * (uint64_t)(DHHV / 128) * (DHQK / 128) < lim;
+         bnh * (uint64_t)((DHHV + 63) / 64) * ((DHQK + 127) / 128) < lim;
 }
 
 // cudaFuncSetAttribute once per kernel and device instead of on every call
@@ -921,8 +932,10 @@ static bool cached_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t
 static bool tok_map(CUtensorMap* m, const void* base, const ChunkwiseDims& d, int cols, int box_rows = 128) {
   return cached_map(m, base, (uint64_t)d.S, (uint64_t)cols, box_rows, 64, (uint64_t)d.B * d.NH, d.dtype == MLSTM_F16);
 }
+// per-chunk states: one slab of DHQK x DHHV per (batch, head, chunk boundary), so that a tile hanging over the edge of
+// a head dim reads zeros (and is clipped on the way out) instead of touching the next slab
 static bool state_map(CUtensorMap* m, const void* base, const ChunkwiseDims& d, int box_rows) {
-  return cached_map(m, base, (uint64_t)d.B * d.NH * (d.NC + 1) * d.DHQK, (uint64_t)d.DHHV, box_rows, 64, 0,
+  return cached_map(m, base, (uint64_t)d.DHQK, (uint64_t)d.DHHV, box_rows, 64, (uint64_t)d.B * d.NH * (d.NC + 1),
                     d.dtype == MLSTM_F16);
 }
 
@@ -932,7 +945,7 @@ static int launch_rec_tn(const CUtensorMap& mL, const CUtensorMap& mR, const CUt
   auto kern = rec_sm100<BWD, TN, F16>;
   static bool attr_done[64] = {};
   if (int rc = set_smem_once(kern, rec_smem_bytes(BWD), attr_done)) return rc;
-  const unsigned grid = (unsigned)(d.DHHV / TN) * (unsigned)(d.DHQK / 128) * (unsigned)units;
+  const unsigned grid = (unsigned)((d.DHHV + TN - 1) / TN) * (unsigned)((d.DHQK + 127) / 128) * (unsigned)units;
   kern<<<grid, REC_THREADS, rec_smem_bytes(BWD), st>>>(mL, mR, mS, rp);
   MLSTM_LAUNCH_CHECK();
   return MLSTM_OK;
@@ -951,7 +964,9 @@ static int sm_count() {
   return cached[dev];
 }
 
-long sm100_recurrence_ctas(const ChunkwiseDims& d) { return (long)(d.DHHV / 128) * (d.DHQK / 128) * d.B * d.NH; }
+long sm100_recurrence_ctas(const ChunkwiseDims& d) {
+  return (long)((d.DHHV + 127) / 128) * ((d.DHQK + 127) / 128) * d.B * d.NH;
+}
 int sm100_sm_count() { return sm_count(); }
 
 template <bool BWD>
@@ -967,7 +982,7 @@ static int launch_rec(const void* left, const void* right, RecParams rp, const C
   if (!state_map(&mS, rp.c_states ? (const void*)rp.c_states : left, d, 128)) return MLSTM_ERR_CUDA;
   // One CTA per SM walks all chunks of its state tile.  With 128-column tiles a launch of few (batch, head) units
   // leaves SMs idle; 64-column tiles double the CTAs as long as they still fit one wave.
-  const long ctas128 = (long)(d.DHHV / 128) * (d.DHQK / 128) * d.B * d.NH;
+  const long ctas128 = sm100_recurrence_ctas(d);
   const bool f16 = d.dtype == MLSTM_F16;
   if (2 * ctas128 <= sm_count())
     return f16 ? launch_rec_tn<BWD, 64, true>(mL, mR, mS, rp, d, units, st) : launch_rec_tn<BWD, 64, false>(mL, mR, mS, rp, d, units, st);
@@ -1019,7 +1034,7 @@ int sm100_parallel_fw(const void* q, const void* k, const void* v, const GateBuf
   if (int rc = f16 ? set_smem_once(par_fw_sm100<true>, PAR_SMEM, attr_done[1])
                    : set_smem_once(par_fw_sm100<false>, PAR_SMEM, attr_done[0])) return rc;
   // up to PAR_MAXSUB output tiles per CTA
-  const unsigned grid = (unsigned)((d.DHHV / 128 + PAR_MAXSUB - 1) / PAR_MAXSUB) * (unsigned)d.NC * (unsigned)units;
+  const unsigned grid = (unsigned)(((d.DHHV + 127) / 128 + PAR_MAXSUB - 1) / PAR_MAXSUB) * (unsigned)d.NC * (unsigned)units;
   if (f16) par_fw_sm100<true><<<grid, PAR_THREADS, PAR_SMEM, st>>>(mQ, mK, mV, mC, pp);
   else par_fw_sm100<false><<<grid, PAR_THREADS, PAR_SMEM, st>>>(mQ, mK, mV, mC, pp);
   MLSTM_LAUNCH_CHECK();
@@ -1046,7 +1061,8 @@ int sm100_parallel_bw(const void* q, const void* k, const void* v, const void* d
   if (int rc = f16 ? set_smem_once(par_bw_sm100<true>, PAR_SMEM, attr_done[1])
                    : set_smem_once(par_bw_sm100<false>, PAR_SMEM, attr_done[0])) return rc;
   // up to PAR_MAXSUB output tiles per CTA
-  const unsigned grid = (unsigned)((d.DHHV / 128 + PAR_MAXSUB - 1) / PAR_MAXSUB + 2 * ((d.DHQK / 128 + PAR_MAXSUB - 1) / PAR_MAXSUB)) *
+  const unsigned grid = (unsigned)(((d.DHHV + 127) / 128 + PAR_MAXSUB - 1) / PAR_MAXSUB +
+                                   2 * (((d.DHQK + 127) / 128 + PAR_MAXSUB - 1) / PAR_MAXSUB)) *
                         (unsigned)d.NC * (unsigned)units;
   if (f16) par_bw_sm100<true><<<grid, PAR_THREADS, PAR_SMEM, st>>>(mQ, mK, mV, mDH, mC_k, mdC_mn, mdC_k, pp);
   else par_bw_sm100<false><<<grid, PAR_THREADS, PAR_SMEM, st>>>(mQ, mK, mV, mDH, mC_k, mdC_mn, mdC_k, pp);

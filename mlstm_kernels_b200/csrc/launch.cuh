@@ -36,7 +36,7 @@ int simt_parallel_bw(int dtype, int state_dtype, const void* q, const void* k, c
                      const GateBuffers& gb, const void* c_states, const void* dc_states, void* dq, void* dk, void* dv,
                      const ChunkwiseDims& d, cudaStream_t st);
 
-// chunkwise_sm100.cu : tcgen05 + TMA kernels (bf16, L = 128, head dims multiples of 128)
+// chunkwise_sm100.cu : tcgen05 + TMA kernels (bf16 / fp16, L = 128, head dims multiples of 8)
 bool sm100_supported(int S, int DHQK, int DHHV, int L, int dtype);
 bool sm100_sizes_ok(int B, int NH, int S, int DHQK, int DHHV);
 // A launch may cover a sub-range of the B * NH independent (batch, head) units; all pointers stay those of the whole

@@ -111,11 +111,17 @@ def test_bf16_vs_oracle(shape, variant, impl):
                                    (1, 1, 256, 128, 1024, 128),   # widest v head (8 output tiles per chunk)
                                    (1, 2, 384, 128, 256, 128),    # odd number of chunks; 128/256 head geometry
                                    (3, 5, 640, 256, 256, 128),    # odd batch x heads, five chunks
-                                   (1, 2, 256, 384, 640, 128)])   # three and five 128-column tiles per chunk
+                                   (1, 2, 256, 384, 640, 128),    # three and five 128-column tiles per chunk
+                                   (1, 2, 384, 64, 64, 128),      # head dims below one tile: zero-padded by TMA
+                                   (2, 2, 384, 96, 192, 128),     # 125M-class geometry
+                                   (1, 2, 256, 192, 320, 128),    # 1.5 and 2.5 tiles
+                                   (1, 1, 256, 72, 136, 128),     # multiples of 8 only
+                                   (1, 2, 256, 32, 32, 128),      # a quarter of a tile
+                                   (1, 2, 256, 8, 24, 128)])      # the smallest head dims (one 16-byte row)
 @pytest.mark.parametrize("variant", ["exp", "sig_nonorm"])
 def test_tcgen05_head_geometries(shape, variant):
-    """Edge geometries of the tcgen05 path (limits of the head dims it accepts, odd chunk and head counts) against
-    the oracle, with initial states and an incoming state gradient."""
+    """Edge geometries of the tcgen05 path (limits of the head dims it accepts, head dims that are no multiples of its
+    128-wide tiles, odd chunk and head counts) against the oracle, with initial states and an incoming state gradient."""
     B, NH, S, DHQK, DHHV, L = shape
     inp = case_inputs(21, B, NH, S, DHQK, DHHV, init=True, dC_last=True)
     siging, normalize = variant != "exp", variant != "sig_nonorm"
@@ -149,9 +155,12 @@ def test_state_passing(variant, dtype):
         hs.append(h)
     tol = 1e-5 if dtype == torch.float32 else 1e-2
     assert max_rel_err(npy(torch.cat(hs, 2)), npy(H_full)) < tol
+    # f32 inputs: exact arithmetic on both sides.  bf16 inputs run on the tensor cores, where the four segments gate
+    # and round their operands with other chunk boundaries than the single pass (f32 states: 1e-4).
+    tol_state = 1e-5 if dtype == torch.float32 else 1e-4
     for a, b in zip(states, last_full):
         assert a.dtype == torch.float32
-        assert max_rel_err(npy(a), npy(b)) < 1e-5
+        assert max_rel_err(npy(a), npy(b)) < tol_state
 
 
 def test_chunk_size_independence_full_head_dims():
@@ -442,7 +451,8 @@ def _largest_divisor_up_to(n, cap):
 
 
 @pytest.mark.parametrize("shape", [(2, 2, 300, 128, 128), (1, 2, 64, 256, 256), (1, 2, 448, 128, 256),
-                                   (1, 1, 129, 256, 256), (1, 2, 1000, 128, 128), (2, 1, 17, 128, 128)])
+                                   (1, 1, 129, 256, 256), (1, 2, 1000, 128, 128), (2, 1, 17, 128, 128),
+                                   (2, 2, 300, 96, 192), (1, 2, 77, 64, 200)])   # ragged in tokens AND head dims
 @pytest.mark.parametrize("variant", ["exp", "sig", "sig_nonorm"])
 def test_tcgen05_any_sequence_length(shape, variant):
     """On the tcgen05 path the sequence length need not be a multiple of the chunk size (nor of 16): the last chunk
