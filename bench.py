@@ -565,6 +565,7 @@ def run_b200(args):
             "l2_flush": timed_reps(torch, fw_only, 30, 10, flush=True)}
         extra["portable_kernels_f32_B4_NH4_S2048_64_128_L64"] = bench_portable(torch, mk, dev)
         extra["arbitrary_length_prefill_bf16_NH16_256_256"] = bench_any_length(torch, mk, dev)
+        extra["head_dims_off_the_tile_bf16_B8_S8192"] = bench_head_dims(torch, mk, dev)
         extra["step_decode"] = bench_step(torch, mk, dev, peaks)
         extra["consttoken_sweep_65536_tokens"] = bench_sweep(torch, mk, dev, peaks)
         if world == 1 and not args.no_triton_ref:
@@ -857,8 +858,8 @@ def bench_triton_reference(torch, devin, leaf, L, flops_fw, flops_fwbw):
 
 
 def bench_portable(torch, mk, dev):
-    """The CUDA-core kernels that take every case the tcgen05 path does not (f32 / f16 inputs, head dims that are no
-    multiples of 128): one f32 case in the reference's own test geometry, forward and forward+backward."""
+    """The CUDA-core kernels that take every case the tcgen05 path does not (f32 inputs, head dims that are no
+    multiples of 8): one f32 case in the reference's own test geometry, forward and forward+backward."""
     B, NH, S, DHQK, DHHV, L = 4, 4, 2048, 64, 128, 64
     g = torch.Generator(device=dev).manual_seed(3)
     mk_t = lambda *sh: torch.randn(*sh, device=dev, generator=g)  # noqa: E731
@@ -878,6 +879,31 @@ def bench_portable(torch, mk, dev):
     ffb = ffw + bw_flops(B, NH, S, DHQK, DHHV, L)
     return dict(fw_ms=ms_fw, fw_tflops=ffw / ms_fw / 1e9, fwbw_ms=ms_fwbw, fwbw_tflops=ffb / ms_fwbw / 1e9,
                 note="exact f32 arithmetic on CUDA cores (coverage path, not tuned)")
+
+
+def bench_head_dims(torch, mk, dev):
+    """Head dims that are no multiples of the kernels' 128-wide tiles (small-model geometries), bf16, B=8, S=8192: the
+    tcgen05 path pads the tiles with zeros inside TMA; the same call on the CUDA-core kernels beside it."""
+    out = {}
+    for NH, DHQK, DHHV in ((4, 96, 192), (8, 64, 128), (4, 192, 384)):
+        B, S = 8, 8192
+        g = torch.Generator(device=dev).manual_seed(DHQK)
+        mk_t = lambda *sh: torch.randn(*sh, device=dev, generator=g).bfloat16()  # noqa: E731
+        q, k, v, dH = mk_t(B, NH, S, DHQK), mk_t(B, NH, S, DHQK), mk_t(B, NH, S, DHHV), mk_t(B, NH, S, DHHV)
+        i, f = mk_t(B, NH, S), (3 + torch.randn(B, NH, S, device=dev, generator=g)).bfloat16()
+        leaf = [t.clone().requires_grad_(True) for t in (q, k, v, i, f)]
+        ffw = fw_flops(B, NH, S, DHQK, DHHV, 128)
+        ffb = ffw + bw_flops(B, NH, S, DHQK, DHHV, 128)
+        res = {}
+        for impl, reps in (("auto", 10), ("simt", 3)):
+            def fwbw():
+                for t in leaf:
+                    t.grad = None
+                mk.mlstm_chunkwise__b200_xl_chunk(*leaf, chunk_size=128, impl=impl).backward(dH)
+            ms = timed_local(torch, fwbw, reps, 3)
+            res["tcgen05" if impl == "auto" else "cuda_cores"] = dict(fwbw_ms=ms, fwbw_tflops=ffb / ms / 1e9)
+        out[f"NH{NH}_{DHQK}_{DHHV}"] = res
+    return out
 
 
 def bench_any_length(torch, mk, dev):
