@@ -90,6 +90,53 @@ static bool want_unit_split(const ChunkwiseDims& d, bool allow) {
   return waves > 1 && ctas * 100 < waves * sms * 95;   // the last wave leaves more than 5 % of the SM time idle
 }
 
+// Fork on construction (when the split is wanted and the second stream exists), join on join() or, if an error path
+// leaves the scope early, in the destructor - a stream that is being captured must never be left forked.
+class UnitChains {
+ public:
+  UnitChains(const ChunkwiseDims& d, cudaStream_t st, bool allow) : st_(st), lk_(g_side_mu, std::defer_lock) {
+    const int units = d.B * d.NH;
+    first_ = UnitRange{0, units};
+    if (!want_unit_split(d, allow)) return;
+    lk_.lock();
+    SideStream* s = side_stream_for_current_device();
+    if (s == nullptr) { lk_.unlock(); return; }
+    if (cudaEventRecord(s->fork, st_) != cudaSuccess || cudaStreamWaitEvent(s->st, s->fork, 0) != cudaSuccess) {
+      set_last_cuda_error(cudaGetLastError(), "fork of the second launch chain");
+      rc_ = MLSTM_ERR_CUDA;
+      lk_.unlock();
+      return;
+    }
+    side_ = s;
+    first_ = UnitRange{0, (units + 1) / 2};
+    second_ = UnitRange{first_.count, -1};
+  }
+  ~UnitChains() { (void)join(); }
+  UnitChains(const UnitChains&) = delete;
+  UnitChains& operator=(const UnitChains&) = delete;
+  int status() const { return rc_; }
+  bool split() const { return side_ != nullptr; }
+  cudaStream_t second_stream() const { return side_->st; }
+  UnitRange first() const { return first_; }
+  UnitRange second() const { return second_; }
+  int join() {
+    if (side_ == nullptr) return MLSTM_OK;
+    SideStream* s = side_;
+    side_ = nullptr;
+    const bool ok = cudaEventRecord(s->join, s->st) == cudaSuccess && cudaStreamWaitEvent(st_, s->join, 0) == cudaSuccess;
+    if (!ok) set_last_cuda_error(cudaGetLastError(), "join of the second launch chain");
+    lk_.unlock();
+    return ok ? MLSTM_OK : MLSTM_ERR_CUDA;
+  }
+
+ private:
+  cudaStream_t st_;
+  std::unique_lock<std::mutex> lk_;
+  SideStream* side_ = nullptr;
+  UnitRange first_, second_;
+  int rc_ = MLSTM_OK;
+};
+
 // S need not be a multiple of L where the tcgen05 kernels run (they mask a ragged last chunk); resolve_impl refuses
 // that case for the portable kernels.
 static int check_dims(int B, int NH, int S, int DHQK, int DHHV, int L) {
@@ -321,22 +368,13 @@ int chunkwise_fw_body(const void* q, const void* k, const void* v, const void* i
 
   if ((rc = launch_gates(gate_dtype, i, f, variant == MLSTM_EXP ? m_initial : nullptr, nullptr, m_out, lay.gb, m_states, d, st)) != MLSTM_OK) return rc;
   if (use_sm100) {
-    std::unique_lock<std::mutex> lk(g_side_mu, std::defer_lock);
-    SideStream* side = nullptr;
-    if (want_unit_split(d, allow_split)) { lk.lock(); side = side_stream_for_current_device(); }
-    const UnitRange first{0, side ? (B * NH + 1) / 2 : B * NH}, second{first.count, -1};
-    if (side) {
-      MLSTM_CUDA_CHECK(cudaEventRecord(side->fork, st));
-      MLSTM_CUDA_CHECK(cudaStreamWaitEvent(side->st, side->fork, 0));
-    }
-    if ((rc = sm100_recurrent_fw(k, v, lay.gb, c_initial, n_initial, c_states, n_states, c_last, n_last, d, st, first)) != MLSTM_OK) return rc;
-    if (side && (rc = sm100_recurrent_fw(k, v, lay.gb, c_initial, n_initial, c_states, n_states, c_last, n_last, d, side->st, second)) != MLSTM_OK) return rc;
-    if ((rc = sm100_parallel_fw(q, k, v, lay.gb, c_states, n_states, h, n_out, d, st, first)) != MLSTM_OK) return rc;
-    if (side) {
-      if ((rc = sm100_parallel_fw(q, k, v, lay.gb, c_states, n_states, h, n_out, d, side->st, second)) != MLSTM_OK) return rc;
-      MLSTM_CUDA_CHECK(cudaEventRecord(side->join, side->st));
-      MLSTM_CUDA_CHECK(cudaStreamWaitEvent(st, side->join, 0));
-    }
+    UnitChains ch(d, st, allow_split);
+    if ((rc = ch.status()) != MLSTM_OK) return rc;
+    if ((rc = sm100_recurrent_fw(k, v, lay.gb, c_initial, n_initial, c_states, n_states, c_last, n_last, d, st, ch.first())) != MLSTM_OK) return rc;
+    if (ch.split() && (rc = sm100_recurrent_fw(k, v, lay.gb, c_initial, n_initial, c_states, n_states, c_last, n_last, d, ch.second_stream(), ch.second())) != MLSTM_OK) return rc;
+    if ((rc = sm100_parallel_fw(q, k, v, lay.gb, c_states, n_states, h, n_out, d, st, ch.first())) != MLSTM_OK) return rc;
+    if (ch.split() && (rc = sm100_parallel_fw(q, k, v, lay.gb, c_states, n_states, h, n_out, d, ch.second_stream(), ch.second())) != MLSTM_OK) return rc;
+    if ((rc = ch.join()) != MLSTM_OK) return rc;
   } else {
     if ((rc = simt_recurrent_fw(dtype, MLSTM_F32, k, v, lay.gb, c_initial, n_initial, c_states, n_states, c_last, n_last, d, st)) != MLSTM_OK) return rc;
     if ((rc = simt_parallel_fw(dtype, MLSTM_F32, q, k, v, lay.gb, c_states, n_states, h, n_out, d, st)) != MLSTM_OK) return rc;
@@ -394,26 +432,17 @@ static int bw_impl(const void* q, const void* k, const void* v, const void* i, c
   }
   if (use_sm100) {
     {
-      std::unique_lock<std::mutex> lk(g_side_mu, std::defer_lock);
-      SideStream* side = nullptr;
-      if (want_unit_split(d, true)) { lk.lock(); side = side_stream_for_current_device(); }
-      const UnitRange first{0, side ? (B * NH + 1) / 2 : B * NH}, second{first.count, -1};
-      if (side) {
-        MLSTM_CUDA_CHECK(cudaEventRecord(side->fork, st));
-        MLSTM_CUDA_CHECK(cudaStreamWaitEvent(side->st, side->fork, 0));
-      }
+      UnitChains ch(d, st, true);
+      if ((rc = ch.status()) != MLSTM_OK) return rc;
       if (recompute_into) {
-        if ((rc = sm100_recurrent_fw(k, v, lay.gb, recompute_c_initial, nullptr, recompute_into, nullptr, nullptr, nullptr, d, st, first)) != MLSTM_OK) return rc;
-        if (side && (rc = sm100_recurrent_fw(k, v, lay.gb, recompute_c_initial, nullptr, recompute_into, nullptr, nullptr, nullptr, d, side->st, second)) != MLSTM_OK) return rc;
+        if ((rc = sm100_recurrent_fw(k, v, lay.gb, recompute_c_initial, nullptr, recompute_into, nullptr, nullptr, nullptr, d, st, ch.first())) != MLSTM_OK) return rc;
+        if (ch.split() && (rc = sm100_recurrent_fw(k, v, lay.gb, recompute_c_initial, nullptr, recompute_into, nullptr, nullptr, nullptr, d, ch.second_stream(), ch.second())) != MLSTM_OK) return rc;
       }
-      if ((rc = sm100_recurrent_bw(q, dh, lay.gb, dc_last, lay.dc_states, dc_initial, d, st, first)) != MLSTM_OK) return rc;
-      if (side && (rc = sm100_recurrent_bw(q, dh, lay.gb, dc_last, lay.dc_states, dc_initial, d, side->st, second)) != MLSTM_OK) return rc;
-      if ((rc = sm100_parallel_bw(q, k, v, dh, lay.gb, c_states, lay.dc_states, dq, dk, dv, lay.acc, lay.kdk, d, st, first)) != MLSTM_OK) return rc;
-      if (side) {
-        if ((rc = sm100_parallel_bw(q, k, v, dh, lay.gb, c_states, lay.dc_states, dq, dk, dv, lay.acc, lay.kdk, d, side->st, second)) != MLSTM_OK) return rc;
-        MLSTM_CUDA_CHECK(cudaEventRecord(side->join, side->st));
-        MLSTM_CUDA_CHECK(cudaStreamWaitEvent(st, side->join, 0));
-      }
+      if ((rc = sm100_recurrent_bw(q, dh, lay.gb, dc_last, lay.dc_states, dc_initial, d, st, ch.first())) != MLSTM_OK) return rc;
+      if (ch.split() && (rc = sm100_recurrent_bw(q, dh, lay.gb, dc_last, lay.dc_states, dc_initial, d, ch.second_stream(), ch.second())) != MLSTM_OK) return rc;
+      if ((rc = sm100_parallel_bw(q, k, v, dh, lay.gb, c_states, lay.dc_states, dq, dk, dv, lay.acc, lay.kdk, d, st, ch.first())) != MLSTM_OK) return rc;
+      if (ch.split() && (rc = sm100_parallel_bw(q, k, v, dh, lay.gb, c_states, lay.dc_states, dq, dk, dv, lay.acc, lay.kdk, d, ch.second_stream(), ch.second())) != MLSTM_OK) return rc;
+      if ((rc = ch.join()) != MLSTM_OK) return rc;
     }
     {
       PhaseScope ps(PH_GATE_GRADS, st);
