@@ -446,6 +446,36 @@ def test_bounded_wait_expiry_is_reported():
     assert _lib.device_status(reset=True) == 903
 
 
+def _random_geometries(count, seed):
+    rng = np.random.default_rng(seed)
+    out = []
+    for _ in range(count):
+        B, NH = int(rng.integers(1, 4)), int(rng.integers(1, 4))
+        S = int(rng.integers(1, 420))
+        DHQK, DHHV = 8 * int(rng.integers(1, 41)), 8 * int(rng.integers(1, 49))   # 8 .. 320, 8 .. 384
+        out.append((B, NH, S, DHQK, DHHV, ["exp", "sig", "sig_nonorm"][int(rng.integers(0, 3))]))
+    return out
+
+
+@pytest.mark.parametrize("geom", _random_geometries(24, 2024))
+def test_tcgen05_random_geometries(geom):
+    """Randomly drawn (seeded) batch, heads, sequence length (any) and head dims (any multiples of 8): every
+    combination of ragged tokens and head dims off the 128-wide tiles, with initial states and an incoming state
+    gradient, against the oracle (run with a chunk size that divides S)."""
+    B, NH, S, DHQK, DHHV, variant = geom
+    inp = case_inputs(1000 + S, B, NH, S, DHQK, DHHV, init=True, dC_last=True)
+    siging, normalize = variant != "exp", variant != "sig_nonorm"
+    got = run_cuda_fwbw(inp, 128, dtype=torch.bfloat16, siging=siging, normalize=normalize, impl="tcgen05")
+    ref = run_oracle_fwbw(inp, _largest_divisor_up_to(S, 128), dtype=torch.bfloat16, siging=siging, normalize=normalize)
+    compare(got, ref, TOL_BF16, TOL_BF16, keys_fw=("H",))
+    if siging:
+        assert max_rel_err(got["C_last"], ref["C_last"]) < TOL_BF16
+    else:
+        sg, sr = np.exp(got["m_last"]), np.exp(ref["m_last"])
+        assert max_rel_err(got["C_last"] * sg[..., None], ref["C_last"] * sr[..., None]) < TOL_BF16
+        assert max_rel_err(got["n_last"] * sg, ref["n_last"] * sr) < TOL_BF16
+
+
 def _largest_divisor_up_to(n, cap):
     return max(d for d in range(1, cap + 1) if n % d == 0)
 
