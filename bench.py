@@ -212,6 +212,65 @@ def time_cpu_reference(steps, warmup):
     return fl / dt / 1e12, dt, sample, kind, threads
 
 
+def cpu_reference_small_cases():
+    """The reference's own CPU code on the cases that fit a CPU: its native chunkwise function at BASELINE config 0
+    (fp32, B=2, NH=4, S=512, 128/256, chunk 64; forward and forward+backward, 3 warm-up + 10 repetitions, median) and
+    its native decode step (bf16 inputs, fp32 state, NH=8, 256/512; chained steps, per-step median)."""
+    fn, why = import_reference_native()
+    if fn is None:
+        return {"unavailable": why}
+    import torch
+    from mlstm_kernels.torch.recurrent.native_step import mlstm_recurrent_step__native
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    out = {"cores": torch.get_num_threads()}
+    B, NH, S, DHQK, DHHV, L = 2, 4, 512, 128, 256, 64
+    g = torch.Generator().manual_seed(0)
+    q, k, v = (torch.randn(B, NH, S, D, generator=g) for D in (DHQK, DHQK, DHHV))
+    i, f, dH = torch.randn(B, NH, S, generator=g), 3 + torch.randn(B, NH, S, generator=g), torch.randn(B, NH, S, DHHV, generator=g)
+    leaves = [t.clone().requires_grad_(True) for t in (q, k, v, i, f)]
+
+    def med(fn_, reps, warm):
+        for _ in range(warm):
+            fn_()
+        ts = []
+        for _ in range(reps):
+            t0 = time.perf_counter()
+            fn_()
+            ts.append(time.perf_counter() - t0)
+        return statistics.median(ts)
+
+    def fw():
+        with torch.no_grad():
+            fn(q, k, v, i, f, return_last_states=True, chunk_size=L)
+
+    def fwbw():
+        for t in leaves:
+            t.grad = None
+        fn(*leaves, return_last_states=True, chunk_size=L)[0].backward(dH)
+    t_fw, t_fb = med(fw, 10, 3), med(fwbw, 10, 3)
+    ffw = fw_flops(B, NH, S, DHQK, DHHV, L)
+    ffb = ffw + bw_flops(B, NH, S, DHQK, DHHV, L)
+    out["c0_chunkwise_native_custbw_fp32_B2_NH4_S512_128_256_L64"] = dict(
+        fw_ms=t_fw * 1e3, fw_gflops=ffw / t_fw / 1e9, fwbw_ms=t_fb * 1e3, fwbw_gflops=ffb / t_fb / 1e9)
+    NH, DHQK, DHHV = 8, 256, 512
+    steps = {}
+    for Bs, n in ((1, 16), (8, 16), (64, 16), (256, 4)):
+        c, nn, m = 0.1 * torch.randn(Bs, NH, DHQK, DHHV, generator=g), torch.randn(Bs, NH, DHQK, generator=g).abs(), torch.randn(Bs, NH, 1, generator=g)
+        tok = [tuple(torch.randn(Bs, NH, D, generator=g).bfloat16() for D in (DHQK, DHQK, DHHV)) +
+               (torch.randn(Bs, NH, 1, generator=g).bfloat16(), (3 + torch.randn(Bs, NH, 1, generator=g)).bfloat16())
+               for _ in range(n)]
+        ts = []
+        with torch.no_grad():
+            for (qq, kk, vv, ii, ff) in tok:
+                t0 = time.perf_counter()
+                _, (c, nn, m) = mlstm_recurrent_step__native(qq, kk, vv, ii, ff, c, nn, m)
+                ts.append(time.perf_counter() - t0)
+        steps[f"B{Bs}"] = dict(ms_per_step=statistics.median(ts) * 1e3, tokens_per_s=Bs / statistics.median(ts))
+    out["step_native_bf16_NH8_256_512"] = steps
+    return out
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -577,6 +636,11 @@ def run_b200(args):
     if rank == 0 and world == 1 and not args.no_cpu:
         val, dt, sample, kind, threads = time_cpu_reference(5, 1)
         cpu = {"value": val, "unit": "TFLOP/s", "cores": threads, "kind": kind, "sample": sample}
+        if not args.no_extra:
+            try:
+                extra["cpu_reference_small_cases"] = cpu_reference_small_cases()
+            except Exception as e:  # noqa: BLE001  (a baseline for context must not take the GPU numbers down with it)
+                extra["cpu_reference_small_cases"] = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
 
     if rank == 0:
         line = {
