@@ -568,6 +568,8 @@ def run_b200(args):
                                                            max_over_ranks, kernel_profile, peaks)
         extra["step_decode_sharded_B256"] = bench_step_sharded(torch, mk, dev, world, rank, barrier, max_over_ranks,
                                                                peaks)
+        extra["step_decode_sharded_B1_over_heads"] = bench_step_sharded(torch, mk, dev, world, rank, barrier,
+                                                                        max_over_ranks, peaks, Btot=1)
         extra["sequence_parallel_prefill_B1_NH8_S131072_256_512_cs256"] = bench_sequence_parallel(
             torch, dist, mk, dev, world, rank, barrier, max_over_ranks, peaks)
 
@@ -709,13 +711,18 @@ def bench_strong(torch, dist, mk, _lib, dev, devin, world, rank, L, barrier, max
                 kernels_rank0={k_: {x: v_[x] for x in ("ms", "tflops", "hbm_frac") if x in v_} for k_, v_ in kern.items()})
 
 
-def bench_step_sharded(torch, mk, dev, world, rank, barrier, max_over_ranks, peaks):
-    """Decode at NH=8, 256/512 with the batch B=256 sharded over the ranks (B / N sequences per rank, no collective):
-    tokens/s of the whole batch = 256 / slowest rank's time per step."""
+def bench_step_sharded(torch, mk, dev, world, rank, barrier, max_over_ranks, peaks, Btot=256):
+    """Decode at NH=8, 256/512 with the batch sharded over the ranks (B / N sequences per rank, no collective):
+    tokens/s of the whole batch = B / slowest rank's time per step.  A single sequence (B=1) cannot be split over the
+    batch: its 8 heads are split over the ranks instead (launch-bound on any number of GPUs)."""
     from mlstm_kernels_b200.sharding import shard_range
-    NH, DHQK, DHHV, Btot = 8, 256, 512, 256
-    lo, hi = shard_range(Btot, world, rank)
-    Bm = hi - lo
+    NH, DHQK, DHHV = 8, 256, 512
+    if Btot == 1:
+        lo, hi = shard_range(NH, min(world, NH), min(rank, NH - 1))
+        Bm, NH = 1, hi - lo
+    else:
+        lo, hi = shard_range(Btot, world, rank)
+        Bm = hi - lo
     g = torch.Generator(device=dev).manual_seed(100 + rank)
     c = torch.randn(Bm, NH, DHQK, DHHV, device=dev, generator=g) * 0.1
     n = torch.randn(Bm, NH, DHQK, device=dev, generator=g).abs()
@@ -745,9 +752,10 @@ def bench_step_sharded(torch, mk, dev, world, rank, barrier, max_over_ranks, pea
     e1.record()
     barrier()
     us = max_over_ranks(e0.elapsed_time(e1) / nsteps * 1e3)
-    gbs = step_bytes(Btot, NH, DHQK, DHHV) / (us * 1e-6) / 1e9
-    return dict(us_per_step=us, tokens_per_s=Btot / (us * 1e-6), batch_total=Btot, batch_per_rank=Bm, n_gpus=world,
-                gbs_all_gpus=gbs, frac_of_n_gpu_hbm=gbs / (world * peaks["hbm"]), scaling="strong", collective="none")
+    gbs = step_bytes(Btot, 8, DHQK, DHHV) / (us * 1e-6) / 1e9
+    return dict(us_per_step=us, tokens_per_s=Btot / (us * 1e-6), batch_total=Btot, batch_per_rank=Bm,
+                heads_per_rank=NH, n_gpus=world, gbs_all_gpus=gbs, frac_of_n_gpu_hbm=gbs / (world * peaks["hbm"]),
+                scaling="strong", collective="none")
 
 
 def bench_sequence_parallel(torch, dist, mk, dev, world, rank, barrier, max_over_ranks, peaks):
