@@ -86,6 +86,10 @@ int mlstm_b200_profile_phases(void);
 const char* mlstm_b200_profile_phase_name(int phase);
 int mlstm_b200_profile_read(float* total_ms, int* count);
 
+/* NVTX ranges (host-side markers named like the profile phases) around every phase of every call, for timeline
+ * profilers; off by default.  Returns the previous setting. */
+int mlstm_b200_nvtx_enable(int on);
+
 /* 1 if the tcgen05 path covers this chunkwise case, else 0. */
 int mlstm_b200_chunkwise_has_tcgen05(int S, int DHQK, int DHHV, int L, int dtype);
 

@@ -52,6 +52,7 @@ SIGNATURES = {
     "mlstm_b200_chunkwise_states": (_i, [_vp] * 4 + [_fp, _fp, _vp, _vp, _sz, _vp, _sz] + [_i] * 6 + [_i, _i, _i, _i, _vp]),
     "mlstm_b200_chunkwise_summary": (_i, [_vp] * 4 + [_fp] * 4 + [_vp, _sz] + [_i] * 6 + [_i, _i, _i, _i, _vp]),
     "mlstm_b200_set_unit_split": (_i, [_i]),
+    "mlstm_b200_nvtx_enable": (_i, [_i]),
     "mlstm_b200_state_combine": (_i, [_fp] * 10 + [_i] * 5 + [_vp]),
     "mlstm_b200_chunkwise_dc_summary": (_i, [_vp, _vp, _fp, _vp, _sz, _fp, _vp, _sz] + [_i] * 6 + [_i, _i, _i, _f, _vp]),
     "mlstm_b200_step": (_i, [_vp] * 12 + [_i] * 7 + [_f, _vp]),

@@ -7,6 +7,8 @@
 #include <mutex>
 #include <vector>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "common.cuh"
 #include "launch.cuh"
 
@@ -29,7 +31,17 @@ static bool g_prof_on = false;
 static std::vector<PhaseRec> g_prof_recs;
 static const size_t kMaxPhaseRecs = 1 << 16;
 
-PhaseScope::PhaseScope(int phase, cudaStream_t s) : slot(-1), st(s) {
+// NVTX ranges around the phases (mlstm_b200_nvtx_enable): host-side markers for a timeline profiler, named like the
+// phases of mlstm_b200_profile_phase_name.  Off by default; the header-only NVTX loads the tools library on first use.
+static std::atomic<int> g_nvtx_on{0};
+static const char* const kPhaseNames[PH_COUNT] = {"gates", "recurrent_fw", "parallel_fw", "recurrent_bw",
+                                                   "parallel_bw", "gate_grads", "step"};
+
+PhaseScope::PhaseScope(int phase, cudaStream_t s) : slot(-1), st(s), nvtx(false) {
+  if (g_nvtx_on.load(std::memory_order_relaxed) != 0 && phase >= 0 && phase < PH_COUNT) {
+    nvtxRangePushA(kPhaseNames[phase]);
+    nvtx = true;
+  }
   if (!g_prof_on) return;
   std::lock_guard<std::mutex> lk(g_prof_mu);
   if (g_prof_recs.size() >= kMaxPhaseRecs) return;
@@ -40,6 +52,7 @@ PhaseScope::PhaseScope(int phase, cudaStream_t s) : slot(-1), st(s) {
   slot = (int)g_prof_recs.size() - 1;
 }
 PhaseScope::~PhaseScope() {
+  if (nvtx) nvtxRangePop();
   if (slot < 0) return;
   std::lock_guard<std::mutex> lk(g_prof_mu);
   if (slot < (int)g_prof_recs.size()) cudaEventRecord(g_prof_recs[slot].b, st);
@@ -284,10 +297,10 @@ int mlstm_b200_profile_enable(int on) {
 int mlstm_b200_profile_phases(void) { return PH_COUNT; }
 
 const char* mlstm_b200_profile_phase_name(int phase) {
-  static const char* names[PH_COUNT] = {"gates", "recurrent_fw", "parallel_fw", "recurrent_bw",
-                                        "parallel_bw", "gate_grads", "step"};
-  return (phase >= 0 && phase < PH_COUNT) ? names[phase] : "?";
+  return (phase >= 0 && phase < PH_COUNT) ? kPhaseNames[phase] : "?";
 }
+
+int mlstm_b200_nvtx_enable(int on) { return g_nvtx_on.exchange(on != 0 ? 1 : 0); }
 
 int mlstm_b200_profile_read(float* total_ms, int* count) {
   std::lock_guard<std::mutex> lk(g_prof_mu);

@@ -65,6 +65,7 @@ struct PhaseScope {
   ~PhaseScope();
   int slot;
   cudaStream_t st;
+  bool nvtx;
 };
 
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }

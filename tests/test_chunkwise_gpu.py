@@ -423,6 +423,23 @@ def test_recompute_states_in_bw(variant, impl, dtype, shape):
     compare(got, ref, tol_fw, tol_bw, keys_fw=("H",))
 
 
+def test_nvtx_ranges_do_not_change_results():
+    """NVTX ranges around the phases are host-side markers: switched on (no profiler attached) a forward + backward
+    gives the same bits, and the setter returns the previous setting."""
+    from mlstm_kernels_b200 import _lib
+    lib = _lib.load()
+    inp = case_inputs(3, 1, 2, 256, 128, 128)
+    off = run_cuda_fwbw(inp, 128, dtype=torch.bfloat16)
+    prev = lib.mlstm_b200_nvtx_enable(1)
+    try:
+        on = run_cuda_fwbw(inp, 128, dtype=torch.bfloat16)
+        assert lib.mlstm_b200_nvtx_enable(1) == 1
+    finally:
+        lib.mlstm_b200_nvtx_enable(prev)
+    for key in off:
+        assert np.array_equal(off[key], on[key]), key
+
+
 def test_bounded_wait_expiry_is_reported():
     """A wait that runs out records its code in the device status word and the context stays usable.  The self-test
     kernel waits a few thousand polls on a barrier that nothing signals (no copy in flight, no tensor memory held),
