@@ -423,6 +423,25 @@ def test_recompute_states_in_bw(variant, impl, dtype, shape):
     compare(got, ref, tol_fw, tol_bw, keys_fw=("H",))
 
 
+@pytest.mark.parametrize("shape", [(2, 3, 200, 72, 136), (1, 2, 384, 256, 256), (2, 2, 96, 16, 32)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_every_output_element_is_written(shape, dtype):
+    """Outputs are allocated uninitialised.  The allocator's free blocks are filled with NaN first, so an element a
+    kernel forgot to write (a masked tail, a tile edge) would surface as NaN in H, the states or a gradient."""
+    B, NH, S, DHQK, DHHV = shape
+    if dtype == torch.float32 and S % 64 != 0:
+        S = 192   # the portable kernels need whole chunks
+    inp = case_inputs(5, B, NH, S, DHQK, DHHV, init=True, dC_last=True)
+    torch.cuda.synchronize()
+    poison = [torch.full((64 << 20,), float("nan"), device="cuda") for _ in range(4)]   # 1 GiB of NaN
+    small = [torch.full((n,), float("nan"), device="cuda") for n in (1 << 10, 1 << 14, 1 << 18, 1 << 20) for _ in range(8)]
+    torch.cuda.synchronize()
+    del poison, small
+    got = run_cuda_fwbw(inp, 64, dtype=dtype)
+    for key, val in got.items():
+        assert np.isfinite(val).all(), key
+
+
 def test_nvtx_ranges_do_not_change_results():
     """NVTX ranges around the phases are host-side markers: switched on (no profiler attached) a forward + backward
     gives the same bits, and the setter returns the previous setting."""
