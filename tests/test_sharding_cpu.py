@@ -93,7 +93,15 @@ def fake_segment_dc_summary(q, dh, saved, *, chunk_size, eps, variant, impl="aut
 CASE = dict(seed=17, B=1, NH=2, S=256, DHQK=16, DHHV=32, f_offset=1.0)
 
 
-def _worker(rank, world, port, mode, siging, out_dir):
+def _initial_state():
+    rng = np.random.default_rng(99)
+    B, NH, DHQK, DHHV = CASE["B"], CASE["NH"], CASE["DHQK"], CASE["DHHV"]
+    return (0.1 * rng.standard_normal((B, NH, DHQK, DHHV)).astype(np.float32),
+            np.abs(rng.standard_normal((B, NH, DHQK))).astype(np.float32),
+            rng.standard_normal((B, NH, 1)).astype(np.float32))
+
+
+def _worker(rank, world, port, mode, siging, out_dir, with_initial=False):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -106,7 +114,13 @@ def _worker(rank, world, port, mode, siging, out_dir):
     seg = CASE["S"] // world
     sl = slice(rank * seg, (rank + 1) * seg)
     q, k, v, i, f = (torch.from_numpy(inp[n][:, :, sl].copy()).requires_grad_(True) for n in "qkvif")
-    h, last = sharding.mlstm_chunkwise_sequence_parallel(q, k, v, i, f, return_last_states=True, chunk_size=32,
+    c0 = n0 = m0 = None
+    if with_initial:   # the state entering the whole sequence: only rank 0's copy is used
+        c0, n0, m0 = (torch.from_numpy(x) for x in _initial_state())
+        if rank != 0:
+            c0, n0, m0 = torch.full_like(c0, 7.0), torch.full_like(n0, 7.0), torch.full_like(m0, 7.0)
+    h, last = sharding.mlstm_chunkwise_sequence_parallel(q, k, v, i, f, c0, n0, None if siging else m0,
+                                                         return_last_states=True, chunk_size=32,
                                                          siging=siging, mode=mode)
     (h * torch.from_numpy(inp["dH"][:, :, sl].copy())).sum().backward()   # chain of messages from the last rank back
     np.savez(os.path.join(out_dir, f"r{rank}.npz"), h=h.detach().numpy(),
@@ -140,3 +154,22 @@ def test_sequence_parallel_gloo_ranks(tmp_path, mode, world, siging):
     for n, key in (("q", "dQ"), ("k", "dK"), ("v", "dV"), ("i", "dI"), ("f", "dF")):
         got = np.concatenate([o["d" + n] for o in outs], axis=2)
         assert max_rel_err(got, full_bw[key]) < 1e-5, key
+
+
+@pytest.mark.parametrize("mode", ["gather", "scan", "chain"])
+@pytest.mark.parametrize("siging", [False, True])
+def test_sequence_parallel_with_an_initial_state(tmp_path, mode, siging):
+    """The state entering the whole sequence is rank 0's argument (the other ranks pass garbage here): every mode has
+    to carry it through the hand-off to every later segment."""
+    world = 4 if mode == "gather" else 2
+    mp.spawn(_worker, args=(world, _free_port(), mode, siging, str(tmp_path), True), nprocs=world, join=True)
+    inp = make_chunkwise_inputs(CASE)
+    c0, n0, m0 = _initial_state()
+    full, full_bw = O.chunkwise_fwbw(*(inp[n] for n in ("q", "k", "v", "i", "f", "dH")), c_initial=c0,
+                                     n_initial=n0, m_initial=None if siging else m0, chunk_size=32, siging=siging)
+    outs = [dict(np.load(tmp_path / f"r{r}.npz")) for r in range(world)]
+    assert max_rel_err(np.concatenate([o["h"] for o in outs], axis=2), full["H"]) < 1e-5
+    for o in outs:
+        assert max_rel_err(o["s0"], full["C_last"]) < 1e-5
+    for n, key in (("q", "dQ"), ("k", "dK"), ("v", "dV"), ("i", "dI"), ("f", "dF")):
+        assert max_rel_err(np.concatenate([o["d" + n] for o in outs], axis=2), full_bw[key]) < 1e-5, key
