@@ -15,7 +15,7 @@ import os
 import torch
 from torch.amp import custom_bwd, custom_fwd
 
-from . import _lib
+from . import _lib, _ops
 
 # MLSTM_B200_CHECK_STATUS=1: after every backward, synchronise and raise if a bounded wait of the tcgen05 kernels
 # ran out (their results are then invalid).  Off by default because the check waits for the device.
@@ -311,9 +311,14 @@ def mlstm_chunkwise__b200_xl_chunk(
     inter-chunk recurrence again in the backward; False keeps the per-chunk C states (faster backward, more
     memory).  Tile / warp / stage arguments and chunk_size_inter / chunk_size_intra are Triton tuning knobs of
     the reference and have no meaning here."""
-    fn = _get_fwbw(autocast_kernel_dtype, _lib.EXP)
-    h, c_last, n_last, m_last = fn.apply(q, k, v, i, f, c_initial, n_initial, m_initial, return_last_states,
-                                         eps, chunk_size, impl, bool(recompute_states_in_bw))
+    if torch.compiler.is_compiling():   # a tracer is watching: go through the custom operators
+        h, c_last, n_last, m_last = _ops.chunkwise_traced(
+            q, k, v, i, f, c_initial, n_initial, m_initial, return_last_states, eps, chunk_size, impl,
+            bool(recompute_states_in_bw), autocast_kernel_dtype, _lib.EXP)
+    else:
+        fn = _get_fwbw(autocast_kernel_dtype, _lib.EXP)
+        h, c_last, n_last, m_last = fn.apply(q, k, v, i, f, c_initial, n_initial, m_initial, return_last_states,
+                                             eps, chunk_size, impl, bool(recompute_states_in_bw))
     if return_last_states:
         return h, (c_last, n_last, m_last)
     return h
@@ -348,9 +353,15 @@ def mlstm_siging_chunkwise__b200_xl_chunk(
 ) -> torch.Tensor | tuple[torch.Tensor, tuple[torch.Tensor, torch.Tensor]]:
     """mLSTMsig (sigmoid input gate) chunkwise forward with autograd.  Returns H, or
     (H, (C_last, n_last)) when return_last_states is set."""
-    fn = _get_fwbw(autocast_kernel_dtype, _lib.SIG if normalize else _lib.SIG_NONORM)
-    h, c_last, n_last, _ = fn.apply(q, k, v, i, f, c_initial, n_initial, None, return_last_states, eps, chunk_size,
-                                    impl, bool(recompute_states_in_bw))
+    variant = _lib.SIG if normalize else _lib.SIG_NONORM
+    if torch.compiler.is_compiling():   # a tracer is watching: go through the custom operators
+        h, c_last, n_last, _ = _ops.chunkwise_traced(
+            q, k, v, i, f, c_initial, n_initial, None, return_last_states, eps, chunk_size, impl,
+            bool(recompute_states_in_bw), autocast_kernel_dtype, variant)
+    else:
+        fn = _get_fwbw(autocast_kernel_dtype, variant)
+        h, c_last, n_last, _ = fn.apply(q, k, v, i, f, c_initial, n_initial, None, return_last_states, eps,
+                                        chunk_size, impl, bool(recompute_states_in_bw))
     if return_last_states:
         return h, (c_last, n_last)
     return h

@@ -15,7 +15,7 @@ from __future__ import annotations
 
 import torch
 
-from . import _lib
+from . import _lib, _ops
 
 _STATE_DTYPES = (torch.float32, torch.bfloat16)
 
@@ -158,6 +158,11 @@ def mlstm_recurrent_step__b200(
     **kwargs,
 ) -> tuple[torch.Tensor, tuple[torch.Tensor, torch.Tensor, torch.Tensor]]:
     """One mLSTM decode step: returns h (B,NH,DHHV) and the new (C, n, m); the old states are untouched."""
+    if torch.compiler.is_compiling():   # a tracer is watching: go through the custom operator
+        if dtype_state not in _STATE_DTYPES:
+            raise ValueError(f"Unsupported state dtype {dtype_state}.")
+        h, c_new, n_new, m_new = _ops.step(q, k, v, i, f, c, n, m, eps, dtype_state is torch.bfloat16)
+        return h, (c_new, n_new, m_new)
     return mlstm_recurrent_step__b200_fw(matC_old=c, vecN_old=n, scaM_old=m, vecQ=q, vecK=k, vecV=v, scaI=i,
                                          scaF=f, eps=eps, dtype_state=dtype_state, **kwargs)
 
@@ -177,6 +182,11 @@ def mlstm_recurrent_sequence__b200(
     **kwargs,
 ):
     """S decode steps in ONE launch with the state held in registers (replaces the per-token Python loop)."""
+    if torch.compiler.is_compiling():   # a tracer is watching: go through the custom operator
+        h, c_new, n_new, m_new = _ops.step_sequence(q, k, v, i, f, c_initial, n_initial, m_initial, eps)
+        if return_last_states:
+            return h, (c_new.to(dtype_state), n_new.to(dtype_state), m_new.to(dtype_state))
+        return h
     _lib.require_cuda(q, k, v, i, f)
     lib = _lib.load()
     B, NH, S, DHQK = q.shape

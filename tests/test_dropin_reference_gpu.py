@@ -127,3 +127,22 @@ def test_single_step_through_backend():
     h_n, st_n = _backend("chunkwise--native_custbw", "inference", step_kernel="native", **kw)(q, k, v, i, f, c0, n0, m0)
     assert max_rel_err(npy(h_b), npy(h_n)) < 1e-5
     assert max_rel_err(npy(st_b[0]), npy(st_n[0])) < 1e-5
+
+
+@pytest.mark.parametrize("mode", ["train", "inference"])
+def test_backend_module_under_torch_compile(mode):
+    """The reference's own backend module, compiled, with the B200 kernels inside (no graph break allowed): same bits
+    as the eager module.  bf16, ragged length in inference mode (one chunkwise call on the tensor-core path)."""
+    mk.register_with_mlstm_kernels()
+    S = 256 if mode == "train" else 300
+    inp = case_inputs(53, 2, 2, 512, 128, 128)
+    q, k, v, i, f = (to_dev(inp[n][:, :, :S], torch.bfloat16) for n in "qkvif")
+    kw = dict(chunk_size=128, return_last_states=True, autocast_kernel_dtype="bfloat16")
+    if mode == "inference":
+        kw.update(sequence_kernel="native_sequence__b200", step_kernel="b200", inference_state_dtype="float32")
+    backend = _backend("chunkwise--b200_xl_chunk", mode, **kw)
+    h_e, st_e = backend(q, k, v, i, f)
+    h_c, st_c = torch.compile(backend, fullgraph=True)(q, k, v, i, f)
+    assert torch.equal(h_e, h_c)
+    for a, b in zip(st_e, st_c):
+        assert torch.equal(a, b)
