@@ -81,3 +81,25 @@ def test_decode_step_and_sequence_compile():
         compiled = torch.compile(fun, fullgraph=True)(q, k, v, i, f, c, n, m)
         for a, b in zip(eager, compiled):
             assert torch.equal(a, b)
+
+
+def test_operator_registrations_pass_opcheck():
+    """PyTorch's own checker: the declared schema matches what the operators do (no hidden mutation or aliasing), the
+    fake implementations agree with the real outputs in shape, dtype and strides, and the autograd registration is of
+    the supported kind."""
+    from mlstm_kernels_b200 import _lib
+    inp = case_inputs(63, 1, 2, 256, 128, 128)
+    q, k, v, i, f = (to_dev(inp[n], torch.bfloat16).requires_grad_(True) for n in "qkvif")
+    utils = ("test_schema", "test_faketensor", "test_autograd_registration")
+    args = (q, k, v, i, f, None, None, None, 128, 1e-6, _lib.EXP, "auto", True, False)
+    torch.library.opcheck(torch.ops.mlstm_b200.chunkwise_fw.default, args, test_utils=utils)
+    out = torch.ops.mlstm_b200.chunkwise_fw(*args)
+    bw_args = (q.detach(), k.detach(), v.detach(), i.detach(), f.detach(), None, None, None, out[1].detach(),
+               out[2].detach(), out[4].detach(), torch.randn_like(out[0]).detach(), None, 128, 1e-6, _lib.EXP, "auto",
+               False)
+    torch.library.opcheck(torch.ops.mlstm_b200.chunkwise_bw.default, bw_args, test_utils=utils)
+    g = torch.Generator(device="cuda").manual_seed(1)
+    rnd = lambda *s: torch.randn(*s, device="cuda", generator=g)  # noqa: E731
+    step_args = (rnd(2, 4, 128).bfloat16(), rnd(2, 4, 128).bfloat16(), rnd(2, 4, 256).bfloat16(), rnd(2, 4, 1).bfloat16(),
+                 rnd(2, 4, 1).bfloat16(), rnd(2, 4, 128, 256), rnd(2, 4, 128).abs(), rnd(2, 4, 1), 1e-6, False)
+    torch.library.opcheck(torch.ops.mlstm_b200.step.default, step_args, test_utils=utils)
