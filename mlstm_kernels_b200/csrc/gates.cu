@@ -24,9 +24,11 @@ template <typename T>
 __global__ void __launch_bounds__(kGateThreads)
 gates_chunk_kernel(const T* __restrict__ vecI, const T* __restrict__ vecF, GateBuffers gb, int S, int SP, int L,
                    int NC, int variant) {
-  const int bh = blockIdx.y;
+  // 1-D grid (no 65535 limit on batch x heads): the chunk groups of one (batch, head) next to each other
+  const int ngrp = (NC + kGateThreads / 32 - 1) / (kGateThreads / 32);
+  const int bh = blockIdx.x / ngrp;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int k = blockIdx.x * (kGateThreads / 32) + warp;
+  const int k = (blockIdx.x % ngrp) * (kGateThreads / 32) + warp;
   if (k >= NC) return;
   const bool siging = variant != MLSTM_EXP;
   float* g_arr = gb.scratch + (size_t)bh * 2 * NC;
@@ -124,9 +126,11 @@ gates_scan_kernel(const float* __restrict__ m_initial, GateBuffers gb, float* __
 __global__ void __launch_bounds__(kGateThreads)
 gates_token_kernel(const float* __restrict__ n_out, float* __restrict__ m_out, GateBuffers gb,
                    const float* __restrict__ m_states, int S, int SP, int L, int NC, int variant, float eps) {
-  const int bh = blockIdx.y;
+  // 1-D grid (no 65535 limit on batch x heads): the chunk groups of one (batch, head) next to each other
+  const int ngrp = (NC + kGateThreads / 32 - 1) / (kGateThreads / 32);
+  const int bh = blockIdx.x / ngrp;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int k = blockIdx.x * (kGateThreads / 32) + warp;
+  const int k = (blockIdx.x % ngrp) * (kGateThreads / 32) + warp;
   if (k >= NC) return;
   const bool siging = variant != MLSTM_EXP;
   const size_t base_in = (size_t)bh * S + (size_t)k * L;
@@ -255,7 +259,8 @@ gate_grad_anchored_kernel(const T* __restrict__ vecI, const T* __restrict__ vecF
                           int SP, int variant, int nparts, size_t part_stride,
                           const float* __restrict__ anchors, int n_anchors) {
   __shared__ float s_warp[kAnchorThreads / 32];
-  const int a = blockIdx.x, bh = blockIdx.y, t = threadIdx.x, lane = t & 31, warp = t >> 5;
+  const int nint = (S + kAnchorThreads - 1) / kAnchorThreads;   // 1-D grid: intervals of one (batch, head) adjacent
+  const int a = blockIdx.x % nint, bh = blockIdx.x / nint, t = threadIdx.x, lane = t & 31, warp = t >> 5;
   const int s = a * kAnchorThreads + t;
   const bool live = s < S;
   float qd = 0.f, kd = 0.f;
@@ -293,7 +298,7 @@ __global__ void __launch_bounds__(256)
 state_dot_kernel(const TS* __restrict__ c_states, const TS* __restrict__ dc_states,
                  float* __restrict__ anchors, int NC, int every, int n_anchors, size_t state_elems) {
   __shared__ float s_w[8];
-  const int bh = blockIdx.y, a = blockIdx.x + 1;
+  const int bh = blockIdx.x / (n_anchors - 1), a = blockIdx.x % (n_anchors - 1) + 1;   // 1-D grid
   const int k = min(a * every, NC);
   const size_t off = ((size_t)bh * (NC + 1) + k) * state_elems;
   const uint4* pc = reinterpret_cast<const uint4*>(c_states + off);
@@ -326,7 +331,7 @@ int launch_gates_t(const void* i, const void* f, const float* m_initial, const f
                    const GateBuffers& gb, float* m_states, const ChunkwiseDims& d, cudaStream_t st, float m_default,
                    float* g_sum) {
   PhaseScope ps(PH_GATES, st);
-  const dim3 grid(ceil_div(d.NC, kGateThreads / 32), d.B * d.NH);
+  const unsigned grid = (unsigned)ceil_div(d.NC, kGateThreads / 32) * (unsigned)(d.B * d.NH);
   gates_chunk_kernel<T><<<grid, kGateThreads, 0, st>>>((const T*)i, (const T*)f, gb, d.S, d.SP, d.L, d.NC, d.variant);
   MLSTM_LAUNCH_CHECK();
   gates_scan_kernel<<<d.B * d.NH, kGateThreads, 0, st>>>(m_initial, gb, m_states, d.NC, d.variant, m_default, g_sum);
@@ -391,8 +396,8 @@ __global__ void __launch_bounds__(256)
 state_combine_kernel(const float* __restrict__ c_in, const float* __restrict__ n_in, const float* __restrict__ m_in,
                      const float* __restrict__ c_loc, const float* __restrict__ n_loc, const float* __restrict__ m_loc,
                      const float* __restrict__ g_total, float* __restrict__ c_out, float* __restrict__ n_out,
-                     float* __restrict__ m_out, int DHQK, int DHHV, int variant) {
-  const int bh = blockIdx.y;
+                     float* __restrict__ m_out, int DHQK, int DHHV, int variant, int nblk) {
+  const int bh = blockIdx.x / nblk, blk = blockIdx.x % nblk;   // 1-D grid: nblk CTAs per (batch, head)
   float a, b, mo = 0.f;
   if (variant == MLSTM_EXP) {
     const float mi = m_in ? m_in[bh] : 0.f, ml = m_loc[bh], G = g_total[bh];
@@ -404,7 +409,7 @@ state_combine_kernel(const float* __restrict__ c_in, const float* __restrict__ n
     b = 1.f;
   }
   const size_t nC = (size_t)DHQK * DHHV;
-  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < nC; e += (size_t)gridDim.x * blockDim.x) {
+  for (size_t e = (size_t)blk * blockDim.x + threadIdx.x; e < nC; e += (size_t)nblk * blockDim.x) {
     const size_t idx = (size_t)bh * nC + e;
     c_out[idx] = a * (c_in ? c_in[idx] : 0.f) + b * c_loc[idx];
     if (e < (size_t)DHQK && n_out != nullptr) {
@@ -412,16 +417,16 @@ state_combine_kernel(const float* __restrict__ c_in, const float* __restrict__ n
       n_out[ni] = a * (n_in ? n_in[ni] : 0.f) + b * n_loc[ni];
     }
   }
-  if (blockIdx.x == 0 && threadIdx.x == 0 && m_out != nullptr) m_out[bh] = mo;
+  if (blk == 0 && threadIdx.x == 0 && m_out != nullptr) m_out[bh] = mo;
 }
 
 int launch_state_combine(const float* c_in, const float* n_in, const float* m_in, const float* c_loc,
                          const float* n_loc, const float* m_loc, const float* g_total, float* c_out, float* n_out,
                          float* m_out, int BNH, int DHQK, int DHHV, int variant, cudaStream_t st) {
   const size_t nC = (size_t)DHQK * DHHV;
-  dim3 grid((unsigned)std::min<size_t>((nC + 255) / 256, 64), BNH);
-  state_combine_kernel<<<grid, 256, 0, st>>>(c_in, n_in, m_in, c_loc, n_loc, m_loc, g_total, c_out, n_out, m_out, DHQK,
-                                            DHHV, variant);
+  const int nblk = (int)std::min<size_t>((nC + 255) / 256, 64);
+  state_combine_kernel<<<(unsigned)nblk * (unsigned)BNH, 256, 0, st>>>(c_in, n_in, m_in, c_loc, n_loc, m_loc, g_total,
+                                                                      c_out, n_out, m_out, DHQK, DHHV, variant, nblk);
   MLSTM_LAUNCH_CHECK();
   return MLSTM_OK;
 }
@@ -457,7 +462,7 @@ static int gate_grad_scan_t(const void* i, const void* f, const float* qdq, cons
                             int anchor_tokens) {
   const size_t stride = (size_t)d.B * d.NH * d.SP;
   if (anchors != nullptr && anchor_tokens == kAnchorThreads) {
-    dim3 grid(ceil_div(d.S, kAnchorThreads), d.B * d.NH);
+    const unsigned grid = (unsigned)ceil_div(d.S, kAnchorThreads) * (unsigned)(d.B * d.NH);
     gate_grad_anchored_kernel<T><<<grid, kAnchorThreads, 0, st>>>((const T*)i, (const T*)f, qdq, kdk, dI, dF, d.S, d.SP,
                                                                   d.variant, nparts, stride, anchors, n_anchors);
   } else {
@@ -483,7 +488,7 @@ int launch_gate_grad_scan(int dtype, const void* i, const void* f, const float* 
 int launch_state_dot(const void* c_states, const void* dc_states, float* anchors, int every, int n_anchors,
                      const ChunkwiseDims& d, cudaStream_t st) {
   if (n_anchors < 2) return MLSTM_OK;
-  dim3 grid(n_anchors - 1, d.B * d.NH);
+  const unsigned grid = (unsigned)(n_anchors - 1) * (unsigned)(d.B * d.NH);
   if (d.dtype == MLSTM_F16)
     state_dot_kernel<__half><<<grid, 256, 0, st>>>((const __half*)c_states, (const __half*)dc_states, anchors, d.NC,
                                                    every, n_anchors, (size_t)d.DHQK * d.DHHV);

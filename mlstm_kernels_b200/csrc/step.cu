@@ -59,7 +59,9 @@ step_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restric
   __shared__ float s_den;
 
   const int tid = threadIdx.x;
-  const int bh = blockIdx.y, e0 = blockIdx.x * STEP_TV;
+  // 1-D grid (no 65535 limit on batch x heads): the column tiles of one (batch, head) next to each other
+  const int ntile = (DHHV + STEP_TV - 1) / STEP_TV;
+  const int bh = blockIdx.x / ntile, tile = blockIdx.x % ntile, e0 = tile * STEP_TV;
   const int cgi = tid % STEP_CG, rg = tid / STEP_CG;
   const int e = e0 + cgi * 4;
 
@@ -80,7 +82,7 @@ step_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restric
     s_q[d] = qs;
     s_k[d] = ik;
     qn = fmaf(qs, nn, qn);
-    if (blockIdx.x == 0) n_new[(size_t)bh * DHQK + d] = from_f32<TS>(nn);
+    if (tile == 0) n_new[(size_t)bh * DHQK + d] = from_f32<TS>(nn);
   }
   qn = warp_sum(qn);
   if ((tid & 31) == 0) s_warp[tid >> 5] = qn;
@@ -89,7 +91,7 @@ step_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restric
     float t = 0.f;
     for (int w = 0; w < STEP_THREADS / 32; ++w) t += s_warp[w];
     s_den = fmaxf(fabsf(t), expf(-m_n)) + eps;
-    if (blockIdx.x == 0) m_new[bh] = from_f32<TS>(m_n);
+    if (tile == 0) m_new[bh] = from_f32<TS>(m_n);
   }
 
   float4 hv = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -165,7 +167,9 @@ step_sequence_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* 
   __shared__ float s_den;
 
   const int tid = threadIdx.x;
-  const int bh = blockIdx.y, e0 = blockIdx.x * STEP_TV;
+  // 1-D grid (no 65535 limit on batch x heads): the column tiles of one (batch, head) next to each other
+  const int ntile = (DHHV + STEP_TV - 1) / STEP_TV;
+  const int bh = blockIdx.x / ntile, tile = blockIdx.x % ntile, e0 = tile * STEP_TV;
   const int cgi = tid % STEP_CG, rg = tid / STEP_CG;
   const int e = e0 + cgi * 4;
   const float scale = rsqrtf((float)DHQK);
@@ -245,7 +249,7 @@ step_sequence_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* 
     const int d = rg + r * STEP_RG;
     if (d < DHQK && e < DHHV) *reinterpret_cast<float4*>(c_new + ((size_t)bh * DHQK + d) * DHHV + e) = C[r];
   }
-  if (blockIdx.x == 0) {
+  if (tile == 0) {
     for (int d = tid; d < DHQK; d += STEP_THREADS) n_new[(size_t)bh * DHQK + d] = s_n[d];
     if (tid == 0) m_new[bh] = m_run;
   }
@@ -257,7 +261,7 @@ int step_t(const void* q, const void* k, const void* v, const void* i, const voi
            const void* n, const void* m, void* h, void* c_new, void* n_new, void* m_new, int B, int NH, int DHQK,
            int DHHV, float eps, cudaStream_t st) {
   PhaseScope ps(PH_STEP, st);
-  dim3 grid(ceil_div(DHHV, STEP_TV), B * NH);
+  const unsigned grid = (unsigned)ceil_div(DHHV, STEP_TV) * (unsigned)(B * NH);
   const size_t smem = sizeof(float) * (2 * (size_t)DHQK + (STEP_THREADS / 32) * STEP_TV);
   auto kern = step_kernel<T, TS>;
   if (smem > 48 * 1024) MLSTM_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -287,7 +291,7 @@ template <typename T, int ROWS>
 int step_seq_t(const void* q, const void* k, const void* v, const void* i, const void* f, int gate_dtype, const float* c,
                const float* n, const float* m, void* h, float* c_new, float* n_new, float* m_new, int B, int NH, int Tn,
                int DHQK, int DHHV, float eps, cudaStream_t st) {
-  dim3 grid(ceil_div(DHHV, STEP_TV), B * NH);
+  const unsigned grid = (unsigned)ceil_div(DHHV, STEP_TV) * (unsigned)(B * NH);
   const size_t smem = sizeof(float) * (3 * (size_t)DHQK + (STEP_THREADS / 32) * STEP_TV);
   auto kern = step_sequence_kernel<T, ROWS>;
   if (smem > 48 * 1024) MLSTM_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
