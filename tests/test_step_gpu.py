@@ -153,3 +153,44 @@ def test_step_full_size_decay_property():
     assert torch.allclose(m2, m_new, rtol=1e-6, atol=1e-6)
     assert torch.allclose(c2, c * scale[..., None], rtol=1e-5, atol=1e-7)
     assert torch.allclose(n2, n * scale, rtol=1e-5, atol=1e-7)
+
+
+def test_more_than_65535_batch_heads():
+    """Batch x heads beyond the 65535 limit of a grid's second dimension (all grids are one-dimensional): decode step,
+    multi-token sequence kernel and the chunkwise forward + backward on both kernel families, tiny head dims so that
+    70 000 units stay small.  A unit computed inside the big launch equals the same unit computed alone, bit for bit,
+    and a sample of units matches the oracle."""
+    B, NH, D, S = 8750, 8, 8, 16          # 70 000 units
+    g = torch.Generator(device="cuda").manual_seed(3)
+    rnd = lambda *s: torch.randn(*s, device="cuda", generator=g)  # noqa: E731
+    c, n, m = rnd(B, NH, D, D) * 0.1, rnd(B, NH, D).abs(), rnd(B, NH, 1)
+    q, k, v = rnd(B, NH, S, D).bfloat16(), rnd(B, NH, S, D).bfloat16(), rnd(B, NH, S, D).bfloat16()
+    i, f = rnd(B, NH, S).bfloat16(), (3 + rnd(B, NH, S)).bfloat16()
+    pick = [0, 8191, 8749]                # first, one past the 65535th unit's batch row, last
+    # decode step and sequence kernel
+    h, st = mk.mlstm_recurrent_step__b200(q[:, :, 0], k[:, :, 0], v[:, :, 0], i[:, :, :1], f[:, :, :1], c, n, m)
+    hs, sts = mk.mlstm_recurrent_sequence__b200(q, k, v, i, f, c, n, m, return_last_states=True)
+    for b in pick:
+        sl = slice(b, b + 1)
+        h1, st1 = mk.mlstm_recurrent_step__b200(q[sl, :, 0], k[sl, :, 0], v[sl, :, 0], i[sl, :, :1], f[sl, :, :1],
+                                                c[sl], n[sl], m[sl])
+        assert torch.equal(h[sl], h1) and all(torch.equal(a[sl], b_) for a, b_ in zip(st, st1))
+        hs1, sts1 = mk.mlstm_recurrent_sequence__b200(q[sl], k[sl], v[sl], i[sl], f[sl], c[sl], n[sl], m[sl],
+                                                      return_last_states=True)
+        assert torch.equal(hs[sl], hs1) and all(torch.equal(a[sl], b_) for a, b_ in zip(sts, sts1))
+    # chunkwise: tensor-core kernels (bf16) and portable kernels (f32)
+    dh = rnd(B, NH, S, D)
+    for dtype in (torch.bfloat16, torch.float32):
+        leaves = [t.to(dtype).detach().requires_grad_(True) for t in (q, k, v, i, f)]
+        H = mk.mlstm_chunkwise__b200_xl_chunk(*leaves, chunk_size=16)
+        H.backward(dh.to(dtype))
+        for b in pick:
+            sl = slice(b, b + 1)
+            one = [t[sl].detach().clone().requires_grad_(True) for t in leaves]
+            H1 = mk.mlstm_chunkwise__b200_xl_chunk(*one, chunk_size=16)
+            H1.backward(dh[sl].to(dtype))
+            assert torch.equal(H[sl], H1)
+            for a, b_ in zip(leaves, one):
+                assert torch.equal(a.grad[sl], b_.grad)
+        ref = O.chunkwise_fw(*(npy(t[-1:]) for t in leaves), chunk_size=16)
+        assert max_rel_err(npy(H[-1:]), ref["H"]) < (2e-2 if dtype == torch.bfloat16 else 1e-4)
