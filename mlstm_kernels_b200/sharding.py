@@ -26,7 +26,8 @@ c_initial / n_initial / m_initial in, last states out: mlstm_kernels/torch/kerne
   multiply-add per hop, (3) all ranks run the full backward of their segment from the true dC_right.  The sum over
   all later tokens needs no message: summed from a chunk boundary to the end of the sequence,
   q . dq - k . dk = <C, dC> at that boundary, so it is <C_last, dC_right> of the rank's own segment.
-  "gather" mode (the default) replaces both chains by one all-gather each: every rank receives all segment summaries
+  "gather" mode (what "auto" picks from three ranks on; with two ranks it picks "scan") replaces both chains by one
+  all-gather each: every rank receives all segment summaries
   and folds those of the ranks before it itself, in rank order (the same arithmetic in the same order as the chain,
   so the same bits); in the backward every rank receives all (dC_own, a) pairs and folds those of the ranks after it.
   The hops of a chain are serial - each costs a message latency plus the launches around it, seven of them on eight
@@ -309,7 +310,7 @@ def mlstm_chunkwise_sequence_parallel(
     chunk_size: int = 128,
     siging: bool = False,
     normalize: bool = True,
-    mode: str = "gather",
+    mode: str = "auto",
     group=None,
     impl: str = "auto",
 ):
@@ -318,9 +319,11 @@ def mlstm_chunkwise_sequence_parallel(
     (identical on every rank).  Ranks are ordered along the sequence: global rank order of the group.
     Differentiable with respect to q, k, v, i, f (every rank must then run the backward: it exchanges
     point-to-point messages from the last rank to the first)."""
-    if mode not in ("gather", "scan", "chain"):
+    if mode not in ("auto", "gather", "scan", "chain"):
         raise ValueError(f"unknown mode {mode}")
     world = dist.get_world_size(group)
+    if mode == "auto":   # a single hop needs no collective; from three ranks on the all-gather beats the serial hops
+        mode = "scan" if world <= 2 else "gather"
     rank = dist.get_rank(group)
     variant = _variant(siging, normalize)
     B, NH, S, DHQK = q.shape
