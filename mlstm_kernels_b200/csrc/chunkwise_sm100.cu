@@ -420,6 +420,24 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
   const size_t out_row0 = (size_t)bh * p.S + y0;  // first row of the chunk in the (B*NH*S)-row token tensors
   const bool use_n = (mode == PM_H) && p.variant != MLSTM_SIG_NONORM && p.n_states != nullptr;
 
+  if (tid == 0) {
+    sh.abort = 0;
+    for (int s = 0; s < PAR_NST; ++s) {
+      mbar_init(&sh.bar_full[s], 1); mbar_init(&sh.bar_empty[s], 1); mbar_init(&sh.bar_qdone[s], 8);
+    }
+    mbar_init(&sh.bar_sfull, 1); mbar_init(&sh.bar_afull, 1); mbar_init(&sh.bar_gated, 256); mbar_init(&sh.bar_hfull, 1); mbar_init(&sh.bar_dot, 256);
+    for (int s = 0; s < 4; ++s) mbar_init(&sh.bar_pair[s], 64);
+    mbar_init(&sh.bar_out, 256); mbar_init(&sh.bar_accfree, 256); mbar_init(&sh.bar_done, 256);
+    fence_barrier_init();
+    tma_prefetch_desc(mapA); tma_prefetch_desc(mapB); tma_prefetch_desc(mapX); tma_prefetch_desc(mapSt);
+    if (HAS_E) tma_prefetch_desc(mapE);
+  }
+  if (warp == 1) { tmem_alloc(&sh.tmem, 256); tmem_relinquish(); }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = sh.tmem;
+  const uint32_t tS = tmem, tAcc = tmem + 128;
   // Ring loads, in order: ND (A, B) slice pairs for the score product, ND (A, state) slice pairs for the inter-chunk
   // product (A comes from L2 the second time), the X tile, the E tile.  The score is complete - and the element-wise
   // warps start gating - while the second group is still arriving.
@@ -440,18 +458,20 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
     return ls == ND ? LK_X : LK_E;
   };
 
-  const int slot = LOWER ? ck : ck + 1;
-  const int sz = bh * (NC + 1) + slot;   // slab of the state tensor (one DHQK x DHHV matrix per chunk boundary)
-  // Producer state (only thread 0 uses it).  Per stage: uses handed back by an MMA commit so far (phase counter of
-  // bar_empty) and score pairs read for q . n so far (phase counter of bar_qdone).  Scalars picked by comparisons,
-  // not arrays: a dynamically indexed array would live in local memory, and with nearly all of L1 configured as
-  // shared memory every access to it is a round trip to L2 on the load-issue path.
-  int issued = 0;
-  int rm0 = 0, rm1 = 0, rm2 = 0, rq0 = 0, rq1 = 0, rq2 = 0;
-  int st = 0, sub = 0, l = 0;                        // stage, tile and position inside the tile of the next load
-  int pk1 = 0, pk2 = 0, pk3 = 0, ps1 = 0, ps2 = 0, ps3 = 0;   // kind and tile of the last three loads
-  // issue load `ld` (waiting first, from the fourth load on, for the stage's previous occupant to be gone)
-  auto issue_load = [&](const int ld) -> bool {
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      const int slot = LOWER ? ck : ck + 1;
+      const int sz = bh * (NC + 1) + slot;   // slab of the state tensor (one DHQK x DHHV matrix per chunk boundary)
+      int issued = 0;
+      // Per stage: uses handed back by an MMA commit so far (phase counter of bar_empty) and score pairs read for
+      // q . n so far (phase counter of bar_qdone).  Scalars picked by comparisons, not arrays: a dynamically indexed
+      // array would live in local memory, and with nearly all of L1 configured as shared memory every access to it
+      // is a round trip to L2 on the load-issue path.
+      int rm0 = 0, rm1 = 0, rm2 = 0, rq0 = 0, rq1 = 0, rq2 = 0;
+      int st = 0, sub = 0, l = 0;                        // stage, tile and position inside the tile of load `ld`
+      int pk1 = 0, pk2 = 0, pk3 = 0, ps1 = 0, ps2 = 0, ps3 = 0;   // kind and tile of the last three loads
+      for (int ld = 0; ld < n_loads; ++ld) {
         int it;
         const int kind = load_kind(sub, l, it);
         if (ld >= PAR_NST) {   // the stage's previous occupant (three loads back) must be gone
@@ -468,7 +488,7 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
           } else {   // the staging buffer of a tile (its E stage, or its X stage in the modes without E) is handed
             okw = mbar_wait(&sh.bar_done, psub & 1, &sh.abort, &g_sm100_status, 215);   // back when the tile has been stored
           }
-          if (!okw) return false;
+          if (!okw) break;
         }
         const int o0 = o00 + 128 * sub;
         uint8_t* sb = smem + st * PAR_STAGE;
@@ -495,34 +515,7 @@ par_body(const int mode, const CUtensorMap* mapA, const CUtensorMap* mapB, const
         pk3 = pk2; pk2 = pk1; pk1 = kind; ps3 = ps2; ps2 = ps1; ps1 = sub;
         st = st == PAR_NST - 1 ? 0 : st + 1;
         if (++l == (sub == 0 ? n0 : n1)) { l = 0; ++sub; }
-        return true;
-  };
-  if (tid == 0) {
-    sh.abort = 0;
-    for (int s = 0; s < PAR_NST; ++s) {
-      mbar_init(&sh.bar_full[s], 1); mbar_init(&sh.bar_empty[s], 1); mbar_init(&sh.bar_qdone[s], 8);
-    }
-    mbar_init(&sh.bar_sfull, 1); mbar_init(&sh.bar_afull, 1); mbar_init(&sh.bar_gated, 256); mbar_init(&sh.bar_hfull, 1); mbar_init(&sh.bar_dot, 256);
-    for (int s = 0; s < 4; ++s) mbar_init(&sh.bar_pair[s], 64);
-    mbar_init(&sh.bar_out, 256); mbar_init(&sh.bar_accfree, 256); mbar_init(&sh.bar_done, 256);
-    fence_barrier_init();
-    tma_prefetch_desc(mapA); tma_prefetch_desc(mapB); tma_prefetch_desc(mapX); tma_prefetch_desc(mapSt);
-    if (HAS_E) tma_prefetch_desc(mapE);
-    // the first ring-full of loads leaves before the CTA-wide sync below (they wait for nothing; only this thread
-    // has touched the barriers so far, and the fence above has made them visible to the copy engine)
-    for (int ld = 0; ld < PAR_NST && ld < n_loads; ++ld) issue_load(ld);
-  }
-  if (warp == 1) { tmem_alloc(&sh.tmem, 256); tmem_relinquish(); }
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-  const uint32_t tmem = sh.tmem;
-  const uint32_t tS = tmem, tAcc = tmem + 128;
-  if (warp == 0) {
-    // ---------------- TMA producer ----------------
-    if (lane == 0) {
-      for (int ld = issued; ld < n_loads; ++ld)
-        if (!issue_load(ld)) break;
+      }
       if (issued < n_loads && issued > 0) {  // error path: let the copies in flight land before the CTA retires
         for (int ld = max(0, issued - PAR_NST); ld < issued; ++ld)
           mbar_wait(&sh.bar_full[ld % PAR_NST], (ld / PAR_NST) & 1, nullptr, nullptr, 0);
